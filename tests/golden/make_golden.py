@@ -1,0 +1,125 @@
+"""Generate the golden vectors under tests/golden/ by running the REAL reference.
+
+Run once, in a container that has the reference checkout (it is not needed,
+and not read, by any test):
+
+    python tests/golden/make_golden.py --reference /path/to/segment-anything-fast
+
+It imports ``segment_anything_fast`` from that checkout with
+``SEGMENT_ANYTHING_FAST_USE_FLASH_4=0`` (CPU, SDPA composite), feeds it the
+seeded weights / inputs that ``oracle.encoder_oracle`` can regenerate anywhere,
+and stores (sub-sampled, float32) outputs as small ``.npz`` files.  The tests
+then check the oracle restatement against these files on CPU and the CUDA
+path against the oracle on the GPU.
+"""
+import argparse
+import hashlib
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+TINY = dict(embed_dim=160, depth=4, num_heads=2, global_attn_indexes=(1, 3), out_chans=32)
+
+
+def sd_digest(sd):
+    h = hashlib.sha256()
+    for k in sorted(sd):
+        h.update(k.encode())
+        h.update(sd[k].detach().to(torch.float32).contiguous().numpy().tobytes())
+    return h.hexdigest()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    os.environ["SEGMENT_ANYTHING_FAST_USE_FLASH_4"] = "0"
+    sys.path.insert(0, args.reference)
+    from functools import partial
+
+    import segment_anything_fast as saf
+    from segment_anything_fast.flash_4 import _attention_rel_h_rel_w
+    from segment_anything_fast.modeling.image_encoder import ImageEncoderViT, add_decomposed_rel_pos
+    from segment_anything_fast.sparse import apply_fake_sparsity
+
+    from oracle import encoder_oracle as eo
+
+    torch.set_grad_enabled(False)
+
+    # (a) tiny encoder, seeded non-zero rel-pos / pos-embed, fp32 -------------------------
+    cfg = eo.EncoderConfig(**TINY)
+    ref = ImageEncoderViT(
+        depth=cfg.depth, embed_dim=cfg.embed_dim, img_size=1024, mlp_ratio=4,
+        norm_layer=partial(torch.nn.LayerNorm, eps=1e-6), num_heads=cfg.num_heads, patch_size=16,
+        qkv_bias=True, use_rel_pos=True, global_attn_indexes=list(cfg.global_attn_indexes),
+        window_size=14, out_chans=cfg.out_chans).eval()
+    sd = eo.seeded_state_dict(cfg, seed=1)
+    ref.load_state_dict(sd)                      # also proves the key set / shapes agree
+    x = eo.seeded_images(1, seed=2)
+    taps = {}
+    hooks = [blk.register_forward_hook(lambda m, i, o, n=n: taps.__setitem__(n, o))
+             for n, blk in enumerate(ref.blocks)]
+    out = ref(x)
+    for h in hooks:
+        h.remove()
+    np.savez_compressed(
+        os.path.join(HERE, "enc_tiny_fp32.npz"),
+        out=out[:, :, ::2, ::2].numpy(),
+        **{f"block{n}": t[0, ::8, ::8, :].numpy() for n, t in taps.items()})
+    # the same model through the reference's bf16 module path on CPU (noise-floor record)
+    ref_bf = ref.to(torch.bfloat16)
+    out_bf = ref_bf(x.to(torch.bfloat16)).float()
+    np.savez_compressed(os.path.join(HERE, "enc_tiny_bf16.npz"), out=out_bf[:, :, ::2, ::2].numpy())
+
+    # (b) ViT-B, torch.manual_seed(0) default init through the reference registry ---------
+    torch.manual_seed(0)
+    sam = saf.sam_model_registry["vit_b"]()
+    enc = sam.image_encoder
+    xb = eo.seeded_images(1, seed=0)
+    outb = enc(xb)
+    np.savez_compressed(
+        os.path.join(HERE, "enc_vit_b_default_init_fp32.npz"),
+        out=outb[:, :, ::4, ::4].numpy(),
+        weights_sha256=np.array(sd_digest(enc.state_dict())),
+        qkv0_head=enc.state_dict()["blocks.0.attn.qkv.weight"][:4, :8].numpy())
+
+    # (c) the attention op: the procedure of test/test_flash_4.py, on CPU --------------------
+    att = {}
+    for name, (B, H, N, d, S) in {"global_d80": (1, 2, 4096, 80, 64), "global_d64": (1, 2, 4096, 64, 64),
+                                  "window_d80": (3, 2, 196, 80, 14)}.items():
+        torch.manual_seed(20)
+        q, k, v = (torch.empty(B, H, N, d).normal_(0.0, 0.5) for _ in range(3))
+        rel_h = torch.empty(B, H, N, S, 1).normal_(0.0, 0.5)
+        rel_w = torch.empty(B, H, N, 1, S).normal_(0.0, 0.5)
+        o = _attention_rel_h_rel_w(q, k, v, rel_h, rel_w)
+        att[name] = o[:, :, ::(16 if N > 256 else 1), :].numpy()
+    np.savez_compressed(os.path.join(HERE, "attention_op_fp32.npz"), **att)
+
+    # (d) decomposed rel-pos --------------------------------------------------------------
+    torch.manual_seed(3)
+    q = torch.randn(4, 14 * 14, 80)
+    rph, rpw = torch.randn(27, 80), torch.randn(27, 80)
+    rh, rw = add_decomposed_rel_pos(q, rph, rpw, (14, 14), (14, 14))
+    np.savez_compressed(os.path.join(HERE, "rel_pos_fp32.npz"), rel_h=rh.squeeze(-1).numpy(),
+                        rel_w=rw.squeeze(-2).numpy())
+
+    # (e) 2:4 mask from the reference's sparsifier flow ------------------------------------
+    torch.manual_seed(4)
+    lin = torch.nn.Sequential(torch.nn.Linear(64, 48), torch.nn.Linear(48, 32))
+    w_before = [m.weight.detach().clone() for m in lin]
+    apply_fake_sparsity(lin)
+    np.savez_compressed(
+        os.path.join(HERE, "sparse24_mask.npz"),
+        w0=w_before[0].numpy(), w1=w_before[1].numpy(),
+        keep0=(lin[0].weight != 0).numpy(), keep1=(lin[1].weight != 0).numpy())
+    print("golden vectors written to", HERE)
+
+
+if __name__ == "__main__":
+    main()
