@@ -1,0 +1,109 @@
+/*
+ * samb200 — C ABI of the B200 (sm_100a) SAM image-encoder kernels.
+ *
+ * Conventions
+ *   - Every entry point returns SAMB_OK (0) or a negative SAMB_E_* code; argument errors are
+ *     detected on the host before anything is launched.  No C++ exception crosses this boundary.
+ *   - All pointers are DEVICE pointers owned by the caller unless the comment says "host".
+ *     The library allocates nothing, frees nothing, keeps no pointer after returning and never
+ *     synchronises: work is enqueued on `stream` (a cudaStream_t passed as void*).
+ *   - `status` is a caller-owned 4-byte device word, zero-initialised by the caller.  Kernels that
+ *     wait on hardware barriers bound every wait; a wait that runs out stores
+ *     (0x7E << 24) | (site << 16) | (cta & 0xffff) there and the kernel drains and returns.
+ *   - bf16 tensors are row-major, 16-byte aligned, with row lengths that are multiples of 8
+ *     elements (16 for int8).  Small vectors (bias, LayerNorm gain/offset, scales) are float32.
+ *   - Citations "ref:" name the file:line of pytorch-labs/segment-anything-fast that the entry
+ *     point replaces on the image-encoder path.
+ */
+#ifndef SAMB200_H_
+#define SAMB200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SAMB_ABI_VERSION 1
+
+enum {
+  SAMB_OK = 0,
+  SAMB_E_BADARG = -1,  /* null pointer / negative size / unknown enum value */
+  SAMB_E_SHAPE = -2,   /* size outside what the kernel supports */
+  SAMB_E_ALIGN = -3,   /* pointer or stride not 16-byte aligned */
+  SAMB_E_ARCH = -4,    /* current device is not sm_100 */
+  SAMB_E_LAUNCH = -5,  /* CUDA reported an error at launch or tensor-map creation */
+  SAMB_E_TIMEOUT = -6  /* reported by samb_decode_status for a device-side bounded-wait expiry */
+};
+
+/* GEMM epilogues (bit flags) */
+enum {
+  SAMB_EPI_BIAS = 1,      /* + bias[n]                                         */
+  SAMB_EPI_GELU = 2,      /* exact (erf) GELU after the bias                   */
+  SAMB_EPI_RESIDUAL = 4,  /* + residual[m, n] (bf16) after bias / GELU          */
+  SAMB_EPI_RAW = 8        /* store the raw accumulator (fp32 / int32), no other flag allowed */
+};
+
+int samb_abi_version(void);
+const char* samb_error_string(int code);
+/* Host helper: maps a status word read back from the device to SAMB_OK / SAMB_E_TIMEOUT. */
+int samb_decode_status(int32_t status_word);
+/* Waits (bounded, ~`limit_polls` polls) on a barrier that nothing signals; the kernel must come
+ * back with the timeout code in *status.  Exercises the give-up path without faulting anything. */
+int samb_selftest_bounded_wait(int32_t* status, uint32_t limit_polls, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * LayerNorm over the last dim of x[rows, C] (bf16 in, fp32 statistics, bf16 out).
+ * ref: nn.LayerNorm in Block.forward, modeling/image_encoder.py:152,162,169,181 (eps 1e-6 from
+ * build_sam.py:112).
+ * If window > 0 the rows are tokens of `rows / (grid*grid)` images on a grid x grid raster and the
+ * output is written in the window-partitioned, zero-padded order of window_partition
+ * (modeling/image_encoder.py:256-277): y[(img*nw*nw + wy*nw + wx)*window*window + ly*window + lx, :],
+ * nw = ceil(grid/window), pad rows are written as zeros.  y then has
+ * images*nw*nw*window*window rows.  With window == 0, y has `rows` rows in the input order.
+ * ------------------------------------------------------------------------------------------- */
+int samb_layernorm_bf16(const void* x, const float* gamma, const float* beta, void* y, int64_t rows, int C,
+                        float eps, int grid, int window, void* stream);
+
+/* Same, fused with per-row symmetric int8 quantisation of the bf16-rounded LayerNorm output:
+ * scale[r] = max(absmax_r, 1e-5) / 127, yq = clamp(rint(y / scale), -127, 127).
+ * ref: torchao apply_dynamic_quant at experiments/eval_combo.py:357-360 (activation side). */
+int samb_layernorm_quant_i8(const void* x, const float* gamma, const float* beta, int8_t* yq, float* scale,
+                            int64_t rows, int C, float eps, int grid, int window, void* stream);
+
+/* Per-row symmetric int8 quantisation of x[rows, C] (bf16), same formula. */
+int samb_quant_rows_i8(const void* x, int8_t* yq, float* scale, int64_t rows, int C, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * out[M, N] = epilogue(A[M, K] * W[N, K]^T), bf16 operands, fp32 accumulation on tcgen05 tensor
+ * cores (TMA-fed, accumulators in tensor memory).  A, W, out, residual row-major bf16 with leading
+ * dimensions lda, ldw, ldo, ldr (elements, multiples of 8).  With SAMB_EPI_RAW `out` is float32.
+ * The residual has res_rows rows and row m adds residual[m % res_rows] (res_rows == M for a plain
+ * residual; res_rows == tokens per image broadcasts one positional table over the batch).
+ * ref: nn.Linear qkv/proj (modeling/image_encoder.py:213-214,228,251), MLPBlock lin1/GELU/lin2
+ * (modeling/common.py:21-26), the residual adds (image_encoder.py:180-181), PatchEmbed conv as a
+ * GEMM (:398-406) and the neck's convolutions (:89-105).
+ * ------------------------------------------------------------------------------------------- */
+int samb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias, const void* residual,
+                   int64_t ldr, int64_t res_rows, void* out, int64_t ldo, int64_t M, int N, int K, int epilogue,
+                   int32_t* status, void* stream);
+
+/* out[M, N] = epilogue(float(int32(Aq[M,K]) * int32(Wq[N,K])^T) * a_scale[m] * w_scale[n]),
+ * int8 operands, exact int32 accumulation on tcgen05 kind::i8.  With SAMB_EPI_RAW `out` is int32
+ * and the scales are ignored.  K multiple of 16.
+ * ref: torchao dynamically-quantised Linear swapped in at experiments/eval_combo.py:357-360. */
+int samb_gemm_i8(const int8_t* Aq, int64_t lda, const float* a_scale, const int8_t* Wq, int64_t ldw,
+                 const float* w_scale, const float* bias, const void* residual, int64_t ldr, int64_t res_rows,
+                 void* out, int64_t ldo, int64_t M, int N, int K, int epilogue, int32_t* status, void* stream);
+
+/* Channel LayerNorm of x[tokens, C] (token-major rows, bf16): each row is normalised over its C
+ * channels in fp32.  With to_nchw != 0 the result is stored as out[tokens/hw, C, hw] (hw multiple
+ * of 32), else in the input layout.
+ * ref: LayerNorm2d, modeling/common.py:31-43, used by the neck (modeling/image_encoder.py:96,104). */
+int samb_layernorm2d_nchw(const void* x, const float* gamma, const float* beta, void* out, int64_t tokens, int C,
+                          int hw, float eps, int to_nchw, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SAMB200_H_ */

@@ -1,0 +1,278 @@
+// Bandwidth kernels: row LayerNorm (optionally scattering into the zero-padded window order and/or
+// quantising each row to int8), plain per-row int8 quantisation, and the neck's channel LayerNorm
+// with an NHWC -> NCHW transposing store.  One warp owns one row; a lane holds up to 8 vectors of
+// 8 bf16 (C <= 2048), so every row is read once and written once with 16-byte accesses.
+#include "common.cuh"
+
+namespace samb {
+namespace {
+
+constexpr int kMaxVec = 8;          // 16-byte vectors per lane
+constexpr int kWarpsPerBlock = 8;
+constexpr float kAbsmaxFloor = 1e-5f;
+
+struct RowMap {
+  // Output row -> input row for the window-partitioned order; window == 0 means identity.
+  int grid, window, nw;
+  __device__ __forceinline__ long long src_row(long long out_row) const {
+    if (window == 0) return out_row;
+    const int ww = window * window;
+    const long long win = out_row / ww;
+    const int l = int(out_row - win * ww);
+    const int ly = l / window, lx = l - ly * window;
+    const long long img = win / (nw * nw);
+    const int wi = int(win - img * nw * nw);
+    const int wy = wi / nw, wx = wi - wy * nw;
+    const int y = wy * window + ly, x = wx * window + lx;
+    if (y >= grid || x >= grid) return -1;      // zero padding
+    return (img * grid + y) * grid + x;
+  }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 t = __bfloat1622float2(p[j]);
+    f[2 * j] = t.x;
+    f[2 * j + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) p[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+  return u;
+}
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// kNorm: apply LayerNorm; kQuant: emit int8 + scale instead of bf16.
+template <bool kNorm, bool kQuant>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+row_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+           __nv_bfloat16* __restrict__ y, int8_t* __restrict__ yq, float* __restrict__ scale, long long out_rows,
+           int C, float eps, RowMap map) {
+  const int lane = threadIdx.x & 31;
+  const long long orow = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (orow >= out_rows) return;
+  const int nvec = C >> 3;
+  const long long irow = map.src_row(orow);
+
+  if (irow < 0) {  // padded window token: zeros (and the floor scale)
+    for (int i = lane; i < nvec; i += 32) {
+      if (kQuant) reinterpret_cast<uint2*>(yq + orow * C)[i] = make_uint2(0u, 0u);
+      else reinterpret_cast<uint4*>(y + orow * C)[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    if (kQuant && lane == 0) scale[orow] = kAbsmaxFloor / 127.0f;
+    return;
+  }
+
+  float v[kMaxVec][8];
+  const uint4* xr = reinterpret_cast<const uint4*>(x + irow * C);
+#pragma unroll
+  for (int i = 0; i < kMaxVec; ++i) {
+    const int vi = i * 32 + lane;
+    if (vi < nvec) unpack8(xr[vi], v[i]);
+  }
+
+  if (kNorm) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i)
+      if (i * 32 + lane < nvec)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += v[i][j];
+    const float mean = warp_sum(s) / float(C);
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i)
+      if (i * 32 + lane < nvec)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float d = v[i][j] - mean;
+          q += d * d;
+        }
+    const float rstd = rsqrtf(warp_sum(q) / float(C) + eps);
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+      const int vi = i * 32 + lane;
+      if (vi < nvec) {
+        const float4 g0 = reinterpret_cast<const float4*>(gamma)[2 * vi], g1 = reinterpret_cast<const float4*>(gamma)[2 * vi + 1];
+        const float4 b0 = reinterpret_cast<const float4*>(beta)[2 * vi], b1 = reinterpret_cast<const float4*>(beta)[2 * vi + 1];
+        const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = (v[i][j] - mean) * rstd * g[j] + b[j];
+      }
+    }
+  }
+
+  if (!kQuant) {
+    uint4* yr = reinterpret_cast<uint4*>(y + orow * C);
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+      const int vi = i * 32 + lane;
+      if (vi < nvec) yr[vi] = pack8(v[i]);
+    }
+    return;
+  }
+
+  // int8: quantise the bf16-rounded value, as a quantised Linear fed a bf16 tensor would see it.
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < kMaxVec; ++i)
+    if (i * 32 + lane < nvec)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (kNorm) v[i][j] = bf16_round(v[i][j]);
+        amax = fmaxf(amax, fabsf(v[i][j]));
+      }
+  amax = warp_max(amax);
+  const float sc = __fdiv_rn(fmaxf(amax, kAbsmaxFloor), 127.0f);
+  if (lane == 0) scale[orow] = sc;
+  uint2* qr = reinterpret_cast<uint2*>(yq + orow * C);
+#pragma unroll
+  for (int i = 0; i < kMaxVec; ++i) {
+    const int vi = i * 32 + lane;
+    if (vi < nvec) {
+      uint32_t w[2] = {0u, 0u};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float t = rintf(__fdiv_rn(v[i][j], sc));
+        t = fminf(fmaxf(t, -127.f), 127.f);
+        w[j >> 2] |= (uint32_t(int(t)) & 0xffu) << ((j & 3) * 8);
+      }
+      qr[vi] = make_uint2(w[0], w[1]);
+    }
+  }
+}
+
+// Channel LayerNorm of x[tokens, C] (NHWC rows) written as out[img, C, hw] (NCHW).  One block
+// normalises 32 consecutive tokens (one warp per token, 4 rounds of 8) into shared memory, then
+// writes 32-token runs per channel.
+template <bool kTranspose>
+__global__ void __launch_bounds__(256)
+ln2d_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+            __nv_bfloat16* __restrict__ out, long long tokens, int C, int hw, float eps) {
+  extern __shared__ __nv_bfloat16 tile[];   // [32][C + 2]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long t0 = (long long)blockIdx.x * 32;
+  const int pitch = C + 2;
+  for (int r = warp; r < 32; r += 8) {
+    const long long t = t0 + r;
+    if (t >= tokens) break;
+    const __nv_bfloat16* xr = x + t * C;
+    float s = 0.f;
+    for (int c = lane; c < C; c += 32) s += __bfloat162float(xr[c]);
+    const float mean = warp_sum(s) / float(C);
+    float q = 0.f;
+    for (int c = lane; c < C; c += 32) {
+      const float d = __bfloat162float(xr[c]) - mean;
+      q += d * d;
+    }
+    const float rstd = rsqrtf(warp_sum(q) / float(C) + eps);
+    for (int c = lane; c < C; c += 32) {
+      const float o = (__bfloat162float(xr[c]) - mean) * rstd * gamma[c] + beta[c];
+      if (kTranspose) tile[r * pitch + c] = __float2bfloat16_rn(o);
+      else out[t * C + c] = __float2bfloat16_rn(o);
+    }
+  }
+  if (!kTranspose) return;
+  __syncthreads();
+  // hw is a multiple of 32 (checked on the host), so a 32-token run never straddles two images.
+  const long long img = t0 / hw;
+  const int p0 = int(t0 - img * hw);
+  for (int c = warp; c < C; c += 8) {
+    if (t0 + lane < tokens) out[(img * C + c) * hw + p0 + lane] = tile[lane * pitch + c];
+  }
+}
+
+int check_rows(const void* x, long long rows, int C) {
+  if (x == nullptr || rows < 0 || C <= 0) return SAMB_E_BADARG;
+  if (C % 8 || C > kMaxVec * 32 * 8) return SAMB_E_SHAPE;
+  if (reinterpret_cast<uintptr_t>(x) & 15u) return SAMB_E_ALIGN;
+  return SAMB_OK;
+}
+
+int make_map(RowMap* m, long long rows, int grid, int window, long long* out_rows) {
+  m->grid = grid;
+  m->window = window;
+  m->nw = 0;
+  *out_rows = rows;
+  if (window < 0 || grid < 0) return SAMB_E_BADARG;
+  if (window == 0) return SAMB_OK;
+  if (grid <= 0 || rows % ((long long)grid * grid)) return SAMB_E_SHAPE;
+  m->nw = (grid + window - 1) / window;
+  *out_rows = rows / ((long long)grid * grid) * m->nw * m->nw * window * window;
+  return SAMB_OK;
+}
+
+template <bool kNorm, bool kQuant>
+int launch_rows(const void* x, const float* gamma, const float* beta, void* y, int8_t* yq, float* scale,
+                int64_t rows, int C, float eps, int grid, int window, void* stream) {
+  if (int e = check_rows(x, rows, C)) return e;
+  if (kNorm && (gamma == nullptr || beta == nullptr)) return SAMB_E_BADARG;
+  if (kQuant ? (yq == nullptr || scale == nullptr) : (y == nullptr)) return SAMB_E_BADARG;
+  RowMap map;
+  long long out_rows;
+  if (int e = make_map(&map, rows, grid, window, &out_rows)) return e;
+  if (out_rows == 0) return SAMB_OK;
+  const long long blocks = (out_rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  if (blocks > 0x7fffffffLL) return SAMB_E_SHAPE;
+  row_kernel<kNorm, kQuant><<<unsigned(blocks), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), gamma, beta, static_cast<__nv_bfloat16*>(y), yq, scale, out_rows, C, eps,
+      map);
+  return launch_status();
+}
+
+}  // namespace
+}  // namespace samb
+
+extern "C" {
+
+int samb_layernorm_bf16(const void* x, const float* gamma, const float* beta, void* y, int64_t rows, int C, float eps,
+                        int grid, int window, void* stream) {
+  return samb::launch_rows<true, false>(x, gamma, beta, y, nullptr, nullptr, rows, C, eps, grid, window, stream);
+}
+
+int samb_layernorm_quant_i8(const void* x, const float* gamma, const float* beta, int8_t* yq, float* scale,
+                            int64_t rows, int C, float eps, int grid, int window, void* stream) {
+  return samb::launch_rows<true, true>(x, gamma, beta, nullptr, yq, scale, rows, C, eps, grid, window, stream);
+}
+
+int samb_quant_rows_i8(const void* x, int8_t* yq, float* scale, int64_t rows, int C, void* stream) {
+  return samb::launch_rows<false, true>(x, nullptr, nullptr, nullptr, yq, scale, rows, C, 0.f, 0, 0, stream);
+}
+
+int samb_layernorm2d_nchw(const void* x, const float* gamma, const float* beta, void* out, int64_t tokens, int C,
+                          int hw, float eps, int to_nchw, void* stream) {
+  if (x == nullptr || gamma == nullptr || beta == nullptr || out == nullptr || tokens < 0 || C <= 0 || hw <= 0)
+    return SAMB_E_BADARG;
+  if (C > 4096 || (to_nchw && (hw % 32 || tokens % hw))) return SAMB_E_SHAPE;
+  if (tokens == 0) return SAMB_OK;
+  const long long blocks = (tokens + 31) / 32;
+  const size_t smem = to_nchw ? size_t(32) * (C + 2) * sizeof(__nv_bfloat16) : 0;
+  if (smem > 48 * 1024) return SAMB_E_SHAPE;
+  auto st = static_cast<cudaStream_t>(stream);
+  if (to_nchw)
+    samb::ln2d_kernel<true><<<unsigned(blocks), 256, smem, st>>>(static_cast<const __nv_bfloat16*>(x), gamma, beta,
+                                                                 static_cast<__nv_bfloat16*>(out), tokens, C, hw, eps);
+  else
+    samb::ln2d_kernel<false><<<unsigned(blocks), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), gamma, beta,
+                                                               static_cast<__nv_bfloat16*>(out), tokens, C, hw, eps);
+  return samb::launch_status();
+}
+
+}  // extern "C"

@@ -1,0 +1,194 @@
+"""Tensor-level wrappers over the C ABI: torch owns memory and streams, the
+library owns every kernel.  Each wrapper validates dtype/device/contiguity,
+passes raw pointers plus the current CUDA stream, and raises on any error code.
+"""
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import EPI_BIAS, EPI_GELU, EPI_RAW, EPI_RESIDUAL  # noqa: F401  (re-exported)
+
+_status_words = {}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 word that kernels write when a bounded wait expires."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    w = _status_words.get(idx)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status_words[idx] = w
+    return w
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+    """Synchronise and raise if any kernel on ``device`` reported a device-side timeout."""
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    w = status_word(device)
+    v = int(w.item())
+    if v != 0:
+        w.zero_()
+        code = _lib.load().samb_decode_status(v)
+        raise RuntimeError(f"device status 0x{v & 0xffffffff:08x}: {_lib.error_string(code)}")
+
+
+def _need(t: torch.Tensor, dtype: torch.dtype, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name}: expected a CUDA tensor (there is no CPU path)")
+    if t.dtype != dtype:
+        raise RuntimeError(f"{name}: expected {dtype}, got {t.dtype}")
+
+
+def _rows2d(t: torch.Tensor, name: str) -> torch.Tensor:
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise RuntimeError(f"{name}: expected a 2-D tensor with unit inner stride")
+    return t
+
+
+def window_rows(rows: int, grid: int, window: int) -> int:
+    """Number of rows of the zero-padded window-partitioned layout."""
+    if window == 0:
+        return rows
+    nw = -(-grid // window)
+    return rows // (grid * grid) * nw * nw * window * window
+
+
+def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float = 1e-6, grid: int = 0,
+              window: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Row LayerNorm of ``x [rows, C]`` (bf16); with ``window > 0`` the result is in the
+    zero-padded window order (see ``samb_layernorm_bf16``)."""
+    _need(x, torch.bfloat16, "x"); _need(gamma, torch.float32, "gamma"); _need(beta, torch.float32, "beta")
+    x = _rows2d(x, "x")
+    if not x.is_contiguous():
+        raise RuntimeError("x must be contiguous")
+    rows, C = x.shape
+    orow = window_rows(rows, grid, window)
+    if out is None:
+        out = torch.empty(orow, C, dtype=torch.bfloat16, device=x.device)
+    _lib.check(_lib.load().samb_layernorm_bf16(x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), out.data_ptr(), rows, C,
+                                               eps, grid, window, _stream()), "samb_layernorm_bf16")
+    return out
+
+
+def layernorm_quant_i8(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float = 1e-6, grid: int = 0,
+                       window: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+    _need(x, torch.bfloat16, "x"); _need(gamma, torch.float32, "gamma"); _need(beta, torch.float32, "beta")
+    x = _rows2d(x, "x")
+    if not x.is_contiguous():
+        raise RuntimeError("x must be contiguous")
+    rows, C = x.shape
+    orow = window_rows(rows, grid, window)
+    yq = torch.empty(orow, C, dtype=torch.int8, device=x.device)
+    scale = torch.empty(orow, dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().samb_layernorm_quant_i8(x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), yq.data_ptr(),
+                                                   scale.data_ptr(), rows, C, eps, grid, window, _stream()),
+               "samb_layernorm_quant_i8")
+    return yq, scale
+
+
+def quant_rows_i8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    _need(x, torch.bfloat16, "x")
+    x = _rows2d(x, "x")
+    if not x.is_contiguous():
+        raise RuntimeError("x must be contiguous")
+    rows, C = x.shape
+    yq = torch.empty(rows, C, dtype=torch.int8, device=x.device)
+    scale = torch.empty(rows, dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().samb_quant_rows_i8(x.data_ptr(), yq.data_ptr(), scale.data_ptr(), rows, C, _stream()),
+               "samb_quant_rows_i8")
+    return yq, scale
+
+
+def gemm_bf16(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+              residual: Optional[torch.Tensor] = None, gelu: bool = False, raw: bool = False,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``epilogue(a [M,K] @ w [N,K]^T)``; residual ``[R, N]`` with ``M % R == 0`` is broadcast over
+    row blocks.  ``raw`` returns the fp32 accumulator."""
+    _need(a, torch.bfloat16, "a"); _need(w, torch.bfloat16, "w")
+    a, w = _rows2d(a, "a"), _rows2d(w, "w")
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise RuntimeError("gemm_bf16: inner dimensions differ")
+    epi = 0
+    if raw:
+        epi = EPI_RAW
+    else:
+        if bias is not None:
+            _need(bias, torch.float32, "bias"); epi |= EPI_BIAS
+        if gelu:
+            epi |= EPI_GELU
+        if residual is not None:
+            _need(residual, torch.bfloat16, "residual"); residual = _rows2d(residual, "residual"); epi |= EPI_RESIDUAL
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.float32 if raw else torch.bfloat16, device=a.device)
+    out = _rows2d(out, "out")
+    st = status_word(a.device)
+    _lib.check(_lib.load().samb_gemm_bf16(
+        a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), _ptr(bias), _ptr(residual),
+        residual.stride(0) if residual is not None else 0, residual.shape[0] if residual is not None else 0,
+        out.data_ptr(), out.stride(0), M, N, K, epi, st.data_ptr(), _stream()), "samb_gemm_bf16")
+    return out
+
+
+def gemm_i8(aq: torch.Tensor, a_scale: Optional[torch.Tensor], wq: torch.Tensor, w_scale: Optional[torch.Tensor],
+            bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None, gelu: bool = False,
+            raw: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """int8 x int8 -> int32 GEMM with the dequantising epilogue; ``raw`` returns the int32 accumulator."""
+    _need(aq, torch.int8, "aq"); _need(wq, torch.int8, "wq")
+    aq, wq = _rows2d(aq, "aq"), _rows2d(wq, "wq")
+    M, K = aq.shape
+    N = wq.shape[0]
+    if wq.shape[1] != K:
+        raise RuntimeError("gemm_i8: inner dimensions differ")
+    epi = 0
+    if raw:
+        epi = EPI_RAW
+    else:
+        _need(a_scale, torch.float32, "a_scale"); _need(w_scale, torch.float32, "w_scale")
+        if bias is not None:
+            _need(bias, torch.float32, "bias"); epi |= EPI_BIAS
+        if gelu:
+            epi |= EPI_GELU
+        if residual is not None:
+            _need(residual, torch.bfloat16, "residual"); residual = _rows2d(residual, "residual"); epi |= EPI_RESIDUAL
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.int32 if raw else torch.bfloat16, device=aq.device)
+    st = status_word(aq.device)
+    _lib.check(_lib.load().samb_gemm_i8(
+        aq.data_ptr(), aq.stride(0), _ptr(a_scale), wq.data_ptr(), wq.stride(0), _ptr(w_scale), _ptr(bias),
+        _ptr(residual), residual.stride(0) if residual is not None else 0,
+        residual.shape[0] if residual is not None else 0, out.data_ptr(), out.stride(0), M, N, K, epi,
+        st.data_ptr(), _stream()), "samb_gemm_i8")
+    return out
+
+
+def layernorm2d(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, hw: int, eps: float = 1e-6,
+                to_nchw: bool = False) -> torch.Tensor:
+    """Channel LayerNorm of token rows ``x [tokens, C]``; ``to_nchw`` stores ``[tokens/hw, C, hw]``."""
+    _need(x, torch.bfloat16, "x"); _need(gamma, torch.float32, "gamma"); _need(beta, torch.float32, "beta")
+    x = _rows2d(x, "x")
+    if not x.is_contiguous():
+        raise RuntimeError("x must be contiguous")
+    tokens, C = x.shape
+    out = torch.empty((tokens // hw, C, hw) if to_nchw else (tokens, C), dtype=torch.bfloat16, device=x.device)
+    _lib.check(_lib.load().samb_layernorm2d_nchw(x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), out.data_ptr(),
+                                                 tokens, C, hw, eps, int(to_nchw), _stream()), "samb_layernorm2d_nchw")
+    return out
+
+
+def selftest_bounded_wait(limit_polls: int = 20000) -> int:
+    """Run the give-up path of the bounded barrier wait; returns the raw status word."""
+    w = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _lib.check(_lib.load().samb_selftest_bounded_wait(w.data_ptr(), limit_polls, _stream()),
+               "samb_selftest_bounded_wait")
+    return int(w.item())

@@ -1,0 +1,166 @@
+"""GPU parity of the individual kernels, called through the C ABI, against the CPU oracle /
+a float32 restatement of the same op on identical seeded inputs."""
+import pytest
+import torch
+
+from oracle import quant_oracle as qo
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from segment_anything_fast_b200 import ops as _ops
+    return _ops
+
+
+def _bf16(t):
+    return t.to(torch.bfloat16)
+
+
+def test_bounded_wait_gives_up_cleanly(ops):
+    word = ops.selftest_bounded_wait(20000)
+    assert (word >> 24) & 0xff == 0x7E and (word >> 16) & 0xff == 0x55
+    # the context is still usable afterwards
+    assert torch.ones(4, device="cuda").sum().item() == 4.0
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 16), (128, 256, 64), (128, 256, 256), (256, 512, 1280),
+                                   (300, 480, 160), (4096, 3840, 1280), (1000, 1280, 5120), (77, 8, 8)])
+def test_gemm_bf16_raw_accumulator(ops, M, N, K):
+    g = torch.Generator().manual_seed(M * 7 + N * 3 + K)
+    a = _bf16(torch.randn(M, K, generator=g))
+    w = _bf16(torch.randn(N, K, generator=g) * 0.05)
+    ref = a.float() @ w.float().t()
+    out = ops.gemm_bf16(a.cuda(), w.cuda(), raw=True)
+    ops.check_status()
+    torch.testing.assert_close(out.cpu(), ref, rtol=2e-4, atol=2e-4 * ref.abs().max().item())
+
+
+def test_gemm_bf16_identity_layout(ops):
+    """W = I: the output must reproduce A column for column (catches any tile/swizzle permutation)."""
+    M, K = 256, 256
+    a = _bf16(torch.arange(M * K, dtype=torch.float32).reshape(M, K) % 251 - 125)
+    w = _bf16(torch.eye(K))
+    out = ops.gemm_bf16(a.cuda(), w.cuda(), raw=True)
+    ops.check_status()
+    assert torch.equal(out.cpu(), a.float())
+
+
+@pytest.mark.parametrize("bias,gelu,res", [(True, False, False), (True, True, False), (True, False, True),
+                                           (False, False, True)])
+def test_gemm_bf16_epilogues(ops, bias, gelu, res):
+    M, N, K = 520, 640, 320
+    g = torch.Generator().manual_seed(5)
+    a = _bf16(torch.randn(M, K, generator=g))
+    w = _bf16(torch.randn(N, K, generator=g) * 0.05)
+    b = torch.randn(N, generator=g)
+    r = _bf16(torch.randn(M, N, generator=g))
+    ref = a.float() @ w.float().t()
+    if bias:
+        ref = ref + b
+    if gelu:
+        ref = torch.nn.functional.gelu(ref)
+    if res:
+        ref = ref + r.float()
+    out = ops.gemm_bf16(a.cuda(), w.cuda(), b.cuda() if bias else None, r.cuda() if res else None, gelu=gelu)
+    ops.check_status()
+    torch.testing.assert_close(out.float().cpu(), ref, rtol=1e-2, atol=1e-2)
+
+
+def test_gemm_bf16_broadcast_residual(ops):
+    M, N, K, R = 512, 256, 64, 128
+    g = torch.Generator().manual_seed(6)
+    a = _bf16(torch.randn(M, K, generator=g))
+    w = _bf16(torch.randn(N, K, generator=g) * 0.1)
+    r = _bf16(torch.randn(R, N, generator=g))
+    ref = a.float() @ w.float().t() + r.float().repeat(M // R, 1)
+    out = ops.gemm_bf16(a.cuda(), w.cuda(), None, r.cuda())
+    ops.check_status()
+    torch.testing.assert_close(out.float().cpu(), ref, rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 32), (128, 256, 128), (300, 480, 160), (4096, 1280, 1280),
+                                   (777, 5120, 1280), (512, 1280, 5120)])
+def test_gemm_i8_accumulator_bit_exact(ops, M, N, K):
+    g = torch.Generator().manual_seed(M + N + K)
+    aq = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8)
+    wq = torch.randint(-127, 128, (N, K), generator=g, dtype=torch.int8)
+    ref = qo.int8_matmul_i32(aq, wq)
+    out = ops.gemm_i8(aq.cuda(), None, wq.cuda(), None, raw=True)
+    ops.check_status()
+    assert torch.equal(out.cpu(), ref)
+
+
+@pytest.mark.parametrize("gelu,res", [(False, False), (True, False), (False, True)])
+def test_gemm_i8_dequant_epilogue_matches_oracle(ops, gelu, res):
+    M, N, K = 392, 640, 320
+    g = torch.Generator().manual_seed(9)
+    x = _bf16(torch.randn(M, K, generator=g))
+    w = torch.randn(N, K, generator=g) * 0.02
+    b = torch.randn(N, generator=g) * 0.02
+    r = _bf16(torch.randn(M, N, generator=g))
+    ref = qo.int8_linear(x.float(), w, b, gelu=gelu, residual=r.float() if res else None)
+    xq, sx = ops.quant_rows_i8(x.cuda())
+    wq, sw = qo.quantize_rows_absmax(w)
+    xq_ref, sx_ref = qo.quantize_rows_absmax(x.float())
+    assert torch.equal(xq.cpu(), xq_ref) and torch.equal(sx.cpu(), sx_ref)
+    out = ops.gemm_i8(xq, sx, wq.cuda(), sw.cuda(), b.cuda(), r.cuda() if res else None, gelu=gelu)
+    ops.check_status()
+    # same int32 accumulators and scales; only fma contraction / erf differences remain
+    torch.testing.assert_close(out.float().cpu(), ref, rtol=8e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("rows,C", [(64 * 64, 1280), (2 * 64 * 64, 768), (1000, 160), (3, 2048)])
+def test_layernorm_rows(ops, rows, C):
+    g = torch.Generator().manual_seed(rows + C)
+    x = _bf16(torch.randn(rows, C, generator=g) * 3 + 0.5)
+    gamma = 1 + 0.1 * torch.randn(C, generator=g)
+    beta = 0.1 * torch.randn(C, generator=g)
+    ref = torch.nn.functional.layer_norm(x.float(), (C,), gamma, beta, 1e-6)
+    out = ops.layernorm(x.cuda(), gamma.cuda(), beta.cuda(), 1e-6)
+    torch.testing.assert_close(out.float().cpu(), ref, rtol=8e-3, atol=8e-3)
+
+
+@pytest.mark.parametrize("grid,window,C,B", [(64, 14, 160, 2), (32, 14, 768, 1), (28, 14, 64, 1)])
+def test_layernorm_window_partition_order(ops, grid, window, C, B):
+    from oracle import encoder_oracle as eo
+    g = torch.Generator().manual_seed(grid)
+    x = _bf16(torch.randn(B * grid * grid, C, generator=g))
+    gamma = 1 + 0.1 * torch.randn(C, generator=g)
+    beta = 0.1 * torch.randn(C, generator=g)
+    y = torch.nn.functional.layer_norm(x.float(), (C,), gamma, beta, 1e-6).to(torch.bfloat16).float()
+    ref, _ = eo.window_partition(y.reshape(B, grid, grid, C), window)
+    ref = ref.reshape(-1, C)
+    out = ops.layernorm(x.cuda(), gamma.cuda(), beta.cuda(), 1e-6, grid=grid, window=window).float().cpu()
+    assert out.shape == ref.shape
+    pad = ref.abs().sum(dim=1) == 0
+    assert (out[pad] == 0).all()          # pad rows are exactly zero
+    torch.testing.assert_close(out, ref, rtol=8e-3, atol=8e-3)
+
+
+def test_layernorm_quant_matches_oracle_bitwise_given_same_ln(ops):
+    rows, C, grid, window = 2 * 64 * 64, 160, 64, 14
+    g = torch.Generator().manual_seed(11)
+    x = _bf16(torch.randn(rows, C, generator=g))
+    gamma = 1 + 0.1 * torch.randn(C, generator=g)
+    beta = 0.1 * torch.randn(C, generator=g)
+    y = ops.layernorm(x.cuda(), gamma.cuda(), beta.cuda(), 1e-6, grid=grid, window=window)
+    yq, sc = ops.layernorm_quant_i8(x.cuda(), gamma.cuda(), beta.cuda(), 1e-6, grid=grid, window=window)
+    q_ref, s_ref = qo.quantize_rows_absmax(y.float().cpu())
+    assert torch.equal(yq.cpu(), q_ref) and torch.equal(sc.cpu(), s_ref)
+
+
+def test_layernorm2d_nchw(ops):
+    B, hw, C = 2, 64 * 64, 256
+    g = torch.Generator().manual_seed(12)
+    x = _bf16(torch.randn(B * hw, C, generator=g) * 2)
+    gamma = 1 + 0.1 * torch.randn(C, generator=g)
+    beta = 0.1 * torch.randn(C, generator=g)
+    ref = torch.nn.functional.layer_norm(x.float(), (C,), gamma, beta, 1e-6)
+    out = ops.layernorm2d(x.cuda(), gamma.cuda(), beta.cuda(), hw, 1e-6, to_nchw=True).float().cpu()
+    torch.testing.assert_close(out, ref.reshape(B, hw, C).permute(0, 2, 1), rtol=8e-3, atol=8e-3)
+    out2 = ops.layernorm2d(x.cuda(), gamma.cuda(), beta.cuda(), hw, 1e-6, to_nchw=False).float().cpu()
+    torch.testing.assert_close(out2, ref, rtol=8e-3, atol=8e-3)
