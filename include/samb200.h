@@ -103,6 +103,30 @@ int samb_gemm_i8(const int8_t* Aq, int64_t lda, const float* a_scale, const int8
 int samb_layernorm2d_nchw(const void* x, const float* gamma, const float* beta, void* out, int64_t tokens, int C,
                           int hw, float eps, int to_nchw, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Attention with the decomposed relative-position bias, global blocks:
+ *   o = softmax(scale * q k^T + rel_h[..., i, kh(j)] + rel_w[..., i, kw(j)]) v,  key j = kh*64 + kw.
+ * q, k, v, o: contiguous bf16 [B, H, N, d]; rel_h: [B, H, N, N/64]; rel_w: [B, H, N, 64] (bf16).
+ * N a multiple of 128, N <= 4096, d in {64, 80}.  tcgen05 flash attention: logits and P·V in tensor
+ * memory, K/V tiles by TMA, rel_w added on the tensor core through a one-hot operand, rel_h folded
+ * into the exponent's FMA.
+ * ref: _attention_rel_h_rel_w and the Triton kernel it dispatches to, flash_4.py:30-145,335-370
+ * (called at modeling/image_encoder.py:245).
+ * ------------------------------------------------------------------------------------------- */
+int samb_attn_relpos_global(const void* q, const void* k, const void* v, const void* rel_h, const void* rel_w,
+                            void* o, int B, int H, int N, int d, float scale, int32_t* status, void* stream);
+
+/* Same attention reading q/k/v straight out of the qkv projection's output qkv[B*N, 3*H*d]
+ * (columns: q | k | v, head major, ref layout modeling/image_encoder.py:228) and writing o[B*N, o_pitch]
+ * with head h at columns [h*d, (h+1)*d) (the layout proj consumes, image_encoder.py:249).  The bias
+ * comes from table products tab[B*N, ldt]: for head h, tab[t, h*t_head_stride + m] = q_t,h . rel_pos_h[m]
+ * (m < 2*N/64-1) and tab[t, h*t_head_stride + t_w_off + m] = q_t,h . rel_pos_w[m] (m < 127); the kernel
+ * reads rel_h[i, kh] = tab[.., qh(i) - kh + N/64 - 1] and rel_w[i, kw] = tab[.., t_w_off + qw(i) - kw + 63]
+ * (get_rel_pos / add_decomposed_rel_pos, modeling/image_encoder.py:305-372). */
+int samb_attn_relpos_global_qkv(const void* qkv, const void* tab, int64_t ldt, int t_head_stride, int t_w_off, void* o,
+                                int64_t o_pitch, int B, int H, int N, int d, float scale, int32_t* status,
+                                void* stream);
+
 #ifdef __cplusplus
 }
 #endif

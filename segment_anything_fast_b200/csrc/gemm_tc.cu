@@ -2,8 +2,9 @@
 //   out[M,N] = epilogue( A[M,K] * W[N,K]^T )
 // One CTA per SM walks 128x256 output tiles.  Warp 0 streams A/W k-slabs (128 bytes of K per row,
 // 128B-swizzled) into a 4-deep shared-memory ring with TMA; warp 1 issues tcgen05.mma into one of two
-// 256-column fp32/int32 accumulators in tensor memory; warps 2..5 drain the other accumulator
-// (tcgen05.ld -> scale/bias/GELU/residual -> bf16 -> global) while the next tile is being multiplied.
+// 256-column fp32/int32 accumulators in tensor memory; warps 2..9 drain the other accumulator
+// (tcgen05.ld -> scale/bias/GELU/residual -> bf16 -> swizzled staging tile -> TMA store) while the
+// next tile is being multiplied.
 // The bf16 (kind::f16) and int8 (kind::i8) variants share every byte offset: 128 bytes of K are
 // 64 bf16 (4 MMAs of K=16) or 128 int8 (4 MMAs of K=32).
 #include "common.cuh"
@@ -21,8 +22,10 @@ constexpr int B_STAGE_BYTES = BN * SLAB_BYTES;  // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int NUM_ACC = 2;
 constexpr int TMEM_COLS = NUM_ACC * BN;         // 512: all of tensor memory, one CTA per SM
-constexpr int NUM_THREADS = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int NUM_THREADS = 320;                // TMA warp, MMA warp, 8 epilogue warps
+constexpr int EPI_THREADS = 256;
+constexpr int OUT_STAGE_BYTES = BM * 128;        // 64 bf16 columns of the tile, 128B-swizzled rows
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_STAGE_BYTES + 2 * BN * 4 + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
 struct GemmParams {
   void* out;
@@ -40,19 +43,56 @@ struct GemmParams {
   int epilogue;
 };
 
-__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+// Exact-form GELU 0.5 x (1 + erf(x / sqrt 2)) with erf from the Abramowitz-Stegun 7.1.26 rational
+// approximation (|error| < 1.5e-7, far below the bf16 output rounding): one rcp, one ex2, five FMAs.
+__device__ __forceinline__ float gelu_erf(float x) {
+  const float z = fabsf(x) * 0.70710678118654752f;
+  float t, e;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, z, 1.0f)));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-z * z * 1.4426950408889634f));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  const float erf_abs = fmaf(-poly * t, e, 1.0f);
+  return 0.5f * x * (1.0f + copysignf(erf_abs, x));
+}
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <bool kInt8>
+// Named barrier over the 256 epilogue threads that also AND-reduces a predicate, so that all of
+// them take the same decision to continue or to drain.
+__device__ __forceinline__ bool epi_all(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.and.pred p, 1, 256, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"(uint32_t(pred))
+      : "memory");
+  return r != 0;
+}
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+// kEpi: compile-time SAMB_EPI_* flags.  SAMB_EPI_RAW stores the accumulator words directly; every
+// other combination goes registers -> 128B-swizzled staging tile -> TMA store, 64 columns at a time.
+template <bool kInt8, int kEpi>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmOut, const GemmParams p) {
+  constexpr bool kRaw = (kEpi & SAMB_EPI_RAW) != 0;
+  constexpr bool kBias = (kEpi & SAMB_EPI_BIAS) != 0;
+  constexpr bool kGelu = (kEpi & SAMB_EPI_GELU) != 0;
+  constexpr bool kRes = (kEpi & SAMB_EPI_RESIDUAL) != 0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* stage_out = smem + STAGES * STAGE_BYTES;                      // [128][64] bf16, 128B swizzle
+  float* s_bias = reinterpret_cast<float*>(stage_out + OUT_STAGE_BYTES);  // [256]
+  float* s_wscale = s_bias + BN;                                          // [256]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_wscale + BN);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* acc_full = empty_bar + STAGES;
   uint64_t* acc_empty = acc_full + NUM_ACC;
@@ -70,11 +110,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int a = 0; a < NUM_ACC; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 128);
+      mbar_init(&acc_empty[a], EPI_THREADS);
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (!kRaw) tma_prefetch_desc(&tmOut);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -139,78 +180,112 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
-    const uint32_t lane_base = uint32_t(warp & 3) * 32u;   // the TMEM lane quarter this warp may read
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    // Two warps share each TMEM lane quarter (a warp may only touch lanes 32*(warp%4)..+31) and split
+    // every 64-column chunk between them: `half` selects the 32-column side.
+    const uint32_t lane_base = uint32_t(warp & 3) * 32u;
+    const int half = (warp - 2) >> 2;
+    const int erow = int(lane_base) + lane;                // row inside the tile
+    const int et = int(threadIdx.x) - 64;                  // 0..255
     uint32_t acc = 0, acc_phase = 0;
-    bool ok = true;
-    const bool raw = (p.epilogue & SAMB_EPI_RAW) != 0;
-    const bool has_bias = (p.epilogue & SAMB_EPI_BIAS) != 0;
-    const bool has_gelu = (p.epilogue & SAMB_EPI_GELU) != 0;
-    const bool has_res = (p.epilogue & SAMB_EPI_RESIDUAL) != 0;
-    for (long long tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+    for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
       const int m0 = int(tile / p.tiles_n) * BM;
       const int n0 = int(tile % p.tiles_n) * BN;
-      if (!(ok = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, 4))) break;
-      tc_fence_after();
-      const long long row = (long long)m0 + lane_base + lane;
+      const long long row = (long long)m0 + erow;
       const bool row_ok = row < p.M;
-      const long long res_row = (has_res && row_ok) ? row % p.res_rows : 0;
-      float a_scale = 1.0f;
-      if (kInt8 && !raw && row_ok) a_scale = p.a_scale[row];
+      if (!kRaw) {
+        // per-column vectors of this tile; the barrier inside epi_all() publishes them
+        const int n = n0 + et;
+        if (kBias) s_bias[et] = n < p.N ? __ldg(p.bias + n) : 0.f;
+        if (kInt8) s_wscale[et] = n < p.N ? __ldg(p.w_scale + n) : 0.f;
+      }
+      const bool got = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, 4);
+      if (!epi_all(got)) break;
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + (lane_base << 16) + acc * BN + half * 32;
+      if (kRaw) {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int col0 = n0 + c * 32;
-        if (col0 >= p.N) break;                       // uniform across the CTA
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld_32x32b_x32(tmem_base + (lane_base << 16) + acc * BN + c * 32, r);
-        tmem_ld_wait();
-        if (!row_ok) continue;                        // lanes past M only take part in the load
-        if (raw) {
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col0 = n0 + c * 64 + half * 32;
+          if (col0 >= p.N) break;                       // uniform across the warp
+          uint32_t r[32];
+          __syncwarp();
+          tmem_ld_32x32b_x32(t_addr + c * 64, r);
+          tmem_ld_wait();
+          if (!row_ok) continue;                        // lanes past M only take part in the load
           uint32_t* o = reinterpret_cast<uint32_t*>(p.out) + row * p.ldo + col0;
 #pragma unroll
           for (int g = 0; g < 8; ++g)
             if (col0 + g * 4 < p.N)
               *reinterpret_cast<uint4*>(o + g * 4) = make_uint4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
-          continue;
         }
-        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ldo + col0;
-        const __nv_bfloat16* res = has_res ? p.residual + res_row * p.ldr + col0 : nullptr;
+      } else {
+        float a_scale = 1.0f;
+        if (kInt8 && row_ok) a_scale = __ldg(p.a_scale + row);
+        const __nv_bfloat16* res_row = nullptr;
+        if (kRes && row_ok) res_row = p.residual + (row % p.res_rows) * p.ldr + n0 + half * 32;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col0 = n0 + c * 64;                 // first column of the chunk
+          if (col0 >= p.N) break;                       // uniform across the CTA
+          const int colh = col0 + half * 32;            // first column of this warp's side
+          uint4 rv[4];
+          if (kRes) {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {                // groups of 8 columns = one 16-byte store
-          if (col0 + g * 8 >= p.N) break;
-          float v[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int n = col0 + g * 8 + j;
-            float x;
-            if (kInt8) {
-              x = __fmul_rn(__fmul_rn(float(int(r[g * 8 + j])), a_scale), __ldg(p.w_scale + n));
-            } else {
-              x = __uint_as_float(r[g * 8 + j]);
-            }
-            if (has_bias) x = __fadd_rn(x, __ldg(p.bias + n));
-            if (has_gelu) x = gelu_erf(x);
-            v[j] = x;
-          }
-          if (has_res) {
-            const uint4 rv = *reinterpret_cast<const uint4*>(res + g * 8);
-            const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = __bfloat1622float2(rp[j]);
-              v[2 * j] += f.x;
-              v[2 * j + 1] += f.y;
+            for (int u = 0; u < 4; ++u) {
+              rv[u] = make_uint4(0u, 0u, 0u, 0u);
+              if (row_ok && colh + u * 8 < p.N) rv[u] = __ldg(reinterpret_cast<const uint4*>(res_row + c * 64) + u);
             }
           }
-          *reinterpret_cast<uint4*>(o + g * 8) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
-                                                            pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_addr + c * 64, r);
+          tmem_ld_wait();
+          uint4 packed[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int cc = u * 8 + j;                 // column inside this warp's 32
+              const int ct = c * 64 + half * 32 + cc;   // column inside the tile
+              float x;
+              if (kInt8) x = __fmul_rn(__fmul_rn(float(int(r[cc])), a_scale), s_wscale[ct]);
+              else x = __uint_as_float(r[cc]);
+              if (kBias) x = __fadd_rn(x, s_bias[ct]);
+              if (kGelu) x = gelu_erf(x);
+              v[j] = x;
+            }
+            if (kRes) {
+              const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv[u]);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(rp[j]);
+                v[2 * j] += f.x;
+                v[2 * j + 1] += f.y;
+              }
+            }
+            packed[u] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                                   pack_bf16x2(v[6], v[7]));
+          }
+          if (et == 0) tma_store_wait_read<0>();        // the staging tile is free again
+          epi_sync();
+          uint8_t* srow = stage_out + erow * 128;
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            *reinterpret_cast<uint4*>(srow + (((half * 4 + u) ^ (erow & 7)) << 4)) = packed[u];
+          fence_proxy_async_smem();
+          epi_sync();
+          if (et == 0) {
+            tma_store_2d(&tmOut, stage_out, col0, m0);  // rows >= M and columns >= N are clipped
+            tma_store_commit();
+          }
         }
       }
       tc_fence_before();
       mbar_arrive(&acc_empty[acc]);
       if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
     }
+    if (!kRaw && et == 0) tma_store_wait_all<0>();
   }
 
   // ------------------------------------------------------------------ teardown
@@ -219,6 +294,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <bool kInt8>
+using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams);
+
+template <bool kInt8>
+KernelFn<kInt8> pick_kernel(int epi) {
+  switch (epi) {
+    case 0: return gemm_tc_kernel<kInt8, 0>;
+    case 1: return gemm_tc_kernel<kInt8, 1>;
+    case 2: return gemm_tc_kernel<kInt8, 2>;
+    case 3: return gemm_tc_kernel<kInt8, 3>;
+    case 4: return gemm_tc_kernel<kInt8, 4>;
+    case 5: return gemm_tc_kernel<kInt8, 5>;
+    case 6: return gemm_tc_kernel<kInt8, 6>;
+    case 7: return gemm_tc_kernel<kInt8, 7>;
+    default: return gemm_tc_kernel<kInt8, SAMB_EPI_RAW>;
   }
 }
 
@@ -281,11 +374,20 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
   p.num_tiles = ((M + BM - 1) / BM) * p.tiles_n;
   p.epilogue = epilogue;
 
-  auto kern = int8 ? gemm_tc_kernel<true> : gemm_tc_kernel<false>;
+  CUtensorMap tmOut = tmA;   // unused by the raw-accumulator variant
+  if (!raw) {
+    const uint64_t dims[2] = {uint64_t(N), uint64_t(M)};
+    const uint64_t strides[2] = {2, uint64_t(ldo) * 2};
+    const uint32_t box[2] = {64, uint32_t(BM)};
+    if (int e = make_tensor_map(&tmOut, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_128B))
+      return e;
+  }
+  auto kern = int8 ? pick_kernel<true>(epilogue) : pick_kernel<false>(epilogue);
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
     return SAMB_E_LAUNCH;
   const long long grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
-  kern<<<dim3(unsigned(grid)), dim3(NUM_THREADS), SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tmA, tmB, p);
+  kern<<<dim3(unsigned(grid)), dim3(NUM_THREADS), SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tmA, tmB, tmOut, p);
   return launch_status();
 }
 

@@ -192,3 +192,39 @@ def selftest_bounded_wait(limit_polls: int = 20000) -> int:
     _lib.check(_lib.load().samb_selftest_bounded_wait(w.data_ptr(), limit_polls, _stream()),
                "samb_selftest_bounded_wait")
     return int(w.item())
+
+
+def attn_relpos_global(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rel_h: torch.Tensor,
+                       rel_w: torch.Tensor, scale: Optional[float] = None) -> torch.Tensor:
+    """Global-block attention with rel-pos bias: q, k, v ``[B,H,N,d]``, rel_h ``[B,H,N,N/64]``,
+    rel_w ``[B,H,N,64]`` (all contiguous bf16) -> ``[B,H,N,d]``."""
+    for name, t in (("q", q), ("k", k), ("v", v), ("rel_h", rel_h), ("rel_w", rel_w)):
+        _need(t, torch.bfloat16, name)
+        if not t.is_contiguous():
+            raise RuntimeError(f"{name} must be contiguous")
+    B, H, N, d = q.shape
+    if rel_h.shape != (B, H, N, N // 64) or rel_w.shape != (B, H, N, 64):
+        raise RuntimeError("rel_h / rel_w shapes do not match q")
+    o = torch.empty_like(q)
+    st = status_word(q.device)
+    _lib.check(_lib.load().samb_attn_relpos_global(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), rel_h.data_ptr(), rel_w.data_ptr(), o.data_ptr(), B, H, N, d,
+        float(scale if scale is not None else d ** -0.5), st.data_ptr(), _stream()), "samb_attn_relpos_global")
+    return o
+
+
+def attn_relpos_global_qkv(qkv: torch.Tensor, tab: torch.Tensor, t_head_stride: int, t_w_off: int, B: int, H: int,
+                           N: int, d: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Global-block attention over the fused ``qkv [B*N, 3*H*d]`` buffer with the bias taken from
+    the table products ``tab [B*N, ldt]``; returns ``[B*N, H*d]``."""
+    _need(qkv, torch.bfloat16, "qkv"); _need(tab, torch.bfloat16, "tab")
+    if not qkv.is_contiguous() or qkv.shape != (B * N, 3 * H * d):
+        raise RuntimeError("qkv must be contiguous [B*N, 3*H*d]")
+    tab = _rows2d(tab, "tab")
+    if out is None:
+        out = torch.empty(B * N, H * d, dtype=torch.bfloat16, device=qkv.device)
+    st = status_word(qkv.device)
+    _lib.check(_lib.load().samb_attn_relpos_global_qkv(
+        qkv.data_ptr(), tab.data_ptr(), tab.stride(0), t_head_stride, t_w_off, out.data_ptr(), out.stride(0), B, H, N,
+        d, float(d ** -0.5), st.data_ptr(), _stream()), "samb_attn_relpos_global_qkv")
+    return out

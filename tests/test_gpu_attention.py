@@ -1,0 +1,82 @@
+"""GPU parity of the relative-position attention kernels (through the C ABI) against the CPU oracle."""
+import math
+
+import pytest
+import torch
+
+from oracle import encoder_oracle as eo
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from segment_anything_fast_b200 import ops as _ops
+    return _ops
+
+
+def _inputs(B, H, N, d, S_h, S_w, std_qkv, std_rel, seed):
+    torch.manual_seed(seed)
+    q, k, v = (torch.empty(B, H, N, d).normal_(0.0, std_qkv).bfloat16() for _ in range(3))
+    rel_h = torch.empty(B, H, N, S_h).normal_(0.0, std_rel).bfloat16()
+    rel_w = torch.empty(B, H, N, S_w).normal_(0.0, std_rel).bfloat16()
+    return q, k, v, rel_h, rel_w
+
+
+def _cos(a, b):
+    return torch.nn.functional.cosine_similarity(a.flatten().double(), b.flatten().double(), dim=0).item()
+
+
+@pytest.mark.parametrize("B,H,N,d", [(1, 2, 4096, 80), (2, 3, 4096, 64), (1, 1, 256, 80), (3, 2, 1024, 80)])
+def test_global_attention_reference_procedure(ops, B, H, N, d):
+    """The procedure of the reference's own op test: seed 20, N(0, 0.5) inputs, atol = rtol = 1e-3."""
+    q, k, v, rel_h, rel_w = _inputs(B, H, N, d, N // 64, 64, 0.5, 0.5, 20)
+    ref = eo.attention_rel_h_rel_w(q.float(), k.float(), v.float(), rel_h.float(), rel_w.float())
+    out = ops.attn_relpos_global(q.cuda(), k.cuda(), v.cuda(), rel_h.cuda(), rel_w.cuda())
+    ops.check_status()
+    torch.testing.assert_close(out.float().cpu(), ref, rtol=1e-3, atol=1e-3)
+
+
+def test_global_attention_unit_variance_inputs(ops):
+    """Benchmark-configuration distributions: q, k, v ~ N(0,1), rel ~ N(0,0.5); bf16 tolerance
+    max-abs 2e-2 and cosine >= 0.999."""
+    q, k, v, rel_h, rel_w = _inputs(2, 4, 4096, 80, 64, 64, 1.0, 0.5, 0)
+    ref = eo.attention_rel_h_rel_w(q.float(), k.float(), v.float(), rel_h.float(), rel_w.float())
+    out = ops.attn_relpos_global(q.cuda(), k.cuda(), v.cuda(), rel_h.cuda(), rel_w.cuda()).float().cpu()
+    ops.check_status()
+    assert (out - ref).abs().max().item() < 2e-2
+    assert _cos(out, ref) > 0.999
+
+
+def test_global_attention_is_deterministic(ops):
+    q, k, v, rel_h, rel_w = (t.cuda() for t in _inputs(1, 2, 2048, 80, 32, 64, 1.0, 0.5, 3))
+    a = ops.attn_relpos_global(q, k, v, rel_h, rel_w)
+    b = ops.attn_relpos_global(q, k, v, rel_h, rel_w)
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("B,H,d", [(2, 2, 80), (1, 3, 64)])
+def test_global_attention_fused_qkv_layout(ops, B, H, d):
+    """q/k/v read from the qkv projection buffer, bias from the q . rel_pos table products."""
+    N, S = 4096, 64
+    torch.manual_seed(7)
+    qkv = torch.empty(B * N, 3 * H * d).normal_(0.0, 1.0).bfloat16()
+    rph = torch.empty(2 * S - 1, d).normal_(0.0, 0.3).bfloat16()
+    rpw = torch.empty(2 * S - 1, d).normal_(0.0, 0.3).bfloat16()
+    t = qkv.float().reshape(B, N, 3, H, d).permute(2, 0, 3, 1, 4)
+    q, k, v = (t[i].reshape(B * H, N, d) for i in range(3))
+    rel_h, rel_w = eo.decomposed_rel_pos(q, rph.float(), rpw.float(), (S, S))
+    rel_h, rel_w = rel_h.bfloat16().float(), rel_w.bfloat16().float()
+    ref = eo.attention_rel_h_rel_w(q, k, v, rel_h, rel_w)                       # [B*H, N, d]
+    ref = ref.reshape(B, H, N, d).permute(0, 2, 1, 3).reshape(B * N, H * d)
+    # table products: per head [127 | pad | 127 | pad] = 256 columns
+    tab = torch.zeros(B * N, H * 256)
+    qh = qkv.float().reshape(B * N, 3, H, d)[:, 0]                                # [B*N, H, d]
+    tab.view(B * N, H, 256)[:, :, :127] = torch.einsum("nhc,mc->nhm", qh, rph.float())
+    tab.view(B * N, H, 256)[:, :, 128:255] = torch.einsum("nhc,mc->nhm", qh, rpw.float())
+    out = ops.attn_relpos_global_qkv(qkv.cuda(), tab.bfloat16().cuda(), 256, 128, B, H, N, d).float().cpu()
+    ops.check_status()
+    assert (out - ref).abs().max().item() < 2e-2
+    assert _cos(out, ref) > 0.999
