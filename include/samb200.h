@@ -120,12 +120,52 @@ int samb_attn_relpos_global(const void* q, const void* k, const void* v, const v
  * (columns: q | k | v, head major, ref layout modeling/image_encoder.py:228) and writing o[B*N, o_pitch]
  * with head h at columns [h*d, (h+1)*d) (the layout proj consumes, image_encoder.py:249).  The bias
  * comes from table products tab[B*N, ldt]: for head h, tab[t, h*t_head_stride + m] = q_t,h . rel_pos_h[m]
- * (m < 2*N/64-1) and tab[t, h*t_head_stride + t_w_off + m] = q_t,h . rel_pos_w[m] (m < 127); the kernel
+ * (m < 2*N/64-1) and tab[t, h*t_head_stride + t_w_off + m] = (q_t,h . rel_pos_w[m]) / scale (m < 127),
+ * i.e. the width products are stored already divided by the softmax scale; the kernel
  * reads rel_h[i, kh] = tab[.., qh(i) - kh + N/64 - 1] and rel_w[i, kw] = tab[.., t_w_off + qw(i) - kw + 63]
  * (get_rel_pos / add_decomposed_rel_pos, modeling/image_encoder.py:305-372). */
 int samb_attn_relpos_global_qkv(const void* qkv, const void* tab, int64_t ldt, int t_head_stride, int t_w_off, void* o,
                                 int64_t o_pitch, int B, int H, int N, int d, float scale, int32_t* status,
                                 void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Attention with the decomposed relative-position bias, windowed blocks: B independent windows of
+ * window x window = N tokens (window must be 14), key j = kh*window + kw.
+ * q, k, v, o: contiguous bf16 [B, H, N, d]; rel_h, rel_w: [B, H, N, window] (bf16); d in {64, 80}.
+ * ref: the SDPA composite _attention_rel_h_rel_w falls back to for N = 196, flash_4.py:368-370.
+ * ------------------------------------------------------------------------------------------- */
+int samb_attn_relpos_window(const void* q, const void* k, const void* v, const void* rel_h, const void* rel_w, void* o,
+                            int B, int H, int window, int d, float scale, int32_t* status, void* stream);
+
+/* Windowed attention over the qkv projection of the window-partitioned, zero-padded token order
+ * (the row order samb_layernorm_bf16 writes with window > 0): qkv[B*nw*nw*N, 3*H*d].  The output goes
+ * straight back to raster order, o[(b*grid + y)*grid + x, h*d ...] with pad tokens dropped, i.e.
+ * window_unpartition (modeling/image_encoder.py:280-302) is folded into the store.  Bias from table
+ * products as in samb_attn_relpos_global_qkv with 2*window-1 entries per table. */
+int samb_attn_relpos_window_qkv(const void* qkv, const void* tab, int64_t ldt, int t_head_stride, int t_w_off, void* o,
+                                int64_t o_pitch, int B, int H, int grid, int window, int d, float scale,
+                                int32_t* status, void* stream);
+
+/* Products of every head's queries with the relative-position tables, for the *_qkv attention
+ * entry points:  tab[t, h*t_head_stride + m] = (qkv[t, h*d : (h+1)*d] . tables[m, :]) * col_scale[m]
+ * for m < t_head_stride (a multiple of 64; tables is bf16 [t_head_stride, d] holding rel_pos_h at
+ * rows [0, 2S-1), rel_pos_w at rows [t_w_off, t_w_off + 2S-1) and zeros elsewhere; col_scale is 1
+ * for the rel_pos_h rows and 1/scale for the rel_pos_w rows).  One batched tcgen05 GEMM over heads.
+ * ref: the two einsums of add_decomposed_rel_pos, modeling/image_encoder.py:365-366. */
+int samb_relpos_table_products(const void* qkv, int64_t ld_qkv, const void* tables, const float* col_scale, void* tab,
+                               int64_t ldt, int64_t rows, int H, int d, int t_head_stride, int32_t* status,
+                               void* stream);
+
+/* x[B, Cin, grid*patch, grid*patch] (bf16, NCHW) -> a[B*grid*grid, Cin*patch*patch]: one row per
+ * patch in raster order, columns ordered [c][ky][kx] like the flattened Conv2d weight, so that
+ * PatchEmbed's strided convolution is a[.] * weight^T.  patch multiple of 8.
+ * ref: PatchEmbed.forward, modeling/image_encoder.py:398-406. */
+int samb_patch_rows(const void* x, void* a, int B, int Cin, int grid, int patch, void* stream);
+
+/* x[tokens, C] (token-major raster of grid x grid per image) -> a[tokens, 9*C]: the 3x3 neighbourhood
+ * [ky][kx][c] of every token with zeros outside the raster (padding 1), the GEMM operand of the
+ * neck's second convolution.  ref: nn.Conv2d(256, 256, 3, padding=1), modeling/image_encoder.py:97-103. */
+int samb_conv3x3_rows(const void* x, void* a, int64_t tokens, int grid, int C, void* stream);
 
 #ifdef __cplusplus
 }

@@ -209,7 +209,8 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16);
     const int n = n0 + i;                                  // token index inside the image
     const int qh = n / SW, qw = n - qh * SW;
-    const float inv_scale = 1.0f / p.scale;
+    // rel_w tensors are divided by scale here; table products arrive already divided (see the ABI header)
+    const float inv_scale = p.rel_mode == 0 ? 1.0f / p.scale : 1.0f;
     // ---- prologue: rel_w/scale -> swizzled A tile, one-hot E row, rel_h column
     {
       const __nv_bfloat16* src_h;

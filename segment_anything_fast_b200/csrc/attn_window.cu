@@ -1,0 +1,376 @@
+// Attention with the decomposed relative-position bias for the windowed blocks: every window is
+// WS x WS = N tokens (14 x 14 = 196) attending to themselves,
+//   O = softmax(scale * Q K^T + rel_h[i, j / WS] + rel_w[i, j % WS]) V.
+//
+// One CTA owns one (window, head): one TMA brings its Q (two 128-row tiles), K and V (N rounded up to
+// 208 rows) into shared memory, warp 1 issues the two Q K^T products into tensor memory, eight
+// softmax warps (one thread per query row, warps 2..5 for rows 0..127, warps 6..9 for the rest) turn
+// the logits into P, and two P V products land where the logits were.
+//  * rel_w rides on the tensor core like in the global kernel: A = [Q | rel_w/scale (16 columns)],
+//    B = [K | E] with E[j, j % WS] = 1.
+//  * rel_h is constant over runs of WS keys; it is folded into the exp2 FMA addend, one value per run.
+// Zero-padded window tokens need no special case: they are ordinary rows of the padded qkv buffer.
+// Rows N..207 of the K/V box belong to the next window; their probabilities are written as zero.
+#include "common.cuh"
+
+namespace samb {
+namespace {
+
+constexpr int NUM_THREADS = 320;
+constexpr int TMEM_COLS = 512;   // logits of tile 0 at column 0, of tile 1 at column 256
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct WinParams {
+  const __nv_bfloat16* rel_h;    // mode 0: [W*H, N, WS]
+  const __nv_bfloat16* rel_w;
+  const __nv_bfloat16* tab;      // mode 1: table products [W*N, ldt]
+  long long ldt;
+  int t_head_stride, t_w_off, rel_mode;
+  __nv_bfloat16* o;
+  long long o_pitch;
+  int qkv_fused;                 // 0: q/k/v/o are [W*H*N, d]; 1: qkv [W*N, 3*H*d], o rows are raster tokens
+  int H, grid, nw;               // raster side and windows per side (fused mode)
+  float scale;
+  int* status;
+};
+
+template <int D, int WS>
+struct WinSmem {
+  static constexpr int N = WS * WS;
+  static constexpr int NK = (N + 15) / 16 * 16;      // keys rounded up to the MMA granule (208)
+  static constexpr int CH = D / 16;
+  static constexpr int KSTEPS = NK / 16;
+  static constexpr int Q_CHUNK = 256 * 32;           // 256 query rows per 16-column chunk
+  static constexpr int KV_CHUNK = NK * 32;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + CH * Q_CHUNK;
+  static constexpr int OFF_V = OFF_K + CH * KV_CHUNK;
+  static constexpr int OFF_RELW = OFF_V + CH * KV_CHUNK;        // [256][16] bf16, 32B swizzle
+  static constexpr int OFF_E = OFF_RELW + Q_CHUNK;              // [NK][16] bf16 one-hot
+  static constexpr int OFF_P = (OFF_E + KV_CHUNK + 1023) / 1024 * 1024;   // 2 x [KSTEPS][128][16] bf16
+  static constexpr int OFF_BAR = OFF_P + 2 * KSTEPS * 4096;
+  static constexpr int BYTES = OFF_BAR + 128 + 1024;
+  static_assert(N <= 256 && NK <= 256 && WS <= 16, "window too large for this kernel");
+};
+
+__device__ __forceinline__ uint32_t wpack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float wexp2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int D, int WS>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const WinParams p) {
+  using L = WinSmem<D, WS>;
+  constexpr int N = L::N, NK = L::NK, CH = L::CH;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* load_full = bars + 0;
+  uint64_t* pro_done = bars + 1;
+  uint64_t* s_full = bars + 2;   // [2]
+  uint64_t* p_full = bars + 4;   // [2]
+  uint64_t* o_full = bars + 6;   // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int w = blockIdx.x / p.H, h = blockIdx.x - w * p.H;
+
+  int row_base, cq, ck, cv;
+  if (p.qkv_fused) {
+    row_base = w * N;
+    cq = (h * D) / 16;
+    ck = (p.H * D + h * D) / 16;
+    cv = (2 * p.H * D + h * D) / 16;
+  } else {
+    row_base = blockIdx.x * N;
+    cq = ck = cv = 0;
+  }
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(load_full, 1);
+    mbar_init(pro_done, 256);
+    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 128); mbar_init(&o_full[t], 1); }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(load_full, CH * (L::Q_CHUNK + 2 * L::KV_CHUNK));
+      tma_load_3d(smem + L::OFF_Q, &tmQ, load_full, 0, row_base, cq);
+      tma_load_3d(smem + L::OFF_K, &tmK, load_full, 0, row_base, ck);
+      tma_load_3d(smem + L::OFF_V, &tmV, load_full, 0, row_base, cv);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc(kAccF32, kFmtBF16, kFmtBF16, 128, NK);
+      constexpr uint32_t idesc_o = make_idesc(kAccF32, kFmtBF16, kFmtBF16, 128, D, false, /*B MN-major*/ true);
+      const uint32_t q_addr = smem_u32(smem + L::OFF_Q), k_addr = smem_u32(smem + L::OFF_K);
+      const uint32_t v_addr = smem_u32(smem + L::OFF_V), relw_addr = smem_u32(smem + L::OFF_RELW);
+      const uint32_t e_addr = smem_u32(smem + L::OFF_E), p_addr = smem_u32(smem + L::OFF_P);
+      bool ok = mbar_wait(load_full, 0, abort_flag, p.status, 1) && mbar_wait(pro_done, 0, abort_flag, p.status, 2);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {            // logits of query tile t
+          const uint32_t d_tmem = tmem_base + t * 256;
+#pragma unroll
+          for (int c = 0; c < CH; ++c)
+            umma_f16_ss(d_tmem, make_smem_desc(q_addr + c * L::Q_CHUNK + t * 4096, 16, 256, kSwizzle32B),
+                        make_smem_desc(k_addr + c * L::KV_CHUNK, 16, 256, kSwizzle32B), idesc_s, c != 0);
+          umma_f16_ss(d_tmem, make_smem_desc(relw_addr + t * 4096, 16, 256, kSwizzle32B),
+                      make_smem_desc(e_addr, 16, 256, kSwizzle32B), idesc_s, 1u);
+          tc_commit(&s_full[t]);
+        }
+        for (int t = 0; ok && t < 2; ++t) {      // P V of query tile t, over the logits' columns
+          if (!(ok = mbar_wait(&p_full[t], 0, abort_flag, p.status, 3))) break;
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + t * 256;
+#pragma unroll
+          for (int kk = 0; kk < L::KSTEPS; ++kk)
+            umma_f16_ss(d_tmem, make_smem_desc(p_addr + (t * L::KSTEPS + kk) * 4096, 16, 256, kSwizzle32B),
+                        make_smem_desc(v_addr + kk * 512, L::KV_CHUNK, 256, kSwizzle32B), idesc_o, kk != 0);
+          tc_commit(&o_full[t]);
+        }
+      }
+    }
+  } else {
+    const int t = (warp - 2) >> 2;                               // query tile of this warp
+    const int i = (warp & 3) * 32 + lane;                        // row in the tile == TMEM lane
+    const int n = t * 128 + i;                                   // token inside the window
+    const bool valid = n < N;
+    const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + t * 256;
+    const int qh = n / WS, qw = n - qh * WS;
+    // ---- prologue: bias values of this row
+    float bh[WS];
+    {
+      const __nv_bfloat16 *src_h = nullptr, *src_w = nullptr;
+      int step = 1;
+      if (valid) {
+        if (p.rel_mode == 0) {
+          src_h = p.rel_h + ((long long)blockIdx.x * N + n) * WS;
+          src_w = p.rel_w + ((long long)blockIdx.x * N + n) * WS;
+        } else {
+          const __nv_bfloat16* tb = p.tab + ((long long)w * N + n) * p.ldt + h * p.t_head_stride;
+          src_h = tb + (qh + WS - 1);
+          src_w = tb + p.t_w_off + (qw + WS - 1);
+          step = -1;
+        }
+      }
+      const float inv_scale = p.rel_mode == 0 ? 1.0f / p.scale : 1.0f;   // table products arrive pre-divided
+      float rw[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) rw[k] = (valid && k < WS) ? __bfloat162float(src_w[step * k]) * inv_scale : 0.f;
+#pragma unroll
+      for (int k = 0; k < WS; ++k) bh[k] = valid ? __bfloat162float(src_h[step * k]) * kLog2e : 0.f;
+      const int sw = (n >> 2) & 1;                               // 32B swizzle: 16-byte halves swap every 4 rows
+      uint8_t* rrow = smem + L::OFF_RELW + n * 32;
+      *reinterpret_cast<uint4*>(rrow + ((0 ^ sw) << 4)) =
+          make_uint4(wpack2(rw[0], rw[1]), wpack2(rw[2], rw[3]), wpack2(rw[4], rw[5]), wpack2(rw[6], rw[7]));
+      *reinterpret_cast<uint4*>(rrow + ((1 ^ sw) << 4)) =
+          make_uint4(wpack2(rw[8], rw[9]), wpack2(rw[10], rw[11]), wpack2(rw[12], rw[13]), wpack2(rw[14], rw[15]));
+      if (n < NK) {                                              // one-hot row of key n
+        uint32_t e[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          e[k] = (valid && qw == 2 * k ? 0x3F80u : 0u) | (valid && qw == 2 * k + 1 ? 0x3F800000u : 0u);
+        uint8_t* erow = smem + L::OFF_E + n * 32;
+        *reinterpret_cast<uint4*>(erow + ((0 ^ sw) << 4)) = make_uint4(e[0], e[1], e[2], e[3]);
+        *reinterpret_cast<uint4*>(erow + ((1 ^ sw) << 4)) = make_uint4(e[4], e[5], e[6], e[7]);
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(pro_done);
+    }
+    const float c2 = p.scale * kLog2e;
+    bool ok = mbar_wait(&s_full[t], 0, abort_flag, p.status, 4);
+    if (ok) {
+      tc_fence_after();
+      // pass 1: per key-row maxima of the raw logits, then the row maximum of the biased logits
+      float mx[WS];
+#pragma unroll
+      for (int k = 0; k < WS; ++k) mx[k] = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < NK / 16; ++c) {
+        uint32_t r[16];
+        tmem_ld_32x32b_x16(lane_addr + c * 16, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          const int j = c * 16 + u;
+          if (j < N) mx[j / WS] = fmaxf(mx[j / WS], __uint_as_float(r[u]));
+        }
+      }
+      float m = -INFINITY;
+#pragma unroll
+      for (int k = 0; k < WS; ++k) m = fmaxf(m, fmaf(mx[k], c2, bh[k]));
+#pragma unroll
+      for (int k = 0; k < WS; ++k) bh[k] -= m;
+      // pass 2: probabilities -> bf16 P (K-major, 32B swizzle, one 16-key chunk per 4 KiB)
+      float l = 0.f;
+      const int sw = (i >> 2) & 1;
+      uint8_t* prow = smem + L::OFF_P + t * L::KSTEPS * 4096 + i * 32;
+#pragma unroll
+      for (int c = 0; c < NK / 16; ++c) {
+        uint32_t r[16];
+        tmem_ld_32x32b_x16(lane_addr + c * 16, r);
+        tmem_ld_wait();
+        float e[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          const int j = c * 16 + u;
+          e[u] = 0.f;
+          if (j < N) {
+            e[u] = wexp2(fmaf(__uint_as_float(r[u]), c2, bh[j / WS]));
+            l += e[u];
+          }
+        }
+        *reinterpret_cast<uint4*>(prow + c * 4096 + ((0 ^ sw) << 4)) =
+            make_uint4(wpack2(e[0], e[1]), wpack2(e[2], e[3]), wpack2(e[4], e[5]), wpack2(e[6], e[7]));
+        *reinterpret_cast<uint4*>(prow + c * 4096 + ((1 ^ sw) << 4)) =
+            make_uint4(wpack2(e[8], e[9]), wpack2(e[10], e[11]), wpack2(e[12], e[13]), wpack2(e[14], e[15]));
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(&p_full[t]);
+      ok = mbar_wait(&o_full[t], 0, abort_flag, p.status, 5);
+      if (ok) {
+        tc_fence_after();
+        const float inv_l = 1.0f / l;
+        __nv_bfloat16* orow = nullptr;
+        if (valid) {
+          if (p.qkv_fused) {
+            const int ww = p.nw * p.nw;
+            const int b = w / ww, wi = w - b * ww;
+            const int wy = wi / p.nw, wx = wi - wy * p.nw;
+            const int y = wy * WS + qh, x = wx * WS + qw;
+            if (y < p.grid && x < p.grid)
+              orow = p.o + (((long long)b * p.grid + y) * p.grid + x) * p.o_pitch + h * D;
+          } else {
+            orow = p.o + ((long long)blockIdx.x * N + n) * p.o_pitch;
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < D / 16; ++c) {
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(lane_addr + c * 16, r);
+          tmem_ld_wait();
+          if (orow != nullptr) {
+            float f[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) f[u] = __uint_as_float(r[u]) * inv_l;
+            *reinterpret_cast<uint4*>(orow + c * 16) =
+                make_uint4(wpack2(f[0], f[1]), wpack2(f[2], f[3]), wpack2(f[4], f[5]), wpack2(f[6], f[7]));
+            *reinterpret_cast<uint4*>(orow + c * 16 + 8) =
+                make_uint4(wpack2(f[8], f[9]), wpack2(f[10], f[11]), wpack2(f[12], f[13]), wpack2(f[14], f[15]));
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int D, int WS>
+int launch_window(const void* q, const void* k, const void* v, long long rows, long long cols, const WinParams& p,
+                  long long ctas, void* stream) {
+  using L = WinSmem<D, WS>;
+  CUtensorMap tmQ, tmK, tmV;
+  const uint64_t dims[3] = {16, uint64_t(rows), uint64_t(cols / 16)};
+  const uint64_t strides[3] = {2, uint64_t(cols) * 2, 32};
+  const uint32_t box_q[3] = {16, 256, uint32_t(D / 16)};
+  const uint32_t box_kv[3] = {16, uint32_t(L::NK), uint32_t(D / 16)};
+  if (int e = make_tensor_map(&tmQ, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box_q,
+                              CU_TENSOR_MAP_SWIZZLE_32B))
+    return e;
+  if (int e = make_tensor_map(&tmK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(k), dims, strides, box_kv,
+                              CU_TENSOR_MAP_SWIZZLE_32B))
+    return e;
+  if (int e = make_tensor_map(&tmV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(v), dims, strides, box_kv,
+                              CU_TENSOR_MAP_SWIZZLE_32B))
+    return e;
+  auto kern = attn_window_kernel<D, WS>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES) != cudaSuccess)
+    return SAMB_E_LAUNCH;
+  if (ctas > 0x7fffffffLL) return SAMB_E_SHAPE;
+  kern<<<unsigned(ctas), NUM_THREADS, L::BYTES, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, p);
+  return launch_status();
+}
+
+}  // namespace
+}  // namespace samb
+
+extern "C" {
+
+int samb_attn_relpos_window(const void* q, const void* k, const void* v, const void* rel_h, const void* rel_w, void* o,
+                            int B, int H, int window, int d, float scale, int32_t* status, void* stream) {
+  using namespace samb;
+  if (!q || !k || !v || !rel_h || !rel_w || !o || !status) return SAMB_E_BADARG;
+  if (B <= 0 || H <= 0) return SAMB_E_BADARG;
+  if (window != 14 || (d != 64 && d != 80)) return SAMB_E_SHAPE;
+  const long long rows = (long long)B * H * window * window;
+  if (rows > 0x7fffffffLL) return SAMB_E_SHAPE;
+  if (reinterpret_cast<uintptr_t>(o) & 15u) return SAMB_E_ALIGN;
+  if (int e = check_device_arch()) return e;
+  WinParams p{};
+  p.rel_h = static_cast<const __nv_bfloat16*>(rel_h);
+  p.rel_w = static_cast<const __nv_bfloat16*>(rel_w);
+  p.rel_mode = 0;
+  p.o = static_cast<__nv_bfloat16*>(o);
+  p.o_pitch = d;
+  p.qkv_fused = 0;
+  p.H = H;
+  p.scale = scale;
+  p.status = status;
+  return d == 80 ? launch_window<80, 14>(q, k, v, rows, d, p, (long long)B * H, stream)
+                 : launch_window<64, 14>(q, k, v, rows, d, p, (long long)B * H, stream);
+}
+
+int samb_attn_relpos_window_qkv(const void* qkv, const void* tab, int64_t ldt, int t_head_stride, int t_w_off, void* o,
+                                int64_t o_pitch, int B, int H, int grid, int window, int d, float scale,
+                                int32_t* status, void* stream) {
+  using namespace samb;
+  if (!qkv || !tab || !o || !status) return SAMB_E_BADARG;
+  if (B <= 0 || H <= 0 || grid <= 0) return SAMB_E_BADARG;
+  if (window != 14 || (d != 64 && d != 80)) return SAMB_E_SHAPE;
+  const int nw = (grid + window - 1) / window;
+  const long long W = (long long)B * nw * nw;
+  if (W * window * window > 0x7fffffffLL || o_pitch % 8 || o_pitch < (int64_t)H * d) return SAMB_E_SHAPE;
+  if (ldt < (int64_t)H * t_head_stride || t_w_off + 2 * window - 1 > t_head_stride || 2 * window - 1 > t_w_off)
+    return SAMB_E_SHAPE;
+  if (reinterpret_cast<uintptr_t>(o) & 15u) return SAMB_E_ALIGN;
+  if (int e = check_device_arch()) return e;
+  WinParams p{};
+  p.tab = static_cast<const __nv_bfloat16*>(tab);
+  p.ldt = ldt; p.t_head_stride = t_head_stride; p.t_w_off = t_w_off; p.rel_mode = 1;
+  p.o = static_cast<__nv_bfloat16*>(o);
+  p.o_pitch = o_pitch;
+  p.qkv_fused = 1;
+  p.H = H; p.grid = grid; p.nw = nw;
+  p.scale = scale;
+  p.status = status;
+  const long long rows = W * window * window, cols = 3LL * H * d;
+  return d == 80 ? launch_window<80, 14>(qkv, qkv, qkv, rows, cols, p, W * H, stream)
+                 : launch_window<64, 14>(qkv, qkv, qkv, rows, cols, p, W * H, stream);
+}
+
+}  // extern "C"

@@ -20,6 +20,7 @@ constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * SLAB_BYTES;  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * SLAB_BYTES;  // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int EPI_COLSCALE = 16;                // internal epilogue flag: out = acc * w_scale[n] (bf16 operands)
 constexpr int NUM_ACC = 2;
 constexpr int TMEM_COLS = NUM_ACC * BN;         // 512: all of tensor memory, one CTA per SM
 constexpr int NUM_THREADS = 320;                // TMA warp, MMA warp, 8 epilogue warps
@@ -40,6 +41,9 @@ struct GemmParams {
   int k_slabs;
   int tiles_n;
   long long num_tiles;
+  long long tiles_per_batch;     // tiles of one column batch (== num_tiles when not batched)
+  int a_col_stride;              // batch b reads A columns [b*a_col_stride, +K)
+  int o_col_stride;              // and writes out columns [b*o_col_stride, +N)
   int epilogue;
 };
 
@@ -87,6 +91,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   constexpr bool kBias = (kEpi & SAMB_EPI_BIAS) != 0;
   constexpr bool kGelu = (kEpi & SAMB_EPI_GELU) != 0;
   constexpr bool kRes = (kEpi & SAMB_EPI_RESIDUAL) != 0;
+  constexpr bool kColScale = kInt8 || (kEpi & EPI_COLSCALE) != 0;   // multiply by w_scale[n]
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_out = smem + STAGES * STAGE_BYTES;                      // [128][64] bf16, 128B swizzle
@@ -134,13 +139,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (long long tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-        const int m0 = int(tile / p.tiles_n) * BM;
-        const int n0 = int(tile % p.tiles_n) * BN;
+        const int bt = int(tile / p.tiles_per_batch);
+        const long long tb = tile - bt * p.tiles_per_batch;
+        const int m0 = int(tb / p.tiles_n) * BM;
+        const int n0 = int(tb % p.tiles_n) * BN;
+        const int a_col0 = bt * p.a_col_stride;
         for (int ks = 0; ks < p.k_slabs; ++ks) {
           if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 1))) break;
           uint8_t* sa = smem + stage * STAGE_BYTES;
           mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
-          tma_load_2d(sa, &tmA, &full_bar[stage], ks * slab_elems, m0);
+          tma_load_2d(sa, &tmA, &full_bar[stage], a_col0 + ks * slab_elems, m0);
           tma_load_2d(sa + A_STAGE_BYTES, &tmB, &full_bar[stage], ks * slab_elems, n0);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -189,15 +197,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int et = int(threadIdx.x) - 64;                  // 0..255
     uint32_t acc = 0, acc_phase = 0;
     for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
-      const int m0 = int(tile / p.tiles_n) * BM;
-      const int n0 = int(tile % p.tiles_n) * BN;
+      const int bt = int(tile / p.tiles_per_batch);
+      const long long tb = tile - bt * p.tiles_per_batch;
+      const int m0 = int(tb / p.tiles_n) * BM;
+      const int n0 = int(tb % p.tiles_n) * BN;
       const long long row = (long long)m0 + erow;
       const bool row_ok = row < p.M;
       if (!kRaw) {
         // per-column vectors of this tile; the barrier inside epi_all() publishes them
         const int n = n0 + et;
         if (kBias) s_bias[et] = n < p.N ? __ldg(p.bias + n) : 0.f;
-        if (kInt8) s_wscale[et] = n < p.N ? __ldg(p.w_scale + n) : 0.f;
+        if (kColScale) s_wscale[et] = n < p.N ? __ldg(p.w_scale + n) : 0.f;
       }
       const bool got = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, 4);
       if (!epi_all(got)) break;
@@ -251,6 +261,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               float x;
               if (kInt8) x = __fmul_rn(__fmul_rn(float(int(r[cc])), a_scale), s_wscale[ct]);
               else x = __uint_as_float(r[cc]);
+              if (kColScale && !kInt8) x *= s_wscale[ct];
               if (kBias) x = __fadd_rn(x, s_bias[ct]);
               if (kGelu) x = gelu_erf(x);
               v[j] = x;
@@ -276,7 +287,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           fence_proxy_async_smem();
           epi_sync();
           if (et == 0) {
-            tma_store_2d(&tmOut, stage_out, col0, m0);  // rows >= M and columns >= N are clipped
+            tma_store_2d(&tmOut, stage_out, bt * p.o_col_stride + col0, m0);  // clipped at M and at the row end
             tma_store_commit();
           }
         }
@@ -311,16 +322,26 @@ KernelFn<kInt8> pick_kernel(int epi) {
     case 5: return gemm_tc_kernel<kInt8, 5>;
     case 6: return gemm_tc_kernel<kInt8, 6>;
     case 7: return gemm_tc_kernel<kInt8, 7>;
+    case EPI_COLSCALE: return gemm_tc_kernel<kInt8, EPI_COLSCALE>;
     default: return gemm_tc_kernel<kInt8, SAMB_EPI_RAW>;
   }
 }
 
+inline int kmul_of(bool int8) { return int8 ? 16 : 8; }
+
 int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ldw, const float* a_scale,
                 const float* w_scale, const float* bias, const void* residual, int64_t ldr, int64_t res_rows,
-                void* out, int64_t ldo, int64_t M, int N, int K, int epilogue, int32_t* status, void* stream) {
+                void* out, int64_t ldo, int64_t M, int N, int K, int epilogue, int32_t* status, void* stream,
+                int batch = 1, int a_col_stride = 0, int o_col_stride = 0) {
   if (A == nullptr || W == nullptr || out == nullptr || status == nullptr) return SAMB_E_BADARG;
-  if (M < 0 || N <= 0 || K <= 0) return SAMB_E_BADARG;
-  if (epilogue & ~(SAMB_EPI_BIAS | SAMB_EPI_GELU | SAMB_EPI_RESIDUAL | SAMB_EPI_RAW)) return SAMB_E_BADARG;
+  if (M < 0 || N <= 0 || K <= 0 || batch <= 0) return SAMB_E_BADARG;
+  if (epilogue == EPI_COLSCALE) {
+    if (int8 || w_scale == nullptr) return SAMB_E_BADARG;
+  } else if (epilogue & ~(SAMB_EPI_BIAS | SAMB_EPI_GELU | SAMB_EPI_RESIDUAL | SAMB_EPI_RAW)) {
+    return SAMB_E_BADARG;
+  }
+  if (batch > 1 && (N % 64 || a_col_stride % kmul_of(int8) || o_col_stride % 8 || (epilogue & SAMB_EPI_RAW)))
+    return SAMB_E_SHAPE;
   const bool raw = (epilogue & SAMB_EPI_RAW) != 0;
   if (raw && epilogue != SAMB_EPI_RAW) return SAMB_E_BADARG;
   if ((epilogue & SAMB_EPI_BIAS) && bias == nullptr) return SAMB_E_BADARG;
@@ -328,9 +349,11 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
   if (int8 && !raw && (a_scale == nullptr || w_scale == nullptr)) return SAMB_E_BADARG;
   const int esz = int8 ? 1 : 2;
   const int kmul = 16 / esz;                       // K and leading dims: 16-byte multiples
-  if (K % kmul || lda % kmul || ldw % kmul || lda < K || ldw < K) return SAMB_E_SHAPE;
+  const long long a_cols = (long long)(batch - 1) * a_col_stride + K;   // columns of A that are read
+  const long long o_cols = (long long)(batch - 1) * o_col_stride + N;   // columns of out that are written
+  if (K % kmul || lda % kmul || ldw % kmul || lda < a_cols || ldw < K) return SAMB_E_SHAPE;
   const int out_mul = raw ? 4 : 8;
-  if (N % 8 || ldo % out_mul || ldo < N) return SAMB_E_SHAPE;
+  if (N % 8 || ldo % out_mul || ldo < o_cols) return SAMB_E_SHAPE;
   if ((epilogue & SAMB_EPI_RESIDUAL) && (ldr % 8 || ldr < N || res_rows <= 0)) return SAMB_E_SHAPE;
   if (M > (int64_t(1) << 31) - BM) return SAMB_E_SHAPE;
   if ((reinterpret_cast<uintptr_t>(out) & 15u) || (residual && (reinterpret_cast<uintptr_t>(residual) & 15u)))
@@ -342,7 +365,8 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
   const uint32_t slab_elems = uint32_t(SLAB_BYTES / esz);
   CUtensorMap tmA, tmB;
   {
-    const uint64_t dims[2] = {uint64_t(K), uint64_t(M)};
+    // batched: columns past a batch's K belong to the next batch; W's zero fill beyond K cancels them
+    const uint64_t dims[2] = {uint64_t(batch > 1 ? lda : K), uint64_t(M)};
     const uint64_t strides[2] = {uint64_t(esz), uint64_t(lda) * esz};
     const uint32_t box[2] = {slab_elems, uint32_t(BM)};
     if (int e = make_tensor_map(&tmA, dt, 2, const_cast<void*>(A), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
@@ -371,12 +395,15 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
   p.K = K;
   p.k_slabs = (K * esz + SLAB_BYTES - 1) / SLAB_BYTES;
   p.tiles_n = (N + BN - 1) / BN;
-  p.num_tiles = ((M + BM - 1) / BM) * p.tiles_n;
+  p.tiles_per_batch = ((M + BM - 1) / BM) * p.tiles_n;
+  p.num_tiles = p.tiles_per_batch * batch;
+  p.a_col_stride = a_col_stride;
+  p.o_col_stride = o_col_stride;
   p.epilogue = epilogue;
 
   CUtensorMap tmOut = tmA;   // unused by the raw-accumulator variant
   if (!raw) {
-    const uint64_t dims[2] = {uint64_t(N), uint64_t(M)};
+    const uint64_t dims[2] = {uint64_t(o_cols), uint64_t(M)};
     const uint64_t strides[2] = {2, uint64_t(ldo) * 2};
     const uint32_t box[2] = {64, uint32_t(BM)};
     if (int e = make_tensor_map(&tmOut, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, dims, strides, box,
@@ -408,6 +435,14 @@ int samb_gemm_i8(const int8_t* Aq, int64_t lda, const float* a_scale, const int8
                  void* out, int64_t ldo, int64_t M, int N, int K, int epilogue, int32_t* status, void* stream) {
   return samb::launch_gemm(true, Aq, lda, Wq, ldw, a_scale, w_scale, bias, residual, ldr, res_rows, out, ldo, M, N, K,
                            epilogue, status, stream);
+}
+
+int samb_relpos_table_products(const void* qkv, int64_t ld_qkv, const void* tables, const float* col_scale, void* tab,
+                               int64_t ldt, int64_t rows, int H, int d, int t_head_stride, int32_t* status,
+                               void* stream) {
+  if (H <= 0 || d <= 0 || t_head_stride <= 0) return SAMB_E_BADARG;
+  return samb::launch_gemm(false, qkv, ld_qkv, tables, d, nullptr, col_scale, nullptr, nullptr, 0, 0, tab, ldt, rows,
+                           t_head_stride, d, samb::EPI_COLSCALE, status, stream, H, d, t_head_stride);
 }
 
 }  // extern "C"

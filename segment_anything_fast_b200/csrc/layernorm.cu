@@ -159,6 +159,52 @@ row_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
   }
 }
 
+// Per-row int8 quantisation for rows of up to kVec*256 elements: the row stays in registers as raw
+// 16-byte vectors between the absmax pass and the rounding pass.
+template <int kVec>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ yq, float* __restrict__ scale,
+                  long long rows, int C) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nvec = C >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
+  uint4 raw[kVec];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < kVec; ++i) {
+    const int vi = i * 32 + lane;
+    if (vi < nvec) {
+      raw[i] = xr[vi];
+      float f[8];
+      unpack8(raw[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+    }
+  }
+  amax = warp_max(amax);
+  const float sc = __fdiv_rn(fmaxf(amax, kAbsmaxFloor), 127.0f);
+  if (lane == 0) scale[row] = sc;
+  uint2* qr = reinterpret_cast<uint2*>(yq + row * C);
+#pragma unroll
+  for (int i = 0; i < kVec; ++i) {
+    const int vi = i * 32 + lane;
+    if (vi < nvec) {
+      float f[8];
+      unpack8(raw[i], f);
+      uint32_t w[2] = {0u, 0u};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float t = rintf(__fdiv_rn(f[j], sc));
+        t = fminf(fmaxf(t, -127.f), 127.f);
+        w[j >> 2] |= (uint32_t(int(t)) & 0xffu) << ((j & 3) * 8);
+      }
+      qr[vi] = make_uint2(w[0], w[1]);
+    }
+  }
+}
+
 // Channel LayerNorm of x[tokens, C] (NHWC rows) written as out[img, C, hw] (NCHW).  One block
 // normalises 32 consecutive tokens (one warp per token, 4 rounds of 8) into shared memory, then
 // writes 32-token runs per channel.
@@ -253,7 +299,18 @@ int samb_layernorm_quant_i8(const void* x, const float* gamma, const float* beta
 }
 
 int samb_quant_rows_i8(const void* x, int8_t* yq, float* scale, int64_t rows, int C, void* stream) {
-  return samb::launch_rows<false, true>(x, nullptr, nullptr, nullptr, yq, scale, rows, C, 0.f, 0, 0, stream);
+  using namespace samb;
+  if (x == nullptr || yq == nullptr || scale == nullptr || rows < 0 || C <= 0) return SAMB_E_BADARG;
+  if (C % 8 || C > 24 * 256) return SAMB_E_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(x) & 15u) || (reinterpret_cast<uintptr_t>(yq) & 7u)) return SAMB_E_ALIGN;
+  if (rows == 0) return SAMB_OK;
+  const long long blocks = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  if (blocks > 0x7fffffffLL) return SAMB_E_SHAPE;
+  auto st = static_cast<cudaStream_t>(stream);
+  auto xb = static_cast<const __nv_bfloat16*>(x);
+  if (C <= 8 * 256) quant_rows_kernel<8><<<unsigned(blocks), kWarpsPerBlock * 32, 0, st>>>(xb, yq, scale, rows, C);
+  else quant_rows_kernel<24><<<unsigned(blocks), kWarpsPerBlock * 32, 0, st>>>(xb, yq, scale, rows, C);
+  return launch_status();
 }
 
 int samb_layernorm2d_nchw(const void* x, const float* gamma, const float* beta, void* out, int64_t tokens, int C,

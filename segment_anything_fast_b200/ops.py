@@ -228,3 +228,84 @@ def attn_relpos_global_qkv(qkv: torch.Tensor, tab: torch.Tensor, t_head_stride: 
         qkv.data_ptr(), tab.data_ptr(), tab.stride(0), t_head_stride, t_w_off, out.data_ptr(), out.stride(0), B, H, N,
         d, float(d ** -0.5), st.data_ptr(), _stream()), "samb_attn_relpos_global_qkv")
     return out
+
+
+def attn_relpos_window(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rel_h: torch.Tensor,
+                       rel_w: torch.Tensor, scale: Optional[float] = None) -> torch.Tensor:
+    """Windowed attention with rel-pos bias: q, k, v ``[B,H,196,d]``, rel_h / rel_w ``[B,H,196,14]``."""
+    for name, t in (("q", q), ("k", k), ("v", v), ("rel_h", rel_h), ("rel_w", rel_w)):
+        _need(t, torch.bfloat16, name)
+        if not t.is_contiguous():
+            raise RuntimeError(f"{name} must be contiguous")
+    B, H, N, d = q.shape
+    ws = int(round(N ** 0.5))
+    if ws * ws != N or rel_h.shape != (B, H, N, ws) or rel_w.shape != (B, H, N, ws):
+        raise RuntimeError("rel_h / rel_w shapes do not match q")
+    o = torch.empty_like(q)
+    st = status_word(q.device)
+    _lib.check(_lib.load().samb_attn_relpos_window(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), rel_h.data_ptr(), rel_w.data_ptr(), o.data_ptr(), B, H, ws, d,
+        float(scale if scale is not None else d ** -0.5), st.data_ptr(), _stream()), "samb_attn_relpos_window")
+    return o
+
+
+def attn_relpos_window_qkv(qkv: torch.Tensor, tab: torch.Tensor, t_head_stride: int, t_w_off: int, B: int, H: int,
+                           grid: int, window: int, d: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Windowed attention over the window-ordered ``qkv [B*nw*nw*window^2, 3*H*d]``; returns raster-order
+    ``[B*grid*grid, H*d]`` (pad tokens dropped)."""
+    _need(qkv, torch.bfloat16, "qkv"); _need(tab, torch.bfloat16, "tab")
+    rows = window_rows(B * grid * grid, grid, window)
+    if not qkv.is_contiguous() or qkv.shape != (rows, 3 * H * d):
+        raise RuntimeError("qkv must be contiguous [B*nw*nw*window^2, 3*H*d]")
+    tab = _rows2d(tab, "tab")
+    if out is None:
+        out = torch.empty(B * grid * grid, H * d, dtype=torch.bfloat16, device=qkv.device)
+    st = status_word(qkv.device)
+    _lib.check(_lib.load().samb_attn_relpos_window_qkv(
+        qkv.data_ptr(), tab.data_ptr(), tab.stride(0), t_head_stride, t_w_off, out.data_ptr(), out.stride(0), B, H,
+        grid, window, d, float(d ** -0.5), st.data_ptr(), _stream()), "samb_attn_relpos_window_qkv")
+    return out
+
+
+def relpos_table_products(qkv: torch.Tensor, tables: torch.Tensor, col_scale: torch.Tensor, H: int, d: int,
+                          out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``tab[t, h*T + m] = (q_{t,h} . tables[m]) * col_scale[m]`` for every head, ``T = tables.shape[0]``."""
+    _need(qkv, torch.bfloat16, "qkv"); _need(tables, torch.bfloat16, "tables"); _need(col_scale, torch.float32, "col_scale")
+    qkv = _rows2d(qkv, "qkv")
+    T = tables.shape[0]
+    if not tables.is_contiguous() or tables.shape != (T, d) or col_scale.shape != (T,):
+        raise RuntimeError("tables must be contiguous [T, d] with a [T] scale")
+    rows = qkv.shape[0]
+    if out is None:
+        out = torch.empty(rows, H * T, dtype=torch.bfloat16, device=qkv.device)
+    st = status_word(qkv.device)
+    _lib.check(_lib.load().samb_relpos_table_products(
+        qkv.data_ptr(), qkv.stride(0), tables.data_ptr(), col_scale.data_ptr(), out.data_ptr(), out.stride(0), rows, H,
+        d, T, st.data_ptr(), _stream()), "samb_relpos_table_products")
+    return out
+
+
+def patch_rows(x: torch.Tensor, patch: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """NCHW image batch ``[B,Cin,S,S]`` (bf16) -> patch rows ``[B*(S/patch)^2, Cin*patch*patch]``."""
+    _need(x, torch.bfloat16, "x")
+    if x.dim() != 4 or not x.is_contiguous() or x.shape[2] != x.shape[3] or x.shape[2] % patch:
+        raise RuntimeError("x must be a contiguous square NCHW batch whose side is a multiple of the patch size")
+    B, Cin, S, _ = x.shape
+    grid = S // patch
+    if out is None:
+        out = torch.empty(B * grid * grid, Cin * patch * patch, dtype=torch.bfloat16, device=x.device)
+    _lib.check(_lib.load().samb_patch_rows(x.data_ptr(), out.data_ptr(), B, Cin, grid, patch, _stream()), "samb_patch_rows")
+    return out
+
+
+def conv3x3_rows(x: torch.Tensor, grid: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Token rows ``[tokens, C]`` -> 3x3 neighbourhood rows ``[tokens, 9*C]`` (zero padding 1)."""
+    _need(x, torch.bfloat16, "x")
+    x = _rows2d(x, "x")
+    if not x.is_contiguous():
+        raise RuntimeError("x must be contiguous")
+    tokens, C = x.shape
+    if out is None:
+        out = torch.empty(tokens, 9 * C, dtype=torch.bfloat16, device=x.device)
+    _lib.check(_lib.load().samb_conv3x3_rows(x.data_ptr(), out.data_ptr(), tokens, grid, C, _stream()), "samb_conv3x3_rows")
+    return out

@@ -63,20 +63,70 @@ def test_global_attention_fused_qkv_layout(ops, B, H, d):
     N, S = 4096, 64
     torch.manual_seed(7)
     qkv = torch.empty(B * N, 3 * H * d).normal_(0.0, 1.0).bfloat16()
-    rph = torch.empty(2 * S - 1, d).normal_(0.0, 0.3).bfloat16()
-    rpw = torch.empty(2 * S - 1, d).normal_(0.0, 0.3).bfloat16()
+    rph = torch.empty(2 * S - 1, d).normal_(0.0, 0.1).bfloat16()
+    rpw = torch.empty(2 * S - 1, d).normal_(0.0, 0.1).bfloat16()
     t = qkv.float().reshape(B, N, 3, H, d).permute(2, 0, 3, 1, 4)
     q, k, v = (t[i].reshape(B * H, N, d) for i in range(3))
     rel_h, rel_w = eo.decomposed_rel_pos(q, rph.float(), rpw.float(), (S, S))
     rel_h, rel_w = rel_h.bfloat16().float(), rel_w.bfloat16().float()
     ref = eo.attention_rel_h_rel_w(q, k, v, rel_h, rel_w)                       # [B*H, N, d]
     ref = ref.reshape(B, H, N, d).permute(0, 2, 1, 3).reshape(B * N, H * d)
-    # table products: per head [127 | pad | 127 | pad] = 256 columns
-    tab = torch.zeros(B * N, H * 256)
+    # table products: per head [127 rel_pos_h | pad | 127 rel_pos_w (pre-divided by scale) | pad] = 256 columns
+    tables = torch.zeros(256, d, dtype=torch.bfloat16)
+    tables[:127], tables[128:255] = rph, rpw
+    col_scale = torch.ones(256)
+    col_scale[128:] = math.sqrt(d)
+    tab = ops.relpos_table_products(qkv.cuda(), tables.cuda(), col_scale.cuda(), H, d)
     qh = qkv.float().reshape(B * N, 3, H, d)[:, 0]                                # [B*N, H, d]
-    tab.view(B * N, H, 256)[:, :, :127] = torch.einsum("nhc,mc->nhm", qh, rph.float())
-    tab.view(B * N, H, 256)[:, :, 128:255] = torch.einsum("nhc,mc->nhm", qh, rpw.float())
-    out = ops.attn_relpos_global_qkv(qkv.cuda(), tab.bfloat16().cuda(), 256, 128, B, H, N, d).float().cpu()
+    tab_ref = torch.einsum("nhc,mc->nhm", qh, tables.float()) * col_scale
+    torch.testing.assert_close(tab.float().cpu().view(B * N, H, 256), tab_ref, rtol=1e-2, atol=1e-2)
+    out = ops.attn_relpos_global_qkv(qkv.cuda(), tab, 256, 128, B, H, N, d).float().cpu()
     ops.check_status()
+    assert (out - ref).abs().max().item() < 2e-2
+    assert _cos(out, ref) > 0.999
+
+
+@pytest.mark.parametrize("B,H,d,std", [(3, 2, 80, 0.5), (25, 4, 80, 1.0), (2, 3, 64, 1.0)])
+def test_window_attention_op(ops, B, H, d, std):
+    """14x14 windows (N = 196): the composite the reference falls back to for the windowed blocks."""
+    q, k, v, rel_h, rel_w = _inputs(B, H, 196, d, 14, 14, std, 0.5, 20)
+    ref = eo.attention_rel_h_rel_w(q.float(), k.float(), v.float(), rel_h.float(), rel_w.float())
+    out = ops.attn_relpos_window(q.cuda(), k.cuda(), v.cuda(), rel_h.cuda(), rel_w.cuda()).float().cpu()
+    ops.check_status()
+    assert (out - ref).abs().max().item() < 2e-2
+    assert _cos(out, ref) > 0.999
+    if std == 0.5:
+        torch.testing.assert_close(out, ref, rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("B,H,d,grid", [(2, 2, 80, 64), (1, 3, 64, 32)])
+def test_window_attention_fused_layout_with_padding(ops, B, H, d, grid):
+    """Window-ordered, zero-padded qkv rows in; raster-order tokens out (pad queries dropped, pad keys live)."""
+    ws, C = 14, H * d
+    nw = -(-grid // ws)
+    torch.manual_seed(11)
+    # what the qkv projection of zero-padded LayerNorm rows looks like: pad rows carry the bias only
+    x = torch.empty(B, grid, grid, 3 * C).normal_(0.0, 1.0).bfloat16().float()
+    bias = torch.empty(3 * C).normal_(0.0, 0.5).bfloat16().float()
+    win, _ = eo.window_partition(x, ws)                                   # zeros at pads
+    pad = (win.abs().sum(-1, keepdim=True) == 0).float()
+    qkv = (win + pad * bias).reshape(-1, 3 * C)                           # [B*nw*nw*196, 3C]
+    rph = torch.empty(2 * ws - 1, d).normal_(0.0, 0.1).bfloat16().float()
+    rpw = torch.empty(2 * ws - 1, d).normal_(0.0, 0.1).bfloat16().float()
+    W, N = B * nw * nw, ws * ws
+    t = qkv.reshape(W, N, 3, H, d).permute(2, 0, 3, 1, 4)
+    q, k, v = (t[i].reshape(W * H, N, d) for i in range(3))
+    rel_h, rel_w = eo.decomposed_rel_pos(q, rph, rpw, (ws, ws))
+    rel_h, rel_w = rel_h.bfloat16().float(), rel_w.bfloat16().float()
+    o = eo.attention_rel_h_rel_w(q, k, v, rel_h, rel_w).reshape(W, H, ws, ws, d).permute(0, 2, 3, 1, 4)
+    ref = eo.window_unpartition(o.reshape(W, ws, ws, C), ws, (nw * ws, nw * ws), (grid, grid)).reshape(-1, C)
+    tables = torch.zeros(64, d, dtype=torch.bfloat16)
+    tables[:27], tables[32:59] = rph.bfloat16(), rpw.bfloat16()
+    col_scale = torch.ones(64)
+    col_scale[32:] = math.sqrt(d)
+    tab = ops.relpos_table_products(qkv.bfloat16().cuda(), tables.cuda(), col_scale.cuda(), H, d)
+    out = ops.attn_relpos_window_qkv(qkv.bfloat16().cuda(), tab, 64, 32, B, H, grid, ws, d)
+    ops.check_status()
+    out = out.float().cpu()
     assert (out - ref).abs().max().item() < 2e-2
     assert _cos(out, ref) > 0.999
