@@ -1,0 +1,310 @@
+#!/usr/bin/env python
+"""Benchmark of the SAM ViT-H image-encoder hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--quant none|int8] [--impl reference]
+
+One step = one pass of the encoder over a batch of 32 synthetic 1024x1024 images per GPU (images
+shard by rank, weak scaling; the only collective is the all-gather of the embeddings at the end of a
+step).  Prints ONE JSON line (rank 0).  `value` is device-resident throughput (CUDA events, max over
+ranks); `e2e` goes through the host-facing session (pinned uint8 images in, H2D, normalise, encoder,
+D2H of the embeddings).  `--impl reference` times the CPU restatement of the reference encoder on the
+host cores (rank 0 only) on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from functools import partial
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BATCH = 32
+METRIC = "ViT-H encoder images/sec at batch 32"
+# Algorithmic FLOPs per ViT-H image (2*M*N*K, real tokens only, no credit for zero-padded window
+# tokens): patch 8.05e9 + linear 5.154e12 + global attention 3.49e11 + window attention 1.475e11 +
+# neck 7.52e9.
+FLOPS_PER_IMAGE = 5.666e12
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# DRAM bytes per launch of the Linear GEMM kernel from the ncu capture summarised in
+# profiles/gemm_tc_kernel_vit_h_linears.md, scaled to the 131072-row launches of this workload.
+GEMM_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def env_int(name, default):
+    return int(os.environ.get(name, default))
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return p, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi samples of the SM clock and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.proc, self.path = gpu_index, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.idx)],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        clocks, reasons, mx = [], set(), None
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 8:
+                    continue
+                try:
+                    clocks.append(float(f[1])); mx = float(f[2])
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[4:8]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if clocks:
+            busy = sorted(clocks)[len(clocks) // 4:]          # drop the idle head/tail samples
+            out.update(sm_mhz=statistics.median(busy), sm_max_mhz=mx, reasons=sorted(reasons), samples=len(clocks))
+        return out
+
+
+class LaunchProfiler:
+    """Counts every samb_* launch and brackets the Linear GEMMs with CUDA events on the launch stream."""
+    GEMMS = {"samb_gemm_bf16": (10, 11, 12), "samb_gemm_i8": (12, 13, 14)}   # positions of M, N, K in the call
+
+    def __init__(self):
+        self.launches = 0
+        self.records = []          # (flops, start_event, end_event)
+
+    def begin(self, name, args):
+        if name in ("samb_abi_version", "samb_error_string", "samb_decode_status"):
+            return None
+        self.launches += 1
+        pos = self.GEMMS.get(name)
+        if pos is None:
+            return None
+        M, N, K = (int(args[i]) for i in pos)
+        if K < 1024:               # patch-embed / neck GEMMs are not "the Linear layers"
+            return None
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        return (2.0 * M * N * K, s, e)
+
+    def end(self, tok):
+        if tok is not None:
+            tok[2].record()
+            self.records.append(tok)
+
+
+def build_vit_h(quant, device):
+    from segment_anything_fast_b200 import build_image_encoder_vit_h
+    torch.manual_seed(0)
+    enc = build_image_encoder_vit_h()
+    g = torch.Generator().manual_seed(1)
+    with torch.no_grad():
+        for name, p in enc.named_parameters():                 # random-init weights of the ViT-H architecture
+            if p.dim() >= 2 or "rel_pos" in name:
+                p.normal_(0.0, 0.02, generator=g)
+    return enc.to(torch.bfloat16).to(device).set_quant(quant)
+
+
+def run_b200(args):
+    from segment_anything_fast_b200 import EncoderSession, _lib, ops
+    world = env_int("WORLD_SIZE", 1)
+    rank = env_int("RANK", 0)
+    local = env_int("LOCAL_RANK", 0)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the B200 path has no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    quant = None if args.quant == "none" else args.quant
+    enc = build_vit_h(quant, device)
+    sess = EncoderSession(enc, BATCH, device)
+    g = torch.Generator().manual_seed(1000 + rank)
+    sess.host_in.copy_(torch.randint(0, 256, sess.host_in.shape, generator=g, dtype=torch.uint8))
+    images_dev = sess.host_in.to(device)
+    gathered = torch.empty(world * BATCH, enc.out_chans, 64, 64, dtype=torch.bfloat16, device=device) if world > 1 else None
+
+    def step_device():
+        emb = sess.encode_device(images_dev)
+        if dist is not None:
+            dist.all_gather_into_tensor(gathered, emb.contiguous())
+        return emb
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step_device()
+    barrier()
+    ops.check_status(device)
+
+    # ---- timed region: device-resident inputs
+    prof = LaunchProfiler()
+    _lib.set_profiler(prof)
+    sampler = ClockSampler(local)
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        step_device()
+    ev1.record()
+    barrier()
+    clocks = sampler.stop()
+    _lib.set_profiler(None)
+    ms = ev0.elapsed_time(ev1)
+    gemm_flops = sum(r[0] for r in prof.records)
+    gemm_ms = sum(r[1].elapsed_time(r[2]) for r in prof.records)
+    launches = prof.launches
+
+    # ---- end to end: pinned host uint8 in, host embeddings out, every step
+    for _ in range(2):
+        sess.encode()
+    barrier()
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        sess.encode()                      # H2D (pinned uint8) -> normalise -> encoder -> D2H, blocking
+    t1.record()
+    barrier()
+    e2e_ms = t0.elapsed_time(t1)
+    ops.check_status(device)
+
+    if dist is not None:
+        t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = t.tolist()
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    pk, pk_kind = peaks()
+XX
+    achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+    value = world * BATCH * args.steps / (ms * 1e-3)
+    line = {
+        "metric": METRIC, "value": round(value, 2), "unit": "img/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8" if quant == "int8" else "bf16", "data": "synthetic",
+        "config": {"workload": "SAM ViT-H image encoder, batch 32 per GPU, 1024x1024 seeded uint8 images, "
+                               "random-init weights" + (", int8 dynamic-quant linears" if quant else ", bf16 linears"),
+                   "batch_per_gpu": BATCH, "parallelism": f"dp{world} (images sharded by rank, all-gather of embeddings)",
+                   "l2": "inputs_larger_than_l2", "quant": quant or "none"},
+        "clocks": clocks,
+        "e2e": {"value": round(world * BATCH * args.steps / (e2e_ms * 1e-3), 2), "unit": "img/s",
+                "h2d_bytes_per_step": sess.h2d_bytes, "d2h_bytes_per_step": sess.d2h_bytes},
+        "gpu_launches": launches,
+        "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel (qkv/proj/lin1/lin2 launches)",
+                     "achieved": None if achieved is None else round(achieved, 1), "peak": peak_tf, "unit": "TFLOP/s",
+                     "frac": None if achieved is None else round(achieved / peak_tf, 4),
+                     "traffic": GEMM_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": peak_note,
+                     "whole_step_frac": round(value / world * FLOPS_PER_IMAGE / 1e12 / peak_tf, 4)},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_reference(sample_only=True)
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def cpu_reference(sample_only=False, steps=1, warmup=0):
+    """CPU restatement of the reference encoder (oracle port), all host threads, fp32, on a bounded
+    sample: one ViT-H image through patch embedding, 3 windowed blocks + 1 global block, and the neck;
+    the block time is scaled by 32/4 to a whole image."""
+    from oracle import encoder_oracle as eo
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    cfg = eo.VIT_H
+    sd = eo.seeded_state_dict(cfg, seed=0)
+    x = eo.seeded_images(1, seed=1000)
+    sample_blocks = (4, 5, 6, 7)            # three windowed + one global: the 28:4 mix of the full depth
+    times = []
+    with torch.no_grad():
+        for it in range(warmup + steps):
+            t0 = time.perf_counter()
+            eo.image_encoder_forward(x, sd, cfg, "fp32", blocks=())
+            t_stem = time.perf_counter() - t0
+            t0 = time.perf_counter()
+            eo.image_encoder_forward(x, sd, cfg, "fp32", blocks=sample_blocks)
+            t_all = time.perf_counter() - t0
+            if it >= warmup:
+                times.append(t_stem + (t_all - t_stem) * cfg.depth / len(sample_blocks))
+    sec_per_image = statistics.median(times)
+    return {"value": round(1.0 / sec_per_image, 5), "unit": "img/s", "cores": cores, "kind": "port",
+            "sample": "1 ViT-H image, fp32: stem + blocks 4-7 (3 windowed, 1 global) + neck, block time x8",
+            "seconds_per_image": round(sec_per_image, 2)}
+
+
+def run_reference(args):
+    rank = env_int("RANK", 0)
+    if rank != 0:
+        return
+    base = cpu_reference(steps=max(1, min(args.steps, 3)), warmup=0)
+    world = env_int("WORLD_SIZE", 1)
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": "img/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(BATCH * base["seconds_per_image"] * 1e3, 1),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "SAM ViT-H image encoder, batch 32 per GPU, 1024x1024 seeded uint8 images, random-init weights "
+                                   "(CPU restatement of the reference path, bounded sample)"},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": "img/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--quant", choices=["none", "int8"], default="none")
+    ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

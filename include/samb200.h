@@ -167,6 +167,12 @@ int samb_patch_rows(const void* x, void* a, int B, int Cin, int grid, int patch,
  * neck's second convolution.  ref: nn.Conv2d(256, 256, 3, padding=1), modeling/image_encoder.py:97-103. */
 int samb_conv3x3_rows(const void* x, void* a, int64_t tokens, int grid, int C, void* stream);
 
+/* y[b,c,h,w] = bf16((x[b,c,h,w] - mean[c]) / std[c]) for uint8 x[B,3,H,W]; mean/std are HOST arrays of
+ * 3 floats.  H*W multiple of 16.  ref: Sam.preprocess normalisation, modeling/sam.py:164-168, and the
+ * cast to the model dtype at predictor.py:88-90. */
+int samb_normalize_u8(const uint8_t* x, void* y, int B, int C, int H, int W, const float* mean_host,
+                      const float* std_host, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -34,19 +34,47 @@ SIGNATURES = {
     "samb_attn_relpos_window": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, _P, _P]),
     "samb_attn_relpos_window_qkv": (c_int, [_P, _P, c_int64, c_int, c_int, _P, c_int64, c_int, c_int, c_int, c_int,
                                             c_int, c_float, _P, _P]),
+    "samb_normalize_u8": (c_int, [_P, _P, c_int, c_int, c_int, c_int, ctypes.POINTER(c_float), ctypes.POINTER(c_float), _P]),
     "samb_patch_rows": (c_int, [_P, _P, c_int, c_int, c_int, c_int, _P]),
     "samb_conv3x3_rows": (c_int, [_P, _P, c_int64, c_int, c_int, _P]),
     "samb_relpos_table_products": (c_int, [_P, c_int64, _P, _P, _P, c_int64, c_int64, c_int, c_int, c_int, _P, _P]),
 }
 
 _lib = None
+_profiler = None
+
+
+class _Profiled:
+    """Forwards every ``samb_*`` call to the library, bracketing it with ``profiler.begin(name, args)``
+    / ``profiler.end(token)`` (used by the benchmark to count launches and time kernels with events)."""
+
+    def __init__(self, lib, profiler):
+        self._lib, self._profiler = lib, profiler
+
+    def __getattr__(self, name):
+        fn = getattr(self._lib, name)
+        prof = self._profiler
+
+        def call(*args):
+            tok = prof.begin(name, args)
+            try:
+                return fn(*args)
+            finally:
+                prof.end(tok)
+        return call
+
+
+def set_profiler(profiler):
+    """Install (or with ``None`` remove) a launch profiler; see :class:`_Profiled`."""
+    global _profiler
+    _profiler = profiler
 
 
 def load():
     """Load the shared library once and attach the declared signatures."""
     global _lib
     if _lib is not None:
-        return _lib
+        return _lib if _profiler is None else _Profiled(_lib, _profiler)
     if not os.path.exists(LIB_PATH):
         raise RuntimeError(
             f"{LIB_PATH} is missing: the sm_100a kernels are not built "

@@ -309,3 +309,18 @@ def conv3x3_rows(x: torch.Tensor, grid: int, out: Optional[torch.Tensor] = None)
         out = torch.empty(tokens, 9 * C, dtype=torch.bfloat16, device=x.device)
     _lib.check(_lib.load().samb_conv3x3_rows(x.data_ptr(), out.data_ptr(), tokens, grid, C, _stream()), "samb_conv3x3_rows")
     return out
+
+
+def normalize_u8(x: torch.Tensor, mean, std, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """uint8 ``[B,3,H,W]`` -> bf16 ``(x - mean[c]) / std[c]``."""
+    import ctypes
+    _need(x, torch.uint8, "x")
+    if x.dim() != 4 or not x.is_contiguous():
+        raise RuntimeError("x must be a contiguous [B,3,H,W] uint8 tensor")
+    B, C, H, W = x.shape
+    if out is None:
+        out = torch.empty(B, C, H, W, dtype=torch.bfloat16, device=x.device)
+    m = (ctypes.c_float * 3)(*[float(v) for v in mean])
+    s = (ctypes.c_float * 3)(*[float(v) for v in std])
+    _lib.check(_lib.load().samb_normalize_u8(x.data_ptr(), out.data_ptr(), B, C, H, W, m, s, _stream()), "samb_normalize_u8")
+    return out
