@@ -57,6 +57,11 @@ VIT_H = EncoderConfig(1280, 32, 16, (7, 15, 23, 31))   # build_sam.py:14-21
 VIT_L = EncoderConfig(1024, 24, 16, (5, 11, 17, 23))   # build_sam.py:27-34
 VIT_B = EncoderConfig(768, 12, 12, (2, 5, 8, 11))      # build_sam.py:37-44
 
+# False: attention written out as matmul / softmax / matmul (the definition the tests check against).
+# True: torch's fused scaled_dot_product_attention with the bias as attn_mask, which is what the
+# reference's CPU path executes; the CPU-baseline timing switches this on.
+USE_SDPA = False
+
 PIXEL_MEAN = (123.675, 116.28, 103.53)                 # build_sam.py:139
 PIXEL_STD = (58.395, 57.12, 57.375)                    # build_sam.py:140
 
@@ -204,6 +209,8 @@ def attention_rel_h_rel_w(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     r = _rounder(precision)
     d = q.shape[-1]
     bias = r(rel_h.unsqueeze(-1) + rel_w.unsqueeze(-2)).flatten(-2)
+    if USE_SDPA:   # the same composite through torch's fused CPU kernel, as the reference calls it (flash_4.py:370)
+        return r(F.scaled_dot_product_attention(q, k, v, attn_mask=bias))
     logits = torch.matmul(q, k.transpose(-1, -2)) * (1.0 / math.sqrt(d)) + bias
     return r(torch.matmul(torch.softmax(logits, dim=-1), v))
 
