@@ -1,10 +1,12 @@
 // Flash attention with the decomposed relative-position bias, for the global blocks
-// (keys on an Sh x 64 raster, N = 64*Sh <= 4096, head dim d in {64, 80}):
+// (keys on an Sh x 64 raster, N = 64*Sh <= 4096 a multiple of 256, head dim d in {64, 80}):
 //   O = softmax(scale * Q K^T + rel_h[i, kh(j)] + rel_w[i, kw(j)]) V
 //
-// One CTA owns 128 query rows of one (image, head) and walks the keys 128 at a time (two raster
-// rows).  Warp 0 feeds K/V tiles through a 3-deep TMA ring, warp 1 issues tcgen05.mma, warps 2..5
-// (one thread per query row) run the online softmax out of tensor memory.
+// One CTA owns 256 query rows (two 128-row tiles A and B) of one (image, head) and walks the keys
+// 128 at a time (two raster rows).  Warp 0 feeds K/V tiles through a TMA ring, warp 1 issues
+// tcgen05.mma, warps 4..7 run the softmax of tile A and warps 8..11 that of tile B (one thread per
+// query row).  While one tile's threads are busy in the exponentials, the tensor core works on the
+// other tile's Q K^T / P V, so neither pipe waits on a single chain.
 //
 // Where the bias goes:
 //  * rel_w depends on the key column kw = j % 64, the same pattern in every key tile.  It rides on
@@ -13,25 +15,27 @@
 //    out of one accumulation and the softmax multiplies everything by scale.
 //  * rel_h depends on the key row kh: two values per query row and key tile.  They are folded into
 //    the addend of the exp2 FMA, which costs nothing per element.
-// The 128x128 logits live in two TMEM buffers (QK^T of tile j+1 overlaps the softmax of tile j), P
-// goes back to the tensor core through shared memory in the 128B-swizzled K-major layout, P V lands
-// in a fresh TMEM buffer per tile and is folded into fp32 register accumulators with the usual
-// running-max rescale.
+// Per tile: the 128x128 logits live in one TMEM buffer and are pulled into registers in one pass
+// (the buffer is handed back to the tensor core right away); P returns through shared memory in the
+// 128B-swizzled K-major layout; O accumulates in TMEM across key tiles.  The running maximum is only
+// raised when it would grow by more than 2^8 (probabilities stay below 256, exact enough in fp32 /
+// bf16); only then is O rescaled in place, which after the first few key tiles almost never happens.
 #include "common.cuh"
 
 namespace samb {
 namespace {
 
-constexpr int BM = 128;          // query rows per CTA
+constexpr int BM = 128;          // query rows per tile
 constexpr int BK = 128;          // keys per tile
 constexpr int SW = 64;           // raster width the kernel is specialised for
-constexpr int KV_STAGES = 3;
-constexpr int NUM_THREADS = 192;
-constexpr int TMEM_COLS = 512;   // S0 @0, S1 @128, O0 @256, O1 @384
+constexpr int KV_STAGES = 2;
+constexpr int NUM_THREADS = 384;   // warpgroup 0: TMA + MMA warps (2 idle); warpgroups 1, 2: softmax of tiles A, B
+constexpr int TMEM_COLS = 512;   // S_A @0, S_B @128, O_A @256, O_B @384
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.0f;   // log2 domain
 
 struct AttnParams {
-  // bias sources: mode 0 = rel_h/rel_w tensors [BH, N, 64]; mode 1 = table products T[row, ldt]
+  // bias sources: mode 0 = rel_h [BH, N, Sh] / rel_w [BH, N, 64] tensors; mode 1 = table products T[row, ldt]
   const __nv_bfloat16* rel_h;
   const __nv_bfloat16* rel_w;
   const __nv_bfloat16* tab;
@@ -51,14 +55,14 @@ struct AttnParams {
 template <int D>
 struct Smem {
   static constexpr int CH = D / 16;                 // 16-element (32-byte) column chunks
-  static constexpr int TILE = 128 * 32 * CH;        // one 128-row tile of D columns, chunk major
+  static constexpr int Q_CHUNK = 256 * 32;          // 256 query rows of one chunk
+  static constexpr int KV_TILE = 128 * 32 * CH;     // one 128-row K or V tile, chunk major
   static constexpr int OFF_Q = 0;
-  static constexpr int OFF_RELW = OFF_Q + TILE;                 // [128][64] bf16, 128B swizzle
-  static constexpr int OFF_E = OFF_RELW + 128 * 128;            // [128][64] bf16 one-hot, 128B swizzle
-  static constexpr int OFF_RELH = OFF_E + 128 * 128;            // [64][128] bf16 (key row major)
-  static constexpr int OFF_P = OFF_RELH + 64 * 128 * 2;         // 2 x [128][64] bf16, 128B swizzle
-  static constexpr int OFF_KV = OFF_P + 2 * 128 * 128;          // ring of (K tile, V tile)
-  static constexpr int OFF_BAR = OFF_KV + KV_STAGES * 2 * TILE;
+  static constexpr int OFF_RELW = OFF_Q + CH * Q_CHUNK;         // 2 x [128][64] bf16, 128B swizzle
+  static constexpr int OFF_E = OFF_RELW + 2 * 128 * 128;        // [64][64] bf16 one-hot, 128B swizzle
+  static constexpr int OFF_P = OFF_E + 64 * 128;                // 2 tiles x 2 x [128][64] bf16, 128B swizzle
+  static constexpr int OFF_KV = OFF_P + 2 * 2 * 128 * 128;      // ring of (K tile, V tile)
+  static constexpr int OFF_BAR = OFF_KV + KV_STAGES * 2 * KV_TILE;
   static constexpr int BYTES = OFF_BAR + 256 + 1024;
 };
 
@@ -83,21 +87,21 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
   uint64_t* q_full = bars + 0;
   uint64_t* pro_done = bars + 1;
-  uint64_t* kv_full = bars + 2;                 // [KV_STAGES]
-  uint64_t* kv_empty = kv_full + KV_STAGES;     // [KV_STAGES]
-  uint64_t* s_full = kv_empty + KV_STAGES;      // [2]
-  uint64_t* s_empty = s_full + 2;               // [2]
-  uint64_t* p_full = s_empty + 2;
-  uint64_t* p_empty = p_full + 1;
-  uint64_t* o_full = p_empty + 1;               // [2]
-  uint64_t* o_empty = o_full + 2;               // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_empty + 2);
+  uint64_t* k_full = bars + 2;                  // [KV_STAGES] K and V tiles travel through separate rings:
+  uint64_t* k_empty = k_full + KV_STAGES;       //   a K tile is free as soon as both Q K^T products have
+  uint64_t* v_full = k_empty + KV_STAGES;       //   read it, a V tile one key tile later, so the next K
+  uint64_t* v_empty = v_full + KV_STAGES;       //   load gets a whole key tile of lead time
+  uint64_t* s_full = v_empty + KV_STAGES;       // [2] logits of tile t are in TMEM
+  uint64_t* s_free = s_full + 2;                // [2] tile t's threads hold the logits in registers
+  uint64_t* p_full = s_free + 2;                // [2] P of tile t is in shared memory (and O rescaled)
+  uint64_t* pv_done = p_full + 2;               // [2] P V of tile t finished: P buffer free, O stable
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_tiles_q = p.N / BM;
+  const int n_tiles_q = p.N / (2 * BM);
   const int bh = blockIdx.x / n_tiles_q;
-  const int n0 = (blockIdx.x - bh * n_tiles_q) * BM;
+  const int n0 = (blockIdx.x - bh * n_tiles_q) * (2 * BM);
   const int b = bh / p.H, h = bh - b * p.H;
   const int nblk = p.N / BK;
 
@@ -116,14 +120,15 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(q_full, 1);
-    mbar_init(pro_done, 128);
-    for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 128);
-      mbar_init(&o_full[i], 1); mbar_init(&o_empty[i], 128);
+    mbar_init(pro_done, 256);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
     }
-    mbar_init(p_full, 128);
-    mbar_init(p_empty, 1);
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&s_full[t], 1); mbar_init(&s_free[t], 128);
+      mbar_init(&p_full[t], 128); mbar_init(&pv_done[t], 1);
+    }
     fence_mbar_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
   }
@@ -133,210 +138,265 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Register budget: the launch gives every thread 168; the data-movement warpgroup hands most of its
+  // share to the two softmax warpgroups, which hold a whole 128-wide logit row per thread.
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      mbar_expect_tx(q_full, L::TILE);
+      mbar_expect_tx(q_full, CH * L::Q_CHUNK);
       tma_load_3d(smem + L::OFF_Q, &tmQ, q_full, 0, row_base + n0, cq);
       uint32_t stage = 0, phase = 0;
       for (int j = 0; j < nblk; ++j) {
-        if (!mbar_wait(&kv_empty[stage], phase ^ 1u, abort_flag, p.status, 1)) break;
-        uint8_t* sk = smem + L::OFF_KV + stage * 2 * L::TILE;
-        mbar_expect_tx(&kv_full[stage], 2 * L::TILE);
-        tma_load_3d(sk, &tmK, &kv_full[stage], 0, row_base + j * BK, ck);
-        tma_load_3d(sk + L::TILE, &tmV, &kv_full[stage], 0, row_base + j * BK, cv);
+        uint8_t* sk = smem + L::OFF_KV + stage * 2 * L::KV_TILE;
+        if (!mbar_wait(&k_empty[stage], phase ^ 1u, abort_flag, p.status, 1)) break;
+        mbar_expect_tx(&k_full[stage], L::KV_TILE);
+        tma_load_3d(sk, &tmK, &k_full[stage], 0, row_base + j * BK, ck);
+        if (!mbar_wait(&v_empty[stage], phase ^ 1u, abort_flag, p.status, 11)) break;
+        mbar_expect_tx(&v_full[stage], L::KV_TILE);
+        tma_load_3d(sk + L::KV_TILE, &tmV, &v_full[stage], 0, row_base + j * BK, cv);
         if (++stage == KV_STAGES) { stage = 0; phase ^= 1u; }
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // The whole warp runs the loop (warp-uniform control flow and descriptors); one elected lane
+    // issues the tensor-core instructions and their commits.
+    {
       constexpr uint32_t idesc_s = make_idesc(kAccF32, kFmtBF16, kFmtBF16, BM, BK);
+      constexpr uint32_t idesc_e = make_idesc(kAccF32, kFmtBF16, kFmtBF16, BM, 64);
       constexpr uint32_t idesc_o = make_idesc(kAccF32, kFmtBF16, kFmtBF16, BM, D, false, /*B MN-major*/ true);
-      const uint32_t q_addr = smem_u32(smem + L::OFF_Q);
-      const uint32_t relw_addr = smem_u32(smem + L::OFF_RELW);
-      const uint32_t e_addr = smem_u32(smem + L::OFF_E);
-      const uint32_t p_addr = smem_u32(smem + L::OFF_P);
-      const uint32_t kv_addr = smem_u32(smem + L::OFF_KV);
+      // Base descriptors; the start-address field counts 16-byte units, so "+ bytes / 16" moves a tile.
+      const uint64_t dq = make_smem_desc(smem_u32(smem + L::OFF_Q), 16, 256, kSwizzle32B);        // K-major, 32B swizzle
+      const uint64_t dk = make_smem_desc(smem_u32(smem + L::OFF_KV), 16, 256, kSwizzle32B);
+      const uint64_t drw = make_smem_desc(smem_u32(smem + L::OFF_RELW), 16, 1024, kSwizzle128B);  // K-major, 128B swizzle
+      const uint64_t de = make_smem_desc(smem_u32(smem + L::OFF_E), 16, 1024, kSwizzle128B);
+      const uint64_t dp = make_smem_desc(smem_u32(smem + L::OFF_P), 16, 1024, kSwizzle128B);
+      // V: MN-major 32B swizzle, column chunks 4096 B apart (LBO), 8-key groups 256 B apart (SBO)
+      const uint64_t dv = make_smem_desc(smem_u32(smem + L::OFF_KV + L::KV_TILE), 4096, 256, kSwizzle32B);
+      constexpr uint32_t kStageUnits = 2 * L::KV_TILE / 16;
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 2) && mbar_wait(pro_done, 0, abort_flag, p.status, 3);
 
-      auto issue_s = [&](int j) -> bool {        // S[j%2] = [Q | relw] * [K_j | E]^T
-        const uint32_t st = uint32_t(j % KV_STAGES), sb = uint32_t(j & 1);
-        if (!mbar_wait(&kv_full[st], uint32_t(j / KV_STAGES) & 1u, abort_flag, p.status, 4)) return false;
-        if (!mbar_wait(&s_empty[sb], (uint32_t(j >> 1) & 1u) ^ 1u, abort_flag, p.status, 5)) return false;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + sb * 128;
-        const uint32_t k_addr = kv_addr + st * 2 * L::TILE;
+      auto issue_s = [&](int t, int j) {         // S_t = [Q_t | relw_t] * [K_j | E]^T
+        if (elect_one()) {
+          const uint32_t d_tmem = tmem_base + t * 128;
+          const uint64_t dkj = dk + uint32_t(j % KV_STAGES) * kStageUnits;
+          const uint64_t dqt = dq + t * (4096 / 16);
+          const uint64_t drwt = drw + t * (16384 / 16);
 #pragma unroll
-        for (int c = 0; c < CH; ++c) {           // K-major, 32B swizzle: 8-row groups 256 B apart
-          umma_f16_ss(d_tmem, make_smem_desc(q_addr + c * 4096, 16, 256, kSwizzle32B),
-                      make_smem_desc(k_addr + c * 4096, 16, 256, kSwizzle32B), idesc_s, c != 0);
-        }
+          for (int c = 0; c < CH; ++c)
+            umma_f16_ss(d_tmem, dqt + c * (L::Q_CHUNK / 16), dkj + c * (4096 / 16), idesc_s, c != 0);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {            // K-major, 128B swizzle
-          umma_f16_ss(d_tmem, make_smem_desc(relw_addr + c * 32, 16, 1024, kSwizzle128B),
-                      make_smem_desc(e_addr + c * 32, 16, 1024, kSwizzle128B), idesc_s, 1u);
+          for (int hcol = 0; hcol < 2; ++hcol)   // the one-hot block covers 64 keys: once per raster row
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+              umma_f16_ss(d_tmem + hcol * 64, drwt + c * 2, de + c * 2, idesc_e, 1u);
+          tc_commit(&s_full[t]);
         }
-        tc_commit(&s_full[sb]);
-        return true;
+        __syncwarp();
       };
 
-      if (ok) ok = issue_s(0);
-      for (int j = 0; ok && j < nblk; ++j) {
-        if (j + 1 < nblk) { if (!(ok = issue_s(j + 1))) break; }
-        const uint32_t st = uint32_t(j % KV_STAGES), ob = uint32_t(j & 1);
-        if (!(ok = mbar_wait(p_full, uint32_t(j) & 1u, abort_flag, p.status, 6))) break;
-        if (!(ok = mbar_wait(&o_empty[ob], (uint32_t(j >> 1) & 1u) ^ 1u, abort_flag, p.status, 7))) break;
-        tc_fence_after();
-        const uint32_t v_addr = kv_addr + st * 2 * L::TILE + L::TILE;
-        const uint32_t d_tmem = tmem_base + 256 + ob * 128;
+      // Event-driven issue: each tile advances on its own (logits of key tile js[t], P V of key tile
+      // jp[t]) as soon as its operands are ready, so a tile that is still in its exponentials never
+      // holds up the other tile's products.  Every condition is polled without blocking; the idle
+      // poll count is bounded.
+      int js[2] = {0, 0}, jp[2] = {0, 0};
+      int k_released = 0, v_released = 0;        // key tiles whose K / V buffers have been handed back
+      uint32_t idle = 0;
+      while (ok && (jp[0] < nblk || jp[1] < nblk)) {
+        bool progress = false;
 #pragma unroll
-        for (int kk = 0; kk < BK / 16; ++kk) {
-          // A = P: K-major 128B swizzle, two [128][64] tiles.  B = V: MN-major 32B swizzle, 16 keys
-          // (512 B) per step, column chunks 4096 B apart (LBO), 8-key groups 256 B apart (SBO).
-          umma_f16_ss(d_tmem,
-                      make_smem_desc(p_addr + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024, kSwizzle128B),
-                      make_smem_desc(v_addr + kk * 512, 4096, 256, kSwizzle32B), idesc_o, kk != 0);
+        for (int t = 0; t < 2; ++t) {
+          const int j = js[t];
+          if (j < nblk && mbar_test_wait(&k_full[j % KV_STAGES], uint32_t(j / KV_STAGES) & 1u) &&
+              (j == 0 || mbar_test_wait(&s_free[t], uint32_t(j - 1) & 1u))) {
+            tc_fence_after();
+            issue_s(t, j);
+            js[t] = j + 1;
+            progress = true;
+          }
+          const int jv = jp[t];
+          if (jv < nblk && jv < js[t] && mbar_test_wait(&p_full[t], uint32_t(jv) & 1u) &&
+              mbar_test_wait(&v_full[jv % KV_STAGES], uint32_t(jv / KV_STAGES) & 1u)) {
+            tc_fence_after();
+            if (elect_one()) {
+              const uint64_t dvj = dv + uint32_t(jv % KV_STAGES) * kStageUnits;
+              const uint64_t dpt = dp + t * (32768 / 16);
+              const uint32_t d_tmem = tmem_base + 256 + t * 128;
+#pragma unroll
+              for (int kk = 0; kk < BK / 16; ++kk)   // 16 keys per step: 32 B of a P row, 512 B of V
+                umma_f16_ss(d_tmem, dpt + (kk >> 2) * (16384 / 16) + (kk & 3) * 2, dvj + kk * (512 / 16), idesc_o,
+                            (jv | kk) != 0);
+              tc_commit(&pv_done[t]);
+            }
+            __syncwarp();
+            jp[t] = jv + 1;
+            progress = true;
+          }
         }
-        tc_commit(&o_full[ob]);
-        tc_commit(&kv_empty[st]);
-        tc_commit(p_empty);
+        // hand buffers back once both tiles have issued everything that reads them
+        const int s_min = js[0] < js[1] ? js[0] : js[1];
+        const int p_min = jp[0] < jp[1] ? jp[0] : jp[1];
+        while (k_released < s_min) {
+          if (elect_one()) tc_commit(&k_empty[k_released % KV_STAGES]);
+          __syncwarp();
+          ++k_released;
+        }
+        while (v_released < p_min) {
+          if (elect_one()) tc_commit(&v_empty[v_released % KV_STAGES]);
+          __syncwarp();
+          ++v_released;
+        }
+        if (progress) {
+          idle = 0;
+        } else if (++idle > kSpinLimit || (idle > 2048u && *abort_flag)) {
+          *abort_flag = 1;
+          if (p.status != nullptr) atomicCAS(p.status, 0, int((kDevTimeout << 24) | (13u << 16) | (blockIdx.x & 0xffffu)));
+          ok = false;
+        } else if (idle > 4096u) {
+          __nanosleep(32);
+        }
       }
     }
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
     // ---------------------------------------------------------------- softmax (one thread = one row)
-    const int i = (warp & 3) * 32 + lane;                 // row in the tile == TMEM lane
+    const int t = (warp - 4) >> 2;                         // query tile
+    const int i = (warp & 3) * 32 + lane;                  // row in the tile == TMEM lane
     const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16);
-    const int n = n0 + i;                                  // token index inside the image
+    const int n = n0 + t * BM + i;                         // token index inside the image
     const int qh = n / SW, qw = n - qh * SW;
-    // rel_w tensors are divided by scale here; table products arrive already divided (see the ABI header)
+    // rel_w tensors are divided by scale here; table products arrive already divided
     const float inv_scale = p.rel_mode == 0 ? 1.0f / p.scale : 1.0f;
-    // ---- prologue: rel_w/scale -> swizzled A tile, one-hot E row, rel_h column
+    const __nv_bfloat16* src_h;
+    int step;                                              // +1: src[k]; -1: src[-k] (table products)
     {
-      const __nv_bfloat16* src_h;
       const __nv_bfloat16* src_w;
-      int step;                                            // +1: src[k]; -1: src[-k] (table products)
       if (p.rel_mode == 0) {
         src_h = p.rel_h + ((long long)bh * p.N + n) * p.Sh;
         src_w = p.rel_w + ((long long)bh * p.N + n) * SW;
         step = 1;
       } else {
-        const __nv_bfloat16* t = p.tab + ((long long)b * p.N + n) * p.ldt + h * p.t_head_stride;
-        src_h = t + (qh + p.Sh - 1);
-        src_w = t + p.t_w_off + (qw + SW - 1);
+        const __nv_bfloat16* tb = p.tab + ((long long)b * p.N + n) * p.ldt + h * p.t_head_stride;
+        src_h = tb + (qh + p.Sh - 1);
+        src_w = tb + p.t_w_off + (qw + SW - 1);
         step = -1;
       }
-      uint8_t* relw_row = smem + L::OFF_RELW + i * 128;
+      uint8_t* relw_row = smem + L::OFF_RELW + t * 16384 + i * 128;
       uint8_t* e_row = smem + L::OFF_E + i * 128;
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         uint32_t w[4], e[4];
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const int k0 = u * 8 + 2 * t;
+        for (int tt = 0; tt < 4; ++tt) {
+          const int k0 = u * 8 + 2 * tt;
           const float a = __bfloat162float(src_w[step * k0]) * inv_scale;
           const float c = __bfloat162float(src_w[step * (k0 + 1)]) * inv_scale;
-          w[t] = pack2(a, c);
-          e[t] = ((i & 63) == k0 ? 0x3F80u : 0u) | ((i & 63) == k0 + 1 ? 0x3F800000u : 0u);
+          w[tt] = pack2(a, c);
+          e[tt] = (i == k0 ? 0x3F80u : 0u) | (i == k0 + 1 ? 0x3F800000u : 0u);
         }
         const int phys = (u ^ (i & 7)) << 4;
         *reinterpret_cast<uint4*>(relw_row + phys) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4*>(e_row + phys) = make_uint4(e[0], e[1], e[2], e[3]);
+        if (t == 0 && i < 64) *reinterpret_cast<uint4*>(e_row + phys) = make_uint4(e[0], e[1], e[2], e[3]);
       }
-      __nv_bfloat16* relh = reinterpret_cast<__nv_bfloat16*>(smem + L::OFF_RELH);
-      for (int kh = 0; kh < p.Sh; ++kh) relh[kh * 128 + i] = src_h[step * kh];
       fence_proxy_async_smem();
       mbar_arrive(pro_done);
     }
-    const __nv_bfloat16* relh = reinterpret_cast<const __nv_bfloat16*>(smem + L::OFF_RELH);
     const float c2 = p.scale * kLog2e;
-    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
-    float acc[D];
-#pragma unroll
-    for (int c = 0; c < D; ++c) acc[c] = 0.f;
+    float m_used = -INFINITY, l_run = 0.f;
+    float bh0 = __bfloat162float(src_h[0]) * kLog2e;
+    float bh1 = __bfloat162float(src_h[step]) * kLog2e;
+    const uint32_t s_addr = lane_addr + t * 128;
+    const uint32_t o_addr = lane_addr + 256 + t * 128;
+    uint8_t* p_tile = smem + L::OFF_P + t * 32768 + i * 128;
     bool ok = true;
 
-    auto fold_o = [&](int j, float alpha) -> bool {       // acc = acc * alpha + (P_j V_j)
-      const uint32_t ob = uint32_t(j & 1);
-      if (!mbar_wait(&o_full[ob], uint32_t(j >> 1) & 1u, abort_flag, p.status, 8)) return false;
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < D / 16; ++c) {
-        uint32_t r[16];
-        tmem_ld_32x32b_x16(lane_addr + 256 + ob * 128 + c * 16, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int t = 0; t < 16; ++t) acc[c * 16 + t] = fmaf(acc[c * 16 + t], alpha, __uint_as_float(r[t]));
-      }
-      tc_fence_before();
-      mbar_arrive(&o_empty[ob]);
-      return true;
-    };
-
     for (int j = 0; j < nblk; ++j) {
-      const uint32_t sb = uint32_t(j & 1);
-      if (!(ok = mbar_wait(&s_full[sb], uint32_t(j >> 1) & 1u, abort_flag, p.status, 9))) break;
-      tc_fence_after();
-      const uint32_t s_addr = lane_addr + sb * 128;
-      // pass 1: row maximum, separately for the two key rows of this tile
-      float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(s_addr + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int t = 0; t < 32; ++t) mx[c >> 1] = fmaxf(mx[c >> 1], __uint_as_float(r[t]));
+      const uint32_t par = uint32_t(j) & 1u;
+      // rel_h of the next key tile (two raster rows), fetched early
+      float nbh0 = 0.f, nbh1 = 0.f;
+      if (j + 1 < nblk) {
+        nbh0 = __bfloat162float(src_h[step * (2 * j + 2)]) * kLog2e;
+        nbh1 = __bfloat162float(src_h[step * (2 * j + 3)]) * kLog2e;
       }
-      const float bh0 = __bfloat162float(relh[(2 * j) * 128 + i]) * kLog2e;
-      const float bh1 = __bfloat162float(relh[(2 * j + 1) * 128 + i]) * kLog2e;
-      const float m_new = fmaxf(m_run, fmaxf(fmaf(mx[0], c2, bh0), fmaf(mx[1], c2, bh1)));
-      const float alpha = fast_exp2(m_run - m_new);
-      const float add[2] = {bh0 - m_new, bh1 - m_new};
-      // P buffer must have been consumed by the previous P V
-      if (!(ok = mbar_wait(p_empty, (uint32_t(j) & 1u) ^ 1u, abort_flag, p.status, 10))) break;
-      // pass 2: p = exp2(s * c2 + add), row sum, bf16 P into the swizzled A tile
+      if (!(ok = mbar_wait(&s_full[t], par, abort_flag, p.status, 8))) break;
+      tc_fence_after();
+      uint32_t s[128];
+      tmem_ld_32x32b_x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_ld_32x32b_x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+      tmem_ld_32x32b_x32(s_addr + 64, *reinterpret_cast<uint32_t(*)[32]>(&s[64]));
+      tmem_ld_32x32b_x32(s_addr + 96, *reinterpret_cast<uint32_t(*)[32]>(&s[96]));
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&s_free[t]);                              // the tensor core may overwrite the logits
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        mx0 = fmaxf(mx0, __uint_as_float(s[c]));
+        mx1 = fmaxf(mx1, __uint_as_float(s[64 + c]));
+      }
+      const float m_blk = fmaxf(fmaf(mx0, c2, bh0), fmaf(mx1, c2, bh1));
+      // P V of the previous key tile must be done: the P buffer is free and O is stable
+      if (!(ok = mbar_wait(&pv_done[t], par ^ 1u, abort_flag, p.status, 9))) break;
+      if (j == 0) {
+        m_used = m_blk;
+      } else if (__any_sync(0xffffffffu, m_blk > m_used + kRescaleThreshold)) {
+        const float m_new = fmaxf(m_used, m_blk);
+        const float alpha = fast_exp2(m_used - m_new);
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < D / 16; ++c) {
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(o_addr + c * 16, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 16; ++q) r[q] = __float_as_uint(__uint_as_float(r[q]) * alpha);
+          tmem_st_32x32b_x16(o_addr + c * 16, r);
+        }
+        tmem_st_wait();
+        l_run *= alpha;
+        m_used = m_new;
+      }
+      const float add0 = bh0 - m_used, add1 = bh1 - m_used;
       float l_blk = 0.f;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(s_addr + c * 32, r);
-        tmem_ld_wait();
-        uint8_t* prow = smem + L::OFF_P + (c >> 1) * 16384 + i * 128;
+      for (int u = 0; u < 16; ++u) {
+        float e[8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          float e[8];
-#pragma unroll
-          for (int t = 0; t < 8; ++t) {
-            e[t] = fast_exp2(fmaf(__uint_as_float(r[u * 8 + t]), c2, add[c >> 1]));
-            l_blk += e[t];
-          }
-          const int unit = (c & 1) * 4 + u;
-          *reinterpret_cast<uint4*>(prow + ((unit ^ (i & 7)) << 4)) =
-              make_uint4(pack2(e[0], e[1]), pack2(e[2], e[3]), pack2(e[4], e[5]), pack2(e[6], e[7]));
+        for (int q = 0; q < 8; ++q) {
+          e[q] = fast_exp2(fmaf(__uint_as_float(s[u * 8 + q]), c2, u < 8 ? add0 : add1));
+          l_blk += e[q];
         }
+        *reinterpret_cast<uint4*>(p_tile + (u >> 3) * 16384 + (((u & 7) ^ (i & 7)) << 4)) =
+            make_uint4(pack2(e[0], e[1]), pack2(e[2], e[3]), pack2(e[4], e[5]), pack2(e[6], e[7]));
       }
+      l_run += l_blk;
       tc_fence_before();
-      mbar_arrive(&s_empty[sb]);
       fence_proxy_async_smem();
-      mbar_arrive(p_full);
-      // fold the previous tile's P V while the tensor core works on this one
-      if (j > 0) { if (!(ok = fold_o(j - 1, alpha_prev))) break; }
-      l_run = fmaf(l_run, alpha, l_blk);
-      m_run = m_new;
-      alpha_prev = alpha;
+      mbar_arrive(&p_full[t]);
+      bh0 = nbh0;
+      bh1 = nbh1;
     }
-    if (ok) ok = fold_o(nblk - 1, alpha_prev);
+    if (ok) ok = mbar_wait(&pv_done[t], uint32_t(nblk - 1) & 1u, abort_flag, p.status, 10);
     if (ok) {
+      tc_fence_after();
       const float inv_l = 1.0f / l_run;
-      // output row: [BH*N, d] rows for the op layout, token rows with a per-head column slice otherwise
       __nv_bfloat16* orow = p.qkv_fused ? p.o + ((long long)b * p.N + n) * p.o_pitch + h * p.o_head_stride
                                         : p.o + ((long long)bh * p.N + n) * p.o_pitch;
 #pragma unroll
-      for (int u = 0; u < D / 8; ++u) {
-        *reinterpret_cast<uint4*>(orow + u * 8) =
-            make_uint4(pack2(acc[u * 8] * inv_l, acc[u * 8 + 1] * inv_l), pack2(acc[u * 8 + 2] * inv_l, acc[u * 8 + 3] * inv_l),
-                       pack2(acc[u * 8 + 4] * inv_l, acc[u * 8 + 5] * inv_l), pack2(acc[u * 8 + 6] * inv_l, acc[u * 8 + 7] * inv_l));
+      for (int c = 0; c < D / 16; ++c) {
+        uint32_t r[16];
+        tmem_ld_32x32b_x16(o_addr + c * 16, r);
+        tmem_ld_wait();
+        float f[16];
+#pragma unroll
+        for (int q = 0; q < 16; ++q) f[q] = __uint_as_float(r[q]) * inv_l;
+        *reinterpret_cast<uint4*>(orow + c * 16) =
+            make_uint4(pack2(f[0], f[1]), pack2(f[2], f[3]), pack2(f[4], f[5]), pack2(f[6], f[7]));
+        *reinterpret_cast<uint4*>(orow + c * 16 + 8) =
+            make_uint4(pack2(f[8], f[9]), pack2(f[10], f[11]), pack2(f[12], f[13]), pack2(f[14], f[15]));
       }
     }
   }
@@ -349,17 +409,15 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   }
 }
 
-}  // namespace
-
 template <int D>
-static int launch_d(const void* q, const void* k, const void* v, long long rows, long long cols, long long pitch_elems,
-                    const AttnParams& p, int BH, void* stream) {
+int launch_d(const void* q, const void* k, const void* v, long long rows, long long cols, long long pitch_elems,
+             const AttnParams& p, int BH, void* stream) {
   CUtensorMap tm[3];
   const void* base[3] = {q, k, v};
   for (int t = 0; t < 3; ++t) {
     const uint64_t dims[3] = {16, uint64_t(rows), uint64_t(cols / 16)};
     const uint64_t strides[3] = {2, uint64_t(pitch_elems) * 2, 32};
-    const uint32_t box[3] = {16, 128, uint32_t(D / 16)};
+    const uint32_t box[3] = {16, t == 0 ? 256u : 128u, uint32_t(D / 16)};
     if (int e = make_tensor_map(&tm[t], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base[t]), dims, strides,
                                 box, CU_TENSOR_MAP_SWIZZLE_32B))
       return e;
@@ -367,12 +425,13 @@ static int launch_d(const void* q, const void* k, const void* v, long long rows,
   auto kern = attn_global_kernel<D>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<D>::BYTES) != cudaSuccess)
     return SAMB_E_LAUNCH;
-  const long long grid = (long long)BH * (p.N / BM);
+  const long long grid = (long long)BH * (p.N / (2 * BM));
   if (grid > 0x7fffffffLL) return SAMB_E_SHAPE;
   kern<<<unsigned(grid), NUM_THREADS, Smem<D>::BYTES, static_cast<cudaStream_t>(stream)>>>(tm[0], tm[1], tm[2], p);
   return launch_status();
 }
 
+}  // namespace
 }  // namespace samb
 
 extern "C" {
@@ -382,7 +441,7 @@ int samb_attn_relpos_global(const void* q, const void* k, const void* v, const v
   using namespace samb;
   if (!q || !k || !v || !rel_h || !rel_w || !o || !status) return SAMB_E_BADARG;
   if (B <= 0 || H <= 0 || N <= 0) return SAMB_E_BADARG;
-  if ((d != 64 && d != 80) || N % 128 || N > 4096) return SAMB_E_SHAPE;
+  if ((d != 64 && d != 80) || N % 256 || N > 4096) return SAMB_E_SHAPE;
   if ((long long)B * H * N > 0x7fffffffLL) return SAMB_E_SHAPE;
   if (reinterpret_cast<uintptr_t>(o) & 15u) return SAMB_E_ALIGN;
   if (int e = check_device_arch()) return e;
@@ -407,7 +466,7 @@ int samb_attn_relpos_global_qkv(const void* qkv, const void* tab, int64_t ldt, i
   using namespace samb;
   if (!qkv || !tab || !o || !status) return SAMB_E_BADARG;
   if (B <= 0 || H <= 0 || N <= 0) return SAMB_E_BADARG;
-  if ((d != 64 && d != 80) || N % 128 || N > 4096) return SAMB_E_SHAPE;
+  if ((d != 64 && d != 80) || N % 256 || N > 4096) return SAMB_E_SHAPE;
   if ((long long)B * N > 0x7fffffffLL || o_pitch % 8 || o_pitch < (int64_t)H * d) return SAMB_E_SHAPE;
   if (ldt < (int64_t)H * t_head_stride || t_w_off + 127 > t_head_stride || N / 64 * 2 - 1 > t_w_off) return SAMB_E_SHAPE;
   if (reinterpret_cast<uintptr_t>(o) & 15u) return SAMB_E_ALIGN;

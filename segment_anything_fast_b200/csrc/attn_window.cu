@@ -116,35 +116,43 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tma_load_3d(smem + L::OFF_V, &tmV, load_full, 0, row_base, cv);
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {   // the whole warp runs this; one elected lane issues the tensor-core instructions
       constexpr uint32_t idesc_s = make_idesc(kAccF32, kFmtBF16, kFmtBF16, 128, NK);
       constexpr uint32_t idesc_o = make_idesc(kAccF32, kFmtBF16, kFmtBF16, 128, D, false, /*B MN-major*/ true);
-      const uint32_t q_addr = smem_u32(smem + L::OFF_Q), k_addr = smem_u32(smem + L::OFF_K);
-      const uint32_t v_addr = smem_u32(smem + L::OFF_V), relw_addr = smem_u32(smem + L::OFF_RELW);
-      const uint32_t e_addr = smem_u32(smem + L::OFF_E), p_addr = smem_u32(smem + L::OFF_P);
+      // K-major, 32B swizzle (8-row groups 256 B apart); start addresses move in 16-byte units
+      const uint64_t dq = make_smem_desc(smem_u32(smem + L::OFF_Q), 16, 256, kSwizzle32B);
+      const uint64_t dk = make_smem_desc(smem_u32(smem + L::OFF_K), 16, 256, kSwizzle32B);
+      const uint64_t drw = make_smem_desc(smem_u32(smem + L::OFF_RELW), 16, 256, kSwizzle32B);
+      const uint64_t de = make_smem_desc(smem_u32(smem + L::OFF_E), 16, 256, kSwizzle32B);
+      const uint64_t dp = make_smem_desc(smem_u32(smem + L::OFF_P), 16, 256, kSwizzle32B);
+      // V: MN-major, column chunks KV_CHUNK apart (LBO), 8-key groups 256 B apart (SBO)
+      const uint64_t dv = make_smem_desc(smem_u32(smem + L::OFF_V), L::KV_CHUNK, 256, kSwizzle32B);
       bool ok = mbar_wait(load_full, 0, abort_flag, p.status, 1) && mbar_wait(pro_done, 0, abort_flag, p.status, 2);
       if (ok) {
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {            // logits of query tile t
-          const uint32_t d_tmem = tmem_base + t * 256;
+          for (int t = 0; t < 2; ++t) {            // logits of query tile t
+            const uint32_t d_tmem = tmem_base + t * 256;
 #pragma unroll
-          for (int c = 0; c < CH; ++c)
-            umma_f16_ss(d_tmem, make_smem_desc(q_addr + c * L::Q_CHUNK + t * 4096, 16, 256, kSwizzle32B),
-                        make_smem_desc(k_addr + c * L::KV_CHUNK, 16, 256, kSwizzle32B), idesc_s, c != 0);
-          umma_f16_ss(d_tmem, make_smem_desc(relw_addr + t * 4096, 16, 256, kSwizzle32B),
-                      make_smem_desc(e_addr, 16, 256, kSwizzle32B), idesc_s, 1u);
-          tc_commit(&s_full[t]);
+            for (int c = 0; c < CH; ++c)
+              umma_f16_ss(d_tmem, dq + (c * L::Q_CHUNK + t * 4096) / 16, dk + c * (L::KV_CHUNK / 16), idesc_s, c != 0);
+            umma_f16_ss(d_tmem, drw + t * (4096 / 16), de, idesc_s, 1u);
+            tc_commit(&s_full[t]);
+          }
         }
+        __syncwarp();
         for (int t = 0; ok && t < 2; ++t) {      // P V of query tile t, over the logits' columns
           if (!(ok = mbar_wait(&p_full[t], 0, abort_flag, p.status, 3))) break;
           tc_fence_after();
-          const uint32_t d_tmem = tmem_base + t * 256;
+          if (elect_one()) {
+            const uint32_t d_tmem = tmem_base + t * 256;
 #pragma unroll
-          for (int kk = 0; kk < L::KSTEPS; ++kk)
-            umma_f16_ss(d_tmem, make_smem_desc(p_addr + (t * L::KSTEPS + kk) * 4096, 16, 256, kSwizzle32B),
-                        make_smem_desc(v_addr + kk * 512, L::KV_CHUNK, 256, kSwizzle32B), idesc_o, kk != 0);
-          tc_commit(&o_full[t]);
+            for (int kk = 0; kk < L::KSTEPS; ++kk)
+              umma_f16_ss(d_tmem, dp + (t * L::KSTEPS + kk) * (4096 / 16), dv + kk * (512 / 16), idesc_o, kk != 0);
+            tc_commit(&o_full[t]);
+          }
+          __syncwarp();
         }
       }
     }
