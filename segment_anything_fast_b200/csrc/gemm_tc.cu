@@ -39,7 +39,9 @@ struct GemmParams {
   long long ldo, ldr, res_rows;
   int N, K;
   int k_slabs;
+  int last_ksteps;               // MMAs (of 32 K-bytes) that the last slab really holds, 1..4
   int tiles_n;
+  int bn;                        // output-tile width actually used: 64, 128 or 256 (narrow N)
   long long num_tiles;
   long long tiles_per_batch;     // tiles of one column batch (== num_tiles when not batched)
   int a_col_stride;              // batch b reads A columns [b*a_col_stride, +K)
@@ -142,12 +144,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int bt = int(tile / p.tiles_per_batch);
         const long long tb = tile - bt * p.tiles_per_batch;
         const int m0 = int(tb / p.tiles_n) * BM;
-        const int n0 = int(tb % p.tiles_n) * BN;
+        const int n0 = int(tb % p.tiles_n) * p.bn;
         const int a_col0 = bt * p.a_col_stride;
         for (int ks = 0; ks < p.k_slabs; ++ks) {
           if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 1))) break;
           uint8_t* sa = smem + stage * STAGE_BYTES;
-          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          mbar_expect_tx(&full_bar[stage], A_STAGE_BYTES + p.bn * SLAB_BYTES);
           tma_load_2d(sa, &tmA, &full_bar[stage], a_col0 + ks * slab_elems, m0);
           tma_load_2d(sa + A_STAGE_BYTES, &tmB, &full_bar[stage], ks * slab_elems, n0);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -156,9 +158,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = kInt8 ? make_idesc(kAccS32, kFmtS8, kFmtS8, BM, BN)
-                                       : make_idesc(kAccF32, kFmtBF16, kFmtBF16, BM, BN);
+    // The whole warp walks the loop (warp-uniform waits and descriptors); one elected lane issues.
+    {
+      const uint32_t idesc = kInt8 ? make_idesc(kAccS32, kFmtS8, kFmtS8, BM, p.bn)
+                                   : make_idesc(kAccF32, kFmtBF16, kFmtBF16, BM, p.bn);
+      // K-major, 128B swizzle: 8-row groups 1024 B apart; the start address moves in 16-byte units.
+      const uint64_t desc0 = make_smem_desc(smem_u32(smem), 16, 1024, kSwizzle128B);
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
       for (long long tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
@@ -168,22 +173,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int ks = 0; ks < p.k_slabs; ++ks) {
           if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3))) break;
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
-          const uint32_t b_addr = a_addr + A_STAGE_BYTES;
+          if (elect_one()) {
+            const uint64_t adesc = desc0 + stage * (STAGE_BYTES / 16);
+            const uint64_t bdesc = adesc + A_STAGE_BYTES / 16;
+            const int nsteps = ks == p.k_slabs - 1 ? p.last_ksteps : 4;
 #pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4) {
-            // K-major, 128B swizzle: 8-row groups 1024 B apart; 32 bytes of K per MMA.
-            const uint64_t adesc = make_smem_desc(a_addr + k4 * 32, 16, 1024, kSwizzle128B);
-            const uint64_t bdesc = make_smem_desc(b_addr + k4 * 32, 16, 1024, kSwizzle128B);
-            const uint32_t accumulate = (ks | k4) != 0 ? 1u : 0u;
-            if (kInt8) umma_i8_ss(d_tmem, adesc, bdesc, idesc, accumulate);
-            else umma_f16_ss(d_tmem, adesc, bdesc, idesc, accumulate);
+            for (int k4 = 0; k4 < 4; ++k4) {         // 32 bytes of K per MMA
+              if (k4 >= nsteps) break;
+              const uint32_t accumulate = (ks | k4) != 0 ? 1u : 0u;
+              if (kInt8) umma_i8_ss(d_tmem, adesc + k4 * 2, bdesc + k4 * 2, idesc, accumulate);
+              else umma_f16_ss(d_tmem, adesc + k4 * 2, bdesc + k4 * 2, idesc, accumulate);
+            }
+            tc_commit(&empty_bar[stage]);             // stage reusable once these MMAs have read it
           }
-          tc_commit(&empty_bar[stage]);   // stage reusable once these MMAs have read it
+          __syncwarp();
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        tc_commit(&acc_full[acc]);        // accumulator complete
+        if (elect_one()) tc_commit(&acc_full[acc]);   // accumulator complete
+        __syncwarp();
         if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
       }
     }
@@ -200,7 +208,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int bt = int(tile / p.tiles_per_batch);
       const long long tb = tile - bt * p.tiles_per_batch;
       const int m0 = int(tb / p.tiles_n) * BM;
-      const int n0 = int(tb % p.tiles_n) * BN;
+      const int n0 = int(tb % p.tiles_n) * p.bn;
       const long long row = (long long)m0 + erow;
       const bool row_ok = row < p.M;
       if (!kRaw) {
@@ -215,7 +223,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t t_addr = tmem_base + (lane_base << 16) + acc * BN + half * 32;
       if (kRaw) {
 #pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
+        for (int c = 0; c < p.bn / 64; ++c) {
           const int col0 = n0 + c * 64 + half * 32;
           if (col0 >= p.N) break;                       // uniform across the warp
           uint32_t r[32];
@@ -235,7 +243,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const __nv_bfloat16* res_row = nullptr;
         if (kRes && row_ok) res_row = p.residual + (row % p.res_rows) * p.ldr + n0 + half * 32;
 #pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
+        for (int c = 0; c < p.bn / 64; ++c) {
           const int col0 = n0 + c * 64;                 // first column of the chunk
           if (col0 >= p.N) break;                       // uniform across the CTA
           const int colh = col0 + half * 32;            // first column of this warp's side
@@ -375,7 +383,7 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
   {
     const uint64_t dims[2] = {uint64_t(K), uint64_t(N)};
     const uint64_t strides[2] = {uint64_t(esz), uint64_t(ldw) * esz};
-    const uint32_t box[2] = {slab_elems, uint32_t(BN)};
+    const uint32_t box[2] = {slab_elems, uint32_t(N <= 64 ? 64 : (N <= 128 ? 128 : BN))};
     if (int e = make_tensor_map(&tmB, dt, 2, const_cast<void*>(W), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
       return e;
   }
@@ -394,7 +402,9 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
   p.N = N;
   p.K = K;
   p.k_slabs = (K * esz + SLAB_BYTES - 1) / SLAB_BYTES;
-  p.tiles_n = (N + BN - 1) / BN;
+  p.last_ksteps = (K * esz - (p.k_slabs - 1) * SLAB_BYTES + 31) / 32;
+  p.bn = N <= 64 ? 64 : (N <= 128 ? 128 : BN);
+  p.tiles_n = (N + p.bn - 1) / p.bn;
   p.tiles_per_batch = ((M + BM - 1) / BM) * p.tiles_n;
   p.num_tiles = p.tiles_per_batch * batch;
   p.a_col_stride = a_col_stride;

@@ -56,7 +56,6 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   for (int j = 0; j < 4; ++j) p[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
   return u;
 }
-__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
 // kNorm: apply LayerNorm; kQuant: emit int8 + scale instead of bf16.
 template <bool kNorm, bool kQuant>
@@ -79,66 +78,85 @@ row_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
     return;
   }
 
-  float v[kMaxVec][8];
+  // The row stays in registers as raw 16-byte vectors (few registers -> many rows in flight per SM);
+  // each pass unpacks on the fly.
+  uint4 raw[kMaxVec];
   const uint4* xr = reinterpret_cast<const uint4*>(x + irow * C);
 #pragma unroll
   for (int i = 0; i < kMaxVec; ++i) {
     const int vi = i * 32 + lane;
-    if (vi < nvec) unpack8(xr[vi], v[i]);
+    if (vi < nvec) raw[i] = xr[vi];
   }
 
+  float mean = 0.f, rstd = 1.f;
   if (kNorm) {
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < kMaxVec; ++i)
-      if (i * 32 + lane < nvec)
+      if (i * 32 + lane < nvec) {
+        float f[8];
+        unpack8(raw[i], f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) s += v[i][j];
-    const float mean = warp_sum(s) / float(C);
+        for (int j = 0; j < 8; ++j) s += f[j];
+      }
+    mean = warp_sum(s) / float(C);
     float q = 0.f;
 #pragma unroll
     for (int i = 0; i < kMaxVec; ++i)
-      if (i * 32 + lane < nvec)
+      if (i * 32 + lane < nvec) {
+        float f[8];
+        unpack8(raw[i], f);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float d = v[i][j] - mean;
+          const float d = f[j] - mean;
           q += d * d;
         }
-    const float rstd = rsqrtf(warp_sum(q) / float(C) + eps);
-#pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
-      const int vi = i * 32 + lane;
-      if (vi < nvec) {
-        const float4 g0 = reinterpret_cast<const float4*>(gamma)[2 * vi], g1 = reinterpret_cast<const float4*>(gamma)[2 * vi + 1];
-        const float4 b0 = reinterpret_cast<const float4*>(beta)[2 * vi], b1 = reinterpret_cast<const float4*>(beta)[2 * vi + 1];
-        const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-        const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[i][j] = (v[i][j] - mean) * rstd * g[j] + b[j];
       }
-    }
+    rstd = rsqrtf(warp_sum(q) / float(C) + eps);
   }
+
+  // normalised (bf16-rounded) values of vector i
+  auto values = [&](int i, int vi, float (&f)[8]) {
+    unpack8(raw[i], f);
+    if (kNorm) {
+      const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * vi), g1 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * vi + 1);
+      const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta) + 2 * vi), b1 = __ldg(reinterpret_cast<const float4*>(beta) + 2 * vi + 1);
+      const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+      const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = (f[j] - mean) * rstd * g[j] + b[j];
+    }
+  };
 
   if (!kQuant) {
     uint4* yr = reinterpret_cast<uint4*>(y + orow * C);
 #pragma unroll
     for (int i = 0; i < kMaxVec; ++i) {
       const int vi = i * 32 + lane;
-      if (vi < nvec) yr[vi] = pack8(v[i]);
+      if (vi < nvec) {
+        float f[8];
+        values(i, vi, f);
+        yr[vi] = pack8(f);
+      }
     }
     return;
   }
 
   // int8: quantise the bf16-rounded value, as a quantised Linear fed a bf16 tensor would see it.
+  // The normalised row replaces the raw one in the same registers (as bf16).
   float amax = 0.f;
 #pragma unroll
-  for (int i = 0; i < kMaxVec; ++i)
-    if (i * 32 + lane < nvec)
+  for (int i = 0; i < kMaxVec; ++i) {
+    const int vi = i * 32 + lane;
+    if (vi < nvec) {
+      float f[8];
+      values(i, vi, f);
+      raw[i] = pack8(f);
+      unpack8(raw[i], f);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (kNorm) v[i][j] = bf16_round(v[i][j]);
-        amax = fmaxf(amax, fabsf(v[i][j]));
-      }
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+    }
+  }
   amax = warp_max(amax);
   const float sc = __fdiv_rn(fmaxf(amax, kAbsmaxFloor), 127.0f);
   if (lane == 0) scale[orow] = sc;
@@ -147,10 +165,12 @@ row_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
   for (int i = 0; i < kMaxVec; ++i) {
     const int vi = i * 32 + lane;
     if (vi < nvec) {
+      float f[8];
+      unpack8(raw[i], f);
       uint32_t w[2] = {0u, 0u};
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        float t = rintf(__fdiv_rn(v[i][j], sc));
+        float t = rintf(__fdiv_rn(f[j], sc));
         t = fminf(fmaxf(t, -127.f), 127.f);
         w[j >> 2] |= (uint32_t(int(t)) & 0xffu) << ((j & 3) * 8);
       }
