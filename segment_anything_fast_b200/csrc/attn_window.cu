@@ -19,6 +19,10 @@ namespace {
 constexpr int NUM_THREADS = 320;
 constexpr int TMEM_COLS = 512;   // logits of tile 0 at column 0, of tile 1 at column 256
 constexpr float kLog2e = 1.4426950408889634f;
+// P goes back to the tensor core through tensor memory (A operand from TMEM, packed bf16 pairs over
+// the logits' own columns) instead of shared memory; the P V result lands at column kOCol of the tile.
+constexpr bool kPTmem = true;
+constexpr int kOCol = 112;
 
 struct WinParams {
   const __nv_bfloat16* rel_h;    // mode 0: [W*H, N, WS]
@@ -97,8 +101,8 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(load_full, 1);
-    mbar_init(pro_done, 256);
-    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 128); mbar_init(&o_full[t], 1); }
+    mbar_init(pro_done, 8);
+    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 4); mbar_init(&o_full[t], 1); }
     fence_mbar_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
   }
@@ -149,7 +153,8 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             const uint32_t d_tmem = tmem_base + t * 256;
 #pragma unroll
             for (int kk = 0; kk < L::KSTEPS; ++kk)
-              umma_f16_ss(d_tmem, dp + (t * L::KSTEPS + kk) * (4096 / 16), dv + kk * (512 / 16), idesc_o, kk != 0);
+              if (kPTmem) umma_f16_ts(d_tmem + kOCol, d_tmem + kk * 8, dv + kk * (512 / 16), idesc_o, kk != 0);
+              else umma_f16_ss(d_tmem, dp + (t * L::KSTEPS + kk) * (4096 / 16), dv + kk * (512 / 16), idesc_o, kk != 0);
             tc_commit(&o_full[t]);
           }
           __syncwarp();
@@ -201,7 +206,7 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         *reinterpret_cast<uint4*>(erow + ((1 ^ sw) << 4)) = make_uint4(e[4], e[5], e[6], e[7]);
       }
       fence_proxy_async_smem();
-      mbar_arrive(pro_done);
+      mbar_arrive_warp(pro_done);
     }
     const float c2 = p.scale * kLog2e;
     bool ok = mbar_wait(&s_full[t], 0, abort_flag, p.status, 4);
@@ -246,14 +251,21 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             l += e[u];
           }
         }
-        *reinterpret_cast<uint4*>(prow + c * 4096 + ((0 ^ sw) << 4)) =
-            make_uint4(wpack2(e[0], e[1]), wpack2(e[2], e[3]), wpack2(e[4], e[5]), wpack2(e[6], e[7]));
-        *reinterpret_cast<uint4*>(prow + c * 4096 + ((1 ^ sw) << 4)) =
-            make_uint4(wpack2(e[8], e[9]), wpack2(e[10], e[11]), wpack2(e[12], e[13]), wpack2(e[14], e[15]));
+        if (kPTmem) {   // columns [8c, 8c+8) were read (as logits) in an earlier iteration of this loop
+          const uint32_t pk[8] = {wpack2(e[0], e[1]), wpack2(e[2], e[3]), wpack2(e[4], e[5]), wpack2(e[6], e[7]),
+                                  wpack2(e[8], e[9]), wpack2(e[10], e[11]), wpack2(e[12], e[13]), wpack2(e[14], e[15])};
+          tmem_st_32x32b_x8(lane_addr + c * 8, pk);
+        } else {
+          *reinterpret_cast<uint4*>(prow + c * 4096 + ((0 ^ sw) << 4)) =
+              make_uint4(wpack2(e[0], e[1]), wpack2(e[2], e[3]), wpack2(e[4], e[5]), wpack2(e[6], e[7]));
+          *reinterpret_cast<uint4*>(prow + c * 4096 + ((1 ^ sw) << 4)) =
+              make_uint4(wpack2(e[8], e[9]), wpack2(e[10], e[11]), wpack2(e[12], e[13]), wpack2(e[14], e[15]));
+        }
       }
+      if (kPTmem) tmem_st_wait();
       tc_fence_before();
       fence_proxy_async_smem();
-      mbar_arrive(&p_full[t]);
+      mbar_arrive_warp(&p_full[t]);
       ok = mbar_wait(&o_full[t], 0, abort_flag, p.status, 5);
       if (ok) {
         tc_fence_after();
@@ -274,7 +286,7 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
         for (int c = 0; c < D / 16; ++c) {
           uint32_t r[16];
-          tmem_ld_32x32b_x16(lane_addr + c * 16, r);
+          tmem_ld_32x32b_x16(lane_addr + (kPTmem ? kOCol : 0) + c * 16, r);
           tmem_ld_wait();
           if (orow != nullptr) {
             float f[16];

@@ -117,7 +117,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int a = 0; a < NUM_ACC; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], EPI_THREADS);
+      mbar_init(&acc_empty[a], EPI_THREADS / 32);   // one arrival per epilogue warp
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
@@ -301,7 +301,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       }
       tc_fence_before();
-      mbar_arrive(&acc_empty[acc]);
+      mbar_arrive_warp(&acc_empty[acc]);
       if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
     }
     if (!kRaw && et == 0) tma_store_wait_all<0>();
