@@ -2,13 +2,19 @@
 // WS x WS = N tokens (14 x 14 = 196) attending to themselves,
 //   O = softmax(scale * Q K^T + rel_h[i, j / WS] + rel_w[i, j % WS]) V.
 //
-// One CTA owns one (window, head): one TMA brings its Q (two 128-row tiles), K and V (N rounded up to
-// 208 rows) into shared memory, warp 1 issues the two Q K^T products into tensor memory, eight
-// softmax warps (one thread per query row, warps 2..5 for rows 0..127, warps 6..9 for the rest) turn
-// the logits into P, and two P V products land where the logits were.
-//  * rel_w rides on the tensor core like in the global kernel: A = [Q | rel_w/scale (16 columns)],
-//    B = [K | E] with E[j, j % WS] = 1.
-//  * rel_h is constant over runs of WS keys; it is folded into the exp2 FMA addend, one value per run.
+// The work items are (window, head) pairs: ~107 KB of q/k/v in, 31 KB out, 39 MFLOP — a memory-bound
+// stream.  One persistent CTA per SM walks its items with a two-deep TMA ring (the loads of item
+// k+1 fly while item k is being computed):
+//   warp 0      TMA producer: Q (two 128-row tiles), K and V (N rounded up to 208 rows) per item
+//   warp 1      tcgen05.mma issue: two Q K^T products into tensor memory, later two P V products
+//   warps 2..9  softmax, one thread per query row (warps 2..5 rows 0..127, warps 6..9 the rest)
+//  * The logits of a tile occupy 208 TMEM columns.  The threads read them twice (row maximum, then
+//    exponentials) and write P back as packed bf16 pairs over the columns already consumed, so P V
+//    takes its A operand from tensor memory and P never touches shared memory.  The product lands in
+//    columns [112, 192) of the same tile.
+//  * rel_w rides on the tensor core: A = [Q | rel_w/scale (16 columns)], B = [K | E], E[j, j % WS] = 1.
+//  * rel_h is constant over runs of WS keys and is folded into the exp2 FMA addend.
+//  * The bias values of item k+1 are fetched into registers before the softmax of item k starts.
 // Zero-padded window tokens need no special case: they are ordinary rows of the padded qkv buffer.
 // Rows N..207 of the K/V box belong to the next window; their probabilities are written as zero.
 #include "common.cuh"
@@ -17,12 +23,10 @@ namespace samb {
 namespace {
 
 constexpr int NUM_THREADS = 320;
-constexpr int TMEM_COLS = 512;   // logits of tile 0 at column 0, of tile 1 at column 256
+constexpr int TMEM_COLS = 512;   // tile 0 at column 0, tile 1 at column 256
+constexpr int kOCol = 112;       // P V result inside a tile's columns (P uses [0, 104))
+constexpr int STAGES = 2;
 constexpr float kLog2e = 1.4426950408889634f;
-// P goes back to the tensor core through tensor memory (A operand from TMEM, packed bf16 pairs over
-// the logits' own columns) instead of shared memory; the P V result lands at column kOCol of the tile.
-constexpr bool kPTmem = true;
-constexpr int kOCol = 112;
 
 struct WinParams {
   const __nv_bfloat16* rel_h;    // mode 0: [W*H, N, WS]
@@ -34,6 +38,7 @@ struct WinParams {
   long long o_pitch;
   int qkv_fused;                 // 0: q/k/v/o are [W*H*N, d]; 1: qkv [W*N, 3*H*d], o rows are raster tokens
   int H, grid, nw;               // raster side and windows per side (fused mode)
+  int items;                     // number of (window, head) pairs
   float scale;
   int* status;
 };
@@ -46,15 +51,15 @@ struct WinSmem {
   static constexpr int KSTEPS = NK / 16;
   static constexpr int Q_CHUNK = 256 * 32;           // 256 query rows per 16-column chunk
   static constexpr int KV_CHUNK = NK * 32;
-  static constexpr int OFF_Q = 0;
-  static constexpr int OFF_K = OFF_Q + CH * Q_CHUNK;
+  static constexpr int STAGE = CH * (Q_CHUNK + 2 * KV_CHUNK);   // Q | K | V of one item
+  static constexpr int OFF_K = CH * Q_CHUNK;         // inside a stage
   static constexpr int OFF_V = OFF_K + CH * KV_CHUNK;
-  static constexpr int OFF_RELW = OFF_V + CH * KV_CHUNK;        // [256][16] bf16, 32B swizzle
-  static constexpr int OFF_E = OFF_RELW + Q_CHUNK;              // [NK][16] bf16 one-hot
-  static constexpr int OFF_P = (OFF_E + KV_CHUNK + 1023) / 1024 * 1024;   // 2 x [KSTEPS][128][16] bf16
-  static constexpr int OFF_BAR = OFF_P + 2 * KSTEPS * 4096;
-  static constexpr int BYTES = OFF_BAR + 128 + 1024;
+  static constexpr int OFF_RELW = STAGES * STAGE;    // [256][16] bf16, 32B swizzle (per item)
+  static constexpr int OFF_E = OFF_RELW + Q_CHUNK;   // [NK][16] bf16 one-hot (constant)
+  static constexpr int OFF_BAR = OFF_E + KV_CHUNK;
+  static constexpr int BYTES = OFF_BAR + 256 + 1024;
   static_assert(N <= 256 && NK <= 256 && WS <= 16, "window too large for this kernel");
+  static_assert(STAGE % 1024 == 0 && NK / 2 <= kOCol && kOCol + D <= 256, "layout");
 };
 
 __device__ __forceinline__ uint32_t wpack2(float lo, float hi) {
@@ -66,6 +71,7 @@ __device__ __forceinline__ float wexp2(float x) {
   asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
 
 template <int D, int WS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -76,33 +82,25 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
-  uint64_t* load_full = bars + 0;
-  uint64_t* pro_done = bars + 1;
-  uint64_t* s_full = bars + 2;   // [2]
-  uint64_t* p_full = bars + 4;   // [2]
-  uint64_t* o_full = bars + 6;   // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* full = bars + 0;        // [STAGES] q/k/v of an item have landed
+  uint64_t* empty = bars + 2;       // [STAGES] every MMA reading the stage has finished
+  uint64_t* pro_done = bars + 4;    //          this item's rel_w tile is in shared memory
+  uint64_t* s_full = bars + 5;      // [2]      logits of tile t are in TMEM
+  uint64_t* p_full = bars + 7;      // [2]      P of tile t is in TMEM
+  uint64_t* o_full = bars + 9;      // [2]      P V of tile t is in TMEM
+  uint64_t* t_free = bars + 11;     // [2]      tile t's TMEM columns may be overwritten (O has been read)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int w = blockIdx.x / p.H, h = blockIdx.x - w * p.H;
-
-  int row_base, cq, ck, cv;
-  if (p.qkv_fused) {
-    row_base = w * N;
-    cq = (h * D) / 16;
-    ck = (p.H * D + h * D) / 16;
-    cv = (2 * p.H * D + h * D) / 16;
-  } else {
-    row_base = blockIdx.x * N;
-    cq = ck = cv = 0;
-  }
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    mbar_init(load_full, 1);
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     mbar_init(pro_done, 8);
-    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 4); mbar_init(&o_full[t], 1); }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 4); mbar_init(&o_full[t], 1); mbar_init(&t_free[t], 4);
+    }
     fence_mbar_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
   }
@@ -113,109 +111,152 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      mbar_expect_tx(load_full, CH * (L::Q_CHUNK + 2 * L::KV_CHUNK));
-      tma_load_3d(smem + L::OFF_Q, &tmQ, load_full, 0, row_base, cq);
-      tma_load_3d(smem + L::OFF_K, &tmK, load_full, 0, row_base, ck);
-      tma_load_3d(smem + L::OFF_V, &tmV, load_full, 0, row_base, cv);
-    }
-  } else if (warp == 1) {
-    {   // the whole warp runs this; one elected lane issues the tensor-core instructions
-      constexpr uint32_t idesc_s = make_idesc(kAccF32, kFmtBF16, kFmtBF16, 128, NK);
-      constexpr uint32_t idesc_o = make_idesc(kAccF32, kFmtBF16, kFmtBF16, 128, D, false, /*B MN-major*/ true);
-      // K-major, 32B swizzle (8-row groups 256 B apart); start addresses move in 16-byte units
-      const uint64_t dq = make_smem_desc(smem_u32(smem + L::OFF_Q), 16, 256, kSwizzle32B);
-      const uint64_t dk = make_smem_desc(smem_u32(smem + L::OFF_K), 16, 256, kSwizzle32B);
-      const uint64_t drw = make_smem_desc(smem_u32(smem + L::OFF_RELW), 16, 256, kSwizzle32B);
-      const uint64_t de = make_smem_desc(smem_u32(smem + L::OFF_E), 16, 256, kSwizzle32B);
-      const uint64_t dp = make_smem_desc(smem_u32(smem + L::OFF_P), 16, 256, kSwizzle32B);
-      // V: MN-major, column chunks KV_CHUNK apart (LBO), 8-key groups 256 B apart (SBO)
-      const uint64_t dv = make_smem_desc(smem_u32(smem + L::OFF_V), L::KV_CHUNK, 256, kSwizzle32B);
-      bool ok = mbar_wait(load_full, 0, abort_flag, p.status, 1) && mbar_wait(pro_done, 0, abort_flag, p.status, 2);
-      if (ok) {
-        tc_fence_after();
-        if (elect_one()) {
-#pragma unroll
-          for (int t = 0; t < 2; ++t) {            // logits of query tile t
-            const uint32_t d_tmem = tmem_base + t * 256;
-#pragma unroll
-            for (int c = 0; c < CH; ++c)
-              umma_f16_ss(d_tmem, dq + (c * L::Q_CHUNK + t * 4096) / 16, dk + c * (L::KV_CHUNK / 16), idesc_s, c != 0);
-            umma_f16_ss(d_tmem, drw + t * (4096 / 16), de, idesc_s, 1u);
-            tc_commit(&s_full[t]);
-          }
+      uint32_t stage = 0, phase = 0;
+      for (int it = blockIdx.x; it < p.items; it += gridDim.x) {
+        const int w = it / p.H, h = it - w * p.H;
+        int row_base, cq, ck, cv;
+        if (p.qkv_fused) {
+          row_base = w * N; cq = (h * D) / 16; ck = (p.H * D + h * D) / 16; cv = (2 * p.H * D + h * D) / 16;
+        } else {
+          row_base = it * N; cq = ck = cv = 0;
         }
-        __syncwarp();
-        for (int t = 0; ok && t < 2; ++t) {      // P V of query tile t, over the logits' columns
-          if (!(ok = mbar_wait(&p_full[t], 0, abort_flag, p.status, 3))) break;
-          tc_fence_after();
-          if (elect_one()) {
-            const uint32_t d_tmem = tmem_base + t * 256;
-#pragma unroll
-            for (int kk = 0; kk < L::KSTEPS; ++kk)
-              if (kPTmem) umma_f16_ts(d_tmem + kOCol, d_tmem + kk * 8, dv + kk * (512 / 16), idesc_o, kk != 0);
-              else umma_f16_ss(d_tmem, dp + (t * L::KSTEPS + kk) * (4096 / 16), dv + kk * (512 / 16), idesc_o, kk != 0);
-            tc_commit(&o_full[t]);
-          }
-          __syncwarp();
-        }
+        if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 1)) break;
+        uint8_t* st = smem + stage * L::STAGE;
+        mbar_expect_tx(&full[stage], L::STAGE);
+        tma_load_3d(st, &tmQ, &full[stage], 0, row_base, cq);
+        tma_load_3d(st + L::OFF_K, &tmK, &full[stage], 0, row_base, ck);
+        tma_load_3d(st + L::OFF_V, &tmV, &full[stage], 0, row_base, cv);
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
     }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issue (whole warp, one elected lane issues)
+    constexpr uint32_t idesc_s = make_idesc(kAccF32, kFmtBF16, kFmtBF16, 128, NK);
+    constexpr uint32_t idesc_o = make_idesc(kAccF32, kFmtBF16, kFmtBF16, 128, D, false, /*B MN-major*/ true);
+    // K-major, 32B swizzle (8-row groups 256 B apart); start addresses move in 16-byte units
+    const uint64_t dq0 = make_smem_desc(smem_u32(smem), 16, 256, kSwizzle32B);
+    const uint64_t drw = make_smem_desc(smem_u32(smem + L::OFF_RELW), 16, 256, kSwizzle32B);
+    const uint64_t de = make_smem_desc(smem_u32(smem + L::OFF_E), 16, 256, kSwizzle32B);
+    // V: MN-major, column chunks KV_CHUNK apart (LBO), 8-key groups 256 B apart (SBO)
+    const uint64_t dv0 = make_smem_desc(smem_u32(smem + L::OFF_V), L::KV_CHUNK, 256, kSwizzle32B);
+    uint32_t stage = 0, phase = 0, k = 0;
+    bool ok = true;
+    for (int it = blockIdx.x; ok && it < p.items; it += gridDim.x, ++k) {
+      const uint32_t par = k & 1u;
+      if (!(ok = mbar_wait(&full[stage], phase, abort_flag, p.status, 2))) break;
+      if (!(ok = mbar_wait(pro_done, par, abort_flag, p.status, 3))) break;
+      const uint64_t dq = dq0 + stage * (L::STAGE / 16);
+      const uint64_t dk = dq + L::OFF_K / 16;
+      const uint64_t dv = dv0 + stage * (L::STAGE / 16);
+      for (int t = 0; ok && t < 2; ++t) {          // logits of query tile t
+        if (!(ok = mbar_wait(&t_free[t], par ^ 1u, abort_flag, p.status, 4))) break;
+        tc_fence_after();
+        if (elect_one()) {
+          const uint32_t d_tmem = tmem_base + t * 256;
+#pragma unroll
+          for (int c = 0; c < CH; ++c)
+            umma_f16_ss(d_tmem, dq + (c * L::Q_CHUNK + t * 4096) / 16, dk + c * (L::KV_CHUNK / 16), idesc_s, c != 0);
+          umma_f16_ss(d_tmem, drw + t * (4096 / 16), de, idesc_s, 1u);
+          tc_commit(&s_full[t]);
+        }
+        __syncwarp();
+      }
+      for (int t = 0; ok && t < 2; ++t) {          // P V of query tile t: A = P from TMEM, B = V
+        if (!(ok = mbar_wait(&p_full[t], par, abort_flag, p.status, 5))) break;
+        tc_fence_after();
+        if (elect_one()) {
+          const uint32_t d_tmem = tmem_base + t * 256;
+#pragma unroll
+          for (int kk = 0; kk < L::KSTEPS; ++kk)
+            umma_f16_ts(d_tmem + kOCol, d_tmem + kk * 8, dv + kk * (512 / 16), idesc_o, kk != 0);
+          tc_commit(&o_full[t]);
+          if (t == 1) tc_commit(&empty[stage]);    // everything that reads this stage has been issued
+        }
+        __syncwarp();
+      }
+      if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+    }
   } else {
+    // ---------------------------------------------------------------- softmax (one thread = one query row)
     const int t = (warp - 2) >> 2;                               // query tile of this warp
     const int i = (warp & 3) * 32 + lane;                        // row in the tile == TMEM lane
     const int n = t * 128 + i;                                   // token inside the window
     const bool valid = n < N;
     const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + t * 256;
     const int qh = n / WS, qw = n - qh * WS;
-    // ---- prologue: bias values of this row
-    float bh[WS];
-    {
-      const __nv_bfloat16 *src_h = nullptr, *src_w = nullptr;
+    const int sw = (n >> 2) & 1;                                 // 32B swizzle: 16-byte halves swap every 4 rows
+    const float inv_scale = p.rel_mode == 0 ? 1.0f / p.scale : 1.0f;   // table products arrive pre-divided
+    const float c2 = p.scale * kLog2e;
+
+    if (n < NK) {                                                // constant one-hot row of key n
+      uint32_t e[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        e[q] = (valid && qw == 2 * q ? 0x3F80u : 0u) | (valid && qw == 2 * q + 1 ? 0x3F800000u : 0u);
+      uint8_t* erow = smem + L::OFF_E + n * 32;
+      *reinterpret_cast<uint4*>(erow + ((0 ^ sw) << 4)) = make_uint4(e[0], e[1], e[2], e[3]);
+      *reinterpret_cast<uint4*>(erow + ((1 ^ sw) << 4)) = make_uint4(e[4], e[5], e[6], e[7]);
+    }
+
+    // raw bf16 bias values of one item; nothing touches them until the item starts, so the loads
+    // issued for item k+1 have the whole of item k to land
+    unsigned short raw_h[WS], raw_w[WS];
+    auto fetch_bias = [&](int it) {
+      const int w = it / p.H, h = it - w * p.H;
+      const unsigned short *src_h, *src_w;
       int step = 1;
+      if (p.rel_mode == 0) {
+        src_h = reinterpret_cast<const unsigned short*>(p.rel_h + ((long long)it * N + n) * WS);
+        src_w = reinterpret_cast<const unsigned short*>(p.rel_w + ((long long)it * N + n) * WS);
+      } else {
+        const __nv_bfloat16* tb = p.tab + ((long long)w * N + n) * p.ldt + h * p.t_head_stride;
+        src_h = reinterpret_cast<const unsigned short*>(tb + (qh + WS - 1));
+        src_w = reinterpret_cast<const unsigned short*>(tb + p.t_w_off + (qw + WS - 1));
+        step = -1;
+      }
       if (valid) {
-        if (p.rel_mode == 0) {
-          src_h = p.rel_h + ((long long)blockIdx.x * N + n) * WS;
-          src_w = p.rel_w + ((long long)blockIdx.x * N + n) * WS;
-        } else {
-          const __nv_bfloat16* tb = p.tab + ((long long)w * N + n) * p.ldt + h * p.t_head_stride;
-          src_h = tb + (qh + WS - 1);
-          src_w = tb + p.t_w_off + (qw + WS - 1);
-          step = -1;
+#pragma unroll
+        for (int q = 0; q < WS; ++q) {
+          raw_h[q] = __ldg(src_h + step * q);
+          raw_w[q] = __ldg(src_w + step * q);
         }
       }
-      const float inv_scale = p.rel_mode == 0 ? 1.0f / p.scale : 1.0f;   // table products arrive pre-divided
-      float rw[16];
+    };
 #pragma unroll
-      for (int k = 0; k < 16; ++k) rw[k] = (valid && k < WS) ? __bfloat162float(src_w[step * k]) * inv_scale : 0.f;
+    for (int q = 0; q < WS; ++q) raw_h[q] = raw_w[q] = 0;
+
+    int it = blockIdx.x;
+    if (it < p.items) fetch_bias(it);
+    bool ok = true;
+    for (uint32_t k = 0; ok && it < p.items; it += gridDim.x, ++k) {
+      const uint32_t par = k & 1u;
+      // ---- this item's bias: rel_h into registers (log2 domain), rel_w/scale into the A-operand tile
+      float bh[WS];
+      {
+        float rw[16];
 #pragma unroll
-      for (int k = 0; k < WS; ++k) bh[k] = valid ? __bfloat162float(src_h[step * k]) * kLog2e : 0.f;
-      const int sw = (n >> 2) & 1;                               // 32B swizzle: 16-byte halves swap every 4 rows
-      uint8_t* rrow = smem + L::OFF_RELW + n * 32;
-      *reinterpret_cast<uint4*>(rrow + ((0 ^ sw) << 4)) =
-          make_uint4(wpack2(rw[0], rw[1]), wpack2(rw[2], rw[3]), wpack2(rw[4], rw[5]), wpack2(rw[6], rw[7]));
-      *reinterpret_cast<uint4*>(rrow + ((1 ^ sw) << 4)) =
-          make_uint4(wpack2(rw[8], rw[9]), wpack2(rw[10], rw[11]), wpack2(rw[12], rw[13]), wpack2(rw[14], rw[15]));
-      if (n < NK) {                                              // one-hot row of key n
-        uint32_t e[8];
+        for (int q = 0; q < 16; ++q) rw[q] = q < WS ? bf16_bits_to_float(raw_w[q < WS ? q : 0]) * inv_scale : 0.f;
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          e[k] = (valid && qw == 2 * k ? 0x3F80u : 0u) | (valid && qw == 2 * k + 1 ? 0x3F800000u : 0u);
-        uint8_t* erow = smem + L::OFF_E + n * 32;
-        *reinterpret_cast<uint4*>(erow + ((0 ^ sw) << 4)) = make_uint4(e[0], e[1], e[2], e[3]);
-        *reinterpret_cast<uint4*>(erow + ((1 ^ sw) << 4)) = make_uint4(e[4], e[5], e[6], e[7]);
+        for (int q = 0; q < WS; ++q) bh[q] = bf16_bits_to_float(raw_h[q]) * kLog2e;
+        uint8_t* rrow = smem + L::OFF_RELW + n * 32;
+        *reinterpret_cast<uint4*>(rrow + ((0 ^ sw) << 4)) =
+            make_uint4(wpack2(rw[0], rw[1]), wpack2(rw[2], rw[3]), wpack2(rw[4], rw[5]), wpack2(rw[6], rw[7]));
+        *reinterpret_cast<uint4*>(rrow + ((1 ^ sw) << 4)) =
+            make_uint4(wpack2(rw[8], rw[9]), wpack2(rw[10], rw[11]), wpack2(rw[12], rw[13]), wpack2(rw[14], rw[15]));
+        fence_proxy_async_smem();
+        mbar_arrive_warp(pro_done);
       }
-      fence_proxy_async_smem();
-      mbar_arrive_warp(pro_done);
-    }
-    const float c2 = p.scale * kLog2e;
-    bool ok = mbar_wait(&s_full[t], 0, abort_flag, p.status, 4);
-    if (ok) {
+      const int it_next = it + gridDim.x;
+      if (it_next < p.items) fetch_bias(it_next);               // lands while this item is being computed
+
+      if (!(ok = mbar_wait(&s_full[t], par, abort_flag, p.status, 6))) break;
       tc_fence_after();
       // pass 1: per key-row maxima of the raw logits, then the row maximum of the biased logits
       float mx[WS];
 #pragma unroll
-      for (int k = 0; k < WS; ++k) mx[k] = -INFINITY;
+      for (int q = 0; q < WS; ++q) mx[q] = -INFINITY;
 #pragma unroll
       for (int c = 0; c < NK / 16; ++c) {
         uint32_t r[16];
@@ -229,18 +270,18 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       float m = -INFINITY;
 #pragma unroll
-      for (int k = 0; k < WS; ++k) m = fmaxf(m, fmaf(mx[k], c2, bh[k]));
+      for (int q = 0; q < WS; ++q) m = fmaxf(m, fmaf(mx[q], c2, bh[q]));
 #pragma unroll
-      for (int k = 0; k < WS; ++k) bh[k] -= m;
-      // pass 2: probabilities -> bf16 P (K-major, 32B swizzle, one 16-key chunk per 4 KiB)
+      for (int q = 0; q < WS; ++q) bh[q] -= m;
+      // pass 2: probabilities -> packed bf16 P over the logit columns already consumed
       float l = 0.f;
-      const int sw = (i >> 2) & 1;
-      uint8_t* prow = smem + L::OFF_P + t * L::KSTEPS * 4096 + i * 32;
+      uint32_t rbuf[2][16];
+      tmem_ld_32x32b_x16(lane_addr, rbuf[0]);
 #pragma unroll
       for (int c = 0; c < NK / 16; ++c) {
-        uint32_t r[16];
-        tmem_ld_32x32b_x16(lane_addr + c * 16, r);
-        tmem_ld_wait();
+        tmem_ld_wait();                                          // chunk c has landed
+        if (c + 1 < NK / 16) tmem_ld_32x32b_x16(lane_addr + (c + 1) * 16, rbuf[(c + 1) & 1]);   // next chunk in flight
+        const uint32_t(&r)[16] = rbuf[c & 1];
         float e[16];
 #pragma unroll
         for (int u = 0; u < 16; ++u) {
@@ -251,54 +292,51 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             l += e[u];
           }
         }
-        if (kPTmem) {   // columns [8c, 8c+8) were read (as logits) in an earlier iteration of this loop
-          const uint32_t pk[8] = {wpack2(e[0], e[1]), wpack2(e[2], e[3]), wpack2(e[4], e[5]), wpack2(e[6], e[7]),
-                                  wpack2(e[8], e[9]), wpack2(e[10], e[11]), wpack2(e[12], e[13]), wpack2(e[14], e[15])};
-          tmem_st_32x32b_x8(lane_addr + c * 8, pk);
+        const uint32_t pk[8] = {wpack2(e[0], e[1]), wpack2(e[2], e[3]), wpack2(e[4], e[5]), wpack2(e[6], e[7]),
+                                wpack2(e[8], e[9]), wpack2(e[10], e[11]), wpack2(e[12], e[13]), wpack2(e[14], e[15])};
+        // columns [8c, 8c+8) hold logits 16..31 of chunk c/2, consumed in an earlier iteration (for c = 0:
+        // chunk 0 itself, already in registers; chunk 1, in flight, starts at column 16)
+        tmem_st_32x32b_x8(lane_addr + c * 8, pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive_warp(&p_full[t]);
+
+      if (!(ok = mbar_wait(&o_full[t], par, abort_flag, p.status, 7))) break;
+      tc_fence_after();
+      const float inv_l = 1.0f / l;
+      __nv_bfloat16* orow = nullptr;
+      if (valid) {
+        if (p.qkv_fused) {
+          const int w = it / p.H, h = it - w * p.H;
+          const int ww = p.nw * p.nw;
+          const int b = w / ww, wi = w - b * ww;
+          const int wy = wi / p.nw, wx = wi - wy * p.nw;
+          const int y = wy * WS + qh, x = wx * WS + qw;
+          if (y < p.grid && x < p.grid) orow = p.o + (((long long)b * p.grid + y) * p.grid + x) * p.o_pitch + h * D;
         } else {
-          *reinterpret_cast<uint4*>(prow + c * 4096 + ((0 ^ sw) << 4)) =
-              make_uint4(wpack2(e[0], e[1]), wpack2(e[2], e[3]), wpack2(e[4], e[5]), wpack2(e[6], e[7]));
-          *reinterpret_cast<uint4*>(prow + c * 4096 + ((1 ^ sw) << 4)) =
-              make_uint4(wpack2(e[8], e[9]), wpack2(e[10], e[11]), wpack2(e[12], e[13]), wpack2(e[14], e[15]));
+          orow = p.o + ((long long)it * N + n) * p.o_pitch;
         }
       }
-      if (kPTmem) tmem_st_wait();
+      uint32_t ro[D / 16][16];
+#pragma unroll
+      for (int c = 0; c < D / 16; ++c) tmem_ld_32x32b_x16(lane_addr + kOCol + c * 16, ro[c]);
+      tmem_ld_wait();
       tc_fence_before();
-      fence_proxy_async_smem();
-      mbar_arrive_warp(&p_full[t]);
-      ok = mbar_wait(&o_full[t], 0, abort_flag, p.status, 5);
-      if (ok) {
-        tc_fence_after();
-        const float inv_l = 1.0f / l;
-        __nv_bfloat16* orow = nullptr;
-        if (valid) {
-          if (p.qkv_fused) {
-            const int ww = p.nw * p.nw;
-            const int b = w / ww, wi = w - b * ww;
-            const int wy = wi / p.nw, wx = wi - wy * p.nw;
-            const int y = wy * WS + qh, x = wx * WS + qw;
-            if (y < p.grid && x < p.grid)
-              orow = p.o + (((long long)b * p.grid + y) * p.grid + x) * p.o_pitch + h * D;
-          } else {
-            orow = p.o + ((long long)blockIdx.x * N + n) * p.o_pitch;
-          }
-        }
+      mbar_arrive_warp(&t_free[t]);                              // O is in registers: the tile's columns are free
+      if (orow != nullptr) {
 #pragma unroll
         for (int c = 0; c < D / 16; ++c) {
-          uint32_t r[16];
-          tmem_ld_32x32b_x16(lane_addr + (kPTmem ? kOCol : 0) + c * 16, r);
-          tmem_ld_wait();
-          if (orow != nullptr) {
-            float f[16];
+          float f[16];
 #pragma unroll
-            for (int u = 0; u < 16; ++u) f[u] = __uint_as_float(r[u]) * inv_l;
-            *reinterpret_cast<uint4*>(orow + c * 16) =
-                make_uint4(wpack2(f[0], f[1]), wpack2(f[2], f[3]), wpack2(f[4], f[5]), wpack2(f[6], f[7]));
-            *reinterpret_cast<uint4*>(orow + c * 16 + 8) =
-                make_uint4(wpack2(f[8], f[9]), wpack2(f[10], f[11]), wpack2(f[12], f[13]), wpack2(f[14], f[15]));
-          }
+          for (int u = 0; u < 16; ++u) f[u] = __uint_as_float(ro[c][u]) * inv_l;
+          *reinterpret_cast<uint4*>(orow + c * 16) =
+              make_uint4(wpack2(f[0], f[1]), wpack2(f[2], f[3]), wpack2(f[4], f[5]), wpack2(f[6], f[7]));
+          *reinterpret_cast<uint4*>(orow + c * 16 + 8) =
+              make_uint4(wpack2(f[8], f[9]), wpack2(f[10], f[11]), wpack2(f[12], f[13]), wpack2(f[14], f[15]));
         }
       }
+
     }
   }
 
@@ -311,8 +349,8 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 }
 
 template <int D, int WS>
-int launch_window(const void* q, const void* k, const void* v, long long rows, long long cols, const WinParams& p,
-                  long long ctas, void* stream) {
+int launch_window(const void* q, const void* k, const void* v, long long rows, long long cols, WinParams p,
+                  long long items, void* stream) {
   using L = WinSmem<D, WS>;
   CUtensorMap tmQ, tmK, tmV;
   const uint64_t dims[3] = {16, uint64_t(rows), uint64_t(cols / 16)};
@@ -331,8 +369,10 @@ int launch_window(const void* q, const void* k, const void* v, long long rows, l
   auto kern = attn_window_kernel<D, WS>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES) != cudaSuccess)
     return SAMB_E_LAUNCH;
-  if (ctas > 0x7fffffffLL) return SAMB_E_SHAPE;
-  kern<<<unsigned(ctas), NUM_THREADS, L::BYTES, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, p);
+  if (items > 0x7fffffffLL) return SAMB_E_SHAPE;
+  p.items = int(items);
+  const long long grid = items < sm_count() ? items : sm_count();
+  kern<<<unsigned(grid), NUM_THREADS, L::BYTES, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, p);
   return launch_status();
 }
 
