@@ -116,8 +116,8 @@ int samb_layernorm2d_nchw(const void* x, const float* gamma, const float* beta, 
 int samb_attn_relpos_global(const void* q, const void* k, const void* v, const void* rel_h, const void* rel_w,
                             void* o, int B, int H, int N, int d, float scale, int32_t* status, void* stream);
 
-/* Same attention reading q/k/v straight out of the qkv projection's output qkv[B*N, 3*H*d]
- * (columns: q | k | v, head major, ref layout modeling/image_encoder.py:228) and writing o[B*N, o_pitch]
+/* Same attention reading q/k/v from the head-major qkv buffer qkv[3*H][B*N][d] written by
+ * samb_gemm_*_heads (planes: q heads, k heads, v heads) and writing o[B*N, o_pitch]
  * with head h at columns [h*d, (h+1)*d) (the layout proj consumes, image_encoder.py:249).  The bias
  * comes from table products tab[B*N, ldt]: for head h, tab[t, h*t_head_stride + m] = q_t,h . rel_pos_h[m]
  * (m < 2*N/64-1) and tab[t, h*t_head_stride + t_w_off + m] = (q_t,h . rel_pos_w[m]) / scale (m < 127),
@@ -137,8 +137,8 @@ int samb_attn_relpos_global_qkv(const void* qkv, const void* tab, int64_t ldt, i
 int samb_attn_relpos_window(const void* q, const void* k, const void* v, const void* rel_h, const void* rel_w, void* o,
                             int B, int H, int window, int d, float scale, int32_t* status, void* stream);
 
-/* Windowed attention over the qkv projection of the window-partitioned, zero-padded token order
- * (the row order samb_layernorm_bf16 writes with window > 0): qkv[B*nw*nw*N, 3*H*d].  The output goes
+/* Windowed attention over the head-major qkv projection of the window-partitioned, zero-padded token
+ * order (the row order samb_layernorm_bf16 writes with window > 0): qkv[3*H][B*nw*nw*N][d].  The output goes
  * straight back to raster order, o[(b*grid + y)*grid + x, h*d ...] with pad tokens dropped, i.e.
  * window_unpartition (modeling/image_encoder.py:280-302) is folded into the store.  Bias from table
  * products as in samb_attn_relpos_global_qkv with 2*window-1 entries per table. */
@@ -146,13 +146,25 @@ int samb_attn_relpos_window_qkv(const void* qkv, const void* tab, int64_t ldt, i
                                 int64_t o_pitch, int B, int H, int grid, int window, int d, float scale,
                                 int32_t* status, void* stream);
 
+/* Head-major variants of the qkv projection: out is [N / head_dim][M][head_dim] (bf16), i.e. one
+ * contiguous [M, head_dim] plane per (q|k|v, head) instead of M rows of N columns, so that the
+ * attention kernels stream whole contiguous tiles.  Epilogue: + bias (may be NULL).  head_dim a
+ * multiple of 16 that divides N.
+ * ref: the reshape/permute/unbind of the qkv output, modeling/image_encoder.py:228-230. */
+int samb_gemm_bf16_heads(const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias, void* out,
+                         int64_t M, int N, int K, int head_dim, int32_t* status, void* stream);
+int samb_gemm_i8_heads(const int8_t* Aq, int64_t lda, const float* a_scale, const int8_t* Wq, int64_t ldw,
+                       const float* w_scale, const float* bias, void* out, int64_t M, int N, int K, int head_dim,
+                       int32_t* status, void* stream);
+
 /* Products of every head's queries with the relative-position tables, for the *_qkv attention
- * entry points:  tab[t, h*t_head_stride + m] = (qkv[t, h*d : (h+1)*d] . tables[m, :]) * col_scale[m]
- * for m < t_head_stride (a multiple of 64; tables is bf16 [t_head_stride, d] holding rel_pos_h at
- * rows [0, 2S-1), rel_pos_w at rows [t_w_off, t_w_off + 2S-1) and zeros elsewhere; col_scale is 1
- * for the rel_pos_h rows and 1/scale for the rel_pos_w rows).  One batched tcgen05 GEMM over heads.
+ * entry points:  tab[t, h*t_head_stride + m] = (q_planes[h][t, :] . tables[m, :]) * col_scale[m]
+ * for m < t_head_stride (a multiple of 64).  q_planes is the head-major qkv buffer (its first H
+ * planes are the queries); tables is bf16 [t_head_stride, d] holding rel_pos_h at rows [0, 2S-1),
+ * rel_pos_w at rows [t_w_off, t_w_off + 2S-1) and zeros elsewhere; col_scale is 1 for the rel_pos_h
+ * rows and 1/scale for the rel_pos_w rows.  One batched tcgen05 GEMM over heads.
  * ref: the two einsums of add_decomposed_rel_pos, modeling/image_encoder.py:365-366. */
-int samb_relpos_table_products(const void* qkv, int64_t ld_qkv, const void* tables, const float* col_scale, void* tab,
+int samb_relpos_table_products(const void* q_planes, const void* tables, const float* col_scale, void* tab,
                                int64_t ldt, int64_t rows, int H, int d, int t_head_stride, int32_t* status,
                                void* stream);
 

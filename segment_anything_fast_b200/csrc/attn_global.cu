@@ -46,7 +46,7 @@ struct AttnParams {
   __nv_bfloat16* o;
   long long o_pitch;             // elements between consecutive output rows
   int o_head_stride;             // column offset per head in the output row
-  int qkv_fused;                 // 0: q/k/v are [BH*N, d]; 1: [B*N, 3*H*d] (q | k | v, head major)
+  int qkv_fused;                 // 0: q/k/v are [BH*N, d] tensors; 1: one head-major buffer [3H][B*N][d]
   int H, N, Sh;
   float scale;
   int* status;
@@ -105,16 +105,16 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int b = bh / p.H, h = bh - b * p.H;
   const int nblk = p.N / BK;
 
-  // tensor-map coordinates of this (image, head): row of token 0, 16-element column chunk of q/k/v
-  int row_base, cq, ck, cv;
+  // rows of token 0 of this (image, head) in the q, k, v operands.  Head-major qkv buffer: planes
+  // [q heads | k heads | v heads], each [B*N, d]; separate tensors: [B*H*N, d] each.
+  int rq, rk, rv;
   if (p.qkv_fused) {
-    row_base = b * p.N;
-    cq = (h * D) / 16;
-    ck = (p.H * D + h * D) / 16;
-    cv = (2 * p.H * D + h * D) / 16;
+    const int R = (gridDim.x / (p.H * n_tiles_q)) * p.N;     // rows per plane = B*N
+    rq = h * R + b * p.N;
+    rk = (p.H + h) * R + b * p.N;
+    rv = (2 * p.H + h) * R + b * p.N;
   } else {
-    row_base = bh * p.N;
-    cq = ck = cv = 0;
+    rq = rk = rv = bh * p.N;
   }
 
   if (threadIdx.x == 0) {
@@ -146,16 +146,16 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       mbar_expect_tx(q_full, CH * L::Q_CHUNK);
-      tma_load_3d(smem + L::OFF_Q, &tmQ, q_full, 0, row_base + n0, cq);
+      tma_load_3d(smem + L::OFF_Q, &tmQ, q_full, 0, rq + n0, 0);
       uint32_t stage = 0, phase = 0;
       for (int j = 0; j < nblk; ++j) {
         uint8_t* sk = smem + L::OFF_KV + stage * 2 * L::KV_TILE;
         if (!mbar_wait(&k_empty[stage], phase ^ 1u, abort_flag, p.status, 1)) break;
         mbar_expect_tx(&k_full[stage], L::KV_TILE);
-        tma_load_3d(sk, &tmK, &k_full[stage], 0, row_base + j * BK, ck);
+        tma_load_3d(sk, &tmK, &k_full[stage], 0, rk + j * BK, 0);
         if (!mbar_wait(&v_empty[stage], phase ^ 1u, abort_flag, p.status, 11)) break;
         mbar_expect_tx(&v_full[stage], L::KV_TILE);
-        tma_load_3d(sk + L::KV_TILE, &tmV, &v_full[stage], 0, row_base + j * BK, cv);
+        tma_load_3d(sk + L::KV_TILE, &tmV, &v_full[stage], 0, rv + j * BK, 0);
         if (++stage == KV_STAGES) { stage = 0; phase ^= 1u; }
       }
     }
@@ -467,7 +467,7 @@ int samb_attn_relpos_global_qkv(const void* qkv, const void* tab, int64_t ldt, i
   if (!qkv || !tab || !o || !status) return SAMB_E_BADARG;
   if (B <= 0 || H <= 0 || N <= 0) return SAMB_E_BADARG;
   if ((d != 64 && d != 80) || N % 256 || N > 4096) return SAMB_E_SHAPE;
-  if ((long long)B * N > 0x7fffffffLL || o_pitch % 8 || o_pitch < (int64_t)H * d) return SAMB_E_SHAPE;
+  if (3LL * H * B * N > 0x7fffffffLL || o_pitch % 8 || o_pitch < (int64_t)H * d) return SAMB_E_SHAPE;
   if (ldt < (int64_t)H * t_head_stride || t_w_off + 127 > t_head_stride || N / 64 * 2 - 1 > t_w_off) return SAMB_E_SHAPE;
   if (reinterpret_cast<uintptr_t>(o) & 15u) return SAMB_E_ALIGN;
   if (int e = check_device_arch()) return e;
@@ -484,9 +484,9 @@ int samb_attn_relpos_global_qkv(const void* qkv, const void* tab, int64_t ldt, i
   p.H = H; p.N = N; p.Sh = N / 64;
   p.scale = scale;
   p.status = status;
-  const long long rows = (long long)B * N, cols = 3LL * H * d;
-  return d == 80 ? launch_d<80>(qkv, qkv, qkv, rows, cols, cols, p, B * H, stream)
-                 : launch_d<64>(qkv, qkv, qkv, rows, cols, cols, p, B * H, stream);
+  const long long rows = 3LL * H * B * N;
+  return d == 80 ? launch_d<80>(qkv, qkv, qkv, rows, d, d, p, B * H, stream)
+                 : launch_d<64>(qkv, qkv, qkv, rows, d, d, p, B * H, stream);
 }
 
 }  // extern "C"

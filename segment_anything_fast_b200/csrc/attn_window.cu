@@ -36,7 +36,7 @@ struct WinParams {
   int t_head_stride, t_w_off, rel_mode;
   __nv_bfloat16* o;
   long long o_pitch;
-  int qkv_fused;                 // 0: q/k/v/o are [W*H*N, d]; 1: qkv [W*N, 3*H*d], o rows are raster tokens
+  int qkv_fused;                 // 0: q/k/v/o are [W*H*N, d]; 1: head-major qkv [3H][W*N][d], o rows are raster tokens
   int H, grid, nw;               // raster side and windows per side (fused mode)
   int items;                     // number of (window, head) pairs
   float scale;
@@ -116,18 +116,19 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       uint32_t stage = 0, phase = 0;
       for (int it = blockIdx.x; it < p.items; it += gridDim.x) {
         const int w = it / p.H, h = it - w * p.H;
-        int row_base, cq, ck, cv;
-        if (p.qkv_fused) {
-          row_base = w * N; cq = (h * D) / 16; ck = (p.H * D + h * D) / 16; cv = (2 * p.H * D + h * D) / 16;
+        int rq, rk, rv;                              // first row of this item in the q, k, v operands
+        if (p.qkv_fused) {                           // head-major buffer: planes [q heads | k heads | v heads]
+          const int R = (p.items / p.H) * N;         // rows per plane
+          rq = h * R + w * N; rk = (p.H + h) * R + w * N; rv = (2 * p.H + h) * R + w * N;
         } else {
-          row_base = it * N; cq = ck = cv = 0;
+          rq = rk = rv = it * N;
         }
         if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 1)) break;
         uint8_t* st = smem + stage * L::STAGE;
         mbar_expect_tx(&full[stage], L::STAGE);
-        tma_load_3d(st, &tmQ, &full[stage], 0, row_base, cq);
-        tma_load_3d(st + L::OFF_K, &tmK, &full[stage], 0, row_base, ck);
-        tma_load_3d(st + L::OFF_V, &tmV, &full[stage], 0, row_base, cv);
+        tma_load_3d(st, &tmQ, &full[stage], 0, rq, 0);
+        tma_load_3d(st + L::OFF_K, &tmK, &full[stage], 0, rk, 0);
+        tma_load_3d(st + L::OFF_V, &tmV, &full[stage], 0, rv, 0);
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
     }
@@ -414,7 +415,7 @@ int samb_attn_relpos_window_qkv(const void* qkv, const void* tab, int64_t ldt, i
   if (window != 14 || (d != 64 && d != 80)) return SAMB_E_SHAPE;
   const int nw = (grid + window - 1) / window;
   const long long W = (long long)B * nw * nw;
-  if (W * window * window > 0x7fffffffLL || o_pitch % 8 || o_pitch < (int64_t)H * d) return SAMB_E_SHAPE;
+  if (3LL * H * W * window * window > 0x7fffffffLL || o_pitch % 8 || o_pitch < (int64_t)H * d) return SAMB_E_SHAPE;
   if (ldt < (int64_t)H * t_head_stride || t_w_off + 2 * window - 1 > t_head_stride || 2 * window - 1 > t_w_off)
     return SAMB_E_SHAPE;
   if (reinterpret_cast<uintptr_t>(o) & 15u) return SAMB_E_ALIGN;
@@ -428,9 +429,9 @@ int samb_attn_relpos_window_qkv(const void* qkv, const void* tab, int64_t ldt, i
   p.H = H; p.grid = grid; p.nw = nw;
   p.scale = scale;
   p.status = status;
-  const long long rows = W * window * window, cols = 3LL * H * d;
-  return d == 80 ? launch_window<80, 14>(qkv, qkv, qkv, rows, cols, p, W * H, stream)
-                 : launch_window<64, 14>(qkv, qkv, qkv, rows, cols, p, W * H, stream);
+  const long long rows = 3LL * H * W * window * window;
+  return d == 80 ? launch_window<80, 14>(qkv, qkv, qkv, rows, d, p, W * H, stream)
+                 : launch_window<64, 14>(qkv, qkv, qkv, rows, d, p, W * H, stream);
 }
 
 }  // extern "C"

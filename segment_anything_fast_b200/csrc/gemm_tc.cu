@@ -46,6 +46,8 @@ struct GemmParams {
   long long tiles_per_batch;     // tiles of one column batch (== num_tiles when not batched)
   int a_col_stride;              // batch b reads A columns [b*a_col_stride, +K)
   int o_col_stride;              // and writes out columns [b*o_col_stride, +N)
+  int a_row_stride;              // batch b reads A rows [b*a_row_stride + m, ...) (head-major operand planes)
+  int hm_group;                  // > 0: head-major output, hm_group 16-column pieces per head (see launch_gemm)
   int epilogue;
 };
 
@@ -150,7 +152,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 1))) break;
           uint8_t* sa = smem + stage * STAGE_BYTES;
           mbar_expect_tx(&full_bar[stage], A_STAGE_BYTES + p.bn * SLAB_BYTES);
-          tma_load_2d(sa, &tmA, &full_bar[stage], a_col0 + ks * slab_elems, m0);
+          tma_load_2d(sa, &tmA, &full_bar[stage], a_col0 + ks * slab_elems, m0 + bt * p.a_row_stride);
           tma_load_2d(sa + A_STAGE_BYTES, &tmB, &full_bar[stage], ks * slab_elems, n0);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -288,14 +290,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           if (et == 0) tma_store_wait_read<0>();        // the staging tile is free again
           epi_sync();
-          uint8_t* srow = stage_out + erow * 128;
+          if (p.hm_group == 0) {
+            uint8_t* srow = stage_out + erow * 128;
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
-            *reinterpret_cast<uint4*>(srow + (((half * 4 + u) ^ (erow & 7)) << 4)) = packed[u];
+            for (int u = 0; u < 4; ++u)
+              *reinterpret_cast<uint4*>(srow + (((half * 4 + u) ^ (erow & 7)) << 4)) = packed[u];
+          } else {
+            // head-major: four [128][16-column] pieces (32-byte rows, 32B swizzle), one TMA store each
+            uint8_t* srow = stage_out + erow * 32;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int unit = half * 4 + u;             // 16-byte unit inside the 64-column chunk
+              *reinterpret_cast<uint4*>(srow + (unit >> 1) * 4096 + (((unit & 1) ^ ((erow >> 2) & 1)) << 4)) = packed[u];
+            }
+          }
           fence_proxy_async_smem();
           epi_sync();
           if (et == 0) {
-            tma_store_2d(&tmOut, stage_out, bt * p.o_col_stride + col0, m0);  // clipped at M and at the row end
+            if (p.hm_group == 0) {
+              tma_store_2d(&tmOut, stage_out, bt * p.o_col_stride + col0, m0);  // clipped at M and at the row end
+            } else {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const int col = col0 + q * 16;
+                if (col < p.N) {
+                  const int g = col >> 4;                // 16-column piece index: plane g / group, piece g % group
+                  tma_store_4d(&tmOut, stage_out + q * 4096, 0, g % p.hm_group, m0, g / p.hm_group);
+                }
+              }
+            }
             tma_store_commit();
           }
         }
@@ -340,7 +363,7 @@ inline int kmul_of(bool int8) { return int8 ? 16 : 8; }
 int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ldw, const float* a_scale,
                 const float* w_scale, const float* bias, const void* residual, int64_t ldr, int64_t res_rows,
                 void* out, int64_t ldo, int64_t M, int N, int K, int epilogue, int32_t* status, void* stream,
-                int batch = 1, int a_col_stride = 0, int o_col_stride = 0) {
+                int batch = 1, int a_col_stride = 0, int o_col_stride = 0, int64_t a_row_stride = 0, int head_dim = 0) {
   if (A == nullptr || W == nullptr || out == nullptr || status == nullptr) return SAMB_E_BADARG;
   if (M < 0 || N <= 0 || K <= 0 || batch <= 0) return SAMB_E_BADARG;
   if (epilogue == EPI_COLSCALE) {
@@ -361,9 +384,10 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
   const long long o_cols = (long long)(batch - 1) * o_col_stride + N;   // columns of out that are written
   if (K % kmul || lda % kmul || ldw % kmul || lda < a_cols || ldw < K) return SAMB_E_SHAPE;
   const int out_mul = raw ? 4 : 8;
-  if (N % 8 || ldo % out_mul || ldo < o_cols) return SAMB_E_SHAPE;
+  if (N % 8 || (!head_dim && (ldo % out_mul || ldo < o_cols))) return SAMB_E_SHAPE;
   if ((epilogue & SAMB_EPI_RESIDUAL) && (ldr % 8 || ldr < N || res_rows <= 0)) return SAMB_E_SHAPE;
-  if (M > (int64_t(1) << 31) - BM) return SAMB_E_SHAPE;
+  if (M > (int64_t(1) << 31) - BM || (a_row_stride * batch) > (int64_t(1) << 31) - BM) return SAMB_E_SHAPE;
+  if (head_dim && (head_dim % 16 || N % head_dim || (epilogue & SAMB_EPI_RAW) || batch != 1)) return SAMB_E_SHAPE;
   if ((reinterpret_cast<uintptr_t>(out) & 15u) || (residual && (reinterpret_cast<uintptr_t>(residual) & 15u)))
     return SAMB_E_ALIGN;
   if (int e = check_device_arch()) return e;
@@ -374,7 +398,7 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
   CUtensorMap tmA, tmB;
   {
     // batched: columns past a batch's K belong to the next batch; W's zero fill beyond K cancels them
-    const uint64_t dims[2] = {uint64_t(batch > 1 ? lda : K), uint64_t(M)};
+    const uint64_t dims[2] = {uint64_t(batch > 1 && a_col_stride ? lda : K), uint64_t(a_row_stride ? a_row_stride * batch : M)};
     const uint64_t strides[2] = {uint64_t(esz), uint64_t(lda) * esz};
     const uint32_t box[2] = {slab_elems, uint32_t(BM)};
     if (int e = make_tensor_map(&tmA, dt, 2, const_cast<void*>(A), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
@@ -409,10 +433,20 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
   p.num_tiles = p.tiles_per_batch * batch;
   p.a_col_stride = a_col_stride;
   p.o_col_stride = o_col_stride;
+  p.a_row_stride = int(a_row_stride);
+  p.hm_group = head_dim / 16;
   p.epilogue = epilogue;
 
   CUtensorMap tmOut = tmA;   // unused by the raw-accumulator variant
-  if (!raw) {
+  if (!raw && head_dim) {
+    // out is [N / head_dim planes][M rows][head_dim]: a 64-column chunk leaves as 16-column pieces
+    const uint64_t dims[4] = {16, uint64_t(head_dim / 16), uint64_t(M), uint64_t(N / head_dim)};
+    const uint64_t strides[4] = {2, 32, uint64_t(head_dim) * 2, uint64_t(M) * head_dim * 2};
+    const uint32_t box[4] = {16, 1, uint32_t(BM), 1};
+    if (int e = make_tensor_map(&tmOut, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, out, dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_32B))
+      return e;
+  } else if (!raw) {
     const uint64_t dims[2] = {uint64_t(o_cols), uint64_t(M)};
     const uint64_t strides[2] = {2, uint64_t(ldo) * 2};
     const uint32_t box[2] = {64, uint32_t(BM)};
@@ -447,12 +481,27 @@ int samb_gemm_i8(const int8_t* Aq, int64_t lda, const float* a_scale, const int8
                            epilogue, status, stream);
 }
 
-int samb_relpos_table_products(const void* qkv, int64_t ld_qkv, const void* tables, const float* col_scale, void* tab,
+int samb_relpos_table_products(const void* q_planes, const void* tables, const float* col_scale, void* tab,
                                int64_t ldt, int64_t rows, int H, int d, int t_head_stride, int32_t* status,
                                void* stream) {
   if (H <= 0 || d <= 0 || t_head_stride <= 0) return SAMB_E_BADARG;
-  return samb::launch_gemm(false, qkv, ld_qkv, tables, d, nullptr, col_scale, nullptr, nullptr, 0, 0, tab, ldt, rows,
-                           t_head_stride, d, samb::EPI_COLSCALE, status, stream, H, d, t_head_stride);
+  return samb::launch_gemm(false, q_planes, d, tables, d, nullptr, col_scale, nullptr, nullptr, 0, 0, tab, ldt, rows,
+                           t_head_stride, d, samb::EPI_COLSCALE, status, stream, H, 0, t_head_stride, rows);
+}
+
+int samb_gemm_bf16_heads(const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias, void* out,
+                         int64_t M, int N, int K, int head_dim, int32_t* status, void* stream) {
+  if (head_dim <= 0) return SAMB_E_BADARG;
+  return samb::launch_gemm(false, A, lda, W, ldw, nullptr, nullptr, bias, nullptr, 0, 0, out, 0, M, N, K,
+                           bias ? SAMB_EPI_BIAS : 0, status, stream, 1, 0, 0, 0, head_dim);
+}
+
+int samb_gemm_i8_heads(const int8_t* Aq, int64_t lda, const float* a_scale, const int8_t* Wq, int64_t ldw,
+                       const float* w_scale, const float* bias, void* out, int64_t M, int N, int K, int head_dim,
+                       int32_t* status, void* stream) {
+  if (head_dim <= 0) return SAMB_E_BADARG;
+  return samb::launch_gemm(true, Aq, lda, Wq, ldw, a_scale, w_scale, bias, nullptr, 0, 0, out, 0, M, N, K,
+                           bias ? SAMB_EPI_BIAS : 0, status, stream, 1, 0, 0, 0, head_dim);
 }
 
 }  // extern "C"

@@ -250,8 +250,10 @@ class ImageEncoderViT(nn.Module):
         for i, bw in enumerate(pk["blocks"]):
             ws = bw["window"]
             xn, xs = self._norm(cur, bw["n1"], grid=g if ws else 0, window=ws)
-            qkv = self._linear(xn, xs, bw["qkv"])
-            tab = ops.relpos_table_products(qkv, bw["tab"], bw["tab_scale"], H, d)
+            wq = bw["qkv"]
+            qkv = (ops.gemm_heads(xn, xs, wq["wq"], wq["ws"], wq["b"], d) if self.quant == "int8"
+                   else ops.gemm_heads(xn, None, wq["w"], None, wq["b"], d))          # [3H, rows, d]
+            tab = ops.relpos_table_products(qkv, bw["tab"], bw["tab_scale"], H)
             if ws:
                 o = ops.attn_relpos_window_qkv(qkv, tab, bw["T"], bw["t_w_off"], B, H, g, ws, d)
             else:

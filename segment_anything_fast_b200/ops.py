@@ -215,11 +215,11 @@ def attn_relpos_global(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rel_h:
 
 def attn_relpos_global_qkv(qkv: torch.Tensor, tab: torch.Tensor, t_head_stride: int, t_w_off: int, B: int, H: int,
                            N: int, d: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Global-block attention over the fused ``qkv [B*N, 3*H*d]`` buffer with the bias taken from
+    """Global-block attention over the head-major ``qkv [3H, B*N, d]`` buffer with the bias taken from
     the table products ``tab [B*N, ldt]``; returns ``[B*N, H*d]``."""
     _need(qkv, torch.bfloat16, "qkv"); _need(tab, torch.bfloat16, "tab")
-    if not qkv.is_contiguous() or qkv.shape != (B * N, 3 * H * d):
-        raise RuntimeError("qkv must be contiguous [B*N, 3*H*d]")
+    if not qkv.is_contiguous() or qkv.shape != (3 * H, B * N, d):
+        raise RuntimeError("qkv must be contiguous [3H, B*N, d]")
     tab = _rows2d(tab, "tab")
     if out is None:
         out = torch.empty(B * N, H * d, dtype=torch.bfloat16, device=qkv.device)
@@ -251,12 +251,12 @@ def attn_relpos_window(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rel_h:
 
 def attn_relpos_window_qkv(qkv: torch.Tensor, tab: torch.Tensor, t_head_stride: int, t_w_off: int, B: int, H: int,
                            grid: int, window: int, d: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Windowed attention over the window-ordered ``qkv [B*nw*nw*window^2, 3*H*d]``; returns raster-order
-    ``[B*grid*grid, H*d]`` (pad tokens dropped)."""
+    """Windowed attention over the window-ordered head-major ``qkv [3H, B*nw*nw*window^2, d]``; returns
+    raster-order ``[B*grid*grid, H*d]`` (pad tokens dropped)."""
     _need(qkv, torch.bfloat16, "qkv"); _need(tab, torch.bfloat16, "tab")
     rows = window_rows(B * grid * grid, grid, window)
-    if not qkv.is_contiguous() or qkv.shape != (rows, 3 * H * d):
-        raise RuntimeError("qkv must be contiguous [B*nw*nw*window^2, 3*H*d]")
+    if not qkv.is_contiguous() or qkv.shape != (3 * H, rows, d):
+        raise RuntimeError("qkv must be contiguous [3H, B*nw*nw*window^2, d]")
     tab = _rows2d(tab, "tab")
     if out is None:
         out = torch.empty(B * grid * grid, H * d, dtype=torch.bfloat16, device=qkv.device)
@@ -267,21 +267,47 @@ def attn_relpos_window_qkv(qkv: torch.Tensor, tab: torch.Tensor, t_head_stride: 
     return out
 
 
-def relpos_table_products(qkv: torch.Tensor, tables: torch.Tensor, col_scale: torch.Tensor, H: int, d: int,
+def gemm_heads(a: torch.Tensor, a_scale: Optional[torch.Tensor], w: torch.Tensor, w_scale: Optional[torch.Tensor],
+               bias: Optional[torch.Tensor], head_dim: int) -> torch.Tensor:
+    """qkv projection with a head-major result ``[N/head_dim, M, head_dim]`` (bf16).  ``a``/``w`` are bf16,
+    or int8 with their row scales."""
+    a, w = _rows2d(a, "a"), _rows2d(w, "w")
+    M, K = a.shape
+    N = w.shape[0]
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+    out = torch.empty(N // head_dim, M, head_dim, dtype=torch.bfloat16, device=a.device)
+    st = status_word(a.device)
+    if a.dtype == torch.int8:
+        _need(w, torch.int8, "w"); _need(a_scale, torch.float32, "a_scale"); _need(w_scale, torch.float32, "w_scale")
+        _lib.check(_lib.load().samb_gemm_i8_heads(a.data_ptr(), a.stride(0), a_scale.data_ptr(), w.data_ptr(), w.stride(0),
+                                                  w_scale.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K, head_dim,
+                                                  st.data_ptr(), _stream()), "samb_gemm_i8_heads")
+    else:
+        _need(a, torch.bfloat16, "a"); _need(w, torch.bfloat16, "w")
+        _lib.check(_lib.load().samb_gemm_bf16_heads(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), _ptr(bias),
+                                                    out.data_ptr(), M, N, K, head_dim, st.data_ptr(), _stream()),
+                   "samb_gemm_bf16_heads")
+    return out
+
+
+def relpos_table_products(qkv_hm: torch.Tensor, tables: torch.Tensor, col_scale: torch.Tensor, H: int,
                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``tab[t, h*T + m] = (q_{t,h} . tables[m]) * col_scale[m]`` for every head, ``T = tables.shape[0]``."""
-    _need(qkv, torch.bfloat16, "qkv"); _need(tables, torch.bfloat16, "tables"); _need(col_scale, torch.float32, "col_scale")
-    qkv = _rows2d(qkv, "qkv")
+    """``tab[t, h*T + m] = (q_h[t] . tables[m]) * col_scale[m]`` for the H query planes of the head-major
+    ``qkv_hm [3H, rows, d]``; ``T = tables.shape[0]``."""
+    _need(qkv_hm, torch.bfloat16, "qkv_hm"); _need(tables, torch.bfloat16, "tables"); _need(col_scale, torch.float32, "col_scale")
+    if qkv_hm.dim() != 3 or not qkv_hm.is_contiguous() or qkv_hm.shape[0] != 3 * H:
+        raise RuntimeError("qkv_hm must be a contiguous [3H, rows, d] tensor")
+    _, rows, d = qkv_hm.shape
     T = tables.shape[0]
     if not tables.is_contiguous() or tables.shape != (T, d) or col_scale.shape != (T,):
         raise RuntimeError("tables must be contiguous [T, d] with a [T] scale")
-    rows = qkv.shape[0]
     if out is None:
-        out = torch.empty(rows, H * T, dtype=torch.bfloat16, device=qkv.device)
-    st = status_word(qkv.device)
+        out = torch.empty(rows, H * T, dtype=torch.bfloat16, device=qkv_hm.device)
+    st = status_word(qkv_hm.device)
     _lib.check(_lib.load().samb_relpos_table_products(
-        qkv.data_ptr(), qkv.stride(0), tables.data_ptr(), col_scale.data_ptr(), out.data_ptr(), out.stride(0), rows, H,
-        d, T, st.data_ptr(), _stream()), "samb_relpos_table_products")
+        qkv_hm.data_ptr(), tables.data_ptr(), col_scale.data_ptr(), out.data_ptr(), out.stride(0), rows, H, d, T,
+        st.data_ptr(), _stream()), "samb_relpos_table_products")
     return out
 
 

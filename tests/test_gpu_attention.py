@@ -59,7 +59,7 @@ def test_global_attention_is_deterministic(ops):
 
 @pytest.mark.parametrize("B,H,d", [(2, 2, 80), (1, 3, 64)])
 def test_global_attention_fused_qkv_layout(ops, B, H, d):
-    """q/k/v read from the qkv projection buffer, bias from the q . rel_pos table products."""
+    """q/k/v read from the head-major qkv projection buffer, bias from the q . rel_pos table products."""
     N, S = 4096, 64
     torch.manual_seed(7)
     qkv = torch.empty(B * N, 3 * H * d).normal_(0.0, 1.0).bfloat16()
@@ -76,11 +76,12 @@ def test_global_attention_fused_qkv_layout(ops, B, H, d):
     tables[:127], tables[128:255] = rph, rpw
     col_scale = torch.ones(256)
     col_scale[128:] = math.sqrt(d)
-    tab = ops.relpos_table_products(qkv.cuda(), tables.cuda(), col_scale.cuda(), H, d)
+    qkv_hm = qkv.reshape(B * N, 3 * H, d).permute(1, 0, 2).contiguous().cuda()         # [3H, B*N, d] planes
+    tab = ops.relpos_table_products(qkv_hm, tables.cuda(), col_scale.cuda(), H)
     qh = qkv.float().reshape(B * N, 3, H, d)[:, 0]                                # [B*N, H, d]
     tab_ref = torch.einsum("nhc,mc->nhm", qh, tables.float()) * col_scale
     torch.testing.assert_close(tab.float().cpu().view(B * N, H, 256), tab_ref, rtol=1e-2, atol=1e-2)
-    out = ops.attn_relpos_global_qkv(qkv.cuda(), tab, 256, 128, B, H, N, d).float().cpu()
+    out = ops.attn_relpos_global_qkv(qkv_hm, tab, 256, 128, B, H, N, d).float().cpu()
     ops.check_status()
     assert (out - ref).abs().max().item() < 2e-2
     assert _cos(out, ref) > 0.999
@@ -124,8 +125,9 @@ def test_window_attention_fused_layout_with_padding(ops, B, H, d, grid):
     tables[:27], tables[32:59] = rph.bfloat16(), rpw.bfloat16()
     col_scale = torch.ones(64)
     col_scale[32:] = math.sqrt(d)
-    tab = ops.relpos_table_products(qkv.bfloat16().cuda(), tables.cuda(), col_scale.cuda(), H, d)
-    out = ops.attn_relpos_window_qkv(qkv.bfloat16().cuda(), tab, 64, 32, B, H, grid, ws, d)
+    qkv_hm = qkv.bfloat16().reshape(W * N, 3 * H, d).permute(1, 0, 2).contiguous().cuda()   # [3H, W*N, d] planes
+    tab = ops.relpos_table_products(qkv_hm, tables.cuda(), col_scale.cuda(), H)
+    out = ops.attn_relpos_window_qkv(qkv_hm, tab, 64, 32, B, H, grid, ws, d)
     ops.check_status()
     out = out.float().cpu()
     assert (out - ref).abs().max().item() < 2e-2

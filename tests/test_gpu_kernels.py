@@ -164,3 +164,25 @@ def test_layernorm2d_nchw(ops):
     torch.testing.assert_close(out, ref.reshape(B, hw, C).permute(0, 2, 1), rtol=8e-3, atol=8e-3)
     out2 = ops.layernorm2d(x.cuda(), gamma.cuda(), beta.cuda(), hw, 1e-6, to_nchw=False).float().cpu()
     torch.testing.assert_close(out2, ref, rtol=8e-3, atol=8e-3)
+
+
+@pytest.mark.parametrize("int8", [False, True])
+def test_gemm_head_major_output(ops, int8):
+    """The qkv projection variant that writes one contiguous [M, head_dim] plane per (q|k|v, head)."""
+    M, H, d, K = 392, 2, 80, 160
+    N = 3 * H * d
+    g = torch.Generator().manual_seed(21)
+    x = _bf16(torch.randn(M, K, generator=g))
+    w = torch.randn(N, K, generator=g) * 0.05
+    b = torch.randn(N, generator=g) * 0.1
+    if int8:
+        xq, sx = ops.quant_rows_i8(x.cuda())
+        wq, sw = qo.quantize_rows_absmax(w)
+        out = ops.gemm_heads(xq, sx, wq.cuda(), sw.cuda(), b.cuda(), d)
+        plain = ops.gemm_i8(xq, sx, wq.cuda(), sw.cuda(), b.cuda())
+    else:
+        out = ops.gemm_heads(x.cuda(), None, _bf16(w).cuda(), None, b.cuda(), d)
+        plain = ops.gemm_bf16(x.cuda(), _bf16(w).cuda(), b.cuda())
+    ops.check_status()
+    assert out.shape == (3 * H, M, d)
+    assert torch.equal(out.permute(1, 0, 2).reshape(M, N), plain)        # same numbers, different layout
