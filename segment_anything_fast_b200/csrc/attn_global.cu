@@ -270,20 +270,59 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int qh = n / SW, qw = n - qh * SW;
     // rel_w tensors are divided by scale here; table products arrive already divided
     const float inv_scale = p.rel_mode == 0 ? 1.0f / p.scale : 1.0f;
-    const __nv_bfloat16* src_h;
-    int step;                                              // +1: src[k]; -1: src[-k] (table products)
+    // ---- prologue: this row's bias values, fetched with 16-byte loads.
+    //  * tensors (mode 0): rel_h [Sh] and rel_w [64] rows, in key order.
+    //  * table products (mode 1): rel[k] = T[pos + S - 1 - k] is contiguous in T in reverse key order starting
+    //    at element `pos` (qh resp. qw) of a 128-byte-aligned slice: load from the aligned address below,
+    //    shift down by pos % 8 elements, read backwards.
+    // rel_w/scale goes to the swizzled A-operand tile; rel_h stays in a per-thread array indexed by the key
+    // tile at run time (local memory: one coalesced word per thread and key tile).
+    uint32_t relh_loc[32];                                 // word j = (rel_h[2j], rel_h[2j+1]) as bf16 bits
     {
-      const __nv_bfloat16* src_w;
-      if (p.rel_mode == 0) {
-        src_h = p.rel_h + ((long long)bh * p.N + n) * p.Sh;
-        src_w = p.rel_w + ((long long)bh * p.N + n) * SW;
-        step = 1;
+      const int rev = p.rel_mode != 0;
+      auto load_row = [&](const __nv_bfloat16* base, int pos, int count, uint32_t (&out)[32]) {
+        // out[e >> 1] halves e = 0..count-1 in key order (count <= 64, multiple of 2)
+        uint32_t v[36];
+        const int sh = rev ? (pos & 7) : 0;
+        const uint4* src = reinterpret_cast<const uint4*>(base + (rev ? pos - sh : 0));
+        const int nvec = rev ? (count + 8 + 7) / 8 : count / 8;
+        if (!rev && (count & 7)) {                       // short rel_h rows (small rasters): plain 4-byte loads
+          const uint32_t* s32 = reinterpret_cast<const uint32_t*>(base);
+#pragma unroll
+          for (int q = 0; q < 36; ++q) v[q] = q < count / 2 ? __ldg(s32 + q) : 0u;
+        } else {
+#pragma unroll
+          for (int q = 0; q < 9; ++q) {
+            uint4 a = make_uint4(0u, 0u, 0u, 0u);
+            if (q < nvec) a = __ldg(src + q);
+            v[4 * q] = a.x; v[4 * q + 1] = a.y; v[4 * q + 2] = a.z; v[4 * q + 3] = a.w;
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < 34; ++q) v[q] = (sh & 4) ? v[q + 2] : v[q];
+#pragma unroll
+        for (int q = 0; q < 33; ++q) v[q] = (sh & 2) ? v[q + 1] : v[q];
+#pragma unroll
+        for (int q = 0; q < 32; ++q) v[q] = (sh & 1) ? __funnelshift_r(v[q], v[q + 1], 16) : v[q];
+        // key order: forward as is; reversed: element e = v-element (count - 1 - e), i.e. swap halves and words
+#pragma unroll
+        for (int q = 0; q < 32; ++q) {
+          const int qq = count / 2 - 1 - q;
+          const uint32_t r = v[qq >= 0 ? qq : 0];
+          out[q] = rev ? ((r >> 16) | (r << 16)) : v[q];
+        }
+      };
+      const __nv_bfloat16 *base_h, *base_w;
+      if (!rev) {
+        base_h = p.rel_h + ((long long)bh * p.N + n) * p.Sh;
+        base_w = p.rel_w + ((long long)bh * p.N + n) * SW;
       } else {
-        const __nv_bfloat16* tb = p.tab + ((long long)b * p.N + n) * p.ldt + h * p.t_head_stride;
-        src_h = tb + (qh + p.Sh - 1);
-        src_w = tb + p.t_w_off + (qw + SW - 1);
-        step = -1;
+        base_h = p.tab + ((long long)b * p.N + n) * p.ldt + h * p.t_head_stride;
+        base_w = base_h + p.t_w_off;
       }
+      uint32_t rw[32];
+      load_row(base_w, qw, SW, rw);
+      load_row(base_h, qh, p.Sh, relh_loc);
       uint8_t* relw_row = smem + L::OFF_RELW + t * 16384 + i * 128;
       uint8_t* e_row = smem + L::OFF_E + i * 128;
 #pragma unroll
@@ -292,9 +331,8 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
         for (int tt = 0; tt < 4; ++tt) {
           const int k0 = u * 8 + 2 * tt;
-          const float a = __bfloat162float(src_w[step * k0]) * inv_scale;
-          const float c = __bfloat162float(src_w[step * (k0 + 1)]) * inv_scale;
-          w[tt] = pack2(a, c);
+          const uint32_t pr = rw[u * 4 + tt];
+          w[tt] = pack2(__uint_as_float(pr << 16) * inv_scale, __uint_as_float(pr & 0xffff0000u) * inv_scale);
           e[tt] = (i == k0 ? 0x3F80u : 0u) | (i == k0 + 1 ? 0x3F800000u : 0u);
         }
         const int phys = (u ^ (i & 7)) << 4;
@@ -306,8 +344,6 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     const float c2 = p.scale * kLog2e;
     float m_used = -INFINITY, l_run = 0.f;
-    float bh0 = __bfloat162float(src_h[0]) * kLog2e;
-    float bh1 = __bfloat162float(src_h[step]) * kLog2e;
     const uint32_t s_addr = lane_addr + t * 128;
     const uint32_t o_addr = lane_addr + 256 + t * 128;
     uint8_t* p_tile = smem + L::OFF_P + t * 32768 + i * 128;
@@ -315,12 +351,9 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
     for (int j = 0; j < nblk; ++j) {
       const uint32_t par = uint32_t(j) & 1u;
-      // rel_h of the next key tile (two raster rows), fetched early
-      float nbh0 = 0.f, nbh1 = 0.f;
-      if (j + 1 < nblk) {
-        nbh0 = __bfloat162float(src_h[step * (2 * j + 2)]) * kLog2e;
-        nbh1 = __bfloat162float(src_h[step * (2 * j + 3)]) * kLog2e;
-      }
+      // rel_h of this key tile's two raster rows
+      const uint32_t hpair = relh_loc[j];
+      const float bh0 = __uint_as_float(hpair << 16) * kLog2e, bh1 = __uint_as_float(hpair & 0xffff0000u) * kLog2e;
       if (!(ok = mbar_wait(&s_full[t], par, abort_flag, p.status, 8))) break;
       tc_fence_after();
       uint32_t s[128];
@@ -376,8 +409,6 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive_warp(&p_full[t]);
-      bh0 = nbh0;
-      bh1 = nbh1;
     }
     if (ok) ok = mbar_wait(&pv_done[t], uint32_t(nblk - 1) & 1u, abort_flag, p.status, 10);
     if (ok) {
@@ -443,7 +474,8 @@ int samb_attn_relpos_global(const void* q, const void* k, const void* v, const v
   if (B <= 0 || H <= 0 || N <= 0) return SAMB_E_BADARG;
   if ((d != 64 && d != 80) || N % 256 || N > 4096) return SAMB_E_SHAPE;
   if ((long long)B * H * N > 0x7fffffffLL) return SAMB_E_SHAPE;
-  if (reinterpret_cast<uintptr_t>(o) & 15u) return SAMB_E_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(rel_h) | reinterpret_cast<uintptr_t>(rel_w)) & 15u)
+    return SAMB_E_ALIGN;
   if (int e = check_device_arch()) return e;
   AttnParams p{};
   p.rel_h = static_cast<const __nv_bfloat16*>(rel_h);
@@ -469,7 +501,9 @@ int samb_attn_relpos_global_qkv(const void* qkv, const void* tab, int64_t ldt, i
   if ((d != 64 && d != 80) || N % 256 || N > 4096) return SAMB_E_SHAPE;
   if (3LL * H * B * N > 0x7fffffffLL || o_pitch % 8 || o_pitch < (int64_t)H * d) return SAMB_E_SHAPE;
   if (ldt < (int64_t)H * t_head_stride || t_w_off + 127 > t_head_stride || N / 64 * 2 - 1 > t_w_off) return SAMB_E_SHAPE;
-  if (reinterpret_cast<uintptr_t>(o) & 15u) return SAMB_E_ALIGN;
+  // the bias prologue reads 16-byte vectors from 128-byte-aligned slices: [0, 128) and [t_w_off, t_w_off + 128)
+  if (ldt % 64 || t_head_stride % 64 || t_w_off % 64 || t_w_off < 128 || t_head_stride - t_w_off < 128) return SAMB_E_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(tab)) & 15u) return SAMB_E_ALIGN;
   if (int e = check_device_arch()) return e;
   AttnParams p{};
   p.tab = static_cast<const __nv_bfloat16*>(tab);

@@ -201,32 +201,55 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       *reinterpret_cast<uint4*>(erow + ((1 ^ sw) << 4)) = make_uint4(e[4], e[5], e[6], e[7]);
     }
 
-    // raw bf16 bias values of one item; nothing touches them until the item starts, so the loads
-    // issued for item k+1 have the whole of item k to land
-    unsigned short raw_h[WS], raw_w[WS];
+    // Raw bf16 bias values of one item, [rel_h | rel_w] x 12 words; nothing touches them until the item
+    // starts, so the loads issued for item k+1 have the whole of item k to land.
+    //  * tensors (mode 0): 14 values = 7 aligned words per part, in key order.
+    //  * table products (mode 1): the 14 values rel[k] = T[pos + 13 - k] are contiguous in T in reverse
+    //    key order, starting at element `pos` of a 128-byte-aligned slice: three 16-byte loads from the
+    //    aligned address below it, shifted down by (pos % 8) elements when the item starts.
+    uint32_t rawv[2][12];
+    const int rev = p.rel_mode != 0;
+    const int sh_h = rev ? (qh & 7) : 0, sh_w = rev ? (qw & 7) : 0;
     auto fetch_bias = [&](int it) {
-      const int w = it / p.H, h = it - w * p.H;
-      const unsigned short *src_h, *src_w;
-      int step = 1;
-      if (p.rel_mode == 0) {
-        src_h = reinterpret_cast<const unsigned short*>(p.rel_h + ((long long)it * N + n) * WS);
-        src_w = reinterpret_cast<const unsigned short*>(p.rel_w + ((long long)it * N + n) * WS);
-      } else {
-        const __nv_bfloat16* tb = p.tab + ((long long)w * N + n) * p.ldt + h * p.t_head_stride;
-        src_h = reinterpret_cast<const unsigned short*>(tb + (qh + WS - 1));
-        src_w = reinterpret_cast<const unsigned short*>(tb + p.t_w_off + (qw + WS - 1));
-        step = -1;
-      }
-      if (valid) {
+      if (!valid) return;
+      if (!rev) {
+        const uint32_t* s_h = reinterpret_cast<const uint32_t*>(p.rel_h + ((long long)it * N + n) * WS);
+        const uint32_t* s_w = reinterpret_cast<const uint32_t*>(p.rel_w + ((long long)it * N + n) * WS);
 #pragma unroll
-        for (int q = 0; q < WS; ++q) {
-          raw_h[q] = __ldg(src_h + step * q);
-          raw_w[q] = __ldg(src_w + step * q);
+        for (int q = 0; q < WS / 2; ++q) { rawv[0][q] = __ldg(s_h + q); rawv[1][q] = __ldg(s_w + q); }
+      } else {
+        const int w = it / p.H, h = it - w * p.H;
+        const __nv_bfloat16* tb = p.tab + ((long long)w * N + n) * p.ldt + h * p.t_head_stride;
+        const uint4* s_h = reinterpret_cast<const uint4*>(tb + (qh - sh_h));
+        const uint4* s_w = reinterpret_cast<const uint4*>(tb + p.t_w_off + (qw - sh_w));
+#pragma unroll
+        for (int q = 0; q < 3; ++q) {
+          const uint4 a = __ldg(s_h + q), c = __ldg(s_w + q);
+          rawv[0][4 * q] = a.x; rawv[0][4 * q + 1] = a.y; rawv[0][4 * q + 2] = a.z; rawv[0][4 * q + 3] = a.w;
+          rawv[1][4 * q] = c.x; rawv[1][4 * q + 1] = c.y; rawv[1][4 * q + 2] = c.z; rawv[1][4 * q + 3] = c.w;
         }
       }
     };
+    // element e (0..13) of part x in key order, after undoing the alignment shift and the reversal
+    auto bias_elems = [&](int x, int sh, uint32_t (&out)[WS]) {
+      uint32_t v[12];
 #pragma unroll
-    for (int q = 0; q < WS; ++q) raw_h[q] = raw_w[q] = 0;
+      for (int q = 0; q < 12; ++q) v[q] = rawv[x][q];
+#pragma unroll
+      for (int q = 0; q < 10; ++q) v[q] = (sh & 4) ? v[q + 2] : v[q];      // 4 elements = 2 words
+#pragma unroll
+      for (int q = 0; q < 9; ++q) v[q] = (sh & 2) ? v[q + 1] : v[q];       // 2 elements = 1 word
+#pragma unroll
+      for (int q = 0; q < 7; ++q) v[q] = (sh & 1) ? __funnelshift_r(v[q], v[q + 1], 16) : v[q];
+#pragma unroll
+      for (int e = 0; e < WS; ++e) {
+        const int f = WS - 1 - e;
+        const uint32_t fwd = (v[e >> 1] >> ((e & 1) * 16)) & 0xffffu, bwd = (v[f >> 1] >> ((f & 1) * 16)) & 0xffffu;
+        out[e] = rev ? bwd : fwd;
+      }
+    };
+#pragma unroll
+    for (int q = 0; q < 12; ++q) rawv[0][q] = rawv[1][q] = 0u;
 
     int it = blockIdx.x;
     if (it < p.items) fetch_bias(it);
@@ -237,10 +260,13 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       float bh[WS];
       {
         float rw[16];
+        uint32_t eh[WS], ew[WS];
+        bias_elems(0, sh_h, eh);
+        bias_elems(1, sh_w, ew);
 #pragma unroll
-        for (int q = 0; q < 16; ++q) rw[q] = q < WS ? bf16_bits_to_float(raw_w[q < WS ? q : 0]) * inv_scale : 0.f;
+        for (int q = 0; q < 16; ++q) rw[q] = q < WS ? bf16_bits_to_float(ew[q < WS ? q : 0]) * inv_scale : 0.f;
 #pragma unroll
-        for (int q = 0; q < WS; ++q) bh[q] = bf16_bits_to_float(raw_h[q]) * kLog2e;
+        for (int q = 0; q < WS; ++q) bh[q] = bf16_bits_to_float(eh[q]) * kLog2e;
         uint8_t* rrow = smem + L::OFF_RELW + n * 32;
         *reinterpret_cast<uint4*>(rrow + ((0 ^ sw) << 4)) =
             make_uint4(wpack2(rw[0], rw[1]), wpack2(rw[2], rw[3]), wpack2(rw[4], rw[5]), wpack2(rw[6], rw[7]));
@@ -418,7 +444,9 @@ int samb_attn_relpos_window_qkv(const void* qkv, const void* tab, int64_t ldt, i
   if (3LL * H * W * window * window > 0x7fffffffLL || o_pitch % 8 || o_pitch < (int64_t)H * d) return SAMB_E_SHAPE;
   if (ldt < (int64_t)H * t_head_stride || t_w_off + 2 * window - 1 > t_head_stride || 2 * window - 1 > t_w_off)
     return SAMB_E_SHAPE;
-  if (reinterpret_cast<uintptr_t>(o) & 15u) return SAMB_E_ALIGN;
+  // the bias prologue reads 16-byte vectors below each needed element and up to the end of a head's slice
+  if (ldt % 8 || t_head_stride % 64 || t_w_off % 8 || t_head_stride - t_w_off < 32 || t_w_off < 32) return SAMB_E_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(tab)) & 15u) return SAMB_E_ALIGN;
   if (int e = check_device_arch()) return e;
   WinParams p{};
   p.tab = static_cast<const __nv_bfloat16*>(tab);
