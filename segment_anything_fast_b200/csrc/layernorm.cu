@@ -57,6 +57,16 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return u;
 }
 
+// rint(x / sc), bit-identical to the IEEE quotient, without paying for a division per element:
+// x * (1/sc) is within 2^-23 relative (1.5e-5 absolute for |x/sc| <= 127.5) of the true quotient, so the
+// two roundings can only disagree next to a half-integer; only there is the real division evaluated.
+__device__ __forceinline__ float div_rint(float x, float sc, float inv_sc) {
+  const float t = x * inv_sc;
+  float r = rintf(t);
+  if (fabsf(fabsf(t - r) - 0.5f) < 4e-5f) r = rintf(__fdiv_rn(x, sc));
+  return r;
+}
+
 // kNorm: apply LayerNorm; kQuant: emit int8 + scale instead of bf16.
 template <bool kNorm, bool kQuant>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
@@ -159,6 +169,7 @@ row_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
   }
   amax = warp_max(amax);
   const float sc = __fdiv_rn(fmaxf(amax, kAbsmaxFloor), 127.0f);
+  const float inv_sc = __frcp_rn(sc);
   if (lane == 0) scale[orow] = sc;
   uint2* qr = reinterpret_cast<uint2*>(yq + orow * C);
 #pragma unroll
@@ -170,7 +181,7 @@ row_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
       uint32_t w[2] = {0u, 0u};
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        float t = rintf(__fdiv_rn(f[j], sc));
+        float t = div_rint(f[j], sc, inv_sc);
         t = fminf(fmaxf(t, -127.f), 127.f);
         w[j >> 2] |= (uint32_t(int(t)) & 0xffu) << ((j & 3) * 8);
       }
@@ -205,6 +216,7 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ yq, 
   }
   amax = warp_max(amax);
   const float sc = __fdiv_rn(fmaxf(amax, kAbsmaxFloor), 127.0f);
+  const float inv_sc = __frcp_rn(sc);
   if (lane == 0) scale[row] = sc;
   uint2* qr = reinterpret_cast<uint2*>(yq + row * C);
 #pragma unroll
@@ -216,7 +228,56 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ yq, 
       uint32_t w[2] = {0u, 0u};
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        float t = rintf(__fdiv_rn(f[j], sc));
+        float t = div_rint(f[j], sc, inv_sc);
+        t = fminf(fmaxf(t, -127.f), 127.f);
+        w[j >> 2] |= (uint32_t(int(t)) & 0xffu) << ((j & 3) * 8);
+      }
+      qr[vi] = make_uint2(w[0], w[1]);
+    }
+  }
+}
+
+// Wide rows (C up to 3 * 256 * 8 = 6144): one 256-thread block per row, up to three 16-byte vectors per
+// thread, absmax through shared memory.
+__global__ void __launch_bounds__(256)
+quant_rows_wide_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ yq, float* __restrict__ scale, int C) {
+  __shared__ float s_max[8];
+  const long long row = blockIdx.x;
+  const int nvec = C >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
+  uint4 raw[3];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    const int vi = i * 256 + threadIdx.x;
+    if (vi < nvec) {
+      raw[i] = xr[vi];
+      float f[8];
+      unpack8(raw[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+    }
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = s_max[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) amax = fmaxf(amax, s_max[w]);
+  const float sc = __fdiv_rn(fmaxf(amax, kAbsmaxFloor), 127.0f);
+  const float inv_sc = __frcp_rn(sc);
+  if (threadIdx.x == 0) scale[row] = sc;
+  uint2* qr = reinterpret_cast<uint2*>(yq + row * C);
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    const int vi = i * 256 + threadIdx.x;
+    if (vi < nvec) {
+      float f[8];
+      unpack8(raw[i], f);
+      uint32_t w[2] = {0u, 0u};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float t = div_rint(f[j], sc, inv_sc);
         t = fminf(fmaxf(t, -127.f), 127.f);
         w[j >> 2] |= (uint32_t(int(t)) & 0xffu) << ((j & 3) * 8);
       }
@@ -329,7 +390,8 @@ int samb_quant_rows_i8(const void* x, int8_t* yq, float* scale, int64_t rows, in
   auto st = static_cast<cudaStream_t>(stream);
   auto xb = static_cast<const __nv_bfloat16*>(x);
   if (C <= 8 * 256) quant_rows_kernel<8><<<unsigned(blocks), kWarpsPerBlock * 32, 0, st>>>(xb, yq, scale, rows, C);
-  else quant_rows_kernel<24><<<unsigned(blocks), kWarpsPerBlock * 32, 0, st>>>(xb, yq, scale, rows, C);
+  else if (rows > 0x7fffffffLL) return SAMB_E_SHAPE;
+  else quant_rows_wide_kernel<<<unsigned(rows), 256, 0, st>>>(xb, yq, scale, C);
   return launch_status();
 }
 

@@ -186,3 +186,13 @@ def test_gemm_head_major_output(ops, int8):
     ops.check_status()
     assert out.shape == (3 * H, M, d)
     assert torch.equal(out.permute(1, 0, 2).reshape(M, N), plain)        # same numbers, different layout
+
+
+@pytest.mark.parametrize("rows,C", [(300, 5120), (65, 4096), (17, 3072), (1000, 1280)])
+def test_quant_rows_wide_and_narrow_bit_exact(ops, rows, C):
+    g = torch.Generator().manual_seed(rows + C)
+    x = _bf16(torch.randn(rows, C, generator=g) * 2.0)
+    x[0].zero_()                                     # an all-zero row must take the floor scale
+    q, s = ops.quant_rows_i8(x.cuda())
+    q_ref, s_ref = qo.quantize_rows_absmax(x.float())
+    assert torch.equal(q.cpu(), q_ref) and torch.equal(s.cpu(), s_ref)
