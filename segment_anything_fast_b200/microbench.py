@@ -1,0 +1,106 @@
+"""Single-kernel timings through the C ABI (CUDA events, L2 flushed by inputs larger than L2 where
+the shape allows it).  One JSON line per run:
+
+    python -m segment_anything_fast_b200.microbench gemm --m 131072 --n 3840 --k 1280 --epilogue bias [--int8]
+    python -m segment_anything_fast_b200.microbench attn-global --batch 8 --heads 16 --tokens 4096 --dim 80
+    python -m segment_anything_fast_b200.microbench attn-window --batch 200 --heads 16 --dim 80
+    python -m segment_anything_fast_b200.microbench layernorm --rows 131072 --cols 1280 [--quant]
+
+The two attention commands at their defaults are the standalone relative-position attention
+benchmark (q, k, v ~ N(0,1), rel_h / rel_w ~ N(0,0.5), bf16).
+"""
+import argparse
+import json
+
+import torch
+
+from . import ops
+
+
+def _time(fn, iters, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    ops.check_status()
+    return a.elapsed_time(b) / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--m", type=int, default=131072); g.add_argument("--n", type=int, default=3840)
+    g.add_argument("--k", type=int, default=1280)
+    g.add_argument("--epilogue", choices=["none", "bias", "gelu", "residual"], default="bias")
+    g.add_argument("--int8", action="store_true")
+    ag = sub.add_parser("attn-global")
+    ag.add_argument("--batch", type=int, default=8); ag.add_argument("--heads", type=int, default=16)
+    ag.add_argument("--tokens", type=int, default=4096); ag.add_argument("--dim", type=int, default=80)
+    aw = sub.add_parser("attn-window")
+    aw.add_argument("--batch", type=int, default=200); aw.add_argument("--heads", type=int, default=16)
+    aw.add_argument("--dim", type=int, default=80)
+    ln = sub.add_parser("layernorm")
+    ln.add_argument("--rows", type=int, default=131072); ln.add_argument("--cols", type=int, default=1280)
+    ln.add_argument("--quant", action="store_true")
+    for p in (g, ag, aw, ln):
+        p.add_argument("--iters", type=int, default=10); p.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args()
+    torch.manual_seed(0)
+    dev = "cuda"
+    out = {"kernel": a.cmd}
+    if a.cmd == "gemm":
+        M, N, K = a.m, a.n, a.k
+        bias = torch.randn(N, device=dev) if a.epilogue != "none" else None
+        res = torch.randn(M, N, device=dev).bfloat16() if a.epilogue == "residual" else None
+        y = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        if a.int8:
+            x = torch.randint(-127, 128, (M, K), device=dev, dtype=torch.int8)
+            w = torch.randint(-127, 128, (N, K), device=dev, dtype=torch.int8)
+            sx, sw = torch.rand(M, device=dev), torch.rand(N, device=dev)
+            fn = lambda: ops.gemm_i8(x, sx, w, sw, bias, res, gelu=a.epilogue == "gelu", out=y)
+        else:
+            x = torch.randn(M, K, device=dev).bfloat16()
+            w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+            fn = lambda: ops.gemm_bf16(x, w, bias, res, gelu=a.epilogue == "gelu", out=y)
+        ms = _time(fn, a.iters, a.warmup)
+        out.update(shape=[M, N, K], epilogue=a.epilogue, dtype="int8" if a.int8 else "bf16", ms=round(ms, 4),
+                   tflops=round(2.0 * M * N * K / ms / 1e9, 1))
+    elif a.cmd == "attn-global":
+        B, H, N, d = a.batch, a.heads, a.tokens, a.dim
+        q, k, v = (torch.randn(B, H, N, d, device=dev).bfloat16() for _ in range(3))
+        rh = (torch.randn(B, H, N, N // 64, device=dev) * 0.5).bfloat16()
+        rw = (torch.randn(B, H, N, 64, device=dev) * 0.5).bfloat16()
+        ms = _time(lambda: ops.attn_relpos_global(q, k, v, rh, rw), a.iters, a.warmup)
+        out.update(shape=[B, H, N, d], ms=round(ms, 4), tflops=round(4.0 * B * H * N * N * d / ms / 1e9, 1))
+    elif a.cmd == "attn-window":
+        B, H, d = a.batch, a.heads, a.dim
+        q, k, v = (torch.randn(B, H, 196, d, device=dev).bfloat16() for _ in range(3))
+        rh = (torch.randn(B, H, 196, 14, device=dev) * 0.5).bfloat16()
+        rw = (torch.randn(B, H, 196, 14, device=dev) * 0.5).bfloat16()
+        ms = _time(lambda: ops.attn_relpos_window(q, k, v, rh, rw), a.iters, a.warmup)
+        nbytes = 4 * B * H * 196 * d * 2 + 2 * B * H * 196 * 14 * 2          # q, k, v, o + rel_h, rel_w
+        out.update(shape=[B, H, 196, d], ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1),
+                   tflops=round(4.0 * B * H * 196 * 196 * d / ms / 1e9, 1))
+    else:
+        R, C = a.rows, a.cols
+        x = torch.randn(R, C, device=dev).bfloat16()
+        gm, bt = torch.ones(C, device=dev), torch.zeros(C, device=dev)
+        if a.quant:
+            ms = _time(lambda: ops.layernorm_quant_i8(x, gm, bt), a.iters, a.warmup)
+            nbytes = R * C * 3 + R * 4
+        else:
+            y = torch.empty(R, C, device=dev, dtype=torch.bfloat16)
+            ms = _time(lambda: ops.layernorm(x, gm, bt, out=y), a.iters, a.warmup)
+            nbytes = R * C * 4
+        out.update(shape=[R, C], quant=bool(a.quant), ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1))
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
