@@ -8,7 +8,7 @@ import os
 from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_uint32, c_void_p
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.environ.get("SAMB200_LIB") or os.path.join(_PKG, "lib", "libsamb200.so")
+LIB_PATH = os.path.join(_PKG, "lib", "libsamb200.so")
 
 OK = 0
 EPI_BIAS, EPI_GELU, EPI_RESIDUAL, EPI_RAW = 1, 2, 4, 8

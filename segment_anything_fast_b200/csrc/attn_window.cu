@@ -76,7 +76,7 @@ __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) { return __
 template <int D, int WS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                   const __grid_constant__ CUtensorMap tmV, const WinParams p) {
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const WinParams p) {
   using L = WinSmem<D, WS>;
   constexpr int N = L::N, NK = L::NK, CH = L::CH;
   extern __shared__ uint8_t smem_raw[];
@@ -89,20 +89,23 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* p_full = bars + 7;      // [2]      P of tile t is in TMEM
   uint64_t* o_full = bars + 9;      // [2]      P V of tile t is in TMEM
   uint64_t* t_free = bars + 11;     // [2]      tile t's TMEM columns may be overwritten (O has been read)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* out_ready = bars + 13;  //          all rows of the item's output are staged in shared memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    // a stage is free when the MMAs that read it have finished AND the output store staged in it has been read
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 2); }
     mbar_init(pro_done, 8);
+    mbar_init(out_ready, 8);
     for (int t = 0; t < 2; ++t) {
       mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 4); mbar_init(&o_full[t], 1); mbar_init(&t_free[t], 4);
     }
     fence_mbar_init();
-    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmO);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
@@ -332,41 +335,47 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (!(ok = mbar_wait(&o_full[t], par, abort_flag, p.status, 7))) break;
       tc_fence_after();
       const float inv_l = 1.0f / l;
-      __nv_bfloat16* orow = nullptr;
-      if (valid) {
-        if (p.qkv_fused) {
-          const int w = it / p.H, h = it - w * p.H;
-          const int ww = p.nw * p.nw;
-          const int b = w / ww, wi = w - b * ww;
-          const int wy = wi / p.nw, wx = wi - wy * p.nw;
-          const int y = wy * WS + qh, x = wx * WS + qw;
-          if (y < p.grid && x < p.grid) orow = p.o + (((long long)b * p.grid + y) * p.grid + x) * p.o_pitch + h * D;
-        } else {
-          orow = p.o + ((long long)it * N + n) * p.o_pitch;
-        }
-      }
       uint32_t ro[D / 16][16];
 #pragma unroll
       for (int c = 0; c < D / 16; ++c) tmem_ld_32x32b_x16(lane_addr + kOCol + c * 16, ro[c]);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive_warp(&t_free[t]);                              // O is in registers: the tile's columns are free
-      if (orow != nullptr) {
+      // The item's output goes through shared memory (the Q region of this stage is dead once the logits
+      // exist) as [token][D] rows and leaves with one TMA store: a WS x WS x D box of the output tensor,
+      // which drops the zero-padded tokens of border windows by clipping.
+      uint8_t* stg = smem + (k % STAGES) * L::STAGE;
+      if (valid) {
 #pragma unroll
         for (int c = 0; c < D / 16; ++c) {
           float f[16];
 #pragma unroll
           for (int u = 0; u < 16; ++u) f[u] = __uint_as_float(ro[c][u]) * inv_l;
-          *reinterpret_cast<uint4*>(orow + c * 16) =
-              make_uint4(wpack2(f[0], f[1]), wpack2(f[2], f[3]), wpack2(f[4], f[5]), wpack2(f[6], f[7]));
-          *reinterpret_cast<uint4*>(orow + c * 16 + 8) =
-              make_uint4(wpack2(f[8], f[9]), wpack2(f[10], f[11]), wpack2(f[12], f[13]), wpack2(f[14], f[15]));
+          uint4* dst = reinterpret_cast<uint4*>(stg + n * (D * 2) + c * 32);
+          dst[0] = make_uint4(wpack2(f[0], f[1]), wpack2(f[2], f[3]), wpack2(f[4], f[5]), wpack2(f[6], f[7]));
+          dst[1] = make_uint4(wpack2(f[8], f[9]), wpack2(f[10], f[11]), wpack2(f[12], f[13]), wpack2(f[14], f[15]));
         }
       }
-
+      fence_proxy_async_smem();
+      mbar_arrive_warp(out_ready);                               // all eight softmax warps arrive
+      if (warp == 2 && lane == 0 && mbar_wait(out_ready, par, abort_flag, p.status, 8)) {
+        int cx = 0, cy = 0, cz = 0, cw = it;
+        if (p.qkv_fused) {
+          const int w = it / p.H, h = it - w * p.H;
+          const int ww = p.nw * p.nw;
+          const int b = w / ww, wi = w - b * ww;
+          const int wy = wi / p.nw, wx = wi - wy * p.nw;
+          cx = h * D; cy = wx * WS; cz = wy * WS; cw = b;
+        }
+        tma_store_4d(&tmO, stg, cx, cy, cz, cw);
+        tma_store_commit();
+        tma_store_wait_read<0>();                                // the staging rows have been read
+        mbar_arrive(&empty[k % STAGES]);
+      }
     }
   }
 
+  if (warp == 2 && lane == 0) tma_store_wait_all<0>();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -393,13 +402,30 @@ int launch_window(const void* q, const void* k, const void* v, long long rows, l
   if (int e = make_tensor_map(&tmV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(v), dims, strides, box_kv,
                               CU_TENSOR_MAP_SWIZZLE_32B))
     return e;
+  CUtensorMap tmO;
+  {
+    const uint64_t pitch = uint64_t(p.o_pitch) * 2;
+    uint64_t dims[4], strides[4];
+    if (p.qkv_fused) {   // o[b][y][x][channels]
+      const uint64_t g = uint64_t(p.grid);
+      dims[0] = uint64_t(p.H) * D; dims[1] = g; dims[2] = g; dims[3] = uint64_t(items / p.H) / (uint64_t(p.nw) * p.nw);
+      strides[0] = 2; strides[1] = pitch; strides[2] = g * pitch; strides[3] = g * g * pitch;
+    } else {             // o[item][WS][WS][D]
+      dims[0] = D; dims[1] = WS; dims[2] = WS; dims[3] = uint64_t(items);
+      strides[0] = 2; strides[1] = pitch; strides[2] = WS * pitch; strides[3] = uint64_t(WS) * WS * pitch;
+    }
+    const uint32_t box[4] = {uint32_t(D), uint32_t(WS), uint32_t(WS), 1};
+    if (int e = make_tensor_map(&tmO, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, p.o, dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_NONE))
+      return e;
+  }
   auto kern = attn_window_kernel<D, WS>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES) != cudaSuccess)
     return SAMB_E_LAUNCH;
   if (items > 0x7fffffffLL) return SAMB_E_SHAPE;
   p.items = int(items);
   const long long grid = items < sm_count() ? items : sm_count();
-  kern<<<unsigned(grid), NUM_THREADS, L::BYTES, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, p);
+  kern<<<unsigned(grid), NUM_THREADS, L::BYTES, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmO, p);
   return launch_status();
 }
 
