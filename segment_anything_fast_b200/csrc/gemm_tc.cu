@@ -47,6 +47,8 @@ struct GemmParams {
   int a_col_stride;              // batch b reads A columns [b*a_col_stride, +K)
   int o_col_stride;              // and writes out columns [b*o_col_stride, +N)
   int a_row_stride;              // batch b reads A rows [b*a_row_stride + m, ...) (head-major operand planes)
+  int tg, tg_bn;                 // tg > 1: a tile is tg independent products of tg_bn columns each (consecutive
+                                 // batches sharing W), so narrow batched outputs still fill a 256-column tile
   int hm_group;                  // > 0: head-major output, hm_group 16-column pieces per head (see launch_gemm)
   int epilogue;
 };
@@ -148,12 +150,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int m0 = int(tb / p.tiles_n) * BM;
         const int n0 = int(tb % p.tiles_n) * p.bn;
         const int a_col0 = bt * p.a_col_stride;
-        for (int ks = 0; ks < p.k_slabs; ++ks) {
+        for (int gk = 0; gk < p.tg * p.k_slabs; ++gk) {
+          const int g = gk / p.k_slabs, ks = gk - g * p.k_slabs;       // product inside the tile, K slab
           if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 1))) break;
           uint8_t* sa = smem + stage * STAGE_BYTES;
-          mbar_expect_tx(&full_bar[stage], A_STAGE_BYTES + p.bn * SLAB_BYTES);
-          tma_load_2d(sa, &tmA, &full_bar[stage], a_col0 + ks * slab_elems, m0 + bt * p.a_row_stride);
-          tma_load_2d(sa + A_STAGE_BYTES, &tmB, &full_bar[stage], ks * slab_elems, n0);
+          mbar_expect_tx(&full_bar[stage], A_STAGE_BYTES + p.tg_bn * SLAB_BYTES);
+          tma_load_2d(sa, &tmA, &full_bar[stage], a_col0 + ks * slab_elems, m0 + (bt * p.tg + g) * p.a_row_stride);
+          tma_load_2d(sa + A_STAGE_BYTES, &tmB, &full_bar[stage], ks * slab_elems, p.tg > 1 ? 0 : n0);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -162,8 +165,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ------------------------------------------------------------------ MMA issuer
     // The whole warp walks the loop (warp-uniform waits and descriptors); one elected lane issues.
     {
-      const uint32_t idesc = kInt8 ? make_idesc(kAccS32, kFmtS8, kFmtS8, BM, p.bn)
-                                   : make_idesc(kAccF32, kFmtBF16, kFmtBF16, BM, p.bn);
+      const uint32_t idesc = kInt8 ? make_idesc(kAccS32, kFmtS8, kFmtS8, BM, p.tg_bn)
+                                   : make_idesc(kAccF32, kFmtBF16, kFmtBF16, BM, p.tg_bn);
       // K-major, 128B swizzle: 8-row groups 1024 B apart; the start address moves in 16-byte units.
       const uint64_t desc0 = make_smem_desc(smem_u32(smem), 16, 1024, kSwizzle128B);
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
@@ -171,8 +174,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (long long tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
         if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, 2))) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int ks = 0; ks < p.k_slabs; ++ks) {
+        for (int gk = 0; gk < p.tg * p.k_slabs; ++gk) {
+          const int g = gk / p.k_slabs, ks = gk - g * p.k_slabs;
+          const uint32_t d_tmem = tmem_base + acc * BN + g * p.tg_bn;
           if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3))) break;
           tc_fence_after();
           if (elect_one()) {
@@ -217,7 +221,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // per-column vectors of this tile; the barrier inside epi_all() publishes them
         const int n = n0 + et;
         if (kBias) s_bias[et] = n < p.N ? __ldg(p.bias + n) : 0.f;
-        if (kColScale) s_wscale[et] = n < p.N ? __ldg(p.w_scale + n) : 0.f;
+        if (kColScale) {
+          const int ns = p.tg > 1 ? et % p.tg_bn : n;       // grouped tiles: every product uses the same W rows
+          s_wscale[et] = ns < p.N ? __ldg(p.w_scale + ns) : 0.f;
+        }
       }
       const bool got = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, 4);
       if (!epi_all(got)) break;
@@ -308,7 +315,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           epi_sync();
           if (et == 0) {
             if (p.hm_group == 0) {
-              tma_store_2d(&tmOut, stage_out, bt * p.o_col_stride + col0, m0);  // clipped at M and at the row end
+              tma_store_2d(&tmOut, stage_out, bt * p.tg * p.o_col_stride + col0, m0);  // clipped at M and at the row end
             } else {
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
@@ -407,7 +414,7 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
   {
     const uint64_t dims[2] = {uint64_t(K), uint64_t(N)};
     const uint64_t strides[2] = {uint64_t(esz), uint64_t(ldw) * esz};
-    const uint32_t box[2] = {slab_elems, uint32_t(N <= 64 ? 64 : (N <= 128 ? 128 : BN))};
+    const uint32_t box[2] = {slab_elems, uint32_t(N <= 64 ? 64 : (N <= 128 ? 128 : BN))};   // == tg_bn
     if (int e = make_tensor_map(&tmB, dt, 2, const_cast<void*>(W), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
       return e;
   }
@@ -428,9 +435,16 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
   p.k_slabs = (K * esz + SLAB_BYTES - 1) / SLAB_BYTES;
   p.last_ksteps = (K * esz - (p.k_slabs - 1) * SLAB_BYTES + 31) / 32;
   p.bn = N <= 64 ? 64 : (N <= 128 ? 128 : BN);
-  p.tiles_n = (N + p.bn - 1) / p.bn;
+  p.tg = 1;
+  p.tg_bn = p.bn;
+  if (batch > 1 && a_row_stride && N == 64 && o_col_stride == N && epilogue == EPI_COLSCALE) {
+    p.tg = batch % 4 == 0 ? 4 : (batch % 2 == 0 ? 2 : 1);        // tg narrow products share one tile
+    p.bn = p.tg * N;
+  }
+  p.tiles_n = p.tg > 1 ? 1 : (N + p.bn - 1) / p.bn;
+  if (p.tg > 1) p.N = p.tg * N;                                  // logical width of a grouped tile
   p.tiles_per_batch = ((M + BM - 1) / BM) * p.tiles_n;
-  p.num_tiles = p.tiles_per_batch * batch;
+  p.num_tiles = p.tiles_per_batch * (batch / p.tg);
   p.a_col_stride = a_col_stride;
   p.o_col_stride = o_col_stride;
   p.a_row_stride = int(a_row_stride);
