@@ -8,3 +8,4 @@ from .build_sam import (build_image_encoder_vit_b, build_image_encoder_vit_h, bu
                         sam_model_registry)
 from .image_encoder import ImageEncoderViT  # noqa: F401
 from .runtime import EncoderSession  # noqa: F401
+from .sparse import apply_fake_sparsity, apply_sparse  # noqa: F401

@@ -92,3 +92,39 @@ def test_cpu_input_is_rejected(cuda):
     enc = build_encoder(TINY, sd)
     with pytest.raises(RuntimeError):
         enc(torch.zeros(1, 3, 1024, 1024))
+
+
+def _pruned_state_dict(sd, mlp_only):
+    from oracle import quant_oracle as qo
+    out = {}
+    for k, v in sd.items():
+        is_lin = v.dim() == 2 and k.endswith(".weight") and (".attn.qkv" in k or ".attn.proj" in k or ".mlp.lin" in k)
+        if is_lin and (not mlp_only or ".mlp.lin" in k):
+            v = v * qo.prune_2_4_mask(v).to(v.dtype)
+        out[k] = v
+    return out
+
+
+@pytest.mark.parametrize("mlp_only,quant", [(False, None), (True, "int8")])
+def test_tiny_encoder_sparse24(cuda, mlp_only, quant):
+    """apply_sparse prunes the same entries as the oracle's 2:4 mask; the pruned encoder matches the
+    oracle run on the pruned weights (bf16 tolerance; int8 adds its quantisation error)."""
+    from segment_anything_fast_b200.sparse import apply_sparse
+    sd = eo.seeded_state_dict(TINY, seed=1)
+    x = eo.seeded_images(1, seed=2)
+    enc = build_encoder(TINY, sd, quant=quant)
+    dense = enc(x.to(torch.bfloat16).cuda()).float().cpu()
+    apply_sparse(enc, mlp_only=mlp_only)
+    sd_bf16 = {k: v.to(torch.bfloat16).float() if v.is_floating_point() else v for k, v in sd.items()}
+    ref_sd = _pruned_state_dict(sd_bf16, mlp_only)
+    for k, v in enc.state_dict().items():
+        if k.endswith("lin1.weight") or (not mlp_only and k.endswith("qkv.weight")):
+            assert torch.equal(v.float().cpu() != 0, ref_sd[k] != 0), k
+            assert ((v != 0).reshape(v.shape[0], -1, 4).sum(-1) <= 2).all()
+    out = enc(x.to(torch.bfloat16).cuda()).float().cpu()       # weights changed in place: repacked
+    cuda.check_status()
+    ref = eo.image_encoder_forward(x, ref_sd, TINY, "fp32")
+    print(f"sparse mlp_only={mlp_only} quant={quant}: cos vs pruned oracle {_cos(out, ref):.6f}, "
+          f"cos vs dense output {_cos(out, dense):.6f}")
+    assert _cos(out, ref) > (0.995 if quant else 0.999)
+    assert _cos(out, dense) < _cos(out, ref)                    # the pruning really took effect

@@ -65,3 +65,21 @@ def test_quant_mode_validation():
     with pytest.raises(ValueError):
         enc.set_quant("fp4")
     assert enc.set_quant("int8").quant == "int8"
+
+
+def test_sparse_prune_matches_reference_sparsifier(golden_dir):
+    """The package's 2:4 pruning keeps exactly what the reference's sparsifier flow kept (golden masks
+    made by running the reference's apply_fake_sparsity)."""
+    import numpy as np
+    import os
+    from segment_anything_fast_b200.sparse import apply_sparse, prune_2_4_
+    g = np.load(os.path.join(golden_dir, "sparse24_mask.npz"))
+    for i in (0, 1):
+        w = torch.from_numpy(g[f"w{i}"]).clone()
+        keep = prune_2_4_(w)
+        assert torch.equal(keep, torch.from_numpy(g[f"keep{i}"]))
+        assert torch.equal(w != 0, keep)
+    m = torch.nn.Sequential(torch.nn.Linear(16, 8), torch.nn.ReLU(), torch.nn.Linear(8, 4))
+    apply_sparse(m)
+    for lin in (m[0], m[2]):
+        assert ((lin.weight != 0).reshape(lin.weight.shape[0], -1, 4).sum(-1) <= 2).all()
