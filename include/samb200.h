@@ -33,7 +33,8 @@ enum {
   SAMB_E_ALIGN = -3,   /* pointer or stride not 16-byte aligned */
   SAMB_E_ARCH = -4,    /* current device is not sm_100 */
   SAMB_E_LAUNCH = -5,  /* CUDA reported an error at launch or tensor-map creation */
-  SAMB_E_TIMEOUT = -6  /* reported by samb_decode_status for a device-side bounded-wait expiry */
+  SAMB_E_TIMEOUT = -6, /* reported by samb_decode_status for a device-side bounded-wait expiry */
+  SAMB_E_NOT24 = -7    /* reported by samb_decode_status: samb_pack_sp24 met a group of four with > 2 non-zeros */
 };
 
 /* GEMM epilogues (bit flags) */
@@ -46,7 +47,7 @@ enum {
 
 int samb_abi_version(void);
 const char* samb_error_string(int code);
-/* Host helper: maps a status word read back from the device to SAMB_OK / SAMB_E_TIMEOUT. */
+/* Host helper: maps a status word read back from the device to SAMB_OK / SAMB_E_TIMEOUT / SAMB_E_NOT24. */
 int samb_decode_status(int32_t status_word);
 /* Waits (bounded, ~`limit_polls` polls) on a barrier that nothing signals; the kernel must come
  * back with the timeout code in *status.  Exercises the give-up path without faulting anything. */
@@ -156,6 +157,27 @@ int samb_gemm_bf16_heads(const void* A, int64_t lda, const void* W, int64_t ldw,
 int samb_gemm_i8_heads(const int8_t* Aq, int64_t lda, const float* a_scale, const int8_t* Wq, int64_t ldw,
                        const float* w_scale, const float* bias, void* out, int64_t M, int N, int K, int head_dim,
                        int32_t* status, void* stream);
+
+/* 2:4 semi-structured sparse int8 weights on the sparse tensor-core path (tcgen05.mma.sp).
+ * ref: apply_sparse / to_sparse_semi_structured, segment_anything_fast/sparse.py:28-32 (the reference
+ * compresses every nn.Linear weight and lets torch's cuSPARSELt/CUTLASS sparse matmul run it); the
+ * int8 + 2:4 combination for mlp.lin1 / mlp.lin2 is the one experiments/eval_combo.py:374-376 names.
+ *
+ * samb_pack_sp24: Wq[N, K] int8 row-major with at most two non-zeros in every aligned group of four
+ * along K (K % 32 == 0) -> Wc[N, K/2] int8 (the kept entries in order; ldc % 16 == 0) and `meta`
+ * (samb_sp24_meta_bytes(N, K) bytes, 16-byte aligned): the 2-bit positions of the kept entries, tiled
+ * for the kernel ([ceil(N/128)][ceil(K/128)][128 rows][16 bytes]).  A group with more than two
+ * non-zeros sets *status (samb_decode_status -> SAMB_E_NOT24).
+ * samb_gemm_i8_sp24: out[T, N] = epilogue((Xq[T, K] . Wsparse[N, K]^T) * x_scale[t] * w_scale[n]) with
+ * the epilogue flags, residual broadcast and SAMB_EPI_RAW (int32 out) of samb_gemm_i8.  The int32
+ * accumulators equal those of the dense product with the uncompressed Wq bit for bit. */
+int64_t samb_sp24_meta_bytes(int N, int K);
+int samb_pack_sp24(const int8_t* Wq, int64_t ldw, int N, int K, int8_t* Wc, int64_t ldc, uint8_t* meta,
+                   int32_t* status, void* stream);
+int samb_gemm_i8_sp24(const int8_t* Xq, int64_t ldx, const float* x_scale, const int8_t* Wc, int64_t ldc,
+                      const uint8_t* meta, const float* w_scale, const float* bias, const void* residual,
+                      int64_t ldr, int64_t res_rows, void* out, int64_t ldo, int64_t T, int N, int K, int epilogue,
+                      int32_t* status, void* stream);
 
 /* Products of every head's queries with the relative-position tables, for the *_qkv attention
  * entry points:  tab[t, h*t_head_stride + m] = (q_planes[h][t, :] . tables[m, :]) * col_scale[m]

@@ -17,6 +17,7 @@ namespace samb {
 // with atomicCAS(status, 0, code), so the first failure is kept.
 // ----------------------------------------------------------------------------------------------
 constexpr uint32_t kDevTimeout = 0x7Eu;
+constexpr uint32_t kDevNot24 = 0x7Du;     // status-word tag: a weight group of four held more than two non-zeros
 
 // Poll budget of one wait: ~4 M polls, the late ones 64 ns apart => a fraction of a second.
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -217,6 +218,23 @@ __device__ __forceinline__ void umma_i8_ss(uint32_t d_tmem, uint64_t a_desc, uin
       : "memory");
 }
 
+// kind::i8 with a 2:4-sparse A operand: A in shared memory holds the kept half of every group of four
+// K elements; the 4-bit position codes (one bit per logical K element, 64 bits per row per MMA of
+// logical K = 64) sit in tensor memory at e_tmem, row r of A in lane r.
+__device__ __forceinline__ void umma_i8_sp_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t e_tmem,
+                                              uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.sp.cta_group::1.kind::i8 [%0], %1, %2, [%3], %4, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(e_tmem), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Shared memory -> tensor memory, 128 lanes x 128 bits (4 columns); ordered with the MMAs that the
+// same thread issues after it.
+__device__ __forceinline__ void tmem_cp_128x128b(uint32_t taddr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.128x128b [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp gets TMEM lane (base lane + t).
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -274,6 +292,26 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t acc_fmt, uint32_t a_f
                                                   bool a_mn_major = false, bool b_mn_major = false) {
   return (acc_fmt << 4) | (a_fmt << 7) | (b_fmt << 10) | (uint32_t(a_mn_major) << 15) |
          (uint32_t(b_mn_major) << 16) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
+}
+
+// Exact-form GELU 0.5 x (1 + erf(x / sqrt 2)) with erf from the Abramowitz-Stegun 7.1.26 rational
+// approximation (|error| < 1.5e-7, far below the bf16 output rounding): one rcp, one ex2, five FMAs.
+__device__ __forceinline__ float gelu_erf(float x) {
+  const float z = fabsf(x) * 0.70710678118654752f;
+  float t, e;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, z, 1.0f)));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-z * z * 1.4426950408889634f));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  const float erf_abs = fmaf(-poly * t, e, 1.0f);
+  return 0.5f * x * (1.0f + copysignf(erf_abs, x));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
 }
 
 __device__ __forceinline__ bool elect_one() {

@@ -1,0 +1,409 @@
+// int8 GEMM with a 2:4-sparse weight on the sparse tensor-core path:
+//   out[T, N] = epilogue( Xq[T, K] * Wsparse[N, K]^T )
+// tcgen05.mma.sp takes the sparse matrix as its A operand, so the roles are swapped with respect to
+// the dense kernel: a tile is 128 output channels (MMA M, rows of the compressed weight) by 224
+// tokens (MMA N, rows of the activation), and the accumulator holds the tile transposed (TMEM lane =
+// channel, column = token).  Per 128 logical K the producer warp brings in 64 compressed weight bytes
+// per channel (64B swizzle), 128 activation bytes per token (128B swizzle) and 16 bytes of position
+// codes per channel; the MMA warp copies the codes to tensor memory (tcgen05.cp) and issues two MMAs
+// of logical K = 64; eight epilogue warps drain the other accumulator through a token-major staging
+// tile and two TMA stores.
+#include "common.cuh"
+
+namespace samb {
+
+namespace {
+
+constexpr int TC = 128;                        // channels per tile
+constexpr int TT = 224;                        // tokens per tile: 2 accumulators + code ring fit 512 columns
+constexpr int KB = 128;                        // logical K per stage
+constexpr int A_BYTES = TC * KB / 2;           // 8 KiB
+constexpr int B_BYTES = TT * KB;               // 28 KiB
+constexpr int E_BYTES = TC * 16;               // 2 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES + E_BYTES;   // 38 KiB, a multiple of 1024
+constexpr int STAGES = 4;
+constexpr int OUT_HALF_BYTES = TT * 128;       // 64 channels of every token row, 128B-swizzled
+constexpr int OUT_BYTES = 2 * OUT_HALF_BYTES;
+constexpr int NUM_ACC = 2;
+constexpr int E_COL = NUM_ACC * TT;            // 448: first column of the code ring (4 columns per stage)
+constexpr int TMEM_COLS = 512;
+constexpr int NUM_THREADS = 320;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_BYTES + TT * 4 + 1024 + 256;
+
+struct SpParams {
+  void* out;
+  const float* bias;
+  const __nv_bfloat16* residual;
+  const float* a_scale;
+  const float* w_scale;
+  int* status;
+  long long T;                  // tokens
+  long long ldo, ldr, res_rows;
+  int N, K;
+  int k_blocks;
+  int tiles_c;
+  long long num_tiles;
+};
+
+__device__ __forceinline__ bool epi_all(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.and.pred p, 1, 256, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"(uint32_t(pred))
+      : "memory");
+  return r != 0;
+}
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+template <int kEpi>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                 const __grid_constant__ CUtensorMap tmE, const __grid_constant__ CUtensorMap tmOut,
+                 const SpParams p) {
+  constexpr bool kRaw = (kEpi & SAMB_EPI_RAW) != 0;
+  constexpr bool kBias = (kEpi & SAMB_EPI_BIAS) != 0;
+  constexpr bool kGelu = (kEpi & SAMB_EPI_GELU) != 0;
+  constexpr bool kRes = (kEpi & SAMB_EPI_RESIDUAL) != 0;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage_out = smem + STAGES * STAGE_BYTES;
+  float* s_tok = reinterpret_cast<float*>(stage_out + OUT_BYTES);          // [224] per-token scales
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_tok + TT);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;
+  uint64_t* acc_empty = acc_full + NUM_ACC;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + NUM_ACC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < NUM_ACC; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 8);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+    tma_prefetch_desc(&tmE);
+    if (!kRaw) tma_prefetch_desc(&tmOut);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (long long tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        const int ct = int(tile % p.tiles_c);
+        const int t0 = int(tile / p.tiles_c) * TT;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 1))) break;
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          tma_load_2d(sa, &tmW, &full_bar[stage], kb * (KB / 2), ct * TC);
+          tma_load_2d(sa + A_BYTES, &tmX, &full_bar[stage], kb * KB, t0);
+          tma_load_2d(sa + A_BYTES + B_BYTES, &tmE, &full_bar[stage], 0, (ct * p.k_blocks + kb) * TC);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    const uint32_t idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, TC, TT) | (1u << 2);   // bit 2: sparse A
+    const uint64_t adesc0 = make_smem_desc(smem_u32(smem), 16, 512, kSwizzle64B);
+    const uint64_t bdesc0 = make_smem_desc(smem_u32(smem) + A_BYTES, 16, 1024, kSwizzle128B);
+    const uint64_t edesc0 = make_smem_desc(smem_u32(smem) + A_BYTES + B_BYTES, 128, 128, kSwizzleNone);
+    uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+    bool ok = true;
+    for (long long tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, 2))) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * TT;
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3))) break;
+        tc_fence_after();
+        if (elect_one()) {
+          const uint32_t e_tmem = tmem_base + E_COL + stage * 4;
+          tmem_cp_128x128b(e_tmem, edesc0 + stage * (STAGE_BYTES / 16));
+#pragma unroll
+          for (int k2 = 0; k2 < 2; ++k2)            // logical K 64: 32 compressed bytes of A, 64 bytes of X
+            umma_i8_sp_ss(d_tmem, adesc0 + stage * (STAGE_BYTES / 16) + k2 * 2,
+                          bdesc0 + stage * (STAGE_BYTES / 16) + k2 * 4, e_tmem + k2 * 2, idesc,
+                          (kb | k2) != 0 ? 1u : 0u);
+          tc_commit(&empty_bar[stage]);
+        }
+        __syncwarp();
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+      if (!ok) break;
+      if (elect_one()) tc_commit(&acc_full[acc]);
+      __syncwarp();
+      if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    // Thread = one channel of the tile (TMEM lane); two warps share a lane quarter and split the
+    // token columns: the first takes tokens 0..127, the second 128..223.
+    const uint32_t lane_base = uint32_t(warp & 3) * 32u;
+    const int half = (warp - 2) >> 2;
+    const int ch = int(lane_base) + lane;                  // channel inside the tile
+    const int et = int(threadIdx.x) - 64;                  // 0..255
+    const int tok_begin = half * 128;
+    const int n_chunks = half == 0 ? 4 : 3;                // 32-token chunks
+    uint32_t acc = 0, acc_phase = 0;
+    for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+      const int ct = int(tile % p.tiles_c);
+      const long long t0 = (tile / p.tiles_c) * TT;
+      const int n = ct * TC + ch;
+      const bool ch_ok = n < p.N;
+      if (!kRaw && et < TT) s_tok[et] = t0 + et < p.T ? __ldg(p.a_scale + t0 + et) : 0.f;
+      float w_scale = 0.f, bias = 0.f;
+      if (!kRaw && ch_ok) {
+        w_scale = __ldg(p.w_scale + n);
+        if (kBias) bias = __ldg(p.bias + n);
+      }
+      const bool got = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, 4);
+      if (!epi_all(got)) break;                            // also publishes s_tok
+      tc_fence_after();
+      if (!kRaw) {
+        if (et == 0) tma_store_wait_read<0>();             // the previous tile's stores have read the staging tile
+        epi_sync();
+      }
+      const uint32_t t_addr = tmem_base + (lane_base << 16) + acc * TT + tok_begin;
+      // staging: [channel half][token][64 channels] bf16, 128-byte rows, 16-byte units XOR (token & 7)
+      uint8_t* s_half = stage_out + (ch >> 6) * OUT_HALF_BYTES;
+      const int unit = (ch & 63) >> 3, sub = (ch & 7) * 2;
+#pragma unroll 1
+      for (int c = 0; c < n_chunks; ++c) {
+        const int tk0 = tok_begin + c * 32;                // first token of the chunk inside the tile
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_addr + c * 32, r);
+        tmem_ld_wait();
+        if (kRaw) {
+          if (ch_ok) {
+            int32_t* o = reinterpret_cast<int32_t*>(p.out) + n;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (t0 + tk0 + j < p.T) o[(t0 + tk0 + j) * p.ldo] = int32_t(r[j]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int tk = tk0 + j;
+            float x = __fmul_rn(__fmul_rn(float(int(r[j])), s_tok[tk]), w_scale);
+            if (kBias) x = __fadd_rn(x, bias);
+            if (kGelu) x = gelu_erf(x);
+            if (kRes) {
+              const long long tr = t0 + tk;
+              if (ch_ok && tr < p.T) x += __bfloat162float(p.residual[(tr % p.res_rows) * p.ldr + n]);
+            }
+            *reinterpret_cast<__nv_bfloat16*>(s_half + tk * 128 + ((unit ^ (tk & 7)) << 4) + sub) = __float2bfloat16_rn(x);
+          }
+        }
+      }
+      if (!kRaw) {
+        fence_proxy_async_smem();
+        epi_sync();
+        if (et == 0) {
+          tma_store_2d(&tmOut, stage_out, ct * TC, int(t0));                       // clipped at T and N
+          if (ct * TC + 64 < p.N) tma_store_2d(&tmOut, stage_out + OUT_HALF_BYTES, ct * TC + 64, int(t0));
+          tma_store_commit();
+        }
+      }
+      tc_fence_before();
+      mbar_arrive_warp(&acc_empty[acc]);
+      if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
+    }
+    if (!kRaw && et == 0) tma_store_wait_all<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// One thread per (weight row, block of 128 logical K): keeps the non-zero entries of every group of
+// four (padding with the lowest unused positions when fewer than two are non-zero), writes the 64 kept
+// bytes and the 16 bytes of position codes (group g of the block in bits 4g..4g+3: first kept position
+// in the low two bits, second in the high two).  Rows and K beyond the matrix get the code 0x4.
+__global__ void pack_sp24_kernel(const int8_t* __restrict__ W, long long ldw, int N, int K, int8_t* __restrict__ Wc,
+                                 long long ldc, uint8_t* __restrict__ meta, int k_blocks, int rows_padded,
+                                 int* status) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)rows_padded * k_blocks) return;
+  const int row = int(idx / k_blocks), kb = int(idx % k_blocks);
+  uint8_t* mrow = meta + (((long long)(row / TC) * k_blocks + kb) * TC + row % TC) * 16;
+  bool bad = false;
+  for (int b = 0; b < 16; ++b) {
+    uint32_t code = 0;
+    for (int h = 0; h < 2; ++h) {
+      const int k = kb * KB + (b * 2 + h) * 4;
+      uint32_t nib = 0x4;                         // positions 0 and 1
+      if (row < N && k < K) {
+        int8_t v[4];
+        *reinterpret_cast<uint32_t*>(v) = *reinterpret_cast<const uint32_t*>(W + row * ldw + k);
+        int pos[2], cnt = 0, nz = 0;
+        for (int i = 0; i < 4; ++i) nz += v[i] != 0;
+        bad |= nz > 2;
+        for (int i = 0; i < 4 && cnt < 2; ++i)
+          if (v[i] != 0) pos[cnt++] = i;
+        for (int i = 0; i < 4 && cnt < 2; ++i) {  // fewer than two non-zeros: fill with unused zeros
+          bool used = false;
+          for (int j = 0; j < cnt; ++j) used |= pos[j] == i;
+          if (!used && v[i] == 0) pos[cnt++] = i;
+        }
+        if (pos[0] > pos[1]) { const int t = pos[0]; pos[0] = pos[1]; pos[1] = t; }
+        nib = uint32_t(pos[0]) | (uint32_t(pos[1]) << 2);
+        int8_t* o = Wc + row * ldc + k / 2;
+        o[0] = v[pos[0]];
+        o[1] = v[pos[1]];
+      }
+      code |= nib << (4 * h);
+    }
+    mrow[b] = uint8_t(code);
+  }
+  if (bad) atomicCAS(status, 0, int((kDevNot24 << 24) | (uint32_t(row) & 0xFFFFFFu)));
+}
+
+using SpKernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const SpParams);
+
+SpKernelFn pick_sp_kernel(int epi) {
+  switch (epi) {
+    case 0: return gemm_sp24_kernel<0>;
+    case 1: return gemm_sp24_kernel<1>;
+    case 2: return gemm_sp24_kernel<2>;
+    case 3: return gemm_sp24_kernel<3>;
+    case 4: return gemm_sp24_kernel<4>;
+    case 5: return gemm_sp24_kernel<5>;
+    case 6: return gemm_sp24_kernel<6>;
+    case 7: return gemm_sp24_kernel<7>;
+    default: return gemm_sp24_kernel<SAMB_EPI_RAW>;
+  }
+}
+
+}  // namespace
+}  // namespace samb
+
+extern "C" {
+
+int64_t samb_sp24_meta_bytes(int N, int K) {
+  if (N <= 0 || K <= 0) return 0;
+  const int64_t tiles_c = (N + samb::TC - 1) / samb::TC, k_blocks = (K + samb::KB - 1) / samb::KB;
+  return tiles_c * k_blocks * samb::TC * 16;
+}
+
+int samb_pack_sp24(const int8_t* Wq, int64_t ldw, int N, int K, int8_t* Wc, int64_t ldc, uint8_t* meta,
+                   int32_t* status, void* stream) {
+  if (Wq == nullptr || Wc == nullptr || meta == nullptr || status == nullptr) return SAMB_E_BADARG;
+  if (N <= 0 || K <= 0) return SAMB_E_BADARG;
+  if (K % 32 || ldw % 4 || ldw < K || ldc % 16 || ldc < K / 2) return SAMB_E_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(Wq) & 3u) || (reinterpret_cast<uintptr_t>(meta) & 15u)) return SAMB_E_ALIGN;
+  const int k_blocks = (K + samb::KB - 1) / samb::KB;
+  const int rows_padded = (N + samb::TC - 1) / samb::TC * samb::TC;
+  const long long threads = (long long)rows_padded * k_blocks;
+  samb::pack_sp24_kernel<<<unsigned((threads + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      Wq, ldw, N, K, Wc, ldc, meta, k_blocks, rows_padded, status);
+  return samb::launch_status();
+}
+
+int samb_gemm_i8_sp24(const int8_t* Xq, int64_t ldx, const float* x_scale, const int8_t* Wc, int64_t ldc,
+                      const uint8_t* meta, const float* w_scale, const float* bias, const void* residual,
+                      int64_t ldr, int64_t res_rows, void* out, int64_t ldo, int64_t T, int N, int K, int epilogue,
+                      int32_t* status, void* stream) {
+  using namespace samb;
+  if (Xq == nullptr || Wc == nullptr || meta == nullptr || out == nullptr || status == nullptr) return SAMB_E_BADARG;
+  if (T < 0 || N <= 0 || K <= 0) return SAMB_E_BADARG;
+  if (epilogue & ~(SAMB_EPI_BIAS | SAMB_EPI_GELU | SAMB_EPI_RESIDUAL | SAMB_EPI_RAW)) return SAMB_E_BADARG;
+  const bool raw = (epilogue & SAMB_EPI_RAW) != 0;
+  if (raw && epilogue != SAMB_EPI_RAW) return SAMB_E_BADARG;
+  if ((epilogue & SAMB_EPI_BIAS) && bias == nullptr) return SAMB_E_BADARG;
+  if ((epilogue & SAMB_EPI_RESIDUAL) && residual == nullptr) return SAMB_E_BADARG;
+  if (!raw && (x_scale == nullptr || w_scale == nullptr)) return SAMB_E_BADARG;
+  if (K % 32 || ldx % 16 || ldx < K || ldc % 16 || ldc < K / 2) return SAMB_E_SHAPE;
+  if (N % 8 || ldo < N || (!raw && ldo % 8)) return SAMB_E_SHAPE;
+  if ((epilogue & SAMB_EPI_RESIDUAL) && (ldr < N || res_rows <= 0)) return SAMB_E_SHAPE;
+  if (T > (int64_t(1) << 31) - TT) return SAMB_E_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(out) & 15u) || (reinterpret_cast<uintptr_t>(meta) & 15u)) return SAMB_E_ALIGN;
+  if (int e = check_device_arch()) return e;
+  if (T == 0) return SAMB_OK;
+
+  SpParams p;
+  p.out = out;
+  p.bias = bias;
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.a_scale = x_scale;
+  p.w_scale = w_scale;
+  p.status = status;
+  p.T = T;
+  p.ldo = ldo;
+  p.ldr = ldr;
+  p.res_rows = res_rows > 0 ? res_rows : 1;
+  p.N = N;
+  p.K = K;
+  p.k_blocks = (K + KB - 1) / KB;
+  p.tiles_c = (N + TC - 1) / TC;
+  p.num_tiles = ((T + TT - 1) / TT) * p.tiles_c;
+
+  CUtensorMap tmW, tmX, tmE, tmOut;
+  {
+    const uint64_t dims[2] = {uint64_t(K / 2), uint64_t(N)};
+    const uint64_t strides[2] = {1, uint64_t(ldc)};
+    const uint32_t box[2] = {uint32_t(KB / 2), uint32_t(TC)};
+    if (int e = make_tensor_map(&tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(Wc), dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_64B))
+      return e;
+  }
+  {
+    const uint64_t dims[2] = {uint64_t(K), uint64_t(T)};
+    const uint64_t strides[2] = {1, uint64_t(ldx)};
+    const uint32_t box[2] = {uint32_t(KB), uint32_t(TT)};
+    if (int e = make_tensor_map(&tmX, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(Xq), dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_128B))
+      return e;
+  }
+  {
+    const uint64_t dims[2] = {16, uint64_t(p.tiles_c) * p.k_blocks * TC};
+    const uint64_t strides[2] = {1, 16};
+    const uint32_t box[2] = {16, uint32_t(TC)};
+    if (int e = make_tensor_map(&tmE, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(meta), dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_NONE))
+      return e;
+  }
+  tmOut = tmX;
+  if (!raw) {
+    const uint64_t dims[2] = {uint64_t(N), uint64_t(T)};
+    const uint64_t strides[2] = {2, uint64_t(ldo) * 2};
+    const uint32_t box[2] = {64, uint32_t(TT)};
+    if (int e = make_tensor_map(&tmOut, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_128B))
+      return e;
+  }
+  auto kern = pick_sp_kernel(epilogue);
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    return SAMB_E_LAUNCH;
+  const long long grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  kern<<<dim3(unsigned(grid)), dim3(NUM_THREADS), SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tmW, tmX, tmE, tmOut, p);
+  return launch_status();
+}
+
+}  // extern "C"

@@ -53,26 +53,6 @@ struct GemmParams {
   int epilogue;
 };
 
-// Exact-form GELU 0.5 x (1 + erf(x / sqrt 2)) with erf from the Abramowitz-Stegun 7.1.26 rational
-// approximation (|error| < 1.5e-7, far below the bf16 output rounding): one rcp, one ex2, five FMAs.
-__device__ __forceinline__ float gelu_erf(float x) {
-  const float z = fabsf(x) * 0.70710678118654752f;
-  float t, e;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, z, 1.0f)));
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-z * z * 1.4426950408889634f));
-  float poly = fmaf(1.061405429f, t, -1.453152027f);
-  poly = fmaf(poly, t, 1.421413741f);
-  poly = fmaf(poly, t, -0.284496736f);
-  poly = fmaf(poly, t, 0.254829592f);
-  const float erf_abs = fmaf(-poly * t, e, 1.0f);
-  return 0.5f * x * (1.0f + copysignf(erf_abs, x));
-}
-
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-
 // Named barrier over the 256 epilogue threads that also AND-reduces a predicate, so that all of
 // them take the same decision to continue or to drain.
 __device__ __forceinline__ bool epi_all(bool pred) {

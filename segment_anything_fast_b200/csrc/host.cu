@@ -97,12 +97,14 @@ const char* samb_error_string(int code) {
     case SAMB_E_ARCH: return "device is not sm_100";
     case SAMB_E_LAUNCH: return "CUDA launch / tensor-map error";
     case SAMB_E_TIMEOUT: return "device-side bounded wait expired";
+    case SAMB_E_NOT24: return "weight is not 2:4 sparse (a group of four holds more than two non-zeros)";
     default: return "unknown error";
   }
 }
 
 int samb_decode_status(int32_t w) {
   if (w == 0) return SAMB_OK;
+  if ((uint32_t(w) >> 24) == samb::kDevNot24) return SAMB_E_NOT24;
   return ((uint32_t(w) >> 24) == samb::kDevTimeout) ? SAMB_E_TIMEOUT : SAMB_E_LAUNCH;
 }
 

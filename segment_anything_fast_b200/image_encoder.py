@@ -177,9 +177,15 @@ class ImageEncoderViT(nn.Module):
         pk["pe_b"] = _f32(pe.bias)
         pk["pos"] = _bf16(self.pos_embed.reshape(g * g, C)) if self.pos_embed is not None else None
 
-        def lin(m: nn.Linear):
+        def lin(m: nn.Linear, sparse_ok: bool = True):
             if self.quant == "int8":
                 q, s = quantize_rows_absmax(m.weight)
+                # a layer pruned by apply_sparse (2 of every 4 in-features zero) runs on the sparse
+                # tensor-core path; the check guards against weights edited after the pruning
+                if (sparse_ok and getattr(m, "_samb_sparse24", False) and q.shape[1] % 32 == 0
+                        and bool(((q != 0).reshape(q.shape[0], -1, 4).sum(-1) <= 2).all())):
+                    wc, meta = ops.pack_sp24(q)
+                    return {"wc": wc, "meta": meta, "ws": s, "b": _f32(m.bias)}
                 return {"wq": q, "ws": s, "b": _f32(m.bias)}
             return {"w": _bf16(m.weight), "b": _f32(m.bias)}
 
@@ -190,7 +196,7 @@ class ImageEncoderViT(nn.Module):
                 "window": blk.window_size,
                 "n1": (_f32(blk.norm1.weight), _f32(blk.norm1.bias), float(blk.norm1.eps)),
                 "n2": (_f32(blk.norm2.weight), _f32(blk.norm2.bias), float(blk.norm2.eps)),
-                "qkv": lin(blk.attn.qkv), "proj": lin(blk.attn.proj),
+                "qkv": lin(blk.attn.qkv, sparse_ok=False), "proj": lin(blk.attn.proj),
                 "lin1": lin(blk.mlp.lin1), "lin2": lin(blk.mlp.lin2),
                 "tab": tab, "tab_scale": cs, "T": T, "t_w_off": t_w_off,
             })
@@ -213,6 +219,8 @@ class ImageEncoderViT(nn.Module):
     # ------------------------------------------------------------------ forward
     def _linear(self, a, a_scale, w, residual=None, gelu=False, out=None):
         if self.quant == "int8":
+            if "wc" in w:
+                return ops.gemm_i8_sp24(a, a_scale, w["wc"], w["meta"], w["ws"], w["b"], residual, gelu=gelu, out=out)
             return ops.gemm_i8(a, a_scale, w["wq"], w["ws"], w["b"], residual, gelu=gelu, out=out)
         return ops.gemm_bf16(a, w["w"], w["b"], residual, gelu=gelu, out=out)
 

@@ -172,6 +172,54 @@ def gemm_i8(aq: torch.Tensor, a_scale: Optional[torch.Tensor], wq: torch.Tensor,
     return out
 
 
+def pack_sp24(wq: torch.Tensor):
+    """Compress a 2:4-sparse int8 weight ``wq [N, K]`` for ``gemm_i8_sp24``: returns ``(wc [N, K/2] int8,
+    meta uint8)``.  A group of four with more than two non-zeros is reported by ``check_status``."""
+    _need(wq, torch.int8, "wq")
+    wq = _rows2d(wq, "wq")
+    N, K = wq.shape
+    lib = _lib.load()
+    wc = torch.zeros(N, K // 2, dtype=torch.int8, device=wq.device)
+    meta = torch.empty(max(int(lib.samb_sp24_meta_bytes(N, K)), 16), dtype=torch.uint8, device=wq.device)
+    st = status_word(wq.device)
+    _lib.check(lib.samb_pack_sp24(wq.data_ptr(), wq.stride(0), N, K, wc.data_ptr(), wc.stride(0), meta.data_ptr(),
+                                  st.data_ptr(), _stream()), "samb_pack_sp24")
+    return wc, meta
+
+
+def gemm_i8_sp24(xq: torch.Tensor, x_scale: Optional[torch.Tensor], wc: torch.Tensor, meta: torch.Tensor,
+                 w_scale: Optional[torch.Tensor], bias: Optional[torch.Tensor] = None,
+                 residual: Optional[torch.Tensor] = None, gelu: bool = False, raw: bool = False,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``gemm_i8`` with the weight given as ``pack_sp24`` output (sparse tensor-core path)."""
+    _need(xq, torch.int8, "xq"); _need(wc, torch.int8, "wc"); _need(meta, torch.uint8, "meta")
+    xq, wc = _rows2d(xq, "xq"), _rows2d(wc, "wc")
+    T, K = xq.shape
+    N = wc.shape[0]
+    if wc.shape[1] * 2 != K:
+        raise RuntimeError("gemm_i8_sp24: inner dimensions differ")
+    epi = 0
+    if raw:
+        epi = EPI_RAW
+    else:
+        _need(x_scale, torch.float32, "x_scale"); _need(w_scale, torch.float32, "w_scale")
+        if bias is not None:
+            _need(bias, torch.float32, "bias"); epi |= EPI_BIAS
+        if gelu:
+            epi |= EPI_GELU
+        if residual is not None:
+            _need(residual, torch.bfloat16, "residual"); residual = _rows2d(residual, "residual"); epi |= EPI_RESIDUAL
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.int32 if raw else torch.bfloat16, device=xq.device)
+    st = status_word(xq.device)
+    _lib.check(_lib.load().samb_gemm_i8_sp24(
+        xq.data_ptr(), xq.stride(0), _ptr(x_scale), wc.data_ptr(), wc.stride(0), meta.data_ptr(), _ptr(w_scale),
+        _ptr(bias), _ptr(residual), residual.stride(0) if residual is not None else 0,
+        residual.shape[0] if residual is not None else 0, out.data_ptr(), out.stride(0), T, N, K, epi,
+        st.data_ptr(), _stream()), "samb_gemm_i8_sp24")
+    return out
+
+
 def layernorm2d(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, hw: int, eps: float = 1e-6,
                 to_nchw: bool = False) -> torch.Tensor:
     """Channel LayerNorm of token rows ``x [tokens, C]``; ``to_nchw`` stores ``[tokens/hw, C, hw]``."""

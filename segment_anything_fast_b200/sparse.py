@@ -5,9 +5,10 @@
 ``nn.Linear`` weight, the 2 entries of smallest magnitude: what the reference's
 ``WeightNormSparsifier(sparsity_level=1.0, sparse_block_shape=(1,4), zeros_per_block=2)`` flow leaves
 after ``squash_mask``.  ``apply_sparse(model)`` does the same and marks the layers as 2:4 so that the
-encoder can pick a sparse kernel for them; until a tcgen05 sparse-MMA kernel exists the pruned weights
-run through the dense tensor-core GEMMs, which is the identical arithmetic (a dense product with the
-masked weight) at dense speed.
+encoder can pick a sparse kernel for them: in int8 mode (``set_quant("int8")``) the marked ``attn.proj``,
+``mlp.lin1`` and ``mlp.lin2`` run compressed on the sparse tensor-core path (``samb_gemm_i8_sp24``); in
+bf16 mode, and for ``attn.qkv``, the pruned weights go through the dense GEMMs, which is the identical
+arithmetic (a dense product with the masked weight).
 """
 from typing import Callable, Optional
 
@@ -43,8 +44,4 @@ def apply_sparse(model: torch.nn.Module, mlp_only: bool = False):
     """The reference's ``apply_sparse``: prune all Linear layers (``mlp_only=True``: only ``mlp.lin1`` /
     ``mlp.lin2``, the combination the sparse + int8 benchmark configuration uses)."""
     f = (lambda n, m: ".mlp.lin" in n or n.startswith("mlp.lin")) if mlp_only else None
-    apply_fake_sparsity(model, f)
-    invalidate = getattr(model, "invalidate_packed", None)
-    if callable(invalidate):
-        invalidate()
-    return model
+    return apply_fake_sparsity(model, f)

@@ -196,3 +196,61 @@ def test_quant_rows_wide_and_narrow_bit_exact(ops, rows, C):
     q, s = ops.quant_rows_i8(x.cuda())
     q_ref, s_ref = qo.quantize_rows_absmax(x.float())
     assert torch.equal(q.cpu(), q_ref) and torch.equal(s.cpu(), s_ref)
+
+
+# ------------------------------------------------------------------ 2:4 sparse int8 GEMM
+def _sparse_weight(N, K, seed):
+    from oracle import quant_oracle as qo
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randn(N, K, generator=g)
+    keep = qo.prune_2_4_mask(w)
+    wq = (torch.randint(-127, 128, (N, K), generator=g) * keep).to(torch.int8)
+    return wq
+
+
+@pytest.mark.parametrize("T,N,K", [(300, 256, 256), (1000, 160, 160), (4096 + 17, 640, 1280), (224, 128, 32)])
+def test_gemm_i8_sp24_accumulators_bit_exact(ops, T, N, K):
+    """Sparse tensor-core path: int32 accumulators equal the dense integer product with the uncompressed
+    weight, bit for bit (token / channel / K tails included)."""
+    wq = _sparse_weight(N, K, 3)
+    g = torch.Generator().manual_seed(4)
+    xq = torch.randint(-127, 128, (T, K), generator=g, dtype=torch.int8)
+    wc, meta = ops.pack_sp24(wq.cuda())
+    acc = ops.gemm_i8_sp24(xq.cuda(), None, wc, meta, None, raw=True)
+    ops.check_status()
+    ref = (xq.double() @ wq.double().t()).to(torch.int32)          # exact: |sum| < 2^53
+    assert torch.equal(acc.cpu(), ref)
+
+
+def test_pack_sp24_round_trip_and_rejects_dense(ops):
+    """Decompressing (values, positions read back through an identity activation) restores the weight;
+    a weight that is not 2:4 sets the status word."""
+    N, K = 256, 384
+    wq = _sparse_weight(N, K, 5)
+    wc, meta = ops.pack_sp24(wq.cuda())
+    eye = torch.eye(K, dtype=torch.int8, device="cuda")
+    back = ops.gemm_i8_sp24(eye, None, wc, meta, None, raw=True).t()
+    ops.check_status()
+    assert torch.equal(back.cpu(), wq.int())
+    dense = torch.ones(128, 64, dtype=torch.int8, device="cuda")
+    ops.pack_sp24(dense)
+    with pytest.raises(RuntimeError, match="2:4"):
+        ops.check_status()
+
+
+@pytest.mark.parametrize("epi", ["bias", "gelu", "residual"])
+def test_gemm_i8_sp24_epilogues_match_dense_kernel(ops, epi):
+    """Same dequantising epilogue as the dense int8 kernel on the same (pruned) weight: bitwise equal."""
+    T, N, K = 1500, 320, 640
+    wq = _sparse_weight(N, K, 6).cuda()
+    g = torch.Generator().manual_seed(7)
+    xq = torch.randint(-127, 128, (T, K), generator=g, dtype=torch.int8).cuda()
+    sx = (torch.rand(T, generator=g) * 0.02 + 0.001).cuda()
+    sw = (torch.rand(N, generator=g) * 0.002 + 0.0001).cuda()
+    bias = torch.randn(N, generator=g).cuda()
+    res = torch.randn(T, N, generator=g).bfloat16().cuda() if epi == "residual" else None
+    wc, meta = ops.pack_sp24(wq)
+    a = ops.gemm_i8_sp24(xq, sx, wc, meta, sw, bias, res, gelu=epi == "gelu")
+    b = ops.gemm_i8(xq, sx, wq, sw, bias, res, gelu=epi == "gelu")
+    ops.check_status()
+    assert torch.equal(a, b)
