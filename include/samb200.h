@@ -169,8 +169,8 @@ int samb_gemm_i8_heads(const int8_t* Aq, int64_t lda, const float* a_scale, cons
  * for the kernel ([ceil(N/128)][ceil(K/128)][128 rows][16 bytes]).  A group with more than two
  * non-zeros sets *status (samb_decode_status -> SAMB_E_NOT24).
  * samb_gemm_i8_sp24: out[T, N] = epilogue((Xq[T, K] . Wsparse[N, K]^T) * x_scale[t] * w_scale[n]) with
- * the epilogue flags, residual broadcast and SAMB_EPI_RAW (int32 out) of samb_gemm_i8.  The int32
- * accumulators equal those of the dense product with the uncompressed Wq bit for bit. */
+ * the epilogue flags and SAMB_EPI_RAW (int32 out) of samb_gemm_i8; the residual is [T, N] (res_rows
+ * must equal T: no row broadcast; ldr % 8 == 0, 16-byte aligned base).  The int32 accumulators equal those of the dense product with the uncompressed Wq bit for bit. */
 int64_t samb_sp24_meta_bytes(int N, int K);
 int samb_pack_sp24(const int8_t* Wq, int64_t ldw, int N, int K, int8_t* Wc, int64_t ldc, uint8_t* meta,
                    int32_t* status, void* stream);

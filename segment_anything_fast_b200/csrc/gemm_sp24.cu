@@ -1,13 +1,14 @@
 // int8 GEMM with a 2:4-sparse weight on the sparse tensor-core path:
 //   out[T, N] = epilogue( Xq[T, K] * Wsparse[N, K]^T )
 // tcgen05.mma.sp takes the sparse matrix as its A operand, so the roles are swapped with respect to
-// the dense kernel: a tile is 128 output channels (MMA M, rows of the compressed weight) by 224
+// the dense kernel: a tile is 128 output channels (MMA M, rows of the compressed weight) by 208
 // tokens (MMA N, rows of the activation), and the accumulator holds the tile transposed (TMEM lane =
 // channel, column = token).  Per 128 logical K the producer warp brings in 64 compressed weight bytes
 // per channel (64B swizzle), 128 activation bytes per token (128B swizzle) and 16 bytes of position
 // codes per channel; the MMA warp copies the codes to tensor memory (tcgen05.cp) and issues two MMAs
-// of logical K = 64; eight epilogue warps drain the other accumulator through a token-major staging
-// tile and two TMA stores.
+// of logical K = 64; eight epilogue warps drain the other accumulator through one of two token-major
+// staging tiles (the residual, when there is one, is brought into the same tile by TMA beforehand)
+// and two TMA stores.
 #include "common.cuh"
 
 namespace samb {
@@ -15,20 +16,20 @@ namespace samb {
 namespace {
 
 constexpr int TC = 128;                        // channels per tile
-constexpr int TT = 224;                        // tokens per tile: 2 accumulators + code ring fit 512 columns
+constexpr int TT = 208;                        // tokens per tile: 2 accumulators + code ring fit 512 columns
 constexpr int KB = 128;                        // logical K per stage
 constexpr int A_BYTES = TC * KB / 2;           // 8 KiB
-constexpr int B_BYTES = TT * KB;               // 28 KiB
+constexpr int B_BYTES = TT * KB;               // 26 KiB
 constexpr int E_BYTES = TC * 16;               // 2 KiB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES + E_BYTES;   // 38 KiB, a multiple of 1024
-constexpr int STAGES = 4;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES + E_BYTES;   // 36 KiB, a multiple of 1024
+constexpr int STAGES = 3;
 constexpr int OUT_HALF_BYTES = TT * 128;       // 64 channels of every token row, 128B-swizzled
-constexpr int OUT_BYTES = 2 * OUT_HALF_BYTES;
+constexpr int OUT_BYTES = 2 * OUT_HALF_BYTES;   // one staging tile; there are two
 constexpr int NUM_ACC = 2;
-constexpr int E_COL = NUM_ACC * TT;            // 448: first column of the code ring (4 columns per stage)
+constexpr int E_COL = NUM_ACC * TT;            // 416: first column of the code ring (4 columns per stage)
 constexpr int TMEM_COLS = 512;
 constexpr int NUM_THREADS = 320;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_BYTES + TT * 4 + 1024 + 256;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * OUT_BYTES + TT * 4 + 1024 + 256;
 
 struct SpParams {
   void* out;
@@ -61,7 +62,7 @@ template <int kEpi>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                  const __grid_constant__ CUtensorMap tmE, const __grid_constant__ CUtensorMap tmOut,
-                 const SpParams p) {
+                 const __grid_constant__ CUtensorMap tmRes, const SpParams p) {
   constexpr bool kRaw = (kEpi & SAMB_EPI_RAW) != 0;
   constexpr bool kBias = (kEpi & SAMB_EPI_BIAS) != 0;
   constexpr bool kGelu = (kEpi & SAMB_EPI_GELU) != 0;
@@ -69,12 +70,13 @@ gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_out = smem + STAGES * STAGE_BYTES;
-  float* s_tok = reinterpret_cast<float*>(stage_out + OUT_BYTES);          // [224] per-token scales
+  float* s_tok = reinterpret_cast<float*>(stage_out + 2 * OUT_BYTES);      // [208] per-token scales
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_tok + TT);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* acc_full = empty_bar + STAGES;
   uint64_t* acc_empty = acc_full + NUM_ACC;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + NUM_ACC);
+  uint64_t* res_bar = acc_empty + NUM_ACC;                                 // residual tile landed, per staging tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -89,12 +91,14 @@ gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     for (int a = 0; a < NUM_ACC; ++a) {
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 8);
+      mbar_init(&res_bar[a], 1);
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmX);
     tma_prefetch_desc(&tmE);
     if (!kRaw) tma_prefetch_desc(&tmOut);
+    if (kRes) tma_prefetch_desc(&tmRes);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -160,71 +164,102 @@ gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     // Thread = one channel of the tile (TMEM lane); two warps share a lane quarter and split the
-    // token columns: the first takes tokens 0..127, the second 128..223.
+    // thirteen 16-token chunks: the first takes chunks 0..6, the second 7..12.
     const uint32_t lane_base = uint32_t(warp & 3) * 32u;
     const int half = (warp - 2) >> 2;
     const int ch = int(lane_base) + lane;                  // channel inside the tile
     const int et = int(threadIdx.x) - 64;                  // 0..255
-    const int tok_begin = half * 128;
-    const int n_chunks = half == 0 ? 4 : 3;                // 32-token chunks
-    uint32_t acc = 0, acc_phase = 0;
-    for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+    const int chunk_begin = half * 7;
+    const int n_chunks = half == 0 ? 7 : 6;
+    const int unit = (ch & 63) >> 3, sub = (ch & 7) * 2;
+    uint32_t acc = 0, acc_phase = 0, it = 0;
+    // The residual tile of the first tile is requested here; that of tile i+1 after tile i's stores.
+    if (kRes && et == 0 && blockIdx.x < p.num_tiles) {
+      const int ct = int(blockIdx.x % p.tiles_c);
+      const int t0 = int(blockIdx.x / p.tiles_c) * TT;
+      mbar_expect_tx(&res_bar[0], OUT_BYTES);
+      tma_load_2d(stage_out, &tmRes, &res_bar[0], ct * TC, t0);
+      tma_load_2d(stage_out + OUT_HALF_BYTES, &tmRes, &res_bar[0], ct * TC + 64, t0);
+    }
+    for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
       const int ct = int(tile % p.tiles_c);
       const long long t0 = (tile / p.tiles_c) * TT;
       const int n = ct * TC + ch;
       const bool ch_ok = n < p.N;
+      const uint32_t buf = it & 1u;
+      // staging: [channel half][token][64 channels] bf16, 128-byte rows, 16-byte units XOR (token & 7)
+      uint8_t* s_tile = stage_out + buf * OUT_BYTES;
+      uint8_t* s_half = s_tile + (ch >> 6) * OUT_HALF_BYTES;
       if (!kRaw && et < TT) s_tok[et] = t0 + et < p.T ? __ldg(p.a_scale + t0 + et) : 0.f;
       float w_scale = 0.f, bias = 0.f;
       if (!kRaw && ch_ok) {
         w_scale = __ldg(p.w_scale + n);
         if (kBias) bias = __ldg(p.bias + n);
       }
-      const bool got = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, 4);
+      // the stores of the tile before last (same staging tile) have been read: et == 0 waited for
+      // them right after it issued the previous tile's stores, before the barrier below
+      bool got = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, 4);
+      if (kRes && got) got = mbar_wait(&res_bar[buf], (it >> 1) & 1u, abort_flag, p.status, 5);
       if (!epi_all(got)) break;                            // also publishes s_tok
       tc_fence_after();
-      if (!kRaw) {
-        if (et == 0) tma_store_wait_read<0>();             // the previous tile's stores have read the staging tile
-        epi_sync();
-      }
-      const uint32_t t_addr = tmem_base + (lane_base << 16) + acc * TT + tok_begin;
-      // staging: [channel half][token][64 channels] bf16, 128-byte rows, 16-byte units XOR (token & 7)
-      uint8_t* s_half = stage_out + (ch >> 6) * OUT_HALF_BYTES;
-      const int unit = (ch & 63) >> 3, sub = (ch & 7) * 2;
+      const uint32_t t_addr = tmem_base + (lane_base << 16) + acc * TT;
 #pragma unroll 1
       for (int c = 0; c < n_chunks; ++c) {
-        const int tk0 = tok_begin + c * 32;                // first token of the chunk inside the tile
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_addr + c * 32, r);
+        const int tk0 = (chunk_begin + c) * 16;            // first token of the chunk inside the tile
+        uint32_t r[16];
+        tmem_ld_32x32b_x16(t_addr + tk0, r);
         tmem_ld_wait();
         if (kRaw) {
           if (ch_ok) {
             int32_t* o = reinterpret_cast<int32_t*>(p.out) + n;
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
+            for (int j = 0; j < 16; ++j)
               if (t0 + tk0 + j < p.T) o[(t0 + tk0 + j) * p.ldo] = int32_t(r[j]);
           }
         } else {
+          // loads, arithmetic and stores in separate passes: shared-memory stores in between would
+          // order the sixteen independent chains one after the other
+          float sc[16], v[16];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int tk = tk0 + j;
-            float x = __fmul_rn(__fmul_rn(float(int(r[j])), s_tok[tk]), w_scale);
+          for (int q = 0; q < 4; ++q) {
+            const float4 f = *reinterpret_cast<const float4*>(s_tok + tk0 + q * 4);
+            sc[q * 4] = f.x; sc[q * 4 + 1] = f.y; sc[q * 4 + 2] = f.z; sc[q * 4 + 3] = f.w;
+          }
+          uint8_t* cell0 = s_half + tk0 * 128 + sub;       // (tk0 + j) & 7 == j & 7
+          if (kRes) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              v[j] = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(cell0 + j * 128 + ((unit ^ (j & 7)) << 4)));
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float x = __fmul_rn(__fmul_rn(float(int(r[j])), sc[j]), w_scale);
             if (kBias) x = __fadd_rn(x, bias);
             if (kGelu) x = gelu_erf(x);
-            if (kRes) {
-              const long long tr = t0 + tk;
-              if (ch_ok && tr < p.T) x += __bfloat162float(p.residual[(tr % p.res_rows) * p.ldr + n]);
-            }
-            *reinterpret_cast<__nv_bfloat16*>(s_half + tk * 128 + ((unit ^ (tk & 7)) << 4) + sub) = __float2bfloat16_rn(x);
+            v[j] = kRes ? x + v[j] : x;
           }
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            *reinterpret_cast<__nv_bfloat16*>(cell0 + j * 128 + ((unit ^ (j & 7)) << 4)) = __float2bfloat16_rn(v[j]);
         }
       }
       if (!kRaw) {
         fence_proxy_async_smem();
         epi_sync();
         if (et == 0) {
-          tma_store_2d(&tmOut, stage_out, ct * TC, int(t0));                       // clipped at T and N
-          if (ct * TC + 64 < p.N) tma_store_2d(&tmOut, stage_out + OUT_HALF_BYTES, ct * TC + 64, int(t0));
+          tma_store_2d(&tmOut, s_tile, ct * TC, int(t0));                          // clipped at T and N
+          if (ct * TC + 64 < p.N) tma_store_2d(&tmOut, s_tile + OUT_HALF_BYTES, ct * TC + 64, int(t0));
           tma_store_commit();
+          tma_store_wait_read<1>();                        // the other staging tile is free again
+          const long long next = tile + gridDim.x;
+          if (kRes && next < p.num_tiles) {
+            const int nct = int(next % p.tiles_c);
+            const int nt0 = int(next / p.tiles_c) * TT;
+            uint8_t* dst = stage_out + (buf ^ 1u) * OUT_BYTES;
+            mbar_expect_tx(&res_bar[buf ^ 1u], OUT_BYTES);
+            tma_load_2d(dst, &tmRes, &res_bar[buf ^ 1u], nct * TC, nt0);
+            tma_load_2d(dst + OUT_HALF_BYTES, &tmRes, &res_bar[buf ^ 1u], nct * TC + 64, nt0);
+          }
         }
       }
       tc_fence_before();
@@ -285,7 +320,8 @@ __global__ void pack_sp24_kernel(const int8_t* __restrict__ W, long long ldw, in
   if (bad) atomicCAS(status, 0, int((kDevNot24 << 24) | (uint32_t(row) & 0xFFFFFFu)));
 }
 
-using SpKernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const SpParams);
+using SpKernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
+                            const CUtensorMap, const SpParams);
 
 SpKernelFn pick_sp_kernel(int epi) {
   switch (epi) {
@@ -341,7 +377,9 @@ int samb_gemm_i8_sp24(const int8_t* Xq, int64_t ldx, const float* x_scale, const
   if (!raw && (x_scale == nullptr || w_scale == nullptr)) return SAMB_E_BADARG;
   if (K % 32 || ldx % 16 || ldx < K || ldc % 16 || ldc < K / 2) return SAMB_E_SHAPE;
   if (N % 8 || ldo < N || (!raw && ldo % 8)) return SAMB_E_SHAPE;
-  if ((epilogue & SAMB_EPI_RESIDUAL) && (ldr < N || res_rows <= 0)) return SAMB_E_SHAPE;
+  // the residual tile is fetched by TMA: no row broadcast here, 16-byte row pitch and base
+  if ((epilogue & SAMB_EPI_RESIDUAL) && (ldr < N || ldr % 8 || res_rows != T)) return SAMB_E_SHAPE;
+  if ((epilogue & SAMB_EPI_RESIDUAL) && (reinterpret_cast<uintptr_t>(residual) & 15u)) return SAMB_E_ALIGN;
   if (T > (int64_t(1) << 31) - TT) return SAMB_E_SHAPE;
   if ((reinterpret_cast<uintptr_t>(out) & 15u) || (reinterpret_cast<uintptr_t>(meta) & 15u)) return SAMB_E_ALIGN;
   if (int e = check_device_arch()) return e;
@@ -398,11 +436,20 @@ int samb_gemm_i8_sp24(const int8_t* Xq, int64_t ldx, const float* x_scale, const
                                 CU_TENSOR_MAP_SWIZZLE_128B))
       return e;
   }
+  CUtensorMap tmRes = tmOut;
+  if (epilogue & SAMB_EPI_RESIDUAL) {
+    const uint64_t dims[2] = {uint64_t(N), uint64_t(T)};
+    const uint64_t strides[2] = {2, uint64_t(ldr) * 2};
+    const uint32_t box[2] = {64, uint32_t(TT)};
+    if (int e = make_tensor_map(&tmRes, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(residual), dims, strides,
+                                box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return e;
+  }
   auto kern = pick_sp_kernel(epilogue);
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
     return SAMB_E_LAUNCH;
   const long long grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
-  kern<<<dim3(unsigned(grid)), dim3(NUM_THREADS), SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tmW, tmX, tmE, tmOut, p);
+  kern<<<dim3(unsigned(grid)), dim3(NUM_THREADS), SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tmW, tmX, tmE, tmOut, tmRes, p);
   return launch_status();
 }
 

@@ -1,7 +1,7 @@
 """Single-kernel timings through the C ABI (CUDA events, L2 flushed by inputs larger than L2 where
 the shape allows it).  One JSON line per run:
 
-    python -m segment_anything_fast_b200.microbench gemm --m 131072 --n 3840 --k 1280 --epilogue bias [--int8]
+    python -m segment_anything_fast_b200.microbench gemm --m 131072 --n 3840 --k 1280 --epilogue bias [--int8 | --sp24]
     python -m segment_anything_fast_b200.microbench attn-global --batch 8 --heads 16 --tokens 4096 --dim 80
     python -m segment_anything_fast_b200.microbench attn-window --batch 200 --heads 16 --dim 80
     python -m segment_anything_fast_b200.microbench layernorm --rows 131072 --cols 1280 [--quant]
@@ -39,6 +39,7 @@ def main():
     g.add_argument("--k", type=int, default=1280)
     g.add_argument("--epilogue", choices=["none", "bias", "gelu", "residual"], default="bias")
     g.add_argument("--int8", action="store_true")
+    g.add_argument("--sp24", action="store_true", help="int8 with a 2:4-sparse weight on the sparse tensor-core path")
     ag = sub.add_parser("attn-global")
     ag.add_argument("--batch", type=int, default=8); ag.add_argument("--heads", type=int, default=16)
     ag.add_argument("--tokens", type=int, default=4096); ag.add_argument("--dim", type=int, default=80)
@@ -59,17 +60,23 @@ def main():
         bias = torch.randn(N, device=dev) if a.epilogue != "none" else None
         res = torch.randn(M, N, device=dev).bfloat16() if a.epilogue == "residual" else None
         y = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
-        if a.int8:
+        if a.int8 or a.sp24:
             x = torch.randint(-127, 128, (M, K), device=dev, dtype=torch.int8)
             w = torch.randint(-127, 128, (N, K), device=dev, dtype=torch.int8)
             sx, sw = torch.rand(M, device=dev), torch.rand(N, device=dev)
-            fn = lambda: ops.gemm_i8(x, sx, w, sw, bias, res, gelu=a.epilogue == "gelu", out=y)
+            if a.sp24:
+                w.view(N, K // 4, 4)[:, :, 2:] = 0               # any 2:4 pattern times the same
+                wc, meta = ops.pack_sp24(w)
+                fn = lambda: ops.gemm_i8_sp24(x, sx, wc, meta, sw, bias, res, gelu=a.epilogue == "gelu", out=y)
+            else:
+                fn = lambda: ops.gemm_i8(x, sx, w, sw, bias, res, gelu=a.epilogue == "gelu", out=y)
         else:
             x = torch.randn(M, K, device=dev).bfloat16()
             w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
             fn = lambda: ops.gemm_bf16(x, w, bias, res, gelu=a.epilogue == "gelu", out=y)
         ms = _time(fn, a.iters, a.warmup)
-        out.update(shape=[M, N, K], epilogue=a.epilogue, dtype="int8" if a.int8 else "bf16", ms=round(ms, 4),
+        out.update(shape=[M, N, K], epilogue=a.epilogue, dtype="int8-sp24" if a.sp24 else ("int8" if a.int8 else "bf16"),
+                   ms=round(ms, 4),
                    tflops=round(2.0 * M * N * K / ms / 1e9, 1))
     elif a.cmd == "attn-global":
         B, H, N, d = a.batch, a.heads, a.tokens, a.dim
