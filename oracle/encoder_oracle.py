@@ -10,12 +10,14 @@ follows.  Parity is pinned: ``tests/golden/make_golden.py`` runs the real
 reference modules on seeded weights/inputs and stores their outputs; the
 CPU test-suite checks this file against those stored vectors.
 
-Two arithmetic modes:
+Three arithmetic modes:
   * ``precision="fp32"``: everything in float32 (the mathematical definition).
   * ``precision="bf16"``: values are rounded to bfloat16 at exactly the points
     where the reference's bf16 eager path materialises a bf16 tensor (each
     module / torch op output); arithmetic inside an op stays float32, as the
     GPU library kernels do.  This is the noise model for the bf16 tolerance.
+  * ``precision="int8"``: the bf16 mode with qkv / proj / lin1 / lin2 evaluated by the
+    dynamic-quantisation restatement in ``oracle/quant_oracle.py`` (parity unpinned, see there).
 """
 from __future__ import annotations
 
@@ -69,7 +71,7 @@ PIXEL_STD = (58.395, 57.12, 57.375)                    # build_sam.py:140
 def _rounder(precision: str):
     if precision == "fp32":
         return lambda t: t
-    if precision == "bf16":
+    if precision in ("bf16", "int8"):
         return lambda t: t.to(torch.bfloat16).to(torch.float32)
     raise ValueError(f"unknown precision {precision!r}")
 
@@ -215,13 +217,23 @@ def attention_rel_h_rel_w(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     return r(torch.matmul(torch.softmax(logits, dim=-1), v))
 
 
+def _linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], precision: str) -> torch.Tensor:
+    """``nn.Linear``; with ``precision="int8"`` the dynamic-quantisation arithmetic of
+    :func:`oracle.quant_oracle.int8_linear` (per-token activations, per-channel weights, int32
+    accumulation) that the benchmark's int8 configuration swaps in for qkv / proj / lin1 / lin2."""
+    if precision == "int8":
+        from . import quant_oracle as qo
+        return qo.int8_linear(x.reshape(-1, x.shape[-1]), w, b).reshape(*x.shape[:-1], w.shape[0])
+    return F.linear(x, w, b)
+
+
 def attention_module(x: torch.Tensor, sd: Dict[str, torch.Tensor], prefix: str, num_heads: int,
                      use_rel_pos: bool, precision: str) -> torch.Tensor:
     """``Attention.forward`` (image_encoder.py:225-253) on ``x [B', S, S, C]``."""
     r = _rounder(precision)
     Bp, H, W, C = x.shape
     N, hd = H * W, C // num_heads
-    qkv = r(F.linear(x, sd[prefix + "qkv.weight"], sd[prefix + "qkv.bias"]))
+    qkv = r(_linear(x, sd[prefix + "qkv.weight"], sd[prefix + "qkv.bias"], precision))
     qkv = qkv.reshape(Bp, N, 3, num_heads, hd).permute(2, 0, 3, 1, 4)       # :228
     q, k, v = qkv.reshape(3, Bp * num_heads, N, hd).unbind(0)               # :230
     if use_rel_pos:
@@ -232,15 +244,15 @@ def attention_module(x: torch.Tensor, sd: Dict[str, torch.Tensor], prefix: str, 
         rel_w = q.new_zeros(Bp * num_heads, N, W)
     o = attention_rel_h_rel_w(q, k, v, rel_h, rel_w, precision)             # :245
     o = o.reshape(Bp, num_heads, H, W, hd).permute(0, 2, 3, 1, 4).reshape(Bp, H, W, C)  # :249
-    return r(F.linear(o, sd[prefix + "proj.weight"], sd[prefix + "proj.bias"]))          # :251
+    return r(_linear(o, sd[prefix + "proj.weight"], sd[prefix + "proj.bias"], precision))          # :251
 
 
 def mlp_block(x: torch.Tensor, sd: Dict[str, torch.Tensor], prefix: str, precision: str) -> torch.Tensor:
     """``lin2(GELU_erf(lin1(x)))`` (common.py:25-26)."""
     r = _rounder(precision)
-    h = r(F.linear(x, sd[prefix + "lin1.weight"], sd[prefix + "lin1.bias"]))
+    h = r(_linear(x, sd[prefix + "lin1.weight"], sd[prefix + "lin1.bias"], precision))
     h = r(F.gelu(h))
-    return r(F.linear(h, sd[prefix + "lin2.weight"], sd[prefix + "lin2.bias"]))
+    return r(_linear(h, sd[prefix + "lin2.weight"], sd[prefix + "lin2.bias"], precision))
 
 
 def block_forward(x: torch.Tensor, sd: Dict[str, torch.Tensor], i: int, cfg: EncoderConfig,

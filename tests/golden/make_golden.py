@@ -35,12 +35,47 @@ def sd_digest(sd):
     return h.hexdigest()
 
 
+def golden_decoder():
+    """(f) prompt encoder + mask decoder + post-processing of the reference's ``Sam`` on seeded decoder
+    weights, a seeded embedding and two box prompts (+ one point prompt through the prompt encoder)."""
+    from segment_anything_fast.build_sam import sam_model_registry
+
+    from oracle import decoder_oracle as do
+
+    torch.manual_seed(0)
+    sam = sam_model_registry["vit_b"]().eval()
+    cfg = do.DecoderConfig()
+    sd = do.seeded_state_dict(cfg, seed=3)
+    pe_sd = {k[len("prompt_encoder."):]: v for k, v in sd.items() if k.startswith("prompt_encoder.")}
+    md_sd = {k[len("mask_decoder."):]: v for k, v in sd.items() if k.startswith("mask_decoder.")}
+    missing = sam.prompt_encoder.load_state_dict(pe_sd, strict=False).missing_keys
+    assert all(k.startswith("mask_downscaling.") for k in missing), missing       # unused without mask prompts
+    sam.mask_decoder.load_state_dict(md_sd)                                        # strict: key set agrees
+    emb = torch.randn(1, 256, 64, 64, generator=torch.Generator().manual_seed(5))
+    boxes = torch.tensor([[100.0, 200.0, 600.0, 800.0], [10.0, 20.0, 300.0, 400.0]])
+    sp, de = sam.prompt_encoder(points=None, boxes=boxes, masks=None)
+    low, iou = sam.mask_decoder(image_embeddings=emb, image_pe=sam.prompt_encoder.get_dense_pe(),
+                                sparse_prompt_embeddings=sp, dense_prompt_embeddings=de, multimask_output=True)
+    full = sam.postprocess_masks(low, (1024, 1024), (1024, 1024))
+    pts = (torch.tensor([[[500.0, 300.0], [100.0, 100.0]]]), torch.tensor([[1, 0]]))
+    sp_pts, _ = sam.prompt_encoder(points=pts, boxes=None, masks=None)
+    np.savez_compressed(
+        os.path.join(HERE, "decoder_fp32.npz"), boxes=boxes.numpy(), sparse=sp.numpy(), low=low[:, :, ::4, ::4].numpy(),
+        iou=iou.numpy(), full_logits=full[:, :, ::16, ::16].numpy(), area=(full > 0).float().mean((2, 3)).numpy(),
+        dense_pe=sam.prompt_encoder.get_dense_pe()[:, :, ::8, ::8].numpy(), sparse_points=sp_pts.numpy())
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--only", choices=["decoder"], default=None, help="regenerate just this file")
     args = ap.parse_args()
     os.environ["SEGMENT_ANYTHING_FAST_USE_FLASH_4"] = "0"
     sys.path.insert(0, args.reference)
+    torch.set_grad_enabled(False)
+    if args.only == "decoder":
+        golden_decoder()
+        return
     from functools import partial
 
     import segment_anything_fast as saf
@@ -118,6 +153,7 @@ def main():
         os.path.join(HERE, "sparse24_mask.npz"),
         w0=w_before[0].numpy(), w1=w_before[1].numpy(),
         keep0=(lin[0].weight != 0).numpy(), keep1=(lin[1].weight != 0).numpy())
+    golden_decoder()
     print("golden vectors written to", HERE)
 
 

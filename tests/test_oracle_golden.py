@@ -99,3 +99,26 @@ def test_int8_accumulator_is_exact_and_matches_int_mm():
     y = qo.int8_linear(x, w, torch.zeros(48))
     full = x @ w.t()
     assert (y - full).abs().max() < 0.05 * full.abs().max()
+
+
+def test_decoder_oracle_matches_reference_modules(golden_dir):
+    """Prompt encoder, two-way transformer mask decoder and post-processing restatement against the
+    outputs of the reference's own modules on the same seeded weights."""
+    from oracle import decoder_oracle as do
+    g = _load(golden_dir, "decoder_fp32.npz")
+    cfg = do.DecoderConfig()
+    sd = do.seeded_state_dict(cfg, seed=3)
+    emb = torch.randn(1, 256, 64, 64, generator=torch.Generator().manual_seed(5))
+    boxes = torch.from_numpy(g["boxes"])
+    sparse, _ = do.prompt_encoder_forward(sd, cfg, boxes=boxes)
+    assert torch.allclose(sparse, torch.from_numpy(g["sparse"]), atol=1e-5)
+    assert torch.allclose(do.dense_pe(sd, cfg)[:, :, ::8, ::8], torch.from_numpy(g["dense_pe"]), atol=1e-5)
+    pts = (torch.tensor([[[500.0, 300.0], [100.0, 100.0]]]), torch.tensor([[1, 0]]))
+    sp_pts, _ = do.prompt_encoder_forward(sd, cfg, points=pts)
+    assert torch.allclose(sp_pts, torch.from_numpy(g["sparse_points"]), atol=1e-5)
+    masks, iou, low = do.predict_masks_from_embedding(sd, cfg, emb, boxes)
+    low_ref = torch.from_numpy(g["low"])
+    assert (low[:, :, ::4, ::4] - low_ref).abs().max().item() < 1e-3 * low_ref.abs().max().item()
+    assert torch.allclose(iou, torch.from_numpy(g["iou"]), atol=1e-4)
+    area = masks.float().mean((2, 3))
+    assert torch.allclose(area, torch.from_numpy(g["area"]), atol=1e-4)
