@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the SAM ViT-H image-encoder hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--quant none|int8] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--quant none|int8|int8-sp24] [--impl reference]
 
 One step = one pass of the encoder over a batch of 32 synthetic 1024x1024 images per GPU (images
 shard by rank, weak scaling; the only collective is the all-gather of the embeddings at the end of a
@@ -32,9 +32,11 @@ METRIC = "ViT-H encoder images/sec at batch 32"
 # neck 7.52e9.
 FLOPS_PER_IMAGE = 5.666e12
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-# DRAM bytes per launch of the Linear GEMM kernel from the ncu capture summarised in
-# profiles/gemm_tc_kernel_vit_h_linears.md, scaled to the 131072-row launches of this workload.
-GEMM_TRAFFIC_BYTES_PER_LAUNCH = None
+# DRAM bytes (read + write) per launch of the Linear GEMM kernel: ncu captures of the 32768-row qkv /
+# lin1 / lin2 launches (292 / 380 / 525 MB), scaled x4 to the 131072-row launches of this workload
+# (traffic grows with the rows; the weights stay in L2), proj taken at its algorithmic 1.0 GB; mean
+# over the four Linear shapes of a block.
+GEMM_TRAFFIC_BYTES_PER_LAUNCH = 1.45e9
 
 
 def env_int(name, default):
@@ -102,25 +104,29 @@ class ClockSampler:
 
 class LaunchProfiler:
     """Counts every samb_* launch and brackets the Linear GEMMs with CUDA events on the launch stream."""
-    GEMMS = {"samb_gemm_bf16": (10, 11, 12), "samb_gemm_i8": (12, 13, 14)}   # positions of M, N, K in the call
+    # positions of M, N, K in the call; the 2:4 kernel is credited with the multiply-adds it executes (half)
+    GEMMS = {"samb_gemm_bf16": (10, 11, 12, 2.0), "samb_gemm_i8": (12, 13, 14, 2.0),
+             "samb_gemm_bf16_heads": (6, 7, 8, 2.0), "samb_gemm_i8_heads": (8, 9, 10, 2.0),
+             "samb_gemm_i8_sp24": (13, 14, 15, 1.0)}
 
     def __init__(self):
         self.launches = 0
         self.records = []          # (flops, start_event, end_event)
 
     def begin(self, name, args):
-        if name in ("samb_abi_version", "samb_error_string", "samb_decode_status"):
+        if name in ("samb_abi_version", "samb_error_string", "samb_decode_status", "samb_sp24_meta_bytes"):
             return None
         self.launches += 1
         pos = self.GEMMS.get(name)
         if pos is None:
             return None
-        M, N, K = (int(args[i]) for i in pos)
+        M, N, K = (int(args[i]) for i in pos[:3])
+        M = min(M, BATCH * 4096)   # algorithmic rows: the window-padding tokens of the qkv projection earn nothing
         if K < 1024:               # patch-embed / neck GEMMs are not "the Linear layers"
             return None
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
-        return (2.0 * M * N * K, s, e)
+        return (pos[3] * M * N * K, s, e)
 
     def end(self, tok):
         if tok is not None:
@@ -128,8 +134,8 @@ class LaunchProfiler:
             self.records.append(tok)
 
 
-def build_vit_h(quant, device):
-    from segment_anything_fast_b200 import build_image_encoder_vit_h
+def build_vit_h(quant, device, sparse_mlp=False):
+    from segment_anything_fast_b200 import apply_sparse, build_image_encoder_vit_h
     torch.manual_seed(0)
     enc = build_image_encoder_vit_h()
     g = torch.Generator().manual_seed(1)
@@ -137,6 +143,8 @@ def build_vit_h(quant, device):
         for name, p in enc.named_parameters():                 # random-init weights of the ViT-H architecture
             if p.dim() >= 2 or "rel_pos" in name:
                 p.normal_(0.0, 0.02, generator=g)
+    if sparse_mlp:                                             # 2:4-pruned mlp.lin1 / mlp.lin2
+        apply_sparse(enc, mlp_only=True)
     return enc.to(torch.bfloat16).to(device).set_quant(quant)
 
 
@@ -154,8 +162,9 @@ def run_b200(args):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
-    quant = None if args.quant == "none" else args.quant
-    enc = build_vit_h(quant, device)
+    sparse_mlp = args.quant == "int8-sp24"
+    quant = None if args.quant == "none" else "int8"
+    enc = build_vit_h(quant, device, sparse_mlp)
     sess = EncoderSession(enc, BATCH, device)
     g = torch.Generator().manual_seed(1000 + rank)
     sess.host_in.copy_(torch.randint(0, 256, sess.host_in.shape, generator=g, dtype=torch.uint8))
@@ -231,14 +240,15 @@ def run_b200(args):
         "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int8" if quant == "int8" else "bf16", "data": "synthetic",
         "config": {"workload": "SAM ViT-H image encoder, batch 32 per GPU, 1024x1024 seeded uint8 images, "
-                               "random-init weights" + (", int8 dynamic-quant linears" if quant else ", bf16 linears"),
+                               "random-init weights" + (", int8 dynamic-quant linears" if quant else ", bf16 linears")
+                               + (", 2:4-sparse mlp.lin1/lin2 on the sparse tensor-core path" if sparse_mlp else ""),
                    "batch_per_gpu": BATCH, "parallelism": f"dp{world} (images sharded by rank, all-gather of embeddings)",
-                   "l2": "inputs_larger_than_l2", "quant": quant or "none"},
+                   "l2": "inputs_larger_than_l2", "quant": args.quant},
         "clocks": clocks,
         "e2e": {"value": round(world * BATCH * args.steps / (e2e_ms * 1e-3), 2), "unit": "img/s",
                 "h2d_bytes_per_step": sess.h2d_bytes, "d2h_bytes_per_step": sess.d2h_bytes},
         "gpu_launches": launches,
-        "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel (qkv/proj/lin1/lin2 launches)",
+        "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel" + (" + gemm_sp24_kernel" if sparse_mlp else "") + " (qkv/proj/lin1/lin2 launches)",
                      "achieved": None if achieved is None else round(achieved, 1), "peak": peak_tf, "unit": "TFLOP/s",
                      "frac": None if achieved is None else round(achieved / peak_tf, 4),
                      "traffic": GEMM_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": peak_note,
@@ -301,7 +311,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--quant", choices=["none", "int8"], default="none")
+    ap.add_argument("--quant", choices=["none", "int8", "int8-sp24"], default="none")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
