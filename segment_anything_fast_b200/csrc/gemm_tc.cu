@@ -20,6 +20,8 @@ constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * SLAB_BYTES;  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * SLAB_BYTES;  // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int K2_A1_OFF = 32 * 1024;            // k2 mode: [128][16] bf16 tail of A inside the stage
+constexpr int K2_B1_OFF = 36 * 1024;            //          [tg_bn][16] bf16 tail of W
 constexpr int EPI_COLSCALE = 16;                // internal epilogue flag: out = acc * w_scale[n] (bf16 operands)
 constexpr int NUM_ACC = 2;
 constexpr int TMEM_COLS = NUM_ACC * BN;         // 512: all of tensor memory, one CTA per SM
@@ -49,6 +51,7 @@ struct GemmParams {
   int a_row_stride;              // batch b reads A rows [b*a_row_stride + m, ...) (head-major operand planes)
   int tg, tg_bn;                 // tg > 1: a tile is tg independent products of tg_bn columns each (consecutive
                                  // batches sharing W), so narrow batched outputs still fill a 256-column tile
+  int k2;                        // grouped tiles with K = 80 bf16: a stage holds a whole product (64 + 16 columns of K)
   int hm_group;                  // > 0: head-major output, hm_group 16-column pieces per head (see launch_gemm)
   int epilogue;
 };
@@ -72,7 +75,8 @@ __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 256;" :::
 template <bool kInt8, int kEpi>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmOut, const GemmParams p) {
+               const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmA2,
+               const __grid_constant__ CUtensorMap tmB2, const GemmParams p) {
   constexpr bool kRaw = (kEpi & SAMB_EPI_RAW) != 0;
   constexpr bool kBias = (kEpi & SAMB_EPI_BIAS) != 0;
   constexpr bool kGelu = (kEpi & SAMB_EPI_GELU) != 0;
@@ -106,6 +110,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (p.k2) {
+      tma_prefetch_desc(&tmA2);
+      tma_prefetch_desc(&tmB2);
+    }
     if (!kRaw) tma_prefetch_desc(&tmOut);
   }
   if (warp == 1) {
@@ -130,6 +138,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int m0 = int(tb / p.tiles_n) * BM;
         const int n0 = int(tb % p.tiles_n) * p.bn;
         const int a_col0 = bt * p.a_col_stride;
+        if (p.k2) {
+          // whole product per stage: K columns 0..63 as 128-byte rows (128B swizzle), 64..79 as 32-byte rows
+          // (32B swizzle), so four independent products are in flight per CTA
+          for (int g = 0; ok && g < p.tg; ++g) {
+            if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 1))) break;
+            uint8_t* sa = smem + stage * STAGE_BYTES;
+            const int arow = m0 + (bt * p.tg + g) * p.a_row_stride;
+            mbar_expect_tx(&full_bar[stage], A_STAGE_BYTES + p.tg_bn * SLAB_BYTES + BM * 32 + p.tg_bn * 32);
+            tma_load_2d(sa, &tmA, &full_bar[stage], 0, arow);
+            tma_load_2d(sa + A_STAGE_BYTES, &tmB, &full_bar[stage], 0, 0);
+            tma_load_2d(sa + K2_A1_OFF, &tmA2, &full_bar[stage], 64, arow);
+            tma_load_2d(sa + K2_B1_OFF, &tmB2, &full_bar[stage], 64, 0);
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+          continue;
+        }
         for (int gk = 0; gk < p.tg * p.k_slabs; ++gk) {
           const int g = gk / p.k_slabs, ks = gk - g * p.k_slabs;       // product inside the tile, K slab
           if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 1))) break;
@@ -154,6 +178,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (long long tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
         if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, 2))) break;
         tc_fence_after();
+        if (p.k2) {
+          const uint64_t desc1 = make_smem_desc(smem_u32(smem), 16, 256, kSwizzle32B);
+          for (int g = 0; g < p.tg; ++g) {
+            const uint32_t d_tmem = tmem_base + acc * BN + g * p.tg_bn;
+            if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3))) break;
+            tc_fence_after();
+            if (elect_one()) {
+              const uint64_t adesc = desc0 + stage * (STAGE_BYTES / 16);
+              const uint64_t bdesc = adesc + A_STAGE_BYTES / 16;
+#pragma unroll
+              for (int k4 = 0; k4 < 4; ++k4) umma_f16_ss(d_tmem, adesc + k4 * 2, bdesc + k4 * 2, idesc, k4 != 0 ? 1u : 0u);
+              umma_f16_ss(d_tmem, desc1 + (stage * STAGE_BYTES + K2_A1_OFF) / 16,
+                          desc1 + (stage * STAGE_BYTES + K2_B1_OFF) / 16, idesc, 1u);
+              tc_commit(&empty_bar[stage]);
+            }
+            __syncwarp();
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+        } else
         for (int gk = 0; gk < p.tg * p.k_slabs; ++gk) {
           const int g = gk / p.k_slabs, ks = gk - g * p.k_slabs;
           const uint32_t d_tmem = tmem_base + acc * BN + g * p.tg_bn;
@@ -327,7 +370,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 }
 
 template <bool kInt8>
-using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams);
+using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
+                          const GemmParams);
 
 template <bool kInt8>
 KernelFn<kInt8> pick_kernel(int epi) {
@@ -421,6 +465,7 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
     p.tg = batch % 4 == 0 ? 4 : (batch % 2 == 0 ? 2 : 1);        // tg narrow products share one tile
     p.bn = p.tg * N;
   }
+  p.k2 = (p.tg > 1 && !int8 && K == 80) ? 1 : 0;
   p.tiles_n = p.tg > 1 ? 1 : (N + p.bn - 1) / p.bn;
   if (p.tg > 1) p.N = p.tg * N;                                  // logical width of a grouped tile
   p.tiles_per_batch = ((M + BM - 1) / BM) * p.tiles_n;
@@ -448,11 +493,24 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
                                 CU_TENSOR_MAP_SWIZZLE_128B))
       return e;
   }
+  CUtensorMap tmA2 = tmA, tmB2 = tmB;
+  if (p.k2) {
+    const uint64_t dimsA[2] = {uint64_t(K), uint64_t(a_row_stride * batch)};
+    const uint64_t stridesA[2] = {2, uint64_t(lda) * 2};
+    const uint32_t boxA[2] = {16, uint32_t(BM)};
+    if (int e = make_tensor_map(&tmA2, dt, 2, const_cast<void*>(A), dimsA, stridesA, boxA, CU_TENSOR_MAP_SWIZZLE_32B))
+      return e;
+    const uint64_t dimsB[2] = {uint64_t(K), uint64_t(N)};
+    const uint64_t stridesB[2] = {2, uint64_t(ldw) * 2};
+    const uint32_t boxB[2] = {16, 64};
+    if (int e = make_tensor_map(&tmB2, dt, 2, const_cast<void*>(W), dimsB, stridesB, boxB, CU_TENSOR_MAP_SWIZZLE_32B))
+      return e;
+  }
   auto kern = int8 ? pick_kernel<true>(epilogue) : pick_kernel<false>(epilogue);
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
     return SAMB_E_LAUNCH;
   const long long grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
-  kern<<<dim3(unsigned(grid)), dim3(NUM_THREADS), SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tmA, tmB, tmOut, p);
+  kern<<<dim3(unsigned(grid)), dim3(NUM_THREADS), SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tmA, tmB, tmOut, tmA2, tmB2, p);
   return launch_status();
 }
 
