@@ -1,0 +1,116 @@
+"""Checks at the benchmark's full sizes through properties that do not need a full CPU evaluation:
+exact integer checksums for the int8 GEMMs, softmax normalisation / linearity in V / a sampled oracle
+comparison for the attention ops, and determinism, batch independence and a one-image oracle
+comparison for the ViT-H encoder."""
+import pytest
+import torch
+
+from oracle import encoder_oracle as eo
+
+pytestmark = pytest.mark.gpu
+
+VIT_H = eo.EncoderConfig(embed_dim=1280, depth=32, num_heads=16, global_attn_indexes=(7, 15, 23, 31), out_chans=256)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from segment_anything_fast_b200 import ops as _ops
+    return _ops
+
+
+def _cos(a, b):
+    return torch.nn.functional.cosine_similarity(a.flatten().double(), b.flatten().double(), dim=0).item()
+
+
+@pytest.mark.parametrize("N,K,sparse", [(5120, 1280, False), (1280, 5120, False), (5120, 1280, True), (1280, 5120, True)])
+def test_int8_gemm_full_size_checksums(ops, N, K, sparse):
+    """131072-token lin1 / lin2 products: the column sums and row sums of the int32 accumulators equal
+    the (exact, int64) products with the summed operands -- a checksum over every accumulator."""
+    M = 131072
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randint(-127, 128, (M, K), generator=g, device="cuda", dtype=torch.int8)
+    w = torch.randint(-127, 128, (N, K), generator=g, device="cuda", dtype=torch.int8)
+    if sparse:
+        w.view(N, K // 4, 4)[:, :, 1] = 0
+        w.view(N, K // 4, 4)[:, :, 3] = 0
+        wc, meta = ops.pack_sp24(w)
+        acc = ops.gemm_i8_sp24(x, None, wc, meta, None, raw=True)
+    else:
+        acc = ops.gemm_i8(x, None, w, None, raw=True)
+    ops.check_status()
+    col = acc.sum(dim=0, dtype=torch.int64).cpu()
+    row = acc.sum(dim=1, dtype=torch.int64).cpu()
+    xs = x.sum(dim=0, dtype=torch.int64).cpu()                      # [K]
+    ws = w.sum(dim=0, dtype=torch.int64).cpu()                      # [K]
+    assert torch.equal(col, w.cpu().to(torch.int64) @ xs)
+    assert torch.equal(row, (x.to(torch.float64) @ ws.to(torch.float64).cuda()).cpu().to(torch.int64))   # |.| < 2^53: exact
+
+
+def test_global_attention_full_size_properties(ops):
+    """q, k, v [8, 16, 4096, 80] ~ N(0,1), rel ~ N(0,0.5) (the standalone benchmark shape): rows of
+    softmax sum to one (v = 1 gives 1), the op is linear in v, and sampled (batch, head) slices agree
+    with the oracle."""
+    B, H, N, d = 8, 16, 4096, 80
+    g = torch.Generator(device="cuda").manual_seed(0)
+    q, k, v, v2 = (torch.randn(B, H, N, d, generator=g, device="cuda").bfloat16() for _ in range(4))
+    rel_h = (torch.randn(B, H, N, 64, generator=g, device="cuda") * 0.5).bfloat16()
+    rel_w = (torch.randn(B, H, N, 64, generator=g, device="cuda") * 0.5).bfloat16()
+    ones = torch.ones_like(v)
+    o1 = ops.attn_relpos_global(q, k, ones, rel_h, rel_w).float()
+    assert (o1 - 1.0).abs().max().item() < 1e-2                    # bf16 rounding of P and of the output
+    oa = ops.attn_relpos_global(q, k, v, rel_h, rel_w).float()
+    ob = ops.attn_relpos_global(q, k, v2, rel_h, rel_w).float()
+    vs = (v.float() + v2.float()).bfloat16()
+    oc = ops.attn_relpos_global(q, k, vs, rel_h, rel_w).float()
+    ops.check_status()
+    assert (oc - (oa + ob)).abs().max().item() < 3e-2
+    assert _cos(oc, oa + ob) > 0.9995
+    for b, h in [(0, 0), (7, 15), (3, 9)]:
+        sl = lambda t: t[b:b + 1, h:h + 1].float().cpu()
+        ref = eo.attention_rel_h_rel_w(sl(q), sl(k), sl(v), sl(rel_h), sl(rel_w))
+        got = oa[b:b + 1, h:h + 1].cpu()
+        assert (got - ref).abs().max().item() < 2e-2
+        assert _cos(got, ref) > 0.999
+
+
+def test_window_attention_full_size_properties(ops):
+    """The windowed sweep of the standalone benchmark, 25 windows x 32 images: q, k, v [800, 16, 196, 80]."""
+    B, H, N, d = 800, 16, 196, 80
+    g = torch.Generator(device="cuda").manual_seed(2)
+    q, k, v = (torch.randn(B, H, N, d, generator=g, device="cuda").bfloat16() for _ in range(3))
+    rel_h = (torch.randn(B, H, N, 14, generator=g, device="cuda") * 0.5).bfloat16()
+    rel_w = (torch.randn(B, H, N, 14, generator=g, device="cuda") * 0.5).bfloat16()
+    o1 = ops.attn_relpos_window(q, k, torch.ones_like(v), rel_h, rel_w).float()
+    assert (o1 - 1.0).abs().max().item() < 1e-2
+    o = ops.attn_relpos_window(q, k, v, rel_h, rel_w).float()
+    ops.check_status()
+    for b in (0, 399, 799):
+        sl = lambda t: t[b:b + 1].float().cpu()
+        ref = eo.attention_rel_h_rel_w(sl(q), sl(k), sl(v), sl(rel_h), sl(rel_w))
+        got = o[b:b + 1].cpu()
+        assert (got - ref).abs().max().item() < 2e-2
+        assert _cos(got, ref) > 0.999
+
+
+def test_vit_h_encoder_full_size(ops):
+    """ViT-H, batch 32 (the benchmark configuration): deterministic, images independent of their batch
+    position, and image 0 within bf16 distance of the fp32 oracle on the same weights."""
+    from test_gpu_encoder import build_encoder
+    sd = eo.seeded_state_dict(VIT_H, seed=21)
+    enc = build_encoder(VIT_H, sd)
+    x = eo.seeded_images(4, seed=22).to(torch.bfloat16).cuda()
+    xb = x.repeat(8, 1, 1, 1)                                       # 32 images: 8 copies of 4
+    a = enc(xb)
+    b = enc(xb)
+    ops.check_status()
+    assert torch.isfinite(a.float()).all()
+    assert torch.equal(a, b)
+    assert torch.equal(a[:4], a[28:])                               # same image, different batch slot
+    single = enc(x[2:3])
+    assert torch.equal(single, a[2:3])
+    ref = eo.image_encoder_forward(x[:1].float().cpu(), sd, VIT_H, "fp32")
+    got = a[:1].float().cpu()
+    print(f"ViT-H image 0 vs fp32 oracle: cosine {_cos(got, ref):.6f}, max-abs {(got - ref).abs().max().item():.4f}")
+    assert _cos(got, ref) > 0.999
