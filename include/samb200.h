@@ -147,6 +147,16 @@ int samb_attn_relpos_window_qkv(const void* qkv, const void* tab, int64_t ldt, i
                                 int64_t o_pitch, int B, int H, int grid, int window, int d, float scale,
                                 int32_t* status, void* stream);
 
+/* Windowed attention straight from raster-order head-major qkv [3H][B*grid*grid][d]: no window-partitioned
+ * copy of the tokens exists.  Each (window, head) gathers its window x window tokens with TMA boxes; the part of
+ * a border window beyond the raster is the reference's zero padding (F.pad in window_partition,
+ * modeling/image_encoder.py:268-271), whose keys / values are the projection biases: qkv_bias is the qkv
+ * Linear's bias as bf16 [3H*d] (zeros for a bias-free projection).  tab [B*grid*grid, ldt] holds the table
+ * products of samb_relpos_table_products in raster row order.  o as in samb_attn_relpos_window_qkv. */
+int samb_attn_relpos_window_raster(const void* qkv, const void* qkv_bias, const void* tab, int64_t ldt,
+                                   int t_head_stride, int t_w_off, void* o, int64_t o_pitch, int B, int H, int grid,
+                                   int window, int d, float scale, int32_t* status, void* stream);
+
 /* Head-major variants of the qkv projection: out is [N / head_dim][M][head_dim] (bf16), i.e. one
  * contiguous [M, head_dim] plane per (q|k|v, head) instead of M rows of N columns, so that the
  * attention kernels stream whole contiguous tiles.  Epilogue: + bias (may be NULL).  head_dim a

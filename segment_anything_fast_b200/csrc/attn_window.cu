@@ -15,8 +15,16 @@
 //  * rel_w rides on the tensor core: A = [Q | rel_w/scale (16 columns)], B = [K | E], E[j, j % WS] = 1.
 //  * rel_h is constant over runs of WS keys and is folded into the exp2 FMA addend.
 //  * The bias values of item k+1 are fetched into registers before the softmax of item k starts.
-// Zero-padded window tokens need no special case: they are ordinary rows of the padded qkv buffer.
-// Rows N..207 of the K/V box belong to the next window; their probabilities are written as zero.
+// Padded layouts (qkv_fused 0 / 1): zero-padded window tokens are ordinary rows of the padded qkv buffer;
+// rows N..207 of the K/V box belong to the next window and their probabilities are written as zero.
+// Raster layout (qkv_fused 2): q/k/v stay in raster token order and never hold pad tokens.  A window is
+// gathered by WS x WS TMA boxes whose out-of-range part (border windows) is zero-filled.  A pad token's
+// key and value are the projection biases (its LayerNorm output is zero), so row N of K / V receives
+// k_bias / v_bias of the head: logit column N is q . k_bias, which the softmax adds to the logits of
+// the pad keys (whose own K rows are zero, their columns hold only the rel_w part), and column N of P
+// receives the summed probability of the pad keys, so that P V adds (sum of pad P) * v_bias.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace samb {
@@ -37,7 +45,8 @@ struct WinParams {
   __nv_bfloat16* o;
   long long o_pitch;
   int qkv_fused;                 // 0: q/k/v/o are [W*H*N, d]; 1: head-major qkv [3H][W*N][d], o rows are raster tokens
-  int H, grid, nw;               // raster side and windows per side (fused mode)
+  int H, grid, nw;               // raster side and windows per side (fused modes)
+  int B, vlast;                  // raster mode: images, valid extent of the last window of a row / column
   int items;                     // number of (window, head) pairs
   float scale;
   int* status;
@@ -59,6 +68,7 @@ struct WinSmem {
   static constexpr int OFF_BAR = OFF_E + KV_CHUNK;
   static constexpr int BYTES = OFF_BAR + 256 + 1024;
   static_assert(N <= 256 && NK <= 256 && WS <= 16, "window too large for this kernel");
+  static_assert(N < NK && (N * 32) % 128 == 0, "raster mode keeps the bias row at key index N (a 128-byte aligned copy target)");
   static_assert(STAGE % 1024 == 0 && NK / 2 <= kOCol && kOCol + D <= 256, "layout");
 };
 
@@ -76,7 +86,8 @@ __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) { return __
 template <int D, int WS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const WinParams p) {
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                   const __grid_constant__ CUtensorMap tmBias, const WinParams p) {
   using L = WinSmem<D, WS>;
   constexpr int N = L::N, NK = L::NK, CH = L::CH;
   extern __shared__ uint8_t smem_raw[];
@@ -106,6 +117,19 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmO);
+    if (p.qkv_fused == 2) tma_prefetch_desc(&tmBias);
+  }
+  if (p.qkv_fused == 2) {
+    // rows N+1..NK-1 of every K / V chunk are never written by a copy in this mode: zero them once (their
+    // probabilities are zero, but 0 x stale bits must not be a NaN)
+    constexpr int kTail = NK - N - 1;
+    for (int idx = threadIdx.x; idx < STAGES * 2 * CH * kTail * 2; idx += NUM_THREADS) {
+      const int half = idx & 1, r = (idx >> 1) % kTail, c = (idx >> 1) / kTail % CH, kv = (idx >> 1) / (kTail * CH) % 2,
+                st = (idx >> 1) / (kTail * CH * 2);
+      uint8_t* row = smem + st * L::STAGE + (kv ? L::OFF_V : L::OFF_K) + c * L::KV_CHUNK + (N + 1 + r) * 32;
+      *reinterpret_cast<uint4*>(row + half * 16) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    fence_proxy_async_smem();
   }
   if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
@@ -128,6 +152,22 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 1)) break;
         uint8_t* st = smem + stage * L::STAGE;
+        if (p.qkv_fused == 2) {
+          const int ww = p.nw * p.nw;
+          const int b = w / ww, wi = w - b * ww;
+          const int wy = wi / p.nw, wx = wi - wy * p.nw;
+          mbar_expect_tx(&full[stage], 3 * CH * N * 32 + 2 * CH * 32);
+#pragma unroll
+          for (int c = 0; c < CH; ++c) {           // one WS x WS box per 16-column chunk, plus the bias rows
+            tma_load_4d(st + c * L::Q_CHUNK, &tmQ, &full[stage], c * 16, wx * WS, wy * WS, h * p.B + b);
+            tma_load_4d(st + L::OFF_K + c * L::KV_CHUNK, &tmQ, &full[stage], c * 16, wx * WS, wy * WS, (p.H + h) * p.B + b);
+            tma_load_4d(st + L::OFF_V + c * L::KV_CHUNK, &tmQ, &full[stage], c * 16, wx * WS, wy * WS, (2 * p.H + h) * p.B + b);
+            tma_load_2d(st + L::OFF_K + c * L::KV_CHUNK + N * 32, &tmBias, &full[stage], c * 16, p.H + h);
+            tma_load_2d(st + L::OFF_V + c * L::KV_CHUNK + N * 32, &tmBias, &full[stage], c * 16, 2 * p.H + h);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          continue;
+        }
         mbar_expect_tx(&full[stage], L::STAGE);
         tma_load_3d(st, &tmQ, &full[stage], 0, rq, 0);
         tma_load_3d(st + L::OFF_K, &tmK, &full[stage], 0, rk, 0);
@@ -222,7 +262,16 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int q = 0; q < WS / 2; ++q) { rawv[0][q] = __ldg(s_h + q); rawv[1][q] = __ldg(s_w + q); }
       } else {
         const int w = it / p.H, h = it - w * p.H;
-        const __nv_bfloat16* tb = p.tab + ((long long)w * N + n) * p.ldt + h * p.t_head_stride;
+        long long trow = (long long)w * N + n;
+        if (p.qkv_fused == 2) {                    // raster rows; pad queries of border windows have none
+          const int ww = p.nw * p.nw;
+          const int b = w / ww, wi = w - b * ww;
+          const int wy = wi / p.nw, wx = wi - wy * p.nw;
+          const int y = wy * WS + qh, x = wx * WS + qw;
+          if (y >= p.grid || x >= p.grid) return;
+          trow = ((long long)b * p.grid + y) * p.grid + x;
+        }
+        const __nv_bfloat16* tb = p.tab + trow * p.ldt + h * p.t_head_stride;
         const uint4* s_h = reinterpret_cast<const uint4*>(tb + (qh - sh_h));
         const uint4* s_w = reinterpret_cast<const uint4*>(tb + p.t_w_off + (qw - sh_w));
 #pragma unroll
@@ -283,51 +332,84 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
       if (!(ok = mbar_wait(&s_full[t], par, abort_flag, p.status, 6))) break;
       tc_fence_after();
-      // pass 1: per key-row maxima of the raw logits, then the row maximum of the biased logits
-      float mx[WS];
-#pragma unroll
-      for (int q = 0; q < WS; ++q) mx[q] = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < NK / 16; ++c) {
-        uint32_t r[16];
-        tmem_ld_32x32b_x16(lane_addr + c * 16, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          const int j = c * 16 + u;
-          if (j < N) mx[j / WS] = fmaxf(mx[j / WS], __uint_as_float(r[u]));
-        }
+      // valid extent of this window (raster mode: border windows are cut by the raster edge)
+      int vy = WS, vx = WS;
+      if (p.qkv_fused == 2) {
+        const int wi = (it / p.H) % (p.nw * p.nw);
+        if (wi / p.nw == p.nw - 1) vy = p.vlast;
+        if (wi % p.nw == p.nw - 1) vx = p.vlast;
       }
-      float m = -INFINITY;
-#pragma unroll
-      for (int q = 0; q < WS; ++q) m = fmaxf(m, fmaf(mx[q], c2, bh[q]));
-#pragma unroll
-      for (int q = 0; q < WS; ++q) bh[q] -= m;
-      // pass 2: probabilities -> packed bf16 P over the logit columns already consumed
       float l = 0.f;
-      uint32_t rbuf[2][16];
-      tmem_ld_32x32b_x16(lane_addr, rbuf[0]);
+      // kPads: some keys of the window are pad tokens (kh >= vy or kw >= vx).  Their logit is their own
+      // column (rel_w part only, the K row is zero) plus column N (q . k_bias); their probabilities are
+      // also summed into column N of P.
+      auto softmax_tile = [&](auto pads_tag) {
+        constexpr bool kPads = decltype(pads_tag)::value;
+        float sb = 0.f;
+        if (kPads) {
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(lane_addr + (N / 16) * 16, r);
+          tmem_ld_wait();
+          sb = __uint_as_float(r[N % 16]);
+        }
+        // pass 1: per key-row maxima of the raw logits, then the row maximum of the biased logits
+        float mx[WS];
 #pragma unroll
-      for (int c = 0; c < NK / 16; ++c) {
-        tmem_ld_wait();                                          // chunk c has landed
-        if (c + 1 < NK / 16) tmem_ld_32x32b_x16(lane_addr + (c + 1) * 16, rbuf[(c + 1) & 1]);   // next chunk in flight
-        const uint32_t(&r)[16] = rbuf[c & 1];
-        float e[16];
+        for (int q = 0; q < WS; ++q) mx[q] = -INFINITY;
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          const int j = c * 16 + u;
-          e[u] = 0.f;
-          if (j < N) {
-            e[u] = wexp2(fmaf(__uint_as_float(r[u]), c2, bh[j / WS]));
-            l += e[u];
+        for (int c = 0; c < NK / 16; ++c) {
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(lane_addr + c * 16, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int u = 0; u < 16; ++u) {
+            const int j = c * 16 + u;
+            if (j < N) {
+              float x = __uint_as_float(r[u]);
+              if (kPads && (j / WS >= vy || j % WS >= vx)) x += sb;
+              mx[j / WS] = fmaxf(mx[j / WS], x);
+            }
           }
         }
-        const uint32_t pk[8] = {wpack2(e[0], e[1]), wpack2(e[2], e[3]), wpack2(e[4], e[5]), wpack2(e[6], e[7]),
-                                wpack2(e[8], e[9]), wpack2(e[10], e[11]), wpack2(e[12], e[13]), wpack2(e[14], e[15])};
-        // columns [8c, 8c+8) hold logits 16..31 of chunk c/2, consumed in an earlier iteration (for c = 0:
-        // chunk 0 itself, already in registers; chunk 1, in flight, starts at column 16)
-        tmem_st_32x32b_x8(lane_addr + c * 8, pk);
-      }
+        float m = -INFINITY;
+#pragma unroll
+        for (int q = 0; q < WS; ++q) m = fmaxf(m, fmaf(mx[q], c2, bh[q]));
+#pragma unroll
+        for (int q = 0; q < WS; ++q) bh[q] -= m;
+        // pass 2: probabilities -> packed bf16 P over the logit columns already consumed
+        float lpad = 0.f;
+        uint32_t rbuf[2][16];
+        tmem_ld_32x32b_x16(lane_addr, rbuf[0]);
+#pragma unroll
+        for (int c = 0; c < NK / 16; ++c) {
+          tmem_ld_wait();                                          // chunk c has landed
+          if (c + 1 < NK / 16) tmem_ld_32x32b_x16(lane_addr + (c + 1) * 16, rbuf[(c + 1) & 1]);   // next chunk in flight
+          const uint32_t(&r)[16] = rbuf[c & 1];
+          float e[16];
+#pragma unroll
+          for (int u = 0; u < 16; ++u) {
+            const int j = c * 16 + u;
+            e[u] = 0.f;
+            if (j < N) {
+              float x = __uint_as_float(r[u]);
+              const bool pad = kPads && (j / WS >= vy || j % WS >= vx);
+              if (pad) x += sb;
+              e[u] = wexp2(fmaf(x, c2, bh[j / WS]));
+              l += e[u];
+              if (pad) lpad += e[u];
+            } else if (kPads && j == N) {
+              e[u] = lpad;                                         // every pad key has been visited by now
+            }
+          }
+          const uint32_t pk[8] = {wpack2(e[0], e[1]), wpack2(e[2], e[3]), wpack2(e[4], e[5]), wpack2(e[6], e[7]),
+                                  wpack2(e[8], e[9]), wpack2(e[10], e[11]), wpack2(e[12], e[13]), wpack2(e[14], e[15])};
+          // columns [8c, 8c+8) hold logits 16..31 of chunk c/2, consumed in an earlier iteration (for c = 0:
+          // chunk 0 itself, already in registers; chunk 1, in flight, starts at column 16)
+          tmem_st_32x32b_x8(lane_addr + c * 8, pk);
+        }
+      };
+      if (vy < WS || vx < WS) softmax_tile(std::true_type{});
+      else softmax_tile(std::false_type{});
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive_warp(&p_full[t]);
@@ -386,9 +468,26 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
 template <int D, int WS>
 int launch_window(const void* q, const void* k, const void* v, long long rows, long long cols, WinParams p,
-                  long long items, void* stream) {
+                  long long items, void* stream, const void* qkv_bias = nullptr) {
   using L = WinSmem<D, WS>;
-  CUtensorMap tmQ, tmK, tmV;
+  CUtensorMap tmQ, tmK, tmV, tmBias;
+  if (p.qkv_fused == 2) {
+    // raster planes [3H * B][grid][grid][D]: one WS x WS box of 16 columns per copy
+    const uint64_t g = uint64_t(p.grid);
+    const uint64_t dims[4] = {uint64_t(D), g, g, uint64_t(3) * p.H * p.B};
+    const uint64_t strides[4] = {2, uint64_t(D) * 2, g * D * 2, g * g * D * 2};
+    const uint32_t box[4] = {16, uint32_t(WS), uint32_t(WS), 1};
+    if (int e = make_tensor_map(&tmQ, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(q), dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_32B))
+      return e;
+    tmK = tmV = tmQ;
+    const uint64_t bdims[2] = {uint64_t(D), uint64_t(3) * p.H};
+    const uint64_t bstrides[2] = {2, uint64_t(D) * 2};
+    const uint32_t bbox[2] = {16, 1};
+    if (int e = make_tensor_map(&tmBias, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(qkv_bias), bdims, bstrides,
+                                bbox, CU_TENSOR_MAP_SWIZZLE_32B))
+      return e;
+  } else {
   const uint64_t dims[3] = {16, uint64_t(rows), uint64_t(cols / 16)};
   const uint64_t strides[3] = {2, uint64_t(cols) * 2, 32};
   const uint32_t box_q[3] = {16, 256, uint32_t(D / 16)};
@@ -402,6 +501,8 @@ int launch_window(const void* q, const void* k, const void* v, long long rows, l
   if (int e = make_tensor_map(&tmV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(v), dims, strides, box_kv,
                               CU_TENSOR_MAP_SWIZZLE_32B))
     return e;
+  tmBias = tmQ;
+  }
   CUtensorMap tmO;
   {
     const uint64_t pitch = uint64_t(p.o_pitch) * 2;
@@ -425,7 +526,7 @@ int launch_window(const void* q, const void* k, const void* v, long long rows, l
   if (items > 0x7fffffffLL) return SAMB_E_SHAPE;
   p.items = int(items);
   const long long grid = items < sm_count() ? items : sm_count();
-  kern<<<unsigned(grid), NUM_THREADS, L::BYTES, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmO, p);
+  kern<<<unsigned(grid), NUM_THREADS, L::BYTES, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmO, tmBias, p);
   return launch_status();
 }
 
@@ -486,6 +587,37 @@ int samb_attn_relpos_window_qkv(const void* qkv, const void* tab, int64_t ldt, i
   const long long rows = 3LL * H * W * window * window;
   return d == 80 ? launch_window<80, 14>(qkv, qkv, qkv, rows, d, p, W * H, stream)
                  : launch_window<64, 14>(qkv, qkv, qkv, rows, d, p, W * H, stream);
+}
+
+int samb_attn_relpos_window_raster(const void* qkv, const void* qkv_bias, const void* tab, int64_t ldt,
+                                   int t_head_stride, int t_w_off, void* o, int64_t o_pitch, int B, int H, int grid,
+                                   int window, int d, float scale, int32_t* status, void* stream) {
+  using namespace samb;
+  if (!qkv || !qkv_bias || !tab || !o || !status) return SAMB_E_BADARG;
+  if (B <= 0 || H <= 0 || grid <= 0) return SAMB_E_BADARG;
+  if (window != 14 || (d != 64 && d != 80)) return SAMB_E_SHAPE;
+  const int nw = (grid + window - 1) / window;
+  const long long W = (long long)B * nw * nw;
+  if (3LL * H * B * grid * grid > 0x7fffffffLL || W * H > 0x7fffffffLL || o_pitch % 8 || o_pitch < (int64_t)H * d)
+    return SAMB_E_SHAPE;
+  if (ldt < (int64_t)H * t_head_stride || t_w_off + 2 * window - 1 > t_head_stride || 2 * window - 1 > t_w_off)
+    return SAMB_E_SHAPE;
+  if (ldt % 8 || t_head_stride % 64 || t_w_off % 8 || t_head_stride - t_w_off < 32 || t_w_off < 32) return SAMB_E_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(tab) | reinterpret_cast<uintptr_t>(qkv) |
+       reinterpret_cast<uintptr_t>(qkv_bias)) & 15u)
+    return SAMB_E_ALIGN;
+  if (int e = check_device_arch()) return e;
+  WinParams p{};
+  p.tab = static_cast<const __nv_bfloat16*>(tab);
+  p.ldt = ldt; p.t_head_stride = t_head_stride; p.t_w_off = t_w_off; p.rel_mode = 1;
+  p.o = static_cast<__nv_bfloat16*>(o);
+  p.o_pitch = o_pitch;
+  p.qkv_fused = 2;
+  p.H = H; p.grid = grid; p.nw = nw; p.B = B; p.vlast = grid - (nw - 1) * window;
+  p.scale = scale;
+  p.status = status;
+  return d == 80 ? launch_window<80, 14>(qkv, qkv, qkv, 0, d, p, W * H, stream, qkv_bias)
+                 : launch_window<64, 14>(qkv, qkv, qkv, 0, d, p, W * H, stream, qkv_bias);
 }
 
 }  // extern "C"

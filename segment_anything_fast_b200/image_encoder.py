@@ -197,6 +197,9 @@ class ImageEncoderViT(nn.Module):
                 "n1": (_f32(blk.norm1.weight), _f32(blk.norm1.bias), float(blk.norm1.eps)),
                 "n2": (_f32(blk.norm2.weight), _f32(blk.norm2.bias), float(blk.norm2.eps)),
                 "qkv": lin(blk.attn.qkv, sparse_ok=False), "proj": lin(blk.attn.proj),
+                # keys / values of the zero-padded tokens of border windows: the projection of a zero row
+                "qkv_b16": (_bf16(blk.attn.qkv.bias) if blk.attn.qkv.bias is not None
+                            else torch.zeros(3 * C, dtype=torch.bfloat16, device=dev)),
                 "lin1": lin(blk.mlp.lin1), "lin2": lin(blk.mlp.lin2),
                 "tab": tab, "tab_scale": cs, "T": T, "t_w_off": t_w_off,
             })
@@ -257,13 +260,13 @@ class ImageEncoderViT(nn.Module):
             taps["patch"] = cur.view(B, g, g, C)
         for i, bw in enumerate(pk["blocks"]):
             ws = bw["window"]
-            xn, xs = self._norm(cur, bw["n1"], grid=g if ws else 0, window=ws)
+            xn, xs = self._norm(cur, bw["n1"])          # raster order for both block kinds
             wq = bw["qkv"]
             qkv = (ops.gemm_heads(xn, xs, wq["wq"], wq["ws"], wq["b"], d) if self.quant == "int8"
                    else ops.gemm_heads(xn, None, wq["w"], None, wq["b"], d))          # [3H, rows, d]
             tab = ops.relpos_table_products(qkv, bw["tab"], bw["tab_scale"], H)
             if ws:
-                o = ops.attn_relpos_window_qkv(qkv, tab, bw["T"], bw["t_w_off"], B, H, g, ws, d)
+                o = ops.attn_relpos_window_raster(qkv, bw["qkv_b16"], tab, bw["T"], bw["t_w_off"], B, H, g, ws, d)
             else:
                 o = ops.attn_relpos_global_qkv(qkv, tab, bw["T"], bw["t_w_off"], B, H, g * g, d)
             del qkv, tab, xn

@@ -315,6 +315,28 @@ def attn_relpos_window_qkv(qkv: torch.Tensor, tab: torch.Tensor, t_head_stride: 
     return out
 
 
+def attn_relpos_window_raster(qkv: torch.Tensor, qkv_bias: torch.Tensor, tab: torch.Tensor, t_head_stride: int,
+                              t_w_off: int, B: int, H: int, grid: int, window: int, d: int,
+                              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Windowed attention over raster-order head-major ``qkv [3H, B*grid*grid, d]`` (no padded copy of the
+    tokens); ``qkv_bias`` is the projection bias as bf16 ``[3H*d]`` (the keys / values of the zero-padded
+    tokens of border windows).  Returns raster-order ``[B*grid*grid, H*d]``."""
+    _need(qkv, torch.bfloat16, "qkv"); _need(tab, torch.bfloat16, "tab"); _need(qkv_bias, torch.bfloat16, "qkv_bias")
+    if not qkv.is_contiguous() or qkv.shape != (3 * H, B * grid * grid, d):
+        raise RuntimeError("qkv must be contiguous [3H, B*grid*grid, d]")
+    if not qkv_bias.is_contiguous() or qkv_bias.numel() != 3 * H * d:
+        raise RuntimeError("qkv_bias must be contiguous [3H*d]")
+    tab = _rows2d(tab, "tab")
+    if out is None:
+        out = torch.empty(B * grid * grid, H * d, dtype=torch.bfloat16, device=qkv.device)
+    st = status_word(qkv.device)
+    _lib.check(_lib.load().samb_attn_relpos_window_raster(
+        qkv.data_ptr(), qkv_bias.data_ptr(), tab.data_ptr(), tab.stride(0), t_head_stride, t_w_off, out.data_ptr(),
+        out.stride(0), B, H, grid, window, d, float(d ** -0.5), st.data_ptr(), _stream()),
+        "samb_attn_relpos_window_raster")
+    return out
+
+
 def gemm_heads(a: torch.Tensor, a_scale: Optional[torch.Tensor], w: torch.Tensor, w_scale: Optional[torch.Tensor],
                bias: Optional[torch.Tensor], head_dim: int) -> torch.Tensor:
     """qkv projection with a head-major result ``[N/head_dim, M, head_dim]`` (bf16).  ``a``/``w`` are bf16,

@@ -132,3 +132,39 @@ def test_window_attention_fused_layout_with_padding(ops, B, H, d, grid):
     out = out.float().cpu()
     assert (out - ref).abs().max().item() < 2e-2
     assert _cos(out, ref) > 0.999
+
+
+@pytest.mark.parametrize("B,H,d,grid", [(2, 2, 80, 64), (1, 3, 64, 32), (1, 2, 80, 28), (3, 1, 80, 64)])
+def test_window_attention_raster_layout(ops, B, H, d, grid):
+    """Raster-order qkv in (no padded copy of the tokens): border windows take the projection bias as the
+    key / value of their pad tokens, exactly as the zero-padded, window-partitioned reference does."""
+    ws, C = 14, H * d
+    nw = -(-grid // ws)
+    torch.manual_seed(11)
+    x = torch.empty(B, grid, grid, 3 * C).normal_(0.0, 1.0).bfloat16().float()      # qkv of the real tokens
+    bias = torch.empty(3 * C).normal_(0.0, 0.5).bfloat16().float()
+    # reference: partition, pad rows carry the bias only (the projection of a zero row)
+    xp = torch.nn.functional.pad(x, (0, 0, 0, nw * ws - grid, 0, nw * ws - grid), value=float("nan"))
+    win, _ = eo.window_partition(xp, ws)
+    qkv = torch.where(torch.isnan(win), bias.expand_as(win), win).reshape(-1, 3 * C)
+    rph = torch.empty(2 * ws - 1, d).normal_(0.0, 0.1).bfloat16().float()
+    rpw = torch.empty(2 * ws - 1, d).normal_(0.0, 0.1).bfloat16().float()
+    W, N = B * nw * nw, ws * ws
+    t = qkv.reshape(W, N, 3, H, d).permute(2, 0, 3, 1, 4)
+    q, k, v = (t[i].reshape(W * H, N, d) for i in range(3))
+    rel_h, rel_w = eo.decomposed_rel_pos(q, rph, rpw, (ws, ws))
+    rel_h, rel_w = rel_h.bfloat16().float(), rel_w.bfloat16().float()
+    o = eo.attention_rel_h_rel_w(q, k, v, rel_h, rel_w).reshape(W, H, ws, ws, d).permute(0, 2, 3, 1, 4)
+    ref = eo.window_unpartition(o.reshape(W, ws, ws, C), ws, (nw * ws, nw * ws), (grid, grid)).reshape(-1, C)
+    tables = torch.zeros(64, d, dtype=torch.bfloat16)
+    tables[:27], tables[32:59] = rph.bfloat16(), rpw.bfloat16()
+    col_scale = torch.ones(64)
+    col_scale[32:] = math.sqrt(d)
+    qkv_hm = x.bfloat16().reshape(B * grid * grid, 3 * H, d).permute(1, 0, 2).contiguous().cuda()   # raster planes
+    tab = ops.relpos_table_products(qkv_hm, tables.cuda(), col_scale.cuda(), H)
+    out = ops.attn_relpos_window_raster(qkv_hm, bias.bfloat16().cuda(), tab, 64, 32, B, H, grid, ws, d)
+    ops.check_status()
+    out = out.float().cpu()
+    print(f"raster window attention grid {grid}: max-abs {(out - ref).abs().max().item():.4f} cos {_cos(out, ref):.6f}")
+    assert (out - ref).abs().max().item() < 2e-2
+    assert _cos(out, ref) > 0.999
