@@ -19,12 +19,10 @@
 // rows N..207 of the K/V box belong to the next window and their probabilities are written as zero.
 // Raster layout (qkv_fused 2): q/k/v stay in raster token order and never hold pad tokens.  A window is
 // gathered by WS x WS TMA boxes whose out-of-range part (border windows) is zero-filled.  A pad token's
-// key and value are the projection biases (its LayerNorm output is zero), so row N of K / V receives
-// k_bias / v_bias of the head: logit column N is q . k_bias, which the softmax adds to the logits of
-// the pad keys (whose own K rows are zero, their columns hold only the rel_w part), and column N of P
-// receives the summed probability of the pad keys, so that P V adds (sum of pad P) * v_bias.
-#include <type_traits>
-
+// key and value are the projection biases (its LayerNorm output is zero), so for border windows the
+// softmax warps overwrite the pad rows of the K tile (tile-0 warps) and of the V tile (tile-1 warps) with
+// k_bias / v_bias of the head before they release the tile's first product; from there on a pad key is
+// an ordinary key, exactly as in the padded layouts.
 #include "common.cuh"
 
 namespace samb {
@@ -47,6 +45,7 @@ struct WinParams {
   int qkv_fused;                 // 0: q/k/v/o are [W*H*N, d]; 1: head-major qkv [3H][W*N][d], o rows are raster tokens
   int H, grid, nw;               // raster side and windows per side (fused modes)
   int B, vlast;                  // raster mode: images, valid extent of the last window of a row / column
+  const __nv_bfloat16* kv_bias;  // raster mode: qkv projection bias [3H * D] (keys / values of pad tokens)
   int items;                     // number of (window, head) pairs
   float scale;
   int* status;
@@ -66,9 +65,9 @@ struct WinSmem {
   static constexpr int OFF_RELW = STAGES * STAGE;    // [256][16] bf16, 32B swizzle (per item)
   static constexpr int OFF_E = OFF_RELW + Q_CHUNK;   // [NK][16] bf16 one-hot (constant)
   static constexpr int OFF_BAR = OFF_E + KV_CHUNK;
-  static constexpr int BYTES = OFF_BAR + 256 + 1024;
+  static constexpr int OFF_PADTAB = OFF_BAR + 256;   // [3][N] key index of the i-th pad token per border-window kind
+  static constexpr int BYTES = OFF_PADTAB + 3 * 256 + 1024;
   static_assert(N <= 256 && NK <= 256 && WS <= 16, "window too large for this kernel");
-  static_assert(N < NK && (N * 32) % 128 == 0, "raster mode keeps the bias row at key index N (a 128-byte aligned copy target)");
   static_assert(STAGE % 1024 == 0 && NK / 2 <= kOCol && kOCol + D <= 256, "layout");
 };
 
@@ -86,23 +85,22 @@ __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) { return __
 template <int D, int WS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
-                   const __grid_constant__ CUtensorMap tmBias, const WinParams p) {
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const WinParams p) {
   using L = WinSmem<D, WS>;
   constexpr int N = L::N, NK = L::NK, CH = L::CH;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
   uint64_t* full = bars + 0;        // [STAGES] q/k/v of an item have landed
-  uint64_t* empty = bars + 2;       // [STAGES] every MMA reading the stage has finished
-  uint64_t* pro_done = bars + 4;    //          this item's rel_w tile is in shared memory
-  uint64_t* s_full = bars + 5;      // [2]      logits of tile t are in TMEM
-  uint64_t* p_full = bars + 7;      // [2]      P of tile t is in TMEM
-  uint64_t* o_full = bars + 9;      // [2]      P V of tile t is in TMEM
-  uint64_t* t_free = bars + 11;     // [2]      tile t's TMEM columns may be overwritten (O has been read)
-  uint64_t* out_ready = bars + 13;  //          all rows of the item's output are staged in shared memory
+  uint64_t* empty = bars + 2;       // [STAGES] every MMA reading the stage has finished and its output store was read
+  uint64_t* pro_done = bars + 4;    // [2]      this item's rel_w rows of tile t are in shared memory
+  uint64_t* s_full = bars + 6;      // [2]      logits of tile t are in TMEM
+  uint64_t* p_full = bars + 8;      // [2]      P of tile t is in TMEM
+  uint64_t* o_full = bars + 10;     // [2]      P V of tile t is in TMEM
+  uint64_t* t_free = bars + 12;     // [2]      tile t's TMEM columns may be overwritten (O has been read)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  unsigned int* out_cnt = reinterpret_cast<unsigned int*>(tmem_slot + 2);   // [STAGES] softmax warps that staged their rows
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -110,23 +108,34 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     *abort_flag = 0;
     // a stage is free when the MMAs that read it have finished AND the output store staged in it has been read
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 2); }
-    mbar_init(pro_done, 8);
-    mbar_init(out_ready, 8);
+    out_cnt[0] = out_cnt[1] = 0u;
     for (int t = 0; t < 2; ++t) {
+      mbar_init(&pro_done[t], 4);
       mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 4); mbar_init(&o_full[t], 1); mbar_init(&t_free[t], 4);
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmO);
-    if (p.qkv_fused == 2) tma_prefetch_desc(&tmBias);
   }
   if (p.qkv_fused == 2) {
-    // rows N+1..NK-1 of every K / V chunk are never written by a copy in this mode: zero them once (their
+    // rows N..NK-1 of every K / V chunk are never written by a copy in this mode: zero them once (their
     // probabilities are zero, but 0 x stale bits must not be a NaN)
-    constexpr int kTail = NK - N - 1;
+    // pad-token lists: kind 0 = right border (columns >= vlast), 1 = bottom border (rows >= vlast), 2 = corner
+    for (int idx = threadIdx.x; idx < 3 * N; idx += NUM_THREADS) {
+      const int kind = idx / N, pi = idx - kind * N;
+      const int vy = kind == 0 ? WS : p.vlast, vx = kind == 1 ? WS : p.vlast;
+      const int n_right = vy * (WS - vx), n_pad = n_right + (WS - vy) * WS;
+      int r = 0;
+      if (pi < n_pad) {
+        if (pi < n_right) r = (pi / (WS - vx)) * WS + vx + pi % (WS - vx);
+        else r = (vy + (pi - n_right) / WS) * WS + (pi - n_right) % WS;
+      }
+      smem[L::OFF_PADTAB + kind * 256 + pi] = uint8_t(r);
+    }
+    constexpr int kTail = NK - N;
     for (int idx = threadIdx.x; idx < STAGES * 2 * CH * kTail * 2; idx += NUM_THREADS) {
       const int half = idx & 1, r = (idx >> 1) % kTail, c = (idx >> 1) / kTail % CH, kv = (idx >> 1) / (kTail * CH) % 2,
                 st = (idx >> 1) / (kTail * CH * 2);
-      uint8_t* row = smem + st * L::STAGE + (kv ? L::OFF_V : L::OFF_K) + c * L::KV_CHUNK + (N + 1 + r) * 32;
+      uint8_t* row = smem + st * L::STAGE + (kv ? L::OFF_V : L::OFF_K) + c * L::KV_CHUNK + (N + r) * 32;
       *reinterpret_cast<uint4*>(row + half * 16) = make_uint4(0u, 0u, 0u, 0u);
     }
     fence_proxy_async_smem();
@@ -156,14 +165,12 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           const int ww = p.nw * p.nw;
           const int b = w / ww, wi = w - b * ww;
           const int wy = wi / p.nw, wx = wi - wy * p.nw;
-          mbar_expect_tx(&full[stage], 3 * CH * N * 32 + 2 * CH * 32);
+          mbar_expect_tx(&full[stage], 3 * CH * N * 32);
 #pragma unroll
-          for (int c = 0; c < CH; ++c) {           // one WS x WS box per 16-column chunk, plus the bias rows
+          for (int c = 0; c < CH; ++c) {           // one WS x WS box per 16-column chunk
             tma_load_4d(st + c * L::Q_CHUNK, &tmQ, &full[stage], c * 16, wx * WS, wy * WS, h * p.B + b);
             tma_load_4d(st + L::OFF_K + c * L::KV_CHUNK, &tmQ, &full[stage], c * 16, wx * WS, wy * WS, (p.H + h) * p.B + b);
             tma_load_4d(st + L::OFF_V + c * L::KV_CHUNK, &tmQ, &full[stage], c * 16, wx * WS, wy * WS, (2 * p.H + h) * p.B + b);
-            tma_load_2d(st + L::OFF_K + c * L::KV_CHUNK + N * 32, &tmBias, &full[stage], c * 16, p.H + h);
-            tma_load_2d(st + L::OFF_V + c * L::KV_CHUNK + N * 32, &tmBias, &full[stage], c * 16, 2 * p.H + h);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
           continue;
@@ -185,43 +192,53 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const uint64_t de = make_smem_desc(smem_u32(smem + L::OFF_E), 16, 256, kSwizzle32B);
     // V: MN-major, column chunks KV_CHUNK apart (LBO), 8-key groups 256 B apart (SBO)
     const uint64_t dv0 = make_smem_desc(smem_u32(smem + L::OFF_V), L::KV_CHUNK, 256, kSwizzle32B);
+    // Issue order S0(k), PV1(k-1), S1(k), PV0(k): the two query tiles run half an item apart, so that one
+    // tile's softmax overlaps the other tile's products (and the next item's, for tile 0).
     uint32_t stage = 0, phase = 0, k = 0;
     bool ok = true;
+    auto issue_s = [&](int t, uint32_t par, uint64_t dq, uint64_t dk) -> bool {
+      if (!mbar_wait(&pro_done[t], par, abort_flag, p.status, 3)) return false;
+      if (!mbar_wait(&t_free[t], par ^ 1u, abort_flag, p.status, 4)) return false;
+      tc_fence_after();
+      if (elect_one()) {
+        const uint32_t d_tmem = tmem_base + t * 256;
+#pragma unroll
+        for (int c = 0; c < CH; ++c)
+          umma_f16_ss(d_tmem, dq + (c * L::Q_CHUNK + t * 4096) / 16, dk + c * (L::KV_CHUNK / 16), idesc_s, c != 0);
+        umma_f16_ss(d_tmem, drw + t * (4096 / 16), de, idesc_s, 1u);
+        tc_commit(&s_full[t]);
+      }
+      __syncwarp();
+      return true;
+    };
+    auto issue_pv = [&](int t, uint32_t par, uint64_t dv, uint32_t st) -> bool {     // A = P from TMEM, B = V
+      if (!mbar_wait(&p_full[t], par, abort_flag, p.status, 5)) return false;
+      tc_fence_after();
+      if (elect_one()) {
+        const uint32_t d_tmem = tmem_base + t * 256;
+#pragma unroll
+        for (int kk = 0; kk < L::KSTEPS; ++kk)
+          umma_f16_ts(d_tmem + kOCol, d_tmem + kk * 8, dv + kk * (512 / 16), idesc_o, kk != 0);
+        tc_commit(&o_full[t]);
+        if (t == 1) tc_commit(&empty[st]);         // everything that reads this stage has been issued
+      }
+      __syncwarp();
+      return true;
+    };
+    uint32_t prev_stage = 0;
     for (int it = blockIdx.x; ok && it < p.items; it += gridDim.x, ++k) {
       const uint32_t par = k & 1u;
       if (!(ok = mbar_wait(&full[stage], phase, abort_flag, p.status, 2))) break;
-      if (!(ok = mbar_wait(pro_done, par, abort_flag, p.status, 3))) break;
       const uint64_t dq = dq0 + stage * (L::STAGE / 16);
       const uint64_t dk = dq + L::OFF_K / 16;
-      const uint64_t dv = dv0 + stage * (L::STAGE / 16);
-      for (int t = 0; ok && t < 2; ++t) {          // logits of query tile t
-        if (!(ok = mbar_wait(&t_free[t], par ^ 1u, abort_flag, p.status, 4))) break;
-        tc_fence_after();
-        if (elect_one()) {
-          const uint32_t d_tmem = tmem_base + t * 256;
-#pragma unroll
-          for (int c = 0; c < CH; ++c)
-            umma_f16_ss(d_tmem, dq + (c * L::Q_CHUNK + t * 4096) / 16, dk + c * (L::KV_CHUNK / 16), idesc_s, c != 0);
-          umma_f16_ss(d_tmem, drw + t * (4096 / 16), de, idesc_s, 1u);
-          tc_commit(&s_full[t]);
-        }
-        __syncwarp();
-      }
-      for (int t = 0; ok && t < 2; ++t) {          // P V of query tile t: A = P from TMEM, B = V
-        if (!(ok = mbar_wait(&p_full[t], par, abort_flag, p.status, 5))) break;
-        tc_fence_after();
-        if (elect_one()) {
-          const uint32_t d_tmem = tmem_base + t * 256;
-#pragma unroll
-          for (int kk = 0; kk < L::KSTEPS; ++kk)
-            umma_f16_ts(d_tmem + kOCol, d_tmem + kk * 8, dv + kk * (512 / 16), idesc_o, kk != 0);
-          tc_commit(&o_full[t]);
-          if (t == 1) tc_commit(&empty[stage]);    // everything that reads this stage has been issued
-        }
-        __syncwarp();
-      }
+      if (!(ok = issue_s(0, par, dq, dk))) break;
+      if (k > 0 && !(ok = issue_pv(1, par ^ 1u, dv0 + prev_stage * (L::STAGE / 16), prev_stage))) break;
+      if (!(ok = issue_s(1, par, dq, dk))) break;
+      if (!(ok = issue_pv(0, par, dv0 + stage * (L::STAGE / 16), stage))) break;
+      prev_stage = stage;
       if (++stage == STAGES) { stage = 0; phase ^= 1u; }
     }
+    if (ok && k > 0) issue_pv(1, (k - 1) & 1u, dv0 + prev_stage * (L::STAGE / 16), prev_stage);
   } else {
     // ---------------------------------------------------------------- softmax (one thread = one query row)
     const int t = (warp - 2) >> 2;                               // query tile of this warp
@@ -324,92 +341,82 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             make_uint4(wpack2(rw[0], rw[1]), wpack2(rw[2], rw[3]), wpack2(rw[4], rw[5]), wpack2(rw[6], rw[7]));
         *reinterpret_cast<uint4*>(rrow + ((1 ^ sw) << 4)) =
             make_uint4(wpack2(rw[8], rw[9]), wpack2(rw[10], rw[11]), wpack2(rw[12], rw[13]), wpack2(rw[14], rw[15]));
+        if (p.qkv_fused == 2) {
+          // border window: pad tokens' K rows (tile-0 warps) / V rows (tile-1 warps) <- projection bias
+          const int wi = (it / p.H) % (p.nw * p.nw);
+          const int vy = wi / p.nw == p.nw - 1 ? p.vlast : WS, vx = wi % p.nw == p.nw - 1 ? p.vlast : WS;
+          if (vy < WS || vx < WS) {
+            const int h = it % p.H;
+            ok = mbar_wait(&full[k % STAGES], (k / STAGES) & 1u, abort_flag, p.status, 9);   // the zero fill has landed
+            const int n_pad = vy * (WS - vx) + (WS - vy) * WS;
+            const uint8_t* tabp = smem + L::OFF_PADTAB + (vy == WS ? 0 : (vx == WS ? 1 : 2)) * 256;
+            uint8_t* region = smem + (k % STAGES) * L::STAGE + (t == 0 ? L::OFF_K : L::OFF_V);
+            // thread = one 16-byte piece (of the 2 * CH per row) for every 12th pad row
+            const int tid = (warp & 3) * 32 + lane, piece = tid % (2 * CH), c = piece >> 1, hf = piece & 1;
+            if (ok && tid < 12 * 2 * CH) {
+              const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.kv_bias + (size_t)((t + 1) * p.H + h) * D) + piece);
+              for (int pi = tid / (2 * CH); pi < n_pad; pi += 12) {
+                const int r = tabp[pi];
+                *reinterpret_cast<uint4*>(region + c * L::KV_CHUNK + r * 32 + ((hf ^ ((r >> 2) & 1)) << 4)) = bv;
+              }
+            }
+          }
+        }
         fence_proxy_async_smem();
-        mbar_arrive_warp(pro_done);
+        mbar_arrive_warp(&pro_done[t]);
+        if (!ok) break;
       }
       const int it_next = it + gridDim.x;
       if (it_next < p.items) fetch_bias(it_next);               // lands while this item is being computed
 
       if (!(ok = mbar_wait(&s_full[t], par, abort_flag, p.status, 6))) break;
       tc_fence_after();
-      // valid extent of this window (raster mode: border windows are cut by the raster edge)
-      int vy = WS, vx = WS;
-      if (p.qkv_fused == 2) {
-        const int wi = (it / p.H) % (p.nw * p.nw);
-        if (wi / p.nw == p.nw - 1) vy = p.vlast;
-        if (wi % p.nw == p.nw - 1) vx = p.vlast;
+      // pass 1: per key-row maxima of the raw logits, then the row maximum of the biased logits
+      float mx[WS];
+#pragma unroll
+      for (int q = 0; q < WS; ++q) mx[q] = -INFINITY;
+      uint32_t rbuf[2][16];
+      tmem_ld_32x32b_x16(lane_addr, rbuf[0]);
+#pragma unroll
+      for (int c = 0; c < NK / 16; ++c) {
+        tmem_ld_wait();                                          // chunk c has landed
+        if (c + 1 < NK / 16) tmem_ld_32x32b_x16(lane_addr + (c + 1) * 16, rbuf[(c + 1) & 1]);   // next chunk in flight
+        const uint32_t(&r)[16] = rbuf[c & 1];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          const int j = c * 16 + u;
+          if (j < N) mx[j / WS] = fmaxf(mx[j / WS], __uint_as_float(r[u]));
+        }
       }
+      float m = -INFINITY;
+#pragma unroll
+      for (int q = 0; q < WS; ++q) m = fmaxf(m, fmaf(mx[q], c2, bh[q]));
+#pragma unroll
+      for (int q = 0; q < WS; ++q) bh[q] -= m;
+      // pass 2: probabilities -> packed bf16 P over the logit columns already consumed
       float l = 0.f;
-      // kPads: some keys of the window are pad tokens (kh >= vy or kw >= vx).  Their logit is their own
-      // column (rel_w part only, the K row is zero) plus column N (q . k_bias); their probabilities are
-      // also summed into column N of P.
-      auto softmax_tile = [&](auto pads_tag) {
-        constexpr bool kPads = decltype(pads_tag)::value;
-        float sb = 0.f;
-        if (kPads) {
-          uint32_t r[16];
-          tmem_ld_32x32b_x16(lane_addr + (N / 16) * 16, r);
-          tmem_ld_wait();
-          sb = __uint_as_float(r[N % 16]);
-        }
-        // pass 1: per key-row maxima of the raw logits, then the row maximum of the biased logits
-        float mx[WS];
+      tmem_ld_32x32b_x16(lane_addr, rbuf[0]);
 #pragma unroll
-        for (int q = 0; q < WS; ++q) mx[q] = -INFINITY;
+      for (int c = 0; c < NK / 16; ++c) {
+        tmem_ld_wait();                                          // chunk c has landed
+        if (c + 1 < NK / 16) tmem_ld_32x32b_x16(lane_addr + (c + 1) * 16, rbuf[(c + 1) & 1]);   // next chunk in flight
+        const uint32_t(&r)[16] = rbuf[c & 1];
+        float e[16];
 #pragma unroll
-        for (int c = 0; c < NK / 16; ++c) {
-          uint32_t r[16];
-          tmem_ld_32x32b_x16(lane_addr + c * 16, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int u = 0; u < 16; ++u) {
-            const int j = c * 16 + u;
-            if (j < N) {
-              float x = __uint_as_float(r[u]);
-              if (kPads && (j / WS >= vy || j % WS >= vx)) x += sb;
-              mx[j / WS] = fmaxf(mx[j / WS], x);
-            }
+        for (int u = 0; u < 16; ++u) {
+          const int j = c * 16 + u;
+          e[u] = 0.f;
+          if (j < N) {
+            e[u] = wexp2(fmaf(__uint_as_float(r[u]), c2, bh[j / WS]));
+            l += e[u];
           }
         }
-        float m = -INFINITY;
-#pragma unroll
-        for (int q = 0; q < WS; ++q) m = fmaxf(m, fmaf(mx[q], c2, bh[q]));
-#pragma unroll
-        for (int q = 0; q < WS; ++q) bh[q] -= m;
-        // pass 2: probabilities -> packed bf16 P over the logit columns already consumed
-        float lpad = 0.f;
-        uint32_t rbuf[2][16];
-        tmem_ld_32x32b_x16(lane_addr, rbuf[0]);
-#pragma unroll
-        for (int c = 0; c < NK / 16; ++c) {
-          tmem_ld_wait();                                          // chunk c has landed
-          if (c + 1 < NK / 16) tmem_ld_32x32b_x16(lane_addr + (c + 1) * 16, rbuf[(c + 1) & 1]);   // next chunk in flight
-          const uint32_t(&r)[16] = rbuf[c & 1];
-          float e[16];
-#pragma unroll
-          for (int u = 0; u < 16; ++u) {
-            const int j = c * 16 + u;
-            e[u] = 0.f;
-            if (j < N) {
-              float x = __uint_as_float(r[u]);
-              const bool pad = kPads && (j / WS >= vy || j % WS >= vx);
-              if (pad) x += sb;
-              e[u] = wexp2(fmaf(x, c2, bh[j / WS]));
-              l += e[u];
-              if (pad) lpad += e[u];
-            } else if (kPads && j == N) {
-              e[u] = lpad;                                         // every pad key has been visited by now
-            }
-          }
-          const uint32_t pk[8] = {wpack2(e[0], e[1]), wpack2(e[2], e[3]), wpack2(e[4], e[5]), wpack2(e[6], e[7]),
-                                  wpack2(e[8], e[9]), wpack2(e[10], e[11]), wpack2(e[12], e[13]), wpack2(e[14], e[15])};
-          // columns [8c, 8c+8) hold logits 16..31 of chunk c/2, consumed in an earlier iteration (for c = 0:
-          // chunk 0 itself, already in registers; chunk 1, in flight, starts at column 16)
-          tmem_st_32x32b_x8(lane_addr + c * 8, pk);
-        }
-      };
-      if (vy < WS || vx < WS) softmax_tile(std::true_type{});
-      else softmax_tile(std::false_type{});
+        const uint32_t pk[8] = {wpack2(e[0], e[1]), wpack2(e[2], e[3]), wpack2(e[4], e[5]), wpack2(e[6], e[7]),
+                                wpack2(e[8], e[9]), wpack2(e[10], e[11]), wpack2(e[12], e[13]), wpack2(e[14], e[15])};
+        // columns [8c, 8c+8) hold logits 16..31 of chunk c/2, consumed in an earlier iteration (for c = 0:
+        // chunk 0 itself, already in registers; chunk 1, in flight, starts at column 16)
+        tmem_st_32x32b_x8(lane_addr + c * 8, pk);
+      }
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive_warp(&p_full[t]);
@@ -439,25 +446,34 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
       fence_proxy_async_smem();
-      mbar_arrive_warp(out_ready);                               // all eight softmax warps arrive
-      if (warp == 2 && lane == 0 && mbar_wait(out_ready, par, abort_flag, p.status, 8)) {
-        int cx = 0, cy = 0, cz = 0, cw = it;
-        if (p.qkv_fused) {
-          const int w = it / p.H, h = it - w * p.H;
-          const int ww = p.nw * p.nw;
-          const int b = w / ww, wi = w - b * ww;
-          const int wy = wi / p.nw, wx = wi - wy * p.nw;
-          cx = h * D; cy = wx * WS; cz = wy * WS; cw = b;
+      // the last of the eight softmax warps to stage its rows sends the item's store
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence_block();
+        const unsigned int prior = atomicAdd(&out_cnt[k % STAGES], 1u);
+        if (prior == 7u) {
+          __threadfence_block();
+          out_cnt[k % STAGES] = 0u;
+          fence_proxy_async_smem();
+          int cx = 0, cy = 0, cz = 0, cw = it;
+          if (p.qkv_fused) {
+            const int w = it / p.H, h = it - w * p.H;
+            const int ww = p.nw * p.nw;
+            const int b = w / ww, wi = w - b * ww;
+            const int wy = wi / p.nw, wx = wi - wy * p.nw;
+            cx = h * D; cy = wx * WS; cz = wy * WS; cw = b;
+          }
+          tma_store_4d(&tmO, stg, cx, cy, cz, cw);
+          tma_store_commit();
+          tma_store_wait_read<0>();                              // the staging rows have been read
+          mbar_arrive(&empty[k % STAGES]);
         }
-        tma_store_4d(&tmO, stg, cx, cy, cz, cw);
-        tma_store_commit();
-        tma_store_wait_read<0>();                                // the staging rows have been read
-        mbar_arrive(&empty[k % STAGES]);
       }
+      __syncwarp();
     }
+    if (lane == 0) tma_store_wait_all<0>();
   }
 
-  if (warp == 2 && lane == 0) tma_store_wait_all<0>();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -468,9 +484,9 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
 template <int D, int WS>
 int launch_window(const void* q, const void* k, const void* v, long long rows, long long cols, WinParams p,
-                  long long items, void* stream, const void* qkv_bias = nullptr) {
+                  long long items, void* stream) {
   using L = WinSmem<D, WS>;
-  CUtensorMap tmQ, tmK, tmV, tmBias;
+  CUtensorMap tmQ, tmK, tmV;
   if (p.qkv_fused == 2) {
     // raster planes [3H * B][grid][grid][D]: one WS x WS box of 16 columns per copy
     const uint64_t g = uint64_t(p.grid);
@@ -481,12 +497,6 @@ int launch_window(const void* q, const void* k, const void* v, long long rows, l
                                 CU_TENSOR_MAP_SWIZZLE_32B))
       return e;
     tmK = tmV = tmQ;
-    const uint64_t bdims[2] = {uint64_t(D), uint64_t(3) * p.H};
-    const uint64_t bstrides[2] = {2, uint64_t(D) * 2};
-    const uint32_t bbox[2] = {16, 1};
-    if (int e = make_tensor_map(&tmBias, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(qkv_bias), bdims, bstrides,
-                                bbox, CU_TENSOR_MAP_SWIZZLE_32B))
-      return e;
   } else {
   const uint64_t dims[3] = {16, uint64_t(rows), uint64_t(cols / 16)};
   const uint64_t strides[3] = {2, uint64_t(cols) * 2, 32};
@@ -501,7 +511,6 @@ int launch_window(const void* q, const void* k, const void* v, long long rows, l
   if (int e = make_tensor_map(&tmV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(v), dims, strides, box_kv,
                               CU_TENSOR_MAP_SWIZZLE_32B))
     return e;
-  tmBias = tmQ;
   }
   CUtensorMap tmO;
   {
@@ -526,7 +535,7 @@ int launch_window(const void* q, const void* k, const void* v, long long rows, l
   if (items > 0x7fffffffLL) return SAMB_E_SHAPE;
   p.items = int(items);
   const long long grid = items < sm_count() ? items : sm_count();
-  kern<<<unsigned(grid), NUM_THREADS, L::BYTES, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmO, tmBias, p);
+  kern<<<unsigned(grid), NUM_THREADS, L::BYTES, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmO, p);
   return launch_status();
 }
 
@@ -614,10 +623,11 @@ int samb_attn_relpos_window_raster(const void* qkv, const void* qkv_bias, const 
   p.o_pitch = o_pitch;
   p.qkv_fused = 2;
   p.H = H; p.grid = grid; p.nw = nw; p.B = B; p.vlast = grid - (nw - 1) * window;
+  p.kv_bias = static_cast<const __nv_bfloat16*>(qkv_bias);
   p.scale = scale;
   p.status = status;
-  return d == 80 ? launch_window<80, 14>(qkv, qkv, qkv, 0, d, p, W * H, stream, qkv_bias)
-                 : launch_window<64, 14>(qkv, qkv, qkv, 0, d, p, W * H, stream, qkv_bias);
+  return d == 80 ? launch_window<80, 14>(qkv, qkv, qkv, 0, d, p, W * H, stream)
+                 : launch_window<64, 14>(qkv, qkv, qkv, 0, d, p, W * H, stream);
 }
 
 }  // extern "C"
