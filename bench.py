@@ -248,7 +248,8 @@ def run_b200(args):
         "e2e": {"value": round(world * BATCH * args.steps / (e2e_ms * 1e-3), 2), "unit": "img/s",
                 "h2d_bytes_per_step": sess.h2d_bytes, "d2h_bytes_per_step": sess.d2h_bytes},
         "gpu_launches": launches,
-        "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel" + (" + gemm_sp24_kernel" if sparse_mlp else "") + " (qkv/proj/lin1/lin2 launches)",
+        "roofline": {"bound": "tensor", "kernel": ("gemm_pair_kernel" if quant is None else "gemm_pair_kernel / gemm_tc_kernel")
+                               + (" + gemm_sp24_kernel" if sparse_mlp else "") + " (qkv/proj/lin1/lin2 launches)",
                      "achieved": None if achieved is None else round(achieved, 1), "peak": peak_tf, "unit": "TFLOP/s",
                      "frac": None if achieved is None else round(achieved / peak_tf, 4),
                      "traffic": GEMM_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": peak_note,

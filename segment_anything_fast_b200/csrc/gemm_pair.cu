@@ -1,0 +1,391 @@
+// The Linear-layer GEMM on CTA pairs (thread-block clusters of two, tcgen05 cta_group::2):
+//   out[M,N] = epilogue( A[M,K] * W[N,K]^T ),  N a multiple of 256.
+// A pair owns a 256 x 256 output tile.  Each CTA streams its own 128 rows of A and its own half (128 rows)
+// of the W tile; one MMA issued by the pair's leader (M = 256, N = 256) reads A and half of W from each
+// CTA's shared memory and accumulates into both CTAs' tensor memory (128 rows each).  Against the
+// single-CTA kernel this halves the W bytes every CTA loads and reads per MMA (8 instead of 12 KB of
+// operands per 128 tensor-pipe cycles), which is what the single-CTA kernel is bound by, and leaves room
+// for a 6-deep ring.  Roles per CTA as in the single-CTA kernel: warp 0 TMA producer, warp 1 MMA issue
+// (leader CTA only), warps 2..9 epilogue of the CTA's own 128 rows.
+// Barriers: `full` lives in the leader (both CTAs' copies are counted there), `empty` and `acc_full`
+// exist in both CTAs and receive one commit each from the leader, `acc_empty` lives in the leader and
+// counts the epilogue warps of both CTAs.  No copy is multicast.
+#include "common.cuh"
+
+namespace samb {
+
+namespace {
+
+constexpr int BM = 128;                        // rows per CTA (256 per pair)
+constexpr int BN = 256;
+constexpr int SLAB_BYTES = 128;
+constexpr int STAGES = 6;
+constexpr int A_STAGE_BYTES = BM * SLAB_BYTES;          // 16 KiB: this CTA's rows of A
+constexpr int B_STAGE_BYTES = (BN / 2) * SLAB_BYTES;    // 16 KiB: this CTA's half of the W tile
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int NUM_ACC = 2;
+constexpr int TMEM_COLS = NUM_ACC * BN;
+constexpr int NUM_THREADS = 320;
+constexpr int OUT_STAGE_BYTES = BM * 128;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_STAGE_BYTES + 2 * BN * 4 + 1024 + 256;
+
+struct PairParams {
+  void* out;
+  const float* bias;
+  const __nv_bfloat16* residual;
+  const float* a_scale;
+  const float* w_scale;
+  int* status;
+  long long M;
+  long long ldr, res_rows;
+  int N, K;
+  int k_slabs, last_ksteps;
+  int tiles_n;
+  long long num_tiles;
+  int hm_group;
+};
+
+__device__ __forceinline__ bool epi_all(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.and.pred p, 1, 256, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"(uint32_t(pred))
+      : "memory");
+  return r != 0;
+}
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+template <bool kInt8, int kEpi>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmOut, const PairParams p) {
+  constexpr bool kBias = (kEpi & SAMB_EPI_BIAS) != 0;
+  constexpr bool kGelu = (kEpi & SAMB_EPI_GELU) != 0;
+  constexpr bool kRes = (kEpi & SAMB_EPI_RESIDUAL) != 0;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage_out = smem + STAGES * STAGE_BYTES;
+  float* s_bias = reinterpret_cast<float*>(stage_out + OUT_STAGE_BYTES);
+  float* s_wscale = s_bias + BN;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_wscale + BN);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;
+  uint64_t* acc_empty = acc_full + NUM_ACC;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + NUM_ACC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();               // 0 = leader of the pair
+  const long long pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < NUM_ACC; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 16);                      // eight epilogue warps of each CTA
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmOut);
+  }
+  cluster_sync_all();                                    // both CTAs' barriers exist before any remote use
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int slab_elems = kInt8 ? SLAB_BYTES : SLAB_BYTES / 2;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      const uint32_t full0 = map_to_cta(&full_bar[0], 0);            // the leader's barriers
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (long long tile = pair; ok && tile < p.num_tiles; tile += num_pairs) {
+        const int m0 = int(tile / p.tiles_n) * (2 * BM) + int(rank) * BM;
+        const int n0 = int(tile % p.tiles_n) * BN + int(rank) * (BN / 2);
+        for (int ks = 0; ks < p.k_slabs; ++ks) {
+          if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 1))) break;
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);   // both CTAs' copies
+          tma_load_2d_pair(sa, &tmA, full0 + stage * 8, ks * slab_elems, m0);
+          tma_load_2d_pair(sa + A_STAGE_BYTES, &tmB, full0 + stage * 8, ks * slab_elems, n0);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issue (leader CTA only)
+    if (rank == 0) {
+      const uint32_t idesc = kInt8 ? make_idesc(kAccS32, kFmtS8, kFmtS8, 2 * BM, BN)
+                                   : make_idesc(kAccF32, kFmtBF16, kFmtBF16, 2 * BM, BN);
+      const uint64_t desc0 = make_smem_desc(smem_u32(smem), 16, 1024, kSwizzle128B);
+      const uint32_t empty_own = map_to_cta(&empty_bar[0], 0), empty_peer = map_to_cta(&empty_bar[0], 1);
+      const uint32_t accf_own = map_to_cta(&acc_full[0], 0), accf_peer = map_to_cta(&acc_full[0], 1);
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (long long tile = pair; ok && tile < p.num_tiles; tile += num_pairs) {
+        if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, 2))) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int ks = 0; ks < p.k_slabs; ++ks) {
+          if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3))) break;
+          tc_fence_after();
+          if (elect_one()) {
+            const uint64_t adesc = desc0 + stage * (STAGE_BYTES / 16);
+            const uint64_t bdesc = adesc + A_STAGE_BYTES / 16;
+            const int nsteps = ks == p.k_slabs - 1 ? p.last_ksteps : 4;
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) {
+              if (k4 >= nsteps) break;
+              const uint32_t accumulate = (ks | k4) != 0 ? 1u : 0u;
+              if (kInt8) umma_i8_ss_pair(d_tmem, adesc + k4 * 2, bdesc + k4 * 2, idesc, accumulate);
+              else umma_f16_ss_pair(d_tmem, adesc + k4 * 2, bdesc + k4 * 2, idesc, accumulate);
+            }
+            tc_commit_pair(empty_own + stage * 8);        // the stage is reusable in both CTAs
+            tc_commit_pair(empty_peer + stage * 8);
+          }
+          __syncwarp();
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        if (elect_one()) {
+          tc_commit_pair(accf_own + acc * 8);             // accumulator complete in both CTAs
+          tc_commit_pair(accf_peer + acc * 8);
+        }
+        __syncwarp();
+        if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..9), own 128 rows
+    const uint32_t lane_base = uint32_t(warp & 3) * 32u;
+    const int half = (warp - 2) >> 2;
+    const int erow = int(lane_base) + lane;
+    const int et = int(threadIdx.x) - 64;
+    const uint32_t acc_empty0 = map_to_cta(&acc_empty[0], 0);        // the leader's barrier
+    uint32_t acc = 0, acc_phase = 0;
+    for (long long tile = pair; tile < p.num_tiles; tile += num_pairs) {
+      const int m0 = int(tile / p.tiles_n) * (2 * BM) + int(rank) * BM;
+      const int n0 = int(tile % p.tiles_n) * BN;
+      const long long row = (long long)m0 + erow;
+      const bool row_ok = row < p.M;
+      if (kBias) s_bias[et] = __ldg(p.bias + n0 + et);
+      if (kInt8) s_wscale[et] = __ldg(p.w_scale + n0 + et);
+      const bool got = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, 4);
+      if (!epi_all(got)) break;
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + (lane_base << 16) + acc * BN + half * 32;
+      float a_scale = 1.0f;
+      if (kInt8 && row_ok) a_scale = __ldg(p.a_scale + row);
+      const __nv_bfloat16* res_row = nullptr;
+      if (kRes && row_ok) res_row = p.residual + (row % p.res_rows) * p.ldr + n0 + half * 32;
+#pragma unroll 1
+      for (int c = 0; c < BN / 64; ++c) {
+        const int col0 = n0 + c * 64;
+        uint4 rv[4];
+        if (kRes) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            rv[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (row_ok) rv[u] = __ldg(reinterpret_cast<const uint4*>(res_row + c * 64) + u);
+          }
+        }
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_addr + c * 64, r);
+        tmem_ld_wait();
+        uint4 packed[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          float v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int cc = u * 8 + j;
+            const int ct = c * 64 + half * 32 + cc;
+            float x;
+            if (kInt8) x = __fmul_rn(__fmul_rn(float(int(r[cc])), a_scale), s_wscale[ct]);
+            else x = __uint_as_float(r[cc]);
+            if (kBias) x = __fadd_rn(x, s_bias[ct]);
+            if (kGelu) x = gelu_erf(x);
+            v[j] = x;
+          }
+          if (kRes) {
+            const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv[u]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = __bfloat1622float2(rp[j]);
+              v[2 * j] += f.x;
+              v[2 * j + 1] += f.y;
+            }
+          }
+          packed[u] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                                 pack_bf16x2(v[6], v[7]));
+        }
+        if (et == 0) tma_store_wait_read<0>();
+        epi_sync();
+        if (p.hm_group == 0) {
+          uint8_t* srow = stage_out + erow * 128;
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            *reinterpret_cast<uint4*>(srow + (((half * 4 + u) ^ (erow & 7)) << 4)) = packed[u];
+        } else {
+          uint8_t* srow = stage_out + erow * 32;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int unit = half * 4 + u;
+            *reinterpret_cast<uint4*>(srow + (unit >> 1) * 4096 + (((unit & 1) ^ ((erow >> 2) & 1)) << 4)) = packed[u];
+          }
+        }
+        fence_proxy_async_smem();
+        epi_sync();
+        if (et == 0) {
+          if (p.hm_group == 0) {
+            tma_store_2d(&tmOut, stage_out, col0, m0);
+          } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int g = (col0 + q * 16) >> 4;
+              tma_store_4d(&tmOut, stage_out + q * 4096, 0, g % p.hm_group, m0, g / p.hm_group);
+            }
+          }
+          tma_store_commit();
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty0 + acc * 8);
+      if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
+    }
+    if (et == 0) tma_store_wait_all<0>();
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                                    // no CTA leaves while its peer may still signal it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+using PairFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const PairParams);
+
+template <bool kInt8>
+PairFn pick_pair(int epi) {
+  switch (epi) {
+    case 0: return gemm_pair_kernel<kInt8, 0>;
+    case 1: return gemm_pair_kernel<kInt8, 1>;
+    case 3: return gemm_pair_kernel<kInt8, 3>;
+    case 5: return gemm_pair_kernel<kInt8, 5>;
+    default: return nullptr;
+  }
+}
+
+}  // namespace
+
+// Returns SAMB_E_SHAPE when the problem is outside what the pair kernel covers (the caller then uses the
+// single-CTA kernel); argument validity has been checked by the caller.
+int launch_gemm_pair(bool int8, const void* A, int64_t lda, const void* W, int64_t ldw, const float* a_scale,
+                     const float* w_scale, const float* bias, const void* residual, int64_t ldr, int64_t res_rows,
+                     void* out, int64_t ldo, int64_t M, int N, int K, int epilogue, int head_dim, int32_t* status,
+                     void* stream) {
+  if (N % BN || M < 8 * 2 * BM) return SAMB_E_SHAPE;
+  auto kern = int8 ? pick_pair<true>(epilogue) : pick_pair<false>(epilogue);
+  if (kern == nullptr) return SAMB_E_SHAPE;
+  const int esz = int8 ? 1 : 2;
+  const CUtensorMapDataType dt = int8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const uint32_t slab_elems = uint32_t(SLAB_BYTES / esz);
+  CUtensorMap tmA, tmB, tmOut;
+  {
+    const uint64_t dims[2] = {uint64_t(K), uint64_t(M)};
+    const uint64_t strides[2] = {uint64_t(esz), uint64_t(lda) * esz};
+    const uint32_t box[2] = {slab_elems, uint32_t(BM)};
+    if (int e = make_tensor_map(&tmA, dt, 2, const_cast<void*>(A), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return e;
+  }
+  {
+    const uint64_t dims[2] = {uint64_t(K), uint64_t(N)};
+    const uint64_t strides[2] = {uint64_t(esz), uint64_t(ldw) * esz};
+    const uint32_t box[2] = {slab_elems, uint32_t(BN / 2)};
+    if (int e = make_tensor_map(&tmB, dt, 2, const_cast<void*>(W), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return e;
+  }
+  if (head_dim) {
+    const uint64_t dims[4] = {16, uint64_t(head_dim / 16), uint64_t(M), uint64_t(N / head_dim)};
+    const uint64_t strides[4] = {2, 32, uint64_t(head_dim) * 2, uint64_t(M) * head_dim * 2};
+    const uint32_t box[4] = {16, 1, uint32_t(BM), 1};
+    if (int e = make_tensor_map(&tmOut, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, out, dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_32B))
+      return e;
+  } else {
+    const uint64_t dims[2] = {uint64_t(N), uint64_t(M)};
+    const uint64_t strides[2] = {2, uint64_t(ldo) * 2};
+    const uint32_t box[2] = {64, uint32_t(BM)};
+    if (int e = make_tensor_map(&tmOut, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_128B))
+      return e;
+  }
+  PairParams p;
+  p.out = out;
+  p.bias = bias;
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.a_scale = a_scale;
+  p.w_scale = w_scale;
+  p.status = status;
+  p.M = M;
+  p.ldr = ldr;
+  p.res_rows = res_rows > 0 ? res_rows : 1;
+  p.N = N;
+  p.K = K;
+  p.k_slabs = (K * esz + SLAB_BYTES - 1) / SLAB_BYTES;
+  p.last_ksteps = (K * esz - (p.k_slabs - 1) * SLAB_BYTES + 31) / 32;
+  p.tiles_n = N / BN;
+  p.num_tiles = ((M + 2 * BM - 1) / (2 * BM)) * p.tiles_n;
+  p.hm_group = head_dim / 16;
+
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    return SAMB_E_LAUNCH;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cfg.gridDim = dim3(unsigned(sm_count() & ~1));
+  static int cached_clusters[2][8] = {};                  // co-resident pairs per kernel variant (0 = not asked yet)
+  int& max_clusters = cached_clusters[int8 ? 1 : 0][epilogue & 7];
+  if (max_clusters == 0 &&
+      (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) != cudaSuccess || max_clusters < 1)) {
+    cudaGetLastError();
+    max_clusters = -1;
+  }
+  if (max_clusters < 1) return SAMB_E_SHAPE;              // pairs cannot be placed: single-CTA kernel
+  long long pairs = max_clusters < sm_count() / 2 ? max_clusters : sm_count() / 2;
+  if (p.num_tiles < pairs) pairs = p.num_tiles;
+  cfg.gridDim = dim3(unsigned(2 * pairs));
+  if (cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmOut, p) != cudaSuccess) {
+    cudaGetLastError();
+    return SAMB_E_LAUNCH;
+  }
+  return launch_status();
+}
+
+}  // namespace samb

@@ -7,6 +7,8 @@
 // next tile is being multiplied.
 // The bf16 (kind::f16) and int8 (kind::i8) variants share every byte offset: 128 bytes of K are
 // 64 bf16 (4 MMAs of K=16) or 128 int8 (4 MMAs of K=32).
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace samb {
@@ -423,6 +425,14 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
     return SAMB_E_ALIGN;
   if (int e = check_device_arch()) return e;
   if (M == 0) return SAMB_OK;
+  // Large plain products run on CTA pairs; SAMB_GEMM_SINGLE_CTA=1 keeps them on this file's kernel (A/B timing).
+  // int8 products with a short K are bound by their epilogue, which the pair's shared accumulator hand-off
+  // only couples more tightly: they stay on the single-CTA kernel.
+  if (!raw && batch == 1 && epilogue != EPI_COLSCALE && (!int8 || K >= 2048) && getenv("SAMB_GEMM_SINGLE_CTA") == nullptr) {
+    const int e = launch_gemm_pair(int8, A, lda, W, ldw, a_scale, w_scale, bias, residual, ldr, res_rows, out, ldo, M, N, K,
+                                   epilogue, head_dim, status, stream);
+    if (e != SAMB_E_SHAPE) return e;
+  }
 
   const CUtensorMapDataType dt = int8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const uint32_t slab_elems = uint32_t(SLAB_BYTES / esz);
