@@ -74,6 +74,10 @@ int samb_layernorm_quant_i8(const void* x, const float* gamma, const float* beta
 
 /* Per-row symmetric int8 quantisation of x[rows, C] (bf16), same formula. */
 int samb_quant_rows_i8(const void* x, int8_t* yq, float* scale, int64_t rows, int C, void* stream);
+/* The same after the exact (erf) GELU: yq, scale = quantise(bf16(gelu(x))): the MLP's activation
+ * (modeling/common.py:25-26, act between lin1 and lin2) applied to a bf16 lin1 output that was produced
+ * without the GELU epilogue. */
+int samb_gelu_quant_rows_i8(const void* x, int8_t* yq, float* scale, int64_t rows, int C, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * out[M, N] = epilogue(A[M, K] * W[N, K]^T), bf16 operands, fp32 accumulation on tcgen05 tensor

@@ -23,6 +23,7 @@ SIGNATURES = {
     "samb_layernorm_bf16": (c_int, [_P, _P, _P, _P, c_int64, c_int, c_float, c_int, c_int, _P]),
     "samb_layernorm_quant_i8": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int, c_float, c_int, c_int, _P]),
     "samb_quant_rows_i8": (c_int, [_P, _P, _P, c_int64, c_int, _P]),
+    "samb_gelu_quant_rows_i8": (c_int, [_P, _P, _P, c_int64, c_int, _P]),
     "samb_gemm_bf16": (c_int, [_P, c_int64, _P, c_int64, _P, _P, c_int64, c_int64, _P, c_int64, c_int64, c_int,
                                c_int, c_int, _P, _P]),
     "samb_gemm_i8": (c_int, [_P, c_int64, _P, _P, c_int64, _P, _P, _P, c_int64, c_int64, _P, c_int64, c_int64,

@@ -6,7 +6,8 @@
 // single-CTA kernel this halves the W bytes every CTA loads and reads per MMA (8 instead of 12 KB of
 // operands per 128 tensor-pipe cycles), which is what the single-CTA kernel is bound by, and leaves room
 // for a 6-deep ring.  Roles per CTA as in the single-CTA kernel: warp 0 TMA producer, warp 1 MMA issue
-// (leader CTA only), warps 2..9 epilogue of the CTA's own 128 rows.
+// (leader CTA only), warps 2..17 epilogue of the CTA's own 128 rows (four warps per tensor-memory lane
+// quarter, 16 of every 64 columns each: the int8 epilogues are issue-bound with fewer).
 // Barriers: `full` lives in the leader (both CTAs' copies are counted there), `empty` and `acc_full`
 // exist in both CTAs and receive one commit each from the leader, `acc_empty` lives in the leader and
 // counts the epilogue warps of both CTAs.  No copy is multicast.
@@ -25,7 +26,7 @@ constexpr int B_STAGE_BYTES = (BN / 2) * SLAB_BYTES;    // 16 KiB: this CTA's ha
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int NUM_ACC = 2;
 constexpr int TMEM_COLS = NUM_ACC * BN;
-constexpr int NUM_THREADS = 320;
+constexpr int MAX_THREADS = 576;                // TMA warp, MMA warp, up to 16 epilogue warps
 constexpr int OUT_STAGE_BYTES = BM * 128;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_STAGE_BYTES + 2 * BN * 4 + 1024 + 256;
 
@@ -45,25 +46,33 @@ struct PairParams {
   int hm_group;
 };
 
+template <int kThreads>
 __device__ __forceinline__ bool epi_all(bool pred) {
   uint32_t r;
   asm volatile(
       "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\t"
-      "bar.red.and.pred p, 1, 256, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      "bar.red.and.pred p, 1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(r)
-      : "r"(uint32_t(pred))
+      : "r"(uint32_t(pred)), "n"(kThreads)
       : "memory");
   return r != 0;
 }
-__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+template <int kThreads>
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory"); }
 
-template <bool kInt8, int kEpi>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// kEpiWarps: 8 (two warps per tensor-memory lane quarter, 32 of every 64 columns each) or 16 (four per
+// quarter, 16 columns each).  The cheap int8 epilogues are issue-latency bound and gain from 16; the
+// bf16 ones are hidden behind the longer bf16 products either way and save barrier traffic with 8.
+template <bool kInt8, int kEpi, int kEpiWarps>
+__global__ void __launch_bounds__(64 + 32 * kEpiWarps, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmOut, const PairParams p) {
   constexpr bool kBias = (kEpi & SAMB_EPI_BIAS) != 0;
   constexpr bool kGelu = (kEpi & SAMB_EPI_GELU) != 0;
   constexpr bool kRes = (kEpi & SAMB_EPI_RESIDUAL) != 0;
+  constexpr int EPI_THREADS = 32 * kEpiWarps;
+  constexpr int CW = 64 / (kEpiWarps / 4);               // columns of a 64-column chunk per warp: 32 or 16
+  constexpr int NV = CW / 8;                             // 16-byte output pieces per thread and chunk
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_out = smem + STAGES * STAGE_BYTES;
@@ -89,7 +98,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int a = 0; a < NUM_ACC; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 16);                      // eight epilogue warps of each CTA
+      mbar_init(&acc_empty[a], 2 * EPI_THREADS / 32);    // the epilogue warps of both CTAs
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
@@ -170,9 +179,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..9), own 128 rows
+    // ------------------------------------------------------------------ epilogue warps, own 128 rows
     const uint32_t lane_base = uint32_t(warp & 3) * 32u;
-    const int half = (warp - 2) >> 2;
+    const int qc = (warp - 2) >> 2;                      // which CW columns of every 64-column chunk
     const int erow = int(lane_base) + lane;
     const int et = int(threadIdx.x) - 64;
     const uint32_t acc_empty0 = map_to_cta(&acc_empty[0], 0);        // the leader's barrier
@@ -182,42 +191,53 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int n0 = int(tile % p.tiles_n) * BN;
       const long long row = (long long)m0 + erow;
       const bool row_ok = row < p.M;
-      if (kBias) s_bias[et] = __ldg(p.bias + n0 + et);
-      if (kInt8) s_wscale[et] = __ldg(p.w_scale + n0 + et);
+      if (et < BN) {
+        if (kBias) s_bias[et] = __ldg(p.bias + n0 + et);
+        if (kInt8) s_wscale[et] = __ldg(p.w_scale + n0 + et);
+      }
       const bool got = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, 4);
-      if (!epi_all(got)) break;
+      if (!epi_all<EPI_THREADS>(got)) break;
       tc_fence_after();
-      const uint32_t t_addr = tmem_base + (lane_base << 16) + acc * BN + half * 32;
+      const uint32_t t_addr = tmem_base + (lane_base << 16) + acc * BN + qc * CW;
       float a_scale = 1.0f;
       if (kInt8 && row_ok) a_scale = __ldg(p.a_scale + row);
       const __nv_bfloat16* res_row = nullptr;
-      if (kRes && row_ok) res_row = p.residual + (row % p.res_rows) * p.ldr + n0 + half * 32;
+      if (kRes && row_ok) res_row = p.residual + (row % p.res_rows) * p.ldr + n0 + qc * CW;
 #pragma unroll 1
       for (int c = 0; c < BN / 64; ++c) {
         const int col0 = n0 + c * 64;
-        uint4 rv[4];
+        uint4 rv[NV];
         if (kRes) {
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
+          for (int u = 0; u < NV; ++u) {
             rv[u] = make_uint4(0u, 0u, 0u, 0u);
             if (row_ok) rv[u] = __ldg(reinterpret_cast<const uint4*>(res_row + c * 64) + u);
           }
         }
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_addr + c * 64, r);
+        uint32_t r[CW];
+        if constexpr (CW == 32) tmem_ld_32x32b_x32(t_addr + c * 64, r);
+        else tmem_ld_32x32b_x16(t_addr + c * 64, r);
         tmem_ld_wait();
-        uint4 packed[4];
+        uint4 packed[NV];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          float v[8];
+        for (int u = 0; u < NV; ++u) {
+          const int ct0 = c * 64 + qc * CW + u * 8;      // first of these eight columns inside the tile
+          float v[8], ws[8], bs[8];
+          if (kInt8) {
+            const float4 w0 = *reinterpret_cast<const float4*>(s_wscale + ct0), w1 = *reinterpret_cast<const float4*>(s_wscale + ct0 + 4);
+            ws[0] = w0.x; ws[1] = w0.y; ws[2] = w0.z; ws[3] = w0.w; ws[4] = w1.x; ws[5] = w1.y; ws[6] = w1.z; ws[7] = w1.w;
+          }
+          if (kBias) {
+            const float4 b0 = *reinterpret_cast<const float4*>(s_bias + ct0), b1 = *reinterpret_cast<const float4*>(s_bias + ct0 + 4);
+            bs[0] = b0.x; bs[1] = b0.y; bs[2] = b0.z; bs[3] = b0.w; bs[4] = b1.x; bs[5] = b1.y; bs[6] = b1.z; bs[7] = b1.w;
+          }
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const int cc = u * 8 + j;
-            const int ct = c * 64 + half * 32 + cc;
             float x;
-            if (kInt8) x = __fmul_rn(__fmul_rn(float(int(r[cc])), a_scale), s_wscale[ct]);
+            if (kInt8) x = __fmul_rn(__fmul_rn(float(int(r[cc])), a_scale), ws[j]);
             else x = __uint_as_float(r[cc]);
-            if (kBias) x = __fadd_rn(x, s_bias[ct]);
+            if (kBias) x = __fadd_rn(x, bs[j]);
             if (kGelu) x = gelu_erf(x);
             v[j] = x;
           }
@@ -234,22 +254,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                  pack_bf16x2(v[6], v[7]));
         }
         if (et == 0) tma_store_wait_read<0>();
-        epi_sync();
+        epi_sync<EPI_THREADS>();
         if (p.hm_group == 0) {
           uint8_t* srow = stage_out + erow * 128;
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
-            *reinterpret_cast<uint4*>(srow + (((half * 4 + u) ^ (erow & 7)) << 4)) = packed[u];
+          for (int u = 0; u < NV; ++u)
+            *reinterpret_cast<uint4*>(srow + (((qc * NV + u) ^ (erow & 7)) << 4)) = packed[u];
         } else {
+          // head-major: four [128][16-column] pieces (32-byte rows, 32B swizzle), one TMA store each
           uint8_t* srow = stage_out + erow * 32;
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int unit = half * 4 + u;
+          for (int u = 0; u < NV; ++u) {
+            const int unit = qc * NV + u;                // 16-byte unit inside the 64-column chunk
             *reinterpret_cast<uint4*>(srow + (unit >> 1) * 4096 + (((unit & 1) ^ ((erow >> 2) & 1)) << 4)) = packed[u];
           }
         }
         fence_proxy_async_smem();
-        epi_sync();
+        epi_sync<EPI_THREADS>();
         if (et == 0) {
           if (p.hm_group == 0) {
             tma_store_2d(&tmOut, stage_out, col0, m0);
@@ -285,11 +306,12 @@ using PairFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap,
 
 template <bool kInt8>
 PairFn pick_pair(int epi) {
+  constexpr int W = kInt8 ? 16 : 8;
   switch (epi) {
-    case 0: return gemm_pair_kernel<kInt8, 0>;
-    case 1: return gemm_pair_kernel<kInt8, 1>;
-    case 3: return gemm_pair_kernel<kInt8, 3>;
-    case 5: return gemm_pair_kernel<kInt8, 5>;
+    case 0: return gemm_pair_kernel<kInt8, 0, W>;
+    case 1: return gemm_pair_kernel<kInt8, 1, W>;
+    case 3: return gemm_pair_kernel<kInt8, 3, W>;
+    case 5: return gemm_pair_kernel<kInt8, 5, W>;
     default: return nullptr;
   }
 }
@@ -366,7 +388,7 @@ int launch_gemm_pair(bool int8, const void* A, int64_t lda, const void* W, int64
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.blockDim = dim3(int8 ? 64 + 32 * 16 : 64 + 32 * 8);
   cfg.dynamicSmemBytes = SMEM_BYTES;
   cfg.stream = static_cast<cudaStream_t>(stream);
   cfg.gridDim = dim3(unsigned(sm_count() & ~1));

@@ -426,9 +426,10 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
   if (int e = check_device_arch()) return e;
   if (M == 0) return SAMB_OK;
   // Large plain products run on CTA pairs; SAMB_GEMM_SINGLE_CTA=1 keeps them on this file's kernel (A/B timing).
-  // int8 products with a short K are bound by their epilogue, which the pair's shared accumulator hand-off
-  // only couples more tightly: they stay on the single-CTA kernel.
-  if (!raw && batch == 1 && epilogue != EPI_COLSCALE && (!int8 || K >= 2048) && getenv("SAMB_GEMM_SINGLE_CTA") == nullptr) {
+  // An int8 product with a short K and the GELU epilogue is bound by that epilogue; the pair's shared
+  // accumulator hand-off only couples it more tightly, so it stays on this file's kernel.
+  const bool epi_bound = int8 && K < 2048 && (epilogue & SAMB_EPI_GELU);
+  if (!raw && batch == 1 && epilogue != EPI_COLSCALE && !epi_bound && getenv("SAMB_GEMM_SINGLE_CTA") == nullptr) {
     const int e = launch_gemm_pair(int8, A, lda, W, ldw, a_scale, w_scale, bias, residual, ldr, res_rows, out, ldo, M, N, K,
                                    epilogue, head_dim, status, stream);
     if (e != SAMB_E_SHAPE) return e;

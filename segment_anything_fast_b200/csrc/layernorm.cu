@@ -192,7 +192,9 @@ row_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
 
 // Per-row int8 quantisation for rows of up to kVec*256 elements: the row stays in registers as raw
 // 16-byte vectors between the absmax pass and the rounding pass.
-template <int kVec>
+// kGelu: the row first goes through the exact-erf GELU and is rounded back to bf16 (the activation tensor
+// the reference materialises between lin1 and lin2), then quantised.
+template <int kVec, bool kGelu>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ yq, float* __restrict__ scale,
                   long long rows, int C) {
@@ -210,6 +212,12 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ yq, 
       raw[i] = xr[vi];
       float f[8];
       unpack8(raw[i], f);
+      if (kGelu) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = gelu_erf(f[j]);
+        raw[i] = pack8(f);
+        unpack8(raw[i], f);
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
     }
@@ -239,6 +247,7 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ yq, 
 
 // Wide rows (C up to 3 * 256 * 8 = 6144): one 256-thread block per row, up to three 16-byte vectors per
 // thread, absmax through shared memory.
+template <bool kGelu>
 __global__ void __launch_bounds__(256)
 quant_rows_wide_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ yq, float* __restrict__ scale, int C) {
   __shared__ float s_max[8];
@@ -254,6 +263,12 @@ quant_rows_wide_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__
       raw[i] = xr[vi];
       float f[8];
       unpack8(raw[i], f);
+      if (kGelu) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = gelu_erf(f[j]);
+        raw[i] = pack8(f);
+        unpack8(raw[i], f);
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
     }
@@ -367,6 +382,32 @@ int launch_rows(const void* x, const float* gamma, const float* beta, void* y, i
 }  // namespace
 }  // namespace samb
 
+namespace samb {
+namespace {
+int launch_quant_rows(const void* x, int8_t* yq, float* scale, int64_t rows, int C, bool gelu, void* stream) {
+  if (x == nullptr || yq == nullptr || scale == nullptr || rows < 0 || C <= 0) return SAMB_E_BADARG;
+  if (C % 8 || C > 24 * 256) return SAMB_E_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(x) & 15u) || (reinterpret_cast<uintptr_t>(yq) & 7u)) return SAMB_E_ALIGN;
+  if (rows == 0) return SAMB_OK;
+  const long long blocks = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  if (blocks > 0x7fffffffLL) return SAMB_E_SHAPE;
+  auto st = static_cast<cudaStream_t>(stream);
+  auto xb = static_cast<const __nv_bfloat16*>(x);
+  if (C <= 8 * 256) {
+    if (gelu) quant_rows_kernel<8, true><<<unsigned(blocks), kWarpsPerBlock * 32, 0, st>>>(xb, yq, scale, rows, C);
+    else quant_rows_kernel<8, false><<<unsigned(blocks), kWarpsPerBlock * 32, 0, st>>>(xb, yq, scale, rows, C);
+  } else if (rows > 0x7fffffffLL) {
+    return SAMB_E_SHAPE;
+  } else if (gelu) {
+    quant_rows_wide_kernel<true><<<unsigned(rows), 256, 0, st>>>(xb, yq, scale, C);
+  } else {
+    quant_rows_wide_kernel<false><<<unsigned(rows), 256, 0, st>>>(xb, yq, scale, C);
+  }
+  return launch_status();
+}
+}  // namespace
+}  // namespace samb
+
 extern "C" {
 
 int samb_layernorm_bf16(const void* x, const float* gamma, const float* beta, void* y, int64_t rows, int C, float eps,
@@ -380,19 +421,11 @@ int samb_layernorm_quant_i8(const void* x, const float* gamma, const float* beta
 }
 
 int samb_quant_rows_i8(const void* x, int8_t* yq, float* scale, int64_t rows, int C, void* stream) {
-  using namespace samb;
-  if (x == nullptr || yq == nullptr || scale == nullptr || rows < 0 || C <= 0) return SAMB_E_BADARG;
-  if (C % 8 || C > 24 * 256) return SAMB_E_SHAPE;
-  if ((reinterpret_cast<uintptr_t>(x) & 15u) || (reinterpret_cast<uintptr_t>(yq) & 7u)) return SAMB_E_ALIGN;
-  if (rows == 0) return SAMB_OK;
-  const long long blocks = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
-  if (blocks > 0x7fffffffLL) return SAMB_E_SHAPE;
-  auto st = static_cast<cudaStream_t>(stream);
-  auto xb = static_cast<const __nv_bfloat16*>(x);
-  if (C <= 8 * 256) quant_rows_kernel<8><<<unsigned(blocks), kWarpsPerBlock * 32, 0, st>>>(xb, yq, scale, rows, C);
-  else if (rows > 0x7fffffffLL) return SAMB_E_SHAPE;
-  else quant_rows_wide_kernel<<<unsigned(rows), 256, 0, st>>>(xb, yq, scale, C);
-  return launch_status();
+  return samb::launch_quant_rows(x, yq, scale, rows, C, false, stream);
+}
+
+int samb_gelu_quant_rows_i8(const void* x, int8_t* yq, float* scale, int64_t rows, int C, void* stream) {
+  return samb::launch_quant_rows(x, yq, scale, rows, C, true, stream);
 }
 
 int samb_layernorm2d_nchw(const void* x, const float* gamma, const float* beta, void* out, int64_t tokens, int C,

@@ -95,7 +95,8 @@ def layernorm_quant_i8(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor,
     return yq, scale
 
 
-def quant_rows_i8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+def quant_rows_i8(x: torch.Tensor, gelu: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-row symmetric int8 quantisation of bf16 rows; ``gelu`` applies the exact GELU (rounded to bf16) first."""
     _need(x, torch.bfloat16, "x")
     x = _rows2d(x, "x")
     if not x.is_contiguous():
@@ -103,8 +104,9 @@ def quant_rows_i8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     rows, C = x.shape
     yq = torch.empty(rows, C, dtype=torch.int8, device=x.device)
     scale = torch.empty(rows, dtype=torch.float32, device=x.device)
-    _lib.check(_lib.load().samb_quant_rows_i8(x.data_ptr(), yq.data_ptr(), scale.data_ptr(), rows, C, _stream()),
-               "samb_quant_rows_i8")
+    fn = _lib.load().samb_gelu_quant_rows_i8 if gelu else _lib.load().samb_quant_rows_i8
+    _lib.check(fn(x.data_ptr(), yq.data_ptr(), scale.data_ptr(), rows, C, _stream()),
+               "samb_gelu_quant_rows_i8" if gelu else "samb_quant_rows_i8")
     return yq, scale
 
 

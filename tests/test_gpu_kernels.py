@@ -254,3 +254,21 @@ def test_gemm_i8_sp24_epilogues_match_dense_kernel(ops, epi):
     b = ops.gemm_i8(xq, sx, wq, sw, bias, res, gelu=epi == "gelu")
     ops.check_status()
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("rows,C", [(500, 5120), (300, 640), (64, 1280)])
+def test_gelu_quant_rows_matches_oracle(ops, rows, C):
+    """GELU + bf16 rounding + per-row quantisation in one pass over the hidden activation: scales equal the
+    oracle's to float rounding, int8 values differ by at most one step on at most 0.1 % of the entries (the
+    erf approximation can move a value across a bf16 rounding boundary)."""
+    from oracle import quant_oracle as qo
+    g = torch.Generator().manual_seed(9)
+    x = (torch.randn(rows, C, generator=g) * 2.0).bfloat16()
+    ref_act = torch.nn.functional.gelu(x.float()).bfloat16().float()
+    rq, rs = qo.quantize_rows_absmax(ref_act)
+    yq, ys = ops.quant_rows_i8(x.cuda(), gelu=True)
+    ops.check_status()
+    torch.testing.assert_close(ys.cpu(), rs, rtol=1e-2, atol=0)
+    d = (yq.cpu().int() - rq.int()).abs()
+    assert d.max().item() <= 1
+    assert (d != 0).float().mean().item() < 1e-3
