@@ -272,3 +272,36 @@ def test_gelu_quant_rows_matches_oracle(ops, rows, C):
     d = (yq.cpu().int() - rq.int()).abs()
     assert d.max().item() <= 1
     assert (d != 0).float().mean().item() < 1e-3
+
+
+# ------------------------------------------------------------------ CTA-pair GEMM
+@pytest.mark.parametrize("M,N,K", [(4096 + 100, 512, 1280), (8192, 1280, 5120), (2048, 256, 64)])
+def test_gemm_pair_kernel_equals_single_cta_kernel(ops, M, N, K, monkeypatch):
+    """Large products run on CTA pairs (cta_group::2); the same call with SAMB_GEMM_SINGLE_CTA=1 runs the
+    single-CTA kernel.  Same accumulation order per output element, same epilogue: bitwise equal, for every
+    epilogue, int8, and the head-major output; and both agree with a float64 reference."""
+    g = torch.Generator().manual_seed(13)
+    x = torch.randn(M, K, generator=g).bfloat16().cuda()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().cuda()
+    b = torch.randn(N, generator=g).cuda()
+    r = torch.randn(M, N, generator=g).bfloat16().cuda()
+    xq = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8).cuda()
+    wq = torch.randint(-127, 128, (N, K), generator=g, dtype=torch.int8).cuda()
+    sx, sw = torch.rand(M, generator=g).cuda(), torch.rand(N, generator=g).cuda()
+    calls = {
+        "bias": lambda: ops.gemm_bf16(x, w, b),
+        "gelu": lambda: ops.gemm_bf16(x, w, b, gelu=True),
+        "residual": lambda: ops.gemm_bf16(x, w, b, r),
+        "int8": lambda: ops.gemm_i8(xq, sx, wq, sw, b),
+        "int8 residual": lambda: ops.gemm_i8(xq, sx, wq, sw, b, r),
+    }
+    if N % 80 == 0:
+        calls["head-major"] = lambda: ops.gemm_heads(x, None, w, None, b, 80)
+    pair = {k: f() for k, f in calls.items()}
+    monkeypatch.setenv("SAMB_GEMM_SINGLE_CTA", "1")
+    single = {k: f() for k, f in calls.items()}
+    ops.check_status()
+    for k in calls:
+        assert torch.equal(pair[k], single[k]), k
+    ref = (x.double() @ w.double().t() + b.double()).float()
+    torch.testing.assert_close(pair["bias"].float(), ref, rtol=2e-2, atol=2e-2)
