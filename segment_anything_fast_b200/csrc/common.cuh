@@ -289,6 +289,18 @@ __device__ __forceinline__ void umma_i8_ss_pair(uint32_t d_tmem, uint64_t a_desc
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void umma_i8_sp_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t e_tmem,
+                                                   uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.sp.cta_group::2.kind::i8 [%0], %1, %2, [%3], %4, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(e_tmem), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Shared memory -> tensor memory in both CTAs of the pair (each from its own shared memory, same offsets).
+__device__ __forceinline__ void tmem_cp_128x128b_pair(uint32_t taddr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::2.128x128b [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
 // Arrives (once all MMAs issued so far by this thread have completed) on the barrier at the given
 // shared::cluster address (this CTA's or the peer's: see map_to_cta).
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster) {

@@ -9,6 +9,12 @@
 // of logical K = 64; eight epilogue warps drain the other accumulator through one of two token-major
 // staging tiles (the residual, when there is one, is brought into the same tile by TMA beforehand)
 // and two TMA stores.
+// kPair: the same on CTA pairs (cluster of two, cta_group::2): a pair owns 256 channels x 224 tokens, each CTA
+// holds its 128 channels of the weight (values + codes) and half of the token tile, one MMA (M = 256) issued
+// by the leader accumulates into both CTAs' tensor memory, so the activation operand is streamed once per
+// 256 channels and its shared-memory reads per CTA are halved.  Barrier scheme as in the dense pair kernel.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace samb {
@@ -30,6 +36,13 @@ constexpr int E_COL = NUM_ACC * TT;            // 416: first column of the code 
 constexpr int TMEM_COLS = 512;
 constexpr int NUM_THREADS = 320;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * OUT_BYTES + TT * 4 + 1024 + 256;
+// pair mode
+constexpr int TT_P = 224;                      // tokens per pair tile (112 streamed by each CTA)
+constexpr int B_BYTES_P = (TT_P / 2) * KB;     // 14 KiB
+constexpr int STAGE_BYTES_P = A_BYTES + B_BYTES_P + E_BYTES;   // 24 KiB
+constexpr int STAGES_P = 4;
+constexpr int OUT_HALF_BYTES_P = TT_P * 128;
+constexpr int SMEM_BYTES_P = STAGES_P * STAGE_BYTES_P + 4 * OUT_HALF_BYTES_P + TT_P * 4 + 1024 + 256;
 
 struct SpParams {
   void* out;
@@ -58,7 +71,7 @@ __device__ __forceinline__ bool epi_all(bool pred) {
 }
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
-template <int kEpi>
+template <int kEpi, bool kPair>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                  const __grid_constant__ CUtensorMap tmE, const __grid_constant__ CUtensorMap tmOut,
@@ -67,10 +80,20 @@ gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   constexpr bool kBias = (kEpi & SAMB_EPI_BIAS) != 0;
   constexpr bool kGelu = (kEpi & SAMB_EPI_GELU) != 0;
   constexpr bool kRes = (kEpi & SAMB_EPI_RESIDUAL) != 0;
+  // geometry of this variant (the names shadow the single-CTA constants of the namespace)
+  constexpr int TT = kPair ? TT_P : samb::TT;
+  constexpr int TB = kPair ? TT_P / 2 : samb::TT;                          // token rows this CTA streams per stage
+  constexpr int B_BYTES = TB * KB;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES + E_BYTES;
+  constexpr int STAGES = kPair ? STAGES_P : samb::STAGES;
+  constexpr int OUT_HALF_BYTES = TT * 128;
+  constexpr int OUT_BYTES = 2 * OUT_HALF_BYTES;
+  constexpr int E_COL = NUM_ACC * TT;
+  constexpr int kChunks = TT / 16;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_out = smem + STAGES * STAGE_BYTES;
-  float* s_tok = reinterpret_cast<float*>(stage_out + 2 * OUT_BYTES);      // [208] per-token scales
+  float* s_tok = reinterpret_cast<float*>(stage_out + 2 * OUT_BYTES);      // [TT] per-token scales
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_tok + TT);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* acc_full = empty_bar + STAGES;
@@ -81,6 +104,9 @@ gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t rank = kPair ? cluster_ctarank() : 0u;                    // 0 = leader of the pair
+  const long long first_tile = kPair ? (blockIdx.x >> 1) : blockIdx.x;
+  const long long tile_step = kPair ? (gridDim.x >> 1) : gridDim.x;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -90,7 +116,7 @@ gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     }
     for (int a = 0; a < NUM_ACC; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 8);
+      mbar_init(&acc_empty[a], kPair ? 16 : 8);                            // the epilogue warps of the CTA / of both CTAs
       mbar_init(&res_bar[a], 1);
     }
     fence_mbar_init();
@@ -100,9 +126,10 @@ gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     if (!kRaw) tma_prefetch_desc(&tmOut);
     if (kRes) tma_prefetch_desc(&tmRes);
   }
+  if (kPair) cluster_sync_all();                         // both CTAs' barriers exist before any remote use
   if (warp == 1) {
-    tmem_alloc(tmem_slot, TMEM_COLS);
-    tmem_relinquish();
+    if (kPair) { tmem_alloc_pair(tmem_slot, TMEM_COLS); tmem_relinquish_pair(); }
+    else { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
   }
   tc_fence_before();
   __syncthreads();
@@ -112,77 +139,100 @@ gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      const uint32_t full0 = kPair ? map_to_cta(&full_bar[0], 0) : 0u;     // pair: bytes are counted by the leader
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (long long tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-        const int ct = int(tile % p.tiles_c);
-        const int t0 = int(tile / p.tiles_c) * TT;
+      for (long long tile = first_tile; ok && tile < p.num_tiles; tile += tile_step) {
+        const int ct = int(tile % p.tiles_c) * (kPair ? 2 : 1) + int(rank);   // this CTA's 128-channel tile
+        const int t0 = int(tile / p.tiles_c) * TT + int(rank) * TB;           // first token row this CTA streams
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 1))) break;
           uint8_t* sa = smem + stage * STAGE_BYTES;
-          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
-          tma_load_2d(sa, &tmW, &full_bar[stage], kb * (KB / 2), ct * TC);
-          tma_load_2d(sa + A_BYTES, &tmX, &full_bar[stage], kb * KB, t0);
-          tma_load_2d(sa + A_BYTES + B_BYTES, &tmE, &full_bar[stage], 0, (ct * p.k_blocks + kb) * TC);
+          if (kPair) {
+            if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
+            tma_load_2d_pair(sa, &tmW, full0 + stage * 8, kb * (KB / 2), ct * TC);
+            tma_load_2d_pair(sa + A_BYTES, &tmX, full0 + stage * 8, kb * KB, t0);
+            tma_load_2d_pair(sa + A_BYTES + B_BYTES, &tmE, full0 + stage * 8, 0, (ct * p.k_blocks + kb) * TC);
+          } else {
+            mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+            tma_load_2d(sa, &tmW, &full_bar[stage], kb * (KB / 2), ct * TC);
+            tma_load_2d(sa + A_BYTES, &tmX, &full_bar[stage], kb * KB, t0);
+            tma_load_2d(sa + A_BYTES + B_BYTES, &tmE, &full_bar[stage], 0, (ct * p.k_blocks + kb) * TC);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    const uint32_t idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, TC, TT) | (1u << 2);   // bit 2: sparse A
-    const uint64_t adesc0 = make_smem_desc(smem_u32(smem), 16, 512, kSwizzle64B);
-    const uint64_t bdesc0 = make_smem_desc(smem_u32(smem) + A_BYTES, 16, 1024, kSwizzle128B);
-    const uint64_t edesc0 = make_smem_desc(smem_u32(smem) + A_BYTES + B_BYTES, 128, 128, kSwizzleNone);
-    uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
-    bool ok = true;
-    for (long long tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-      if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, 2))) break;
-      tc_fence_after();
-      const uint32_t d_tmem = tmem_base + acc * TT;
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
-        if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3))) break;
+    // ------------------------------------------------------------------ MMA issuer (pair: the leader CTA only)
+    if (rank == 0) {
+      const uint32_t idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, kPair ? 2 * TC : TC, TT) | (1u << 2);   // bit 2: sparse A
+      const uint64_t adesc0 = make_smem_desc(smem_u32(smem), 16, 512, kSwizzle64B);
+      const uint64_t bdesc0 = make_smem_desc(smem_u32(smem) + A_BYTES, 16, 1024, kSwizzle128B);
+      const uint64_t edesc0 = make_smem_desc(smem_u32(smem) + A_BYTES + B_BYTES, 128, 128, kSwizzleNone);
+      uint32_t empty_own = 0, empty_peer = 0, accf_own = 0, accf_peer = 0;
+      if (kPair) {
+        empty_own = map_to_cta(&empty_bar[0], 0); empty_peer = map_to_cta(&empty_bar[0], 1);
+        accf_own = map_to_cta(&acc_full[0], 0); accf_peer = map_to_cta(&acc_full[0], 1);
+      }
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (long long tile = first_tile; ok && tile < p.num_tiles; tile += tile_step) {
+        if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, 2))) break;
         tc_fence_after();
-        if (elect_one()) {
-          const uint32_t e_tmem = tmem_base + E_COL + stage * 4;
-          tmem_cp_128x128b(e_tmem, edesc0 + stage * (STAGE_BYTES / 16));
+        const uint32_t d_tmem = tmem_base + acc * TT;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3))) break;
+          tc_fence_after();
+          if (elect_one()) {
+            const uint32_t e_tmem = tmem_base + E_COL + stage * 4;
+            const uint64_t so = uint64_t(stage) * (STAGE_BYTES / 16);
+            if (kPair) tmem_cp_128x128b_pair(e_tmem, edesc0 + so);
+            else tmem_cp_128x128b(e_tmem, edesc0 + so);
 #pragma unroll
-          for (int k2 = 0; k2 < 2; ++k2)            // logical K 64: 32 compressed bytes of A, 64 bytes of X
-            umma_i8_sp_ss(d_tmem, adesc0 + stage * (STAGE_BYTES / 16) + k2 * 2,
-                          bdesc0 + stage * (STAGE_BYTES / 16) + k2 * 4, e_tmem + k2 * 2, idesc,
-                          (kb | k2) != 0 ? 1u : 0u);
-          tc_commit(&empty_bar[stage]);
+            for (int k2 = 0; k2 < 2; ++k2) {        // logical K 64: 32 compressed bytes of A, 64 bytes of X
+              const uint32_t accumulate = (kb | k2) != 0 ? 1u : 0u;
+              if (kPair) umma_i8_sp_ss_pair(d_tmem, adesc0 + so + k2 * 2, bdesc0 + so + k2 * 4, e_tmem + k2 * 2, idesc, accumulate);
+              else umma_i8_sp_ss(d_tmem, adesc0 + so + k2 * 2, bdesc0 + so + k2 * 4, e_tmem + k2 * 2, idesc, accumulate);
+            }
+            if (kPair) { tc_commit_pair(empty_own + stage * 8); tc_commit_pair(empty_peer + stage * 8); }
+            else tc_commit(&empty_bar[stage]);
+          }
+          __syncwarp();
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        if (elect_one()) {
+          if (kPair) { tc_commit_pair(accf_own + acc * 8); tc_commit_pair(accf_peer + acc * 8); }
+          else tc_commit(&acc_full[acc]);
         }
         __syncwarp();
-        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
       }
-      if (!ok) break;
-      if (elect_one()) tc_commit(&acc_full[acc]);
-      __syncwarp();
-      if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     // Thread = one channel of the tile (TMEM lane); two warps share a lane quarter and split the
-    // thirteen 16-token chunks: the first takes chunks 0..6, the second 7..12.
+    // 16-token chunks (13 or, on pairs, 14): the first takes chunks 0..6, the second the rest.
     const uint32_t lane_base = uint32_t(warp & 3) * 32u;
     const int half = (warp - 2) >> 2;
     const int ch = int(lane_base) + lane;                  // channel inside the tile
     const int et = int(threadIdx.x) - 64;                  // 0..255
     const int chunk_begin = half * 7;
-    const int n_chunks = half == 0 ? 7 : 6;
+    const int n_chunks = half == 0 ? 7 : kChunks - 7;
     const int unit = (ch & 63) >> 3, sub = (ch & 7) * 2;
+    const uint32_t acc_empty0 = kPair ? map_to_cta(&acc_empty[0], 0) : 0u;   // pair: the leader's barrier
     uint32_t acc = 0, acc_phase = 0, it = 0;
     // The residual tile of the first tile is requested here; that of tile i+1 after tile i's stores.
-    if (kRes && et == 0 && blockIdx.x < p.num_tiles) {
-      const int ct = int(blockIdx.x % p.tiles_c);
-      const int t0 = int(blockIdx.x / p.tiles_c) * TT;
+    if (kRes && et == 0 && first_tile < p.num_tiles) {
+      const int ct = int(first_tile % p.tiles_c) * (kPair ? 2 : 1) + int(rank);
+      const int t0 = int(first_tile / p.tiles_c) * TT;
       mbar_expect_tx(&res_bar[0], OUT_BYTES);
       tma_load_2d(stage_out, &tmRes, &res_bar[0], ct * TC, t0);
       tma_load_2d(stage_out + OUT_HALF_BYTES, &tmRes, &res_bar[0], ct * TC + 64, t0);
     }
-    for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
-      const int ct = int(tile % p.tiles_c);
+    for (long long tile = first_tile; tile < p.num_tiles; tile += tile_step, ++it) {
+      const int ct = int(tile % p.tiles_c) * (kPair ? 2 : 1) + int(rank);   // this CTA's 128-channel tile
       const long long t0 = (tile / p.tiles_c) * TT;
       const int n = ct * TC + ch;
       const bool ch_ok = n < p.N;
@@ -251,9 +301,9 @@ gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           if (ct * TC + 64 < p.N) tma_store_2d(&tmOut, s_tile + OUT_HALF_BYTES, ct * TC + 64, int(t0));
           tma_store_commit();
           tma_store_wait_read<1>();                        // the other staging tile is free again
-          const long long next = tile + gridDim.x;
+          const long long next = tile + tile_step;
           if (kRes && next < p.num_tiles) {
-            const int nct = int(next % p.tiles_c);
+            const int nct = int(next % p.tiles_c) * (kPair ? 2 : 1) + int(rank);
             const int nt0 = int(next / p.tiles_c) * TT;
             uint8_t* dst = stage_out + (buf ^ 1u) * OUT_BYTES;
             mbar_expect_tx(&res_bar[buf ^ 1u], OUT_BYTES);
@@ -263,7 +313,12 @@ gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         }
       }
       tc_fence_before();
-      mbar_arrive_warp(&acc_empty[acc]);
+      if (kPair) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty0 + acc * 8);
+      } else {
+        mbar_arrive_warp(&acc_empty[acc]);
+      }
       if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
     }
     if (!kRaw && et == 0) tma_store_wait_all<0>();
@@ -271,9 +326,11 @@ gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 
   tc_fence_before();
   __syncthreads();
+  if (kPair) cluster_sync_all();                         // no CTA leaves while its peer may still signal it
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (kPair) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -323,17 +380,25 @@ __global__ void pack_sp24_kernel(const int8_t* __restrict__ W, long long ldw, in
 using SpKernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
                             const CUtensorMap, const SpParams);
 
-SpKernelFn pick_sp_kernel(int epi) {
+SpKernelFn pick_sp_kernel(int epi, bool pair) {
+  if (pair) {
+    switch (epi) {
+      case 1: return gemm_sp24_kernel<1, true>;
+      case 5: return gemm_sp24_kernel<5, true>;
+      case SAMB_EPI_RAW: return gemm_sp24_kernel<SAMB_EPI_RAW, true>;
+      default: return nullptr;
+    }
+  }
   switch (epi) {
-    case 0: return gemm_sp24_kernel<0>;
-    case 1: return gemm_sp24_kernel<1>;
-    case 2: return gemm_sp24_kernel<2>;
-    case 3: return gemm_sp24_kernel<3>;
-    case 4: return gemm_sp24_kernel<4>;
-    case 5: return gemm_sp24_kernel<5>;
-    case 6: return gemm_sp24_kernel<6>;
-    case 7: return gemm_sp24_kernel<7>;
-    default: return gemm_sp24_kernel<SAMB_EPI_RAW>;
+    case 0: return gemm_sp24_kernel<0, false>;
+    case 1: return gemm_sp24_kernel<1, false>;
+    case 2: return gemm_sp24_kernel<2, false>;
+    case 3: return gemm_sp24_kernel<3, false>;
+    case 4: return gemm_sp24_kernel<4, false>;
+    case 5: return gemm_sp24_kernel<5, false>;
+    case 6: return gemm_sp24_kernel<6, false>;
+    case 7: return gemm_sp24_kernel<7, false>;
+    default: return gemm_sp24_kernel<SAMB_EPI_RAW, false>;
   }
 }
 
@@ -399,8 +464,13 @@ int samb_gemm_i8_sp24(const int8_t* Xq, int64_t ldx, const float* x_scale, const
   p.N = N;
   p.K = K;
   p.k_blocks = (K + KB - 1) / KB;
-  p.tiles_c = (N + TC - 1) / TC;
-  p.num_tiles = ((T + TT - 1) / TT) * p.tiles_c;
+  // CTA pairs for the products without the GELU epilogue (that one is bound by its epilogue either way)
+  auto pair_kern = pick_sp_kernel(epilogue, true);
+  const bool pair = pair_kern != nullptr && N % (2 * TC) == 0 && T >= 2048 && getenv("SAMB_GEMM_SINGLE_CTA") == nullptr;
+  const int tt = pair ? TT_P : TT;                       // tokens per tile
+  const int tiles128 = (N + TC - 1) / TC;                // 128-channel tiles of the weight (layout of `meta`)
+  p.tiles_c = pair ? N / (2 * TC) : tiles128;
+  p.num_tiles = ((T + tt - 1) / tt) * p.tiles_c;
 
   CUtensorMap tmW, tmX, tmE, tmOut;
   {
@@ -414,13 +484,13 @@ int samb_gemm_i8_sp24(const int8_t* Xq, int64_t ldx, const float* x_scale, const
   {
     const uint64_t dims[2] = {uint64_t(K), uint64_t(T)};
     const uint64_t strides[2] = {1, uint64_t(ldx)};
-    const uint32_t box[2] = {uint32_t(KB), uint32_t(TT)};
+    const uint32_t box[2] = {uint32_t(KB), uint32_t(pair ? TT_P / 2 : TT)};
     if (int e = make_tensor_map(&tmX, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(Xq), dims, strides, box,
                                 CU_TENSOR_MAP_SWIZZLE_128B))
       return e;
   }
   {
-    const uint64_t dims[2] = {16, uint64_t(p.tiles_c) * p.k_blocks * TC};
+    const uint64_t dims[2] = {16, uint64_t(tiles128) * p.k_blocks * TC};
     const uint64_t strides[2] = {1, 16};
     const uint32_t box[2] = {16, uint32_t(TC)};
     if (int e = make_tensor_map(&tmE, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(meta), dims, strides, box,
@@ -431,7 +501,7 @@ int samb_gemm_i8_sp24(const int8_t* Xq, int64_t ldx, const float* x_scale, const
   if (!raw) {
     const uint64_t dims[2] = {uint64_t(N), uint64_t(T)};
     const uint64_t strides[2] = {2, uint64_t(ldo) * 2};
-    const uint32_t box[2] = {64, uint32_t(TT)};
+    const uint32_t box[2] = {64, uint32_t(tt)};
     if (int e = make_tensor_map(&tmOut, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, dims, strides, box,
                                 CU_TENSOR_MAP_SWIZZLE_128B))
       return e;
@@ -440,12 +510,35 @@ int samb_gemm_i8_sp24(const int8_t* Xq, int64_t ldx, const float* x_scale, const
   if (epilogue & SAMB_EPI_RESIDUAL) {
     const uint64_t dims[2] = {uint64_t(N), uint64_t(T)};
     const uint64_t strides[2] = {2, uint64_t(ldr) * 2};
-    const uint32_t box[2] = {64, uint32_t(TT)};
+    const uint32_t box[2] = {64, uint32_t(tt)};
     if (int e = make_tensor_map(&tmRes, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(residual), dims, strides,
                                 box, CU_TENSOR_MAP_SWIZZLE_128B))
       return e;
   }
-  auto kern = pick_sp_kernel(epilogue);
+  if (pair) {
+    if (cudaFuncSetAttribute(pair_kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_P) != cudaSuccess)
+      return SAMB_E_LAUNCH;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES_P;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    long long pairs = sm_count() / 2;
+    if (p.num_tiles < pairs) pairs = p.num_tiles;
+    cfg.gridDim = dim3(unsigned(2 * pairs));
+    if (cudaLaunchKernelEx(&cfg, pair_kern, tmW, tmX, tmE, tmOut, tmRes, p) != cudaSuccess) {
+      cudaGetLastError();
+      return SAMB_E_LAUNCH;
+    }
+    return launch_status();
+  }
+  auto kern = pick_sp_kernel(epilogue, false);
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
     return SAMB_E_LAUNCH;
   const long long grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();

@@ -208,7 +208,8 @@ def _sparse_weight(N, K, seed):
     return wq
 
 
-@pytest.mark.parametrize("T,N,K", [(300, 256, 256), (1000, 160, 160), (4096 + 17, 640, 1280), (224, 128, 32)])
+@pytest.mark.parametrize("T,N,K", [(300, 256, 256), (1000, 160, 160), (4096 + 17, 640, 1280), (224, 128, 32),
+                                   (3000, 512, 640), (4096 + 17, 1280, 5120)])       # the last two run on CTA pairs
 def test_gemm_i8_sp24_accumulators_bit_exact(ops, T, N, K):
     """Sparse tensor-core path: int32 accumulators equal the dense integer product with the uncompressed
     weight, bit for bit (token / channel / K tails included)."""
@@ -238,10 +239,11 @@ def test_pack_sp24_round_trip_and_rejects_dense(ops):
         ops.check_status()
 
 
-@pytest.mark.parametrize("epi", ["bias", "gelu", "residual"])
-def test_gemm_i8_sp24_epilogues_match_dense_kernel(ops, epi):
+@pytest.mark.parametrize("epi,T,N", [("bias", 1500, 320), ("gelu", 1500, 320), ("residual", 1500, 320),
+                                     ("bias", 3000, 512), ("residual", 5000, 1280)])   # the last two run on CTA pairs
+def test_gemm_i8_sp24_epilogues_match_dense_kernel(ops, epi, T, N):
     """Same dequantising epilogue as the dense int8 kernel on the same (pruned) weight: bitwise equal."""
-    T, N, K = 1500, 320, 640
+    K = 640
     wq = _sparse_weight(N, K, 6).cuda()
     g = torch.Generator().manual_seed(7)
     xq = torch.randint(-127, 128, (T, K), generator=g, dtype=torch.int8).cuda()
