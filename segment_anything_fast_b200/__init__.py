@@ -9,3 +9,4 @@ from .build_sam import (build_image_encoder_vit_b, build_image_encoder_vit_h, bu
 from .image_encoder import ImageEncoderViT  # noqa: F401
 from .runtime import EncoderSession  # noqa: F401
 from .sparse import apply_fake_sparsity, apply_sparse  # noqa: F401
+from .sam_heads import MaskDecoder, PromptEncoder, Sam, TwoWayTransformer  # noqa: F401

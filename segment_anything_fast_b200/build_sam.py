@@ -1,10 +1,10 @@
 """Registries with the reference's names and signatures (build_sam.py:14-92).
 
-``build_image_encoder_vit_{h,l,b}`` build only the B200 image encoder (all this package implements).
-``sam_model_registry`` / ``sam_model_fast_registry`` build a full ``Sam`` by asking an installed
-``segment_anything_fast`` (or ``segment_anything``) package for the prompt encoder / mask decoder and
-then putting the B200 encoder in the ``image_encoder`` slot with the same weights: the exact
-substitution the reference's own fast registry performs when it reassigns ``sam.image_encoder``
+``build_image_encoder_vit_{h,l,b}`` build only the B200 image encoder.  ``sam_model_registry`` /
+``sam_model_fast_registry`` build a full ``Sam`` from this package's encoder and its torch prompt encoder /
+mask decoder (``sam_heads.py``; reference checkpoints load unchanged).  ``install(sam)`` instead takes a
+``Sam`` built by the reference package and puts the B200 encoder in its ``image_encoder`` slot with the same
+weights: the substitution the reference's own fast registry performs when it reassigns ``sam.image_encoder``
 (build_sam.py:70,78,84).  ``compile_mode`` is accepted and ignored: nothing here is traced or compiled.
 """
 from functools import partial
@@ -62,21 +62,16 @@ def install(sam, quant: Optional[str] = None):
     return sam
 
 
-def _reference_registry():
-    for mod in ("segment_anything_fast", "segment_anything"):
-        try:
-            return __import__(mod).sam_model_registry
-        except ImportError:
-            continue
-    raise ImportError(
-        "building a full Sam needs the prompt encoder / mask decoder of an installed `segment_anything_fast` "
-        "(or `segment_anything`) package; this package implements the image encoder only "
-        "(use build_image_encoder_vit_* for the encoder alone)")
-
-
 def _build_sam(name: str, checkpoint=None):
-    sam = _reference_registry()[name](checkpoint=checkpoint)
-    return install(sam)
+    """Full ``Sam`` (this package's encoder, prompt encoder and mask decoder; build_sam.py:95-149).  ``checkpoint``
+    is a path to a reference ``state_dict`` file."""
+    from .sam_heads import Sam, build_heads
+    prompt_encoder, mask_decoder = build_heads()
+    sam = Sam(_build_image_encoder(name), prompt_encoder, mask_decoder).eval()
+    if checkpoint is not None:
+        with open(checkpoint, "rb") as f:
+            sam.load_state_dict(torch.load(f, map_location="cpu"))
+    return sam
 
 
 def build_sam_vit_h(checkpoint=None):

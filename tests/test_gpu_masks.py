@@ -97,3 +97,36 @@ def test_masks_iou_against_oracle_pipeline(mode):
             else:
                 assert diff_frac[j].item() < 5e-4
     assert sum(ious) / len(ious) >= 0.99 and worst >= 0.975
+
+
+def test_sam_predict_boxes_end_to_end_on_gpu():
+    """The package's own Sam (B200 encoder + torch prompt encoder / mask decoder on the GPU) against the oracle
+    pipeline (encoder oracle fp32 + decoder oracle) with the same weights, one box per image."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from test_gpu_encoder import build_encoder
+    from segment_anything_fast_b200 import ops
+    from segment_anything_fast_b200.sam_heads import Sam, build_heads
+    n_img = 2
+    sd = eo.seeded_state_dict(CFG, seed=11)
+    x = scene_images(n_img, seed=12)
+    dcfg = do.DecoderConfig()
+    dsd = do.seeded_state_dict(dcfg, seed=3)
+    pe, md = build_heads()
+    pe.load_state_dict({k[len("prompt_encoder."):]: v for k, v in dsd.items() if k.startswith("prompt_encoder.")}, strict=False)
+    md.load_state_dict({k[len("mask_decoder."):]: v for k, v in dsd.items() if k.startswith("mask_decoder.")})
+    sam = Sam(build_encoder(CFG, sd), pe, md).cuda().eval()      # encoder bf16, heads fp32
+    boxes = _boxes(n_img, seed=13)
+    masks, iou_pred, low = sam.predict_boxes(x.to(torch.bfloat16).cuda(), boxes.cuda())
+    ops.check_status()
+    ref_sd = {k: v.to(torch.bfloat16).float() if v.is_floating_point() else v for k, v in sd.items()}
+    emb_ref = eo.image_encoder_forward(x, ref_sd, CFG, "fp32")
+    for i in range(n_img):
+        m_ref, iou_ref, low_ref = do.predict_masks_from_embedding(dsd, dcfg, emb_ref[i:i + 1], boxes[i:i + 1])
+        iou = _iou(masks[i:i + 1].cpu(), m_ref)[0]
+        area = m_ref.float().mean((2, 3))[0]
+        print(f"Sam.predict_boxes image {i}: IoU vs fp32 oracle pipeline {[round(v, 5) for v in iou.tolist()]}")
+        for j in range(iou.numel()):
+            if area[j] >= 1e-3:
+                assert iou[j].item() >= 0.99
+        assert (iou_pred[i].float().cpu() - iou_ref[0]).abs().max().item() < 5e-2

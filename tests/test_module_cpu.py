@@ -83,3 +83,35 @@ def test_sparse_prune_matches_reference_sparsifier(golden_dir):
     apply_sparse(m)
     for lin in (m[0], m[2]):
         assert ((lin.weight != 0).reshape(lin.weight.shape[0], -1, 4).sum(-1) <= 2).all()
+
+
+def test_sam_heads_match_decoder_oracle_and_reference_keys(golden_dir):
+    """The package's prompt encoder / mask decoder modules: reference key set, and the same numbers as the
+    decoder oracle (itself pinned to the reference modules) on seeded weights."""
+    import numpy as np
+    import os
+    from oracle import decoder_oracle as do
+    from segment_anything_fast_b200.sam_heads import build_heads
+    cfg = do.DecoderConfig()
+    sd = do.seeded_state_dict(cfg, seed=3)
+    pe, md = build_heads()
+    keys = {"prompt_encoder." + k for k in pe.state_dict()} | {"mask_decoder." + k for k in md.state_dict()}
+    extra = {k for k in keys - set(sd) if "mask_downscaling" not in k}
+    assert not extra and not (set(sd) - keys)
+    pe.load_state_dict({k[len("prompt_encoder."):]: v for k, v in sd.items() if k.startswith("prompt_encoder.")}, strict=False)
+    md.load_state_dict({k[len("mask_decoder."):]: v for k, v in sd.items() if k.startswith("mask_decoder.")})
+    g = np.load(os.path.join(golden_dir, "decoder_fp32.npz"))
+    emb = torch.randn(1, 256, 64, 64, generator=torch.Generator().manual_seed(5))
+    boxes = torch.from_numpy(g["boxes"])
+    with torch.no_grad():
+        sparse, dense = pe(None, boxes)
+        low, iou = md(emb, pe.get_dense_pe(), sparse, dense, True)
+        pts = (torch.tensor([[[500.0, 300.0], [100.0, 100.0]]]), torch.tensor([[1, 0]]))
+        sp_pts, _ = pe(pts, None)
+    assert torch.allclose(sparse, torch.from_numpy(g["sparse"]), atol=1e-5)
+    assert torch.allclose(sp_pts, torch.from_numpy(g["sparse_points"]), atol=1e-5)
+    low_ref = torch.from_numpy(g["low"])
+    assert (low[:, :, ::4, ::4] - low_ref).abs().max().item() < 1e-3 * low_ref.abs().max().item()
+    assert torch.allclose(iou, torch.from_numpy(g["iou"]), atol=1e-4)
+    _, _, low_o = do.predict_masks_from_embedding(sd, cfg, emb, boxes)
+    assert (low - low_o).abs().max().item() < 1e-3 * low_o.abs().max().item()
