@@ -221,6 +221,16 @@ int samb_conv3x3_rows(const void* x, void* a, int64_t tokens, int grid, int C, v
 int samb_normalize_u8(const uint8_t* x, void* y, int B, int C, int H, int W, const float* mean_host,
                       const float* std_host, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Mask filters of the automatic mask generator in one pass over the predicted logits [N, H, W]
+ * (fp32, or bf16 when is_bf16): inter[n] / uni[n] = pixels above thr + offset / above thr - offset,
+ * boxes[n] = XYXY bounds of (logit > thr) or zeros when empty, binary (optional, may be NULL) =
+ * (logit > thr) as bytes.
+ * ref: calculate_stability_score (utils/amg.py:193-213, stability = inter / uni), the thresholding and
+ * batched_mask_to_box (utils/amg.py:340-383) at automatic_mask_generator.py:335-345. */
+int samb_mask_stats(const void* logits, int is_bf16, int64_t N, int H, int W, float thr, float offset,
+                    int32_t* inter, int32_t* uni, int32_t* boxes, uint8_t* binary, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,35 @@
+"""CPU restatement of the mask filters the automatic mask generator applies to predicted mask logits.
+
+TEST INFRASTRUCTURE ONLY (checker for ``samb_mask_stats``).  numpy, integer-exact.  Pinned by
+``tests/golden/amg_fp32.npz``, outputs of the reference's own functions on seeded logits.
+
+Reference code followed (segment_anything_fast/utils/amg.py):
+  calculate_stability_score :193-213 — IoU of the masks thresholded at ``thr + offset`` and ``thr - offset``
+  (one contains the other, so the IoU is a ratio of two pixel counts);
+  batched_mask_to_box :340-383 — XYXY bounds of a boolean mask, [0,0,0,0] when it is empty.
+"""
+import numpy as np
+
+
+def stability_counts(logits: np.ndarray, thr: float, offset: float):
+    """``logits [N, H, W]`` -> pixel counts above ``thr + offset`` and above ``thr - offset`` (int32 each)."""
+    hi = np.float32(thr) + np.float32(offset)
+    lo = np.float32(thr) - np.float32(offset)
+    x = logits.astype(np.float32)
+    return (x > hi).reshape(x.shape[0], -1).sum(1).astype(np.int32), (x > lo).reshape(x.shape[0], -1).sum(1).astype(np.int32)
+
+
+def calculate_stability_score(logits: np.ndarray, thr: float, offset: float) -> np.ndarray:
+    inter, uni = stability_counts(logits, thr, offset)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        return inter.astype(np.float32) / uni.astype(np.float32)
+
+
+def batched_mask_to_box(masks: np.ndarray) -> np.ndarray:
+    """Boolean ``[N, H, W]`` -> int ``[N, 4]`` (x0, y0, x1, y1), zeros for an empty mask."""
+    out = np.zeros((masks.shape[0], 4), dtype=np.int64)
+    for i, m in enumerate(masks):
+        ys, xs = np.nonzero(m)
+        if ys.size:
+            out[i] = (xs.min(), ys.min(), xs.max(), ys.max())
+    return out

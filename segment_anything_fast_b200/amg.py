@@ -1,0 +1,46 @@
+"""The automatic mask generator's per-mask filters on the GPU, under the reference's function names
+(segment_anything_fast/utils/amg.py:193-213, 340-383), so that ``automatic_mask_generator.py`` can import
+them from here instead.  ``mask_stats`` is the fused form: one pass over the logits gives the stability
+score, the boxes and the thresholded masks that ``_process_batch`` computes with four passes
+(automatic_mask_generator.py:335-345).
+"""
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from .ops import _need, _stream
+
+
+def mask_stats(logits: torch.Tensor, mask_threshold: float, threshold_offset: float,
+               want_binary: bool = True) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    """``logits [..., H, W]`` (fp32 / bf16, CUDA) -> stability score ``[...]`` (float32), XYXY boxes ``[..., 4]``
+    (int32) of ``logits > mask_threshold``, and that boolean mask (or None)."""
+    if logits.dtype not in (torch.float32, torch.bfloat16):
+        raise RuntimeError("mask_stats: logits must be float32 or bfloat16")
+    _need(logits, logits.dtype, "logits")
+    lead, (H, W) = logits.shape[:-2], logits.shape[-2:]
+    x = logits.reshape(-1, H, W).contiguous()
+    N = x.shape[0]
+    inter = torch.empty(N, dtype=torch.int32, device=x.device)
+    uni = torch.empty(N, dtype=torch.int32, device=x.device)
+    boxes = torch.empty(N, 4, dtype=torch.int32, device=x.device)
+    binary = torch.empty(N, H, W, dtype=torch.uint8, device=x.device) if want_binary else None
+    _lib.check(_lib.load().samb_mask_stats(
+        x.data_ptr(), int(x.dtype == torch.bfloat16), N, H, W, float(mask_threshold), float(threshold_offset),
+        inter.data_ptr(), uni.data_ptr(), boxes.data_ptr(), binary.data_ptr() if want_binary else None, _stream()),
+        "samb_mask_stats")
+    score = inter / uni                                   # int32 / int32 -> float32, as the reference divides
+    return (score.reshape(lead), boxes.reshape(*lead, 4),
+            binary.view(torch.bool).reshape(*lead, H, W) if want_binary else None)
+
+
+def calculate_stability_score(masks: torch.Tensor, mask_threshold: float, threshold_offset: float) -> torch.Tensor:
+    return mask_stats(masks, mask_threshold, threshold_offset, want_binary=False)[0]
+
+
+def batched_mask_to_box(masks: torch.Tensor) -> torch.Tensor:
+    """Boolean masks ``[..., H, W]`` -> XYXY boxes, zeros for empty masks."""
+    if masks.numel() == 0:
+        return torch.zeros(*masks.shape[:-2], 4, device=masks.device)
+    return mask_stats(masks.to(torch.float32), 0.5, 0.0, want_binary=False)[1].to(torch.int64)

@@ -5,6 +5,7 @@ the shape allows it).  One JSON line per run:
     python -m segment_anything_fast_b200.microbench attn-global --batch 8 --heads 16 --tokens 4096 --dim 80
     python -m segment_anything_fast_b200.microbench attn-window --batch 200 --heads 16 --dim 80
     python -m segment_anything_fast_b200.microbench layernorm --rows 131072 --cols 1280 [--quant]
+    python -m segment_anything_fast_b200.microbench mask-stats --n 192 --h 1024 --w 1024 [--bf16]
 
 The two attention commands at their defaults are the standalone relative-position attention
 benchmark (q, k, v ~ N(0,1), rel_h / rel_w ~ N(0,0.5), bf16).
@@ -49,7 +50,10 @@ def main():
     ln = sub.add_parser("layernorm")
     ln.add_argument("--rows", type=int, default=131072); ln.add_argument("--cols", type=int, default=1280)
     ln.add_argument("--quant", action="store_true")
-    for p in (g, ag, aw, ln):
+    ms_ = sub.add_parser("mask-stats")
+    ms_.add_argument("--n", type=int, default=192); ms_.add_argument("--h", type=int, default=1024)
+    ms_.add_argument("--w", type=int, default=1024); ms_.add_argument("--bf16", action="store_true")
+    for p in (g, ag, aw, ln, ms_):
         p.add_argument("--iters", type=int, default=10); p.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
     torch.manual_seed(0)
@@ -94,6 +98,12 @@ def main():
         nbytes = 4 * B * H * 196 * d * 2 + 2 * B * H * 196 * 14 * 2          # q, k, v, o + rel_h, rel_w
         out.update(shape=[B, H, 196, d], ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1),
                    tflops=round(4.0 * B * H * 196 * 196 * d / ms / 1e9, 1))
+    elif a.cmd == "mask-stats":
+        from . import amg
+        x = (torch.randn(a.n, a.h, a.w, device=dev) * 2.0).to(torch.bfloat16 if a.bf16 else torch.float32)
+        ms = _time(lambda: amg.mask_stats(x, 0.0, 1.0), a.iters, a.warmup)
+        nbytes = x.numel() * (x.element_size() + 1)                            # logits in, binary masks out
+        out.update(shape=[a.n, a.h, a.w], dtype="bf16" if a.bf16 else "f32", ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1))
     else:
         R, C = a.rows, a.cols
         x = torch.randn(R, C, device=dev).bfloat16()

@@ -65,16 +65,33 @@ def golden_decoder():
         dense_pe=sam.prompt_encoder.get_dense_pe()[:, :, ::8, ::8].numpy(), sparse_points=sp_pts.numpy())
 
 
+def golden_amg():
+    """(g) the automatic mask generator's logit filters on seeded logits (an empty and a full mask included)."""
+    from segment_anything_fast.utils.amg import batched_mask_to_box, calculate_stability_score
+    g = torch.Generator().manual_seed(8)
+    logits = torch.randn(6, 37, 50, generator=g) * 2.0
+    logits[1] = -5.0                      # empty at every threshold
+    logits[2] = 5.0                       # full
+    logits[3, :, :] = -3.0
+    logits[3, 5:9, 40:50] = 4.0           # one rectangle touching the right border
+    score = calculate_stability_score(logits, 0.0, 1.0)
+    boxes = batched_mask_to_box(logits > 0.0)
+    np.savez_compressed(os.path.join(HERE, "amg_fp32.npz"), logits=logits.numpy(), score=score.numpy(), boxes=boxes.numpy())
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
-    ap.add_argument("--only", choices=["decoder"], default=None, help="regenerate just this file")
+    ap.add_argument("--only", choices=["decoder", "amg"], default=None, help="regenerate just this file")
     args = ap.parse_args()
     os.environ["SEGMENT_ANYTHING_FAST_USE_FLASH_4"] = "0"
     sys.path.insert(0, args.reference)
     torch.set_grad_enabled(False)
     if args.only == "decoder":
         golden_decoder()
+        return
+    if args.only == "amg":
+        golden_amg()
         return
     from functools import partial
 
@@ -154,6 +171,7 @@ def main():
         w0=w_before[0].numpy(), w1=w_before[1].numpy(),
         keep0=(lin[0].weight != 0).numpy(), keep1=(lin[1].weight != 0).numpy())
     golden_decoder()
+    golden_amg()
     print("golden vectors written to", HERE)
 
 
