@@ -1,6 +1,9 @@
 """Host-facing session around the encoder: pinned staging buffers, one H2D copy of the uint8 image
 batch, normalisation + encoder on the device, one D2H copy of the embeddings.
 
+``encode`` is the blocking form; ``submit`` / ``result`` is the pipelined form (two slots, copies on their own
+streams): the upload of batch i+1 and the download of batch i-1 overlap the encoder pass of batch i.
+
 This is the call a data-parallel worker makes per batch (one process per GPU).  It replaces the
 upload + ``Sam.preprocess`` + ``image_encoder`` sequence of ``SamPredictor.set_torch_image``
 (predictor.py:57-58,88-90; sam.py:164-174) for a batch of already-resized 1024x1024 images.
@@ -29,6 +32,9 @@ class EncoderSession:
         self.host_out = torch.empty(batch, oc, g, g, dtype=torch.bfloat16).pin_memory()
         self.dev_in = torch.empty(batch, 3, S, S, dtype=torch.uint8, device=self.device)
         self.dev_norm = torch.empty(batch, 3, S, S, dtype=torch.bfloat16, device=self.device)
+        # second slot and the copy streams of the pipelined form are created on first use
+        self._slots = None
+        self._next = 0
 
     @property
     def h2d_bytes(self) -> int:
@@ -53,3 +59,61 @@ class EncoderSession:
         self.host_out.copy_(emb, non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
         return self.host_out
+
+    # ------------------------------------------------------------------ pipelined form
+    def _init_slots(self) -> None:
+        S = self.host_in.shape[-1]
+        mk = lambda: torch.cuda.Event()
+        self._slots = []
+        for i in range(2):
+            self._slots.append({
+                "host_in": self.host_in if i == 0 else torch.empty_like(self.host_in).pin_memory(),
+                "host_out": self.host_out if i == 0 else torch.empty_like(self.host_out).pin_memory(),
+                "dev_in": self.dev_in if i == 0 else torch.empty_like(self.dev_in),
+                "uploaded": mk(), "computed": mk(), "downloaded": mk(), "emb": None, "busy": False})
+        self._s_in = torch.cuda.Stream(self.device)
+        self._s_out = torch.cuda.Stream(self.device)
+
+    def slot_input(self, slot: int) -> torch.Tensor:
+        """Pinned uint8 staging buffer of a slot (fill it, then ``submit(slot=...)``)."""
+        if self._slots is None:
+            self._init_slots()
+        return self._slots[slot]["host_in"]
+
+    def submit(self, images_u8_host: Optional[torch.Tensor] = None, slot: Optional[int] = None) -> int:
+        """Queue one batch: upload (copy stream) -> normalise + encoder (current stream) -> download (copy
+        stream).  Returns the slot to pass to ``result``.  At most two batches are in flight; a slot must have
+        been collected with ``result`` before it is submitted again."""
+        if self._slots is None:
+            self._init_slots()
+        if slot is None:
+            slot, self._next = self._next, self._next ^ 1
+        sl = self._slots[slot]
+        if sl["busy"]:
+            raise RuntimeError("EncoderSession.submit: slot still in flight; call result(slot) first")
+        if images_u8_host is not None:
+            sl["host_in"].copy_(images_u8_host)
+        main = torch.cuda.current_stream(self.device)
+        self._s_in.wait_event(sl["computed"])             # the previous pass that read this slot's device input
+        with torch.cuda.stream(self._s_in):
+            sl["dev_in"].copy_(sl["host_in"], non_blocking=True)
+            sl["uploaded"].record(self._s_in)
+        main.wait_event(sl["uploaded"])
+        emb = self.encode_device(sl["dev_in"])
+        sl["computed"].record(main)
+        self._s_out.wait_event(sl["computed"])
+        with torch.cuda.stream(self._s_out):
+            sl["host_out"].copy_(emb, non_blocking=True)
+            sl["downloaded"].record(self._s_out)
+        emb.record_stream(self._s_out)
+        sl["emb"], sl["busy"] = emb, True
+        return slot
+
+    def result(self, slot: int) -> torch.Tensor:
+        """Block until the batch submitted in ``slot`` is in host memory; returns the pinned bf16 embeddings."""
+        sl = self._slots[slot]
+        if not sl["busy"]:
+            raise RuntimeError("EncoderSession.result: nothing was submitted in this slot")
+        sl["downloaded"].synchronize()
+        sl["emb"], sl["busy"] = None, False
+        return sl["host_out"]

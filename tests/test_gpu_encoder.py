@@ -128,3 +128,27 @@ def test_tiny_encoder_sparse24(cuda, mlp_only, quant):
           f"cos vs dense output {_cos(out, dense):.6f}")
     assert _cos(out, ref) > (0.995 if quant else 0.999)
     assert _cos(out, dense) < _cos(out, ref)                    # the pruning really took effect
+
+
+def test_encoder_session_blocking_and_pipelined_agree(cuda):
+    """EncoderSession: host uint8 in, host bf16 embeddings out.  The pipelined form (two batches in flight, copies
+    on their own streams) returns bit for bit what the blocking form returns, batch after batch."""
+    from segment_anything_fast_b200 import EncoderSession
+    sd = eo.seeded_state_dict(TINY, seed=1)
+    enc = build_encoder(TINY, sd)
+    sess = EncoderSession(enc, batch=2)
+    g = torch.Generator().manual_seed(31)
+    batches = [torch.randint(0, 256, (2, 3, 1024, 1024), generator=g, dtype=torch.uint8) for _ in range(4)]
+    want = [sess.encode(b).clone() for b in batches]
+    got, pending = [], None
+    for b in batches:
+        slot = sess.submit(b)
+        if pending is not None:
+            got.append(sess.result(pending).clone())
+        pending = slot
+    got.append(sess.result(pending).clone())
+    cuda.check_status()
+    for a, b in zip(want, got):
+        assert torch.equal(a, b)
+    with pytest.raises(RuntimeError):
+        sess.result(0)                                   # nothing in flight any more
