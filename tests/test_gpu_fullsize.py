@@ -114,3 +114,21 @@ def test_vit_h_encoder_full_size(ops):
     got = a[:1].float().cpu()
     print(f"ViT-H image 0 vs fp32 oracle: cosine {_cos(got, ref):.6f}, max-abs {(got - ref).abs().max().item():.4f}")
     assert _cos(got, ref) > 0.999
+
+
+@pytest.mark.parametrize("name,cfg", [
+    ("vit_b", eo.EncoderConfig(embed_dim=768, depth=12, num_heads=12, global_attn_indexes=(2, 5, 8, 11), out_chans=256)),
+    ("vit_l (first 6 blocks)", eo.EncoderConfig(embed_dim=1024, depth=6, num_heads=16, global_attn_indexes=(5,), out_chans=256)),
+])
+def test_other_registry_sizes_against_oracle(ops, name, cfg):
+    """The ViT-B / ViT-L shapes of the registries (head dim 64, 768 / 1024 channels): one image against the
+    fp32 oracle on the same weights."""
+    from test_gpu_encoder import build_encoder
+    sd = eo.seeded_state_dict(cfg, seed=41)
+    enc = build_encoder(cfg, sd)
+    x = eo.seeded_images(1, seed=42)
+    got = enc(x.to(torch.bfloat16).cuda()).float().cpu()
+    ops.check_status()
+    ref = eo.image_encoder_forward(x, sd, cfg, "fp32")
+    print(f"{name}: cosine {_cos(got, ref):.6f}, max-abs {(got - ref).abs().max().item():.4f}")
+    assert _cos(got, ref) > 0.999
