@@ -6,7 +6,7 @@
 // stream.  One persistent CTA per SM walks its items with a two-deep TMA ring (the loads of item
 // k+1 fly while item k is being computed):
 //   warp 0      TMA producer: Q (two 128-row tiles), K and V (N rounded up to 208 rows) per item
-//   warp 1      tcgen05.mma issue: two Q K^T products into tensor memory, later two P V products
+//   warps 1, 10 tcgen05.mma issue, one warp per query tile: Q K^T into tensor memory, later P V
 //   warps 2..9  softmax, one thread per query row (warps 2..5 rows 0..127, warps 6..9 the rest)
 //  * The logits of a tile occupy 208 TMEM columns.  The threads read them twice (row maximum, then
 //    exponentials) and write P back as packed bf16 pairs over the columns already consumed, so P V
@@ -20,15 +20,15 @@
 // Raster layout (qkv_fused 2): q/k/v stay in raster token order and never hold pad tokens.  A window is
 // gathered by WS x WS TMA boxes whose out-of-range part (border windows) is zero-filled.  A pad token's
 // key and value are the projection biases (its LayerNorm output is zero), so for border windows the
-// softmax warps overwrite the pad rows of the K tile (tile-0 warps) and of the V tile (tile-1 warps) with
-// k_bias / v_bias of the head before they release the tile's first product; from there on a pad key is
+// softmax warps overwrite the pad rows of the K and V tiles with k_bias / v_bias of the head before they
+// release their tile's first product; from there on a pad key is
 // an ordinary key, exactly as in the padded layouts.
 #include "common.cuh"
 
 namespace samb {
 namespace {
 
-constexpr int NUM_THREADS = 320;
+constexpr int NUM_THREADS = 352;   // TMA warp, tile-0 MMA warp, 8 softmax warps, tile-1 MMA warp
 constexpr int TMEM_COLS = 512;   // tile 0 at column 0, tile 1 at column 256
 constexpr int kOCol = 112;       // P V result inside a tile's columns (P uses [0, 104))
 constexpr int STAGES = 2;
@@ -98,7 +98,10 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* p_full = bars + 8;      // [2]      P of tile t is in TMEM
   uint64_t* o_full = bars + 10;     // [2]      P V of tile t is in TMEM
   uint64_t* t_free = bars + 12;     // [2]      tile t's TMEM columns may be overwritten (O has been read)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* s_done = bars + 14;     // [2][2]   logits product of tile t for items of parity k & 1 has read its Q rows:
+                                    //          what the OTHER tile waits for before it stages output over them.  Two
+                                    //          barriers per tile because a tile may be a whole item ahead of the other.
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   unsigned int* out_cnt = reinterpret_cast<unsigned int*>(tmem_slot + 2);   // [STAGES] softmax warps that staged their rows
 
@@ -106,11 +109,12 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    // a stage is free when the MMAs that read it have finished AND the output store staged in it has been read
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 2); }
+    // a stage is free when both tiles' MMAs that read it have finished AND the output store staged in it has been read
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 3); }
     out_cnt[0] = out_cnt[1] = 0u;
     for (int t = 0; t < 2; ++t) {
       mbar_init(&pro_done[t], 4);
+      mbar_init(&s_done[t * 2], 1); mbar_init(&s_done[t * 2 + 1], 1);
       mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 4); mbar_init(&o_full[t], 1); mbar_init(&t_free[t], 4);
     }
     fence_mbar_init();
@@ -182,8 +186,12 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
     }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issue (whole warp, one elected lane issues)
+  } else if (warp == 1 || warp == 10) {
+    // ---------------------------------------------------------------- MMA issue, one warp per query tile
+    // (whole warp, one elected lane issues).  Issuing holds the thread until the tensor pipe has taken the
+    // instructions, and each tile's chain S -> softmax -> P V -> output is serial: with a warp per tile the
+    // two chains only meet in the tensor pipe, one tile's softmax overlapping the other tile's products.
+    const int t = warp == 1 ? 0 : 1;
     constexpr uint32_t idesc_s = make_idesc(kAccF32, kFmtBF16, kFmtBF16, 128, NK);
     constexpr uint32_t idesc_o = make_idesc(kAccF32, kFmtBF16, kFmtBF16, 128, D, false, /*B MN-major*/ true);
     // K-major, 32B swizzle (8-row groups 256 B apart); start addresses move in 16-byte units
@@ -192,53 +200,39 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const uint64_t de = make_smem_desc(smem_u32(smem + L::OFF_E), 16, 256, kSwizzle32B);
     // V: MN-major, column chunks KV_CHUNK apart (LBO), 8-key groups 256 B apart (SBO)
     const uint64_t dv0 = make_smem_desc(smem_u32(smem + L::OFF_V), L::KV_CHUNK, 256, kSwizzle32B);
-    // Issue order S0(k), PV1(k-1), S1(k), PV0(k): the two query tiles run half an item apart, so that one
-    // tile's softmax overlaps the other tile's products (and the next item's, for tile 0).
+    const uint32_t d_tmem = tmem_base + t * 256;
     uint32_t stage = 0, phase = 0, k = 0;
     bool ok = true;
-    auto issue_s = [&](int t, uint32_t par, uint64_t dq, uint64_t dk) -> bool {
-      if (!mbar_wait(&pro_done[t], par, abort_flag, p.status, 3)) return false;
-      if (!mbar_wait(&t_free[t], par ^ 1u, abort_flag, p.status, 4)) return false;
+    for (int it = blockIdx.x; ok && it < p.items; it += gridDim.x, ++k) {
+      const uint32_t par = k & 1u;
+      if (!(ok = mbar_wait(&full[stage], phase, abort_flag, p.status, 2))) break;
+      if (!(ok = mbar_wait(&pro_done[t], par, abort_flag, p.status, 3))) break;
+      if (!(ok = mbar_wait(&t_free[t], par ^ 1u, abort_flag, p.status, 4))) break;
       tc_fence_after();
-      if (elect_one()) {
-        const uint32_t d_tmem = tmem_base + t * 256;
+      if (elect_one()) {                           // logits of this tile
+        const uint64_t dq = dq0 + stage * (L::STAGE / 16);
+        const uint64_t dk = dq + L::OFF_K / 16;
 #pragma unroll
         for (int c = 0; c < CH; ++c)
           umma_f16_ss(d_tmem, dq + (c * L::Q_CHUNK + t * 4096) / 16, dk + c * (L::KV_CHUNK / 16), idesc_s, c != 0);
         umma_f16_ss(d_tmem, drw + t * (4096 / 16), de, idesc_s, 1u);
         tc_commit(&s_full[t]);
+        tc_commit(&s_done[t * 2 + par]);
       }
       __syncwarp();
-      return true;
-    };
-    auto issue_pv = [&](int t, uint32_t par, uint64_t dv, uint32_t st) -> bool {     // A = P from TMEM, B = V
-      if (!mbar_wait(&p_full[t], par, abort_flag, p.status, 5)) return false;
+      if (!(ok = mbar_wait(&p_full[t], par, abort_flag, p.status, 5))) break;
       tc_fence_after();
-      if (elect_one()) {
-        const uint32_t d_tmem = tmem_base + t * 256;
+      if (elect_one()) {                           // P V of this tile: A = P from TMEM, B = V
+        const uint64_t dv = dv0 + stage * (L::STAGE / 16);
 #pragma unroll
         for (int kk = 0; kk < L::KSTEPS; ++kk)
           umma_f16_ts(d_tmem + kOCol, d_tmem + kk * 8, dv + kk * (512 / 16), idesc_o, kk != 0);
         tc_commit(&o_full[t]);
-        if (t == 1) tc_commit(&empty[st]);         // everything that reads this stage has been issued
+        tc_commit(&empty[stage]);                  // this tile has issued everything that reads the stage
       }
       __syncwarp();
-      return true;
-    };
-    uint32_t prev_stage = 0;
-    for (int it = blockIdx.x; ok && it < p.items; it += gridDim.x, ++k) {
-      const uint32_t par = k & 1u;
-      if (!(ok = mbar_wait(&full[stage], phase, abort_flag, p.status, 2))) break;
-      const uint64_t dq = dq0 + stage * (L::STAGE / 16);
-      const uint64_t dk = dq + L::OFF_K / 16;
-      if (!(ok = issue_s(0, par, dq, dk))) break;
-      if (k > 0 && !(ok = issue_pv(1, par ^ 1u, dv0 + prev_stage * (L::STAGE / 16), prev_stage))) break;
-      if (!(ok = issue_s(1, par, dq, dk))) break;
-      if (!(ok = issue_pv(0, par, dv0 + stage * (L::STAGE / 16), stage))) break;
-      prev_stage = stage;
       if (++stage == STAGES) { stage = 0; phase ^= 1u; }
     }
-    if (ok && k > 0) issue_pv(1, (k - 1) & 1u, dv0 + prev_stage * (L::STAGE / 16), prev_stage);
   } else {
     // ---------------------------------------------------------------- softmax (one thread = one query row)
     const int t = (warp - 2) >> 2;                               // query tile of this warp
@@ -328,6 +322,19 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       // ---- this item's bias: rel_h into registers (log2 domain), rel_w/scale into the A-operand tile
       float bh[WS];
       {
+        // border window (raster layout): this thread's 16-byte piece of the projection bias, requested first
+        int vy = WS, vx = WS;
+        uint4 bk = make_uint4(0u, 0u, 0u, 0u), bv = bk;
+        const int ptid = (warp & 3) * 32 + lane, piece = ptid % (2 * CH);
+        if (p.qkv_fused == 2) {
+          const int wi = (it / p.H) % (p.nw * p.nw);
+          if (wi / p.nw == p.nw - 1) vy = p.vlast;
+          if (wi % p.nw == p.nw - 1) vx = p.vlast;
+          if ((vy < WS || vx < WS) && ptid < 12 * 2 * CH) {
+            bk = __ldg(reinterpret_cast<const uint4*>(p.kv_bias + (size_t)(p.H + it % p.H) * D) + piece);
+            bv = __ldg(reinterpret_cast<const uint4*>(p.kv_bias + (size_t)(2 * p.H + it % p.H) * D) + piece);
+          }
+        }
         float rw[16];
         uint32_t eh[WS], ew[WS];
         bias_elems(0, sh_h, eh);
@@ -341,24 +348,21 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             make_uint4(wpack2(rw[0], rw[1]), wpack2(rw[2], rw[3]), wpack2(rw[4], rw[5]), wpack2(rw[6], rw[7]));
         *reinterpret_cast<uint4*>(rrow + ((1 ^ sw) << 4)) =
             make_uint4(wpack2(rw[8], rw[9]), wpack2(rw[10], rw[11]), wpack2(rw[12], rw[13]), wpack2(rw[14], rw[15]));
-        if (p.qkv_fused == 2) {
-          // border window: pad tokens' K rows (tile-0 warps) / V rows (tile-1 warps) <- projection bias
-          const int wi = (it / p.H) % (p.nw * p.nw);
-          const int vy = wi / p.nw == p.nw - 1 ? p.vlast : WS, vx = wi % p.nw == p.nw - 1 ? p.vlast : WS;
-          if (vy < WS || vx < WS) {
-            const int h = it % p.H;
-            ok = mbar_wait(&full[k % STAGES], (k / STAGES) & 1u, abort_flag, p.status, 9);   // the zero fill has landed
-            const int n_pad = vy * (WS - vx) + (WS - vy) * WS;
-            const uint8_t* tabp = smem + L::OFF_PADTAB + (vy == WS ? 0 : (vx == WS ? 1 : 2)) * 256;
-            uint8_t* region = smem + (k % STAGES) * L::STAGE + (t == 0 ? L::OFF_K : L::OFF_V);
-            // thread = one 16-byte piece (of the 2 * CH per row) for every 12th pad row
-            const int tid = (warp & 3) * 32 + lane, piece = tid % (2 * CH), c = piece >> 1, hf = piece & 1;
-            if (ok && tid < 12 * 2 * CH) {
-              const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.kv_bias + (size_t)((t + 1) * p.H + h) * D) + piece);
-              for (int pi = tid / (2 * CH); pi < n_pad; pi += 12) {
-                const int r = tabp[pi];
-                *reinterpret_cast<uint4*>(region + c * L::KV_CHUNK + r * 32 + ((hf ^ ((r >> 2) & 1)) << 4)) = bv;
-              }
+        if (vy < WS || vx < WS) {
+          // border window: pad tokens' K and V rows <- projection bias.  Both tile groups write both (the same
+          // values), so neither tile's products depend on the other group's progress.
+          ok = mbar_wait(&full[k % STAGES], (k / STAGES) & 1u, abort_flag, p.status, 9);   // the zero fill has landed
+          const int n_pad = vy * (WS - vx) + (WS - vy) * WS;
+          const uint8_t* tabp = smem + L::OFF_PADTAB + (vy == WS ? 0 : (vx == WS ? 1 : 2)) * 256;
+          uint8_t* stage_base = smem + (k % STAGES) * L::STAGE;
+          // thread = one 16-byte piece (of the 2 * CH per row) for every 12th pad row
+          const int c = piece >> 1, hf = piece & 1;
+          if (ok && ptid < 12 * 2 * CH) {
+            for (int pi = ptid / (2 * CH); pi < n_pad; pi += 12) {
+              const int r = tabp[pi];
+              const int off = c * L::KV_CHUNK + r * 32 + ((hf ^ ((r >> 2) & 1)) << 4);
+              *reinterpret_cast<uint4*>(stage_base + L::OFF_K + off) = bk;
+              *reinterpret_cast<uint4*>(stage_base + L::OFF_V + off) = bv;
             }
           }
         }
@@ -366,9 +370,6 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mbar_arrive_warp(&pro_done[t]);
         if (!ok) break;
       }
-      const int it_next = it + gridDim.x;
-      if (it_next < p.items) fetch_bias(it_next);               // lands while this item is being computed
-
       if (!(ok = mbar_wait(&s_full[t], par, abort_flag, p.status, 6))) break;
       tc_fence_after();
       // pass 1: per key-row maxima of the raw logits, then the row maximum of the biased logits
@@ -420,6 +421,11 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive_warp(&p_full[t]);
+      // The next item's bias values are requested here, where few registers are live: they land during the
+      // P V product and the output staging.  (Requested before the softmax they had to be spilled, and the spill
+      // waited for the loads.)
+      const int it_next = it + gridDim.x;
+      if (it_next < p.items) fetch_bias(it_next);
 
       if (!(ok = mbar_wait(&o_full[t], par, abort_flag, p.status, 7))) break;
       tc_fence_after();
@@ -434,6 +440,8 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       // exist) as [token][D] rows and leaves with one TMA store: a WS x WS x D box of the output tensor,
       // which drops the zero-padded tokens of border windows by clipping.
       uint8_t* stg = smem + (k % STAGES) * L::STAGE;
+      // the staging rows overlap the other tile's Q rows: its logits product must have read them
+      if (!(ok = mbar_wait(&s_done[(t ^ 1) * 2 + par], (k >> 1) & 1u, abort_flag, p.status, 10))) break;
       if (valid) {
 #pragma unroll
         for (int c = 0; c < D / 16; ++c) {
