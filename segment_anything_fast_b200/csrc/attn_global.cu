@@ -12,7 +12,9 @@
 //  * rel_w depends on the key column kw = j % 64, the same pattern in every key tile.  It rides on
 //    the tensor core (adding it per element in the softmax threads was measured 20% slower): the A operand is [Q | rel_w/scale] (K = d + 64) and the B operand is
 //    [K_tile | E] with E a constant one-hot matrix (E[j, kw(j)] = 1), so Q K^T + rel_w/scale comes
-//    out of one accumulation and the softmax multiplies everything by scale.
+//    out of one accumulation and the softmax multiplies everything by scale.  The rel_w/scale part of A sits in
+//    tensor memory (32 columns per tile), E in shared memory as one [128 x 64] block: four products of N = 128
+//    per key tile (issuing a tcgen05.mma costs the issuing thread about as much whatever its size).
 //  * rel_h depends on the key row kh: two values per query row and key tile.  They are folded into
 //    the addend of the exp2 FMA, which costs nothing per element.
 // Per tile: the 128x128 logits live in one TMEM buffer and are pulled into registers in one pass
@@ -30,7 +32,8 @@ constexpr int BK = 128;          // keys per tile
 constexpr int SW = 64;           // raster width the kernel is specialised for
 constexpr int KV_STAGES = 2;
 constexpr int NUM_THREADS = 384;   // warpgroup 0: TMA + MMA warps (2 idle); warpgroups 1, 2: softmax of tiles A, B
-constexpr int TMEM_COLS = 512;   // S_A @0, S_B @128, O_A @256, O_B @384
+constexpr int TMEM_COLS = 512;   // S_A @0, S_B @128, O_A @256, O_B @384; rel_w/scale (bf16 pairs) A @336, B @464
+__host__ __device__ constexpr int relw_col(int t) { return t == 0 ? 336 : 464; }
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 domain
 
@@ -58,9 +61,8 @@ struct Smem {
   static constexpr int Q_CHUNK = 256 * 32;          // 256 query rows of one chunk
   static constexpr int KV_TILE = 128 * 32 * CH;     // one 128-row K or V tile, chunk major
   static constexpr int OFF_Q = 0;
-  static constexpr int OFF_RELW = OFF_Q + CH * Q_CHUNK;         // 2 x [128][64] bf16, 128B swizzle
-  static constexpr int OFF_E = OFF_RELW + 2 * 128 * 128;        // [64][64] bf16 one-hot, 128B swizzle
-  static constexpr int OFF_P = OFF_E + 64 * 128;                // 2 tiles x 2 x [128][64] bf16, 128B swizzle
+  static constexpr int OFF_E = OFF_Q + CH * Q_CHUNK;            // [128][64] bf16 one-hot (key j -> column j % 64), 128B swizzle
+  static constexpr int OFF_P = OFF_E + 128 * 128;               // 2 tiles x 2 x [128][64] bf16, 128B swizzle
   static constexpr int OFF_KV = OFF_P + 2 * 2 * 128 * 128;      // ring of (K tile, V tile)
   static constexpr int OFF_BAR = OFF_KV + KV_STAGES * 2 * KV_TILE;
   static constexpr int BYTES = OFF_BAR + 256 + 1024;
@@ -165,12 +167,10 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // issues the tensor-core instructions and their commits.
     {
       constexpr uint32_t idesc_s = make_idesc(kAccF32, kFmtBF16, kFmtBF16, BM, BK);
-      constexpr uint32_t idesc_e = make_idesc(kAccF32, kFmtBF16, kFmtBF16, BM, 64);
       constexpr uint32_t idesc_o = make_idesc(kAccF32, kFmtBF16, kFmtBF16, BM, D, false, /*B MN-major*/ true);
       // Base descriptors; the start-address field counts 16-byte units, so "+ bytes / 16" moves a tile.
       const uint64_t dq = make_smem_desc(smem_u32(smem + L::OFF_Q), 16, 256, kSwizzle32B);        // K-major, 32B swizzle
       const uint64_t dk = make_smem_desc(smem_u32(smem + L::OFF_KV), 16, 256, kSwizzle32B);
-      const uint64_t drw = make_smem_desc(smem_u32(smem + L::OFF_RELW), 16, 1024, kSwizzle128B);  // K-major, 128B swizzle
       const uint64_t de = make_smem_desc(smem_u32(smem + L::OFF_E), 16, 1024, kSwizzle128B);
       const uint64_t dp = make_smem_desc(smem_u32(smem + L::OFF_P), 16, 1024, kSwizzle128B);
       // V: MN-major 32B swizzle, column chunks 4096 B apart (LBO), 8-key groups 256 B apart (SBO)
@@ -183,15 +183,12 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           const uint32_t d_tmem = tmem_base + t * 128;
           const uint64_t dkj = dk + uint32_t(j % KV_STAGES) * kStageUnits;
           const uint64_t dqt = dq + t * (4096 / 16);
-          const uint64_t drwt = drw + t * (16384 / 16);
 #pragma unroll
           for (int c = 0; c < CH; ++c)
             umma_f16_ss(d_tmem, dqt + c * (L::Q_CHUNK / 16), dkj + c * (4096 / 16), idesc_s, c != 0);
 #pragma unroll
-          for (int hcol = 0; hcol < 2; ++hcol)   // the one-hot block covers 64 keys: once per raster row
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-              umma_f16_ss(d_tmem + hcol * 64, drwt + c * 2, de + c * 2, idesc_e, 1u);
+          for (int c = 0; c < 4; ++c)            // + (rel_w/scale)[128 x 64] (from tensor memory) * E^T: 16 columns per product
+            umma_f16_ts(d_tmem, tmem_base + relw_col(t) + c * 8, de + c * 2, idesc_s, 1u);
           tc_commit(&s_full[t]);
         }
         __syncwarp();
@@ -275,7 +272,7 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     //  * table products (mode 1): rel[k] = T[pos + S - 1 - k] is contiguous in T in reverse key order starting
     //    at element `pos` (qh resp. qw) of a 128-byte-aligned slice: load from the aligned address below,
     //    shift down by pos % 8 elements, read backwards.
-    // rel_w/scale goes to the swizzled A-operand tile; rel_h stays in a per-thread array indexed by the key
+    // rel_w/scale goes to tensor memory as the A operand of the one-hot products; rel_h stays in a per-thread array indexed by the key
     // tile at run time (local memory: one coalesced word per thread and key tile).
     uint32_t relh_loc[32];                                 // word j = (rel_h[2j], rel_h[2j+1]) as bf16 bits
     {
@@ -323,22 +320,25 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       uint32_t rw[32];
       load_row(base_w, qw, SW, rw);
       load_row(base_h, qh, p.Sh, relh_loc);
-      uint8_t* relw_row = smem + L::OFF_RELW + t * 16384 + i * 128;
       uint8_t* e_row = smem + L::OFF_E + i * 128;
+      uint32_t wpk[32];                                    // (rel_w[2k], rel_w[2k+1]) / scale as bf16 pairs: the A operand row
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
-        uint32_t w[4], e[4];
+        uint32_t e[4];
 #pragma unroll
         for (int tt = 0; tt < 4; ++tt) {
           const int k0 = u * 8 + 2 * tt;
           const uint32_t pr = rw[u * 4 + tt];
-          w[tt] = pack2(__uint_as_float(pr << 16) * inv_scale, __uint_as_float(pr & 0xffff0000u) * inv_scale);
-          e[tt] = (i == k0 ? 0x3F80u : 0u) | (i == k0 + 1 ? 0x3F800000u : 0u);
+          wpk[u * 4 + tt] = pack2(__uint_as_float(pr << 16) * inv_scale, __uint_as_float(pr & 0xffff0000u) * inv_scale);
+          e[tt] = ((i & 63) == k0 ? 0x3F80u : 0u) | ((i & 63) == k0 + 1 ? 0x3F800000u : 0u);
         }
         const int phys = (u ^ (i & 7)) << 4;
-        *reinterpret_cast<uint4*>(relw_row + phys) = make_uint4(w[0], w[1], w[2], w[3]);
-        if (t == 0 && i < 64) *reinterpret_cast<uint4*>(e_row + phys) = make_uint4(e[0], e[1], e[2], e[3]);
+        if (t == 0) *reinterpret_cast<uint4*>(e_row + phys) = make_uint4(e[0], e[1], e[2], e[3]);
       }
+      tmem_st_32x32b_x16(lane_addr + relw_col(t), *reinterpret_cast<uint32_t(*)[16]>(&wpk[0]));
+      tmem_st_32x32b_x16(lane_addr + relw_col(t) + 16, *reinterpret_cast<uint32_t(*)[16]>(&wpk[16]));
+      tmem_st_wait();
+      tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive_warp(pro_done);
     }
