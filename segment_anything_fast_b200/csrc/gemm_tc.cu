@@ -54,6 +54,10 @@ struct GemmParams {
   int tg, tg_bn;                 // tg > 1: a tile is tg independent products of tg_bn columns each (consecutive
                                  // batches sharing W), so narrow batched outputs still fill a 256-column tile
   int k2;                        // grouped tiles with K = 80 bf16: a stage holds a whole product (64 + 16 columns of K)
+  int nstages;                   // pipeline stages in use: STAGES, or STAGES - 1 when the last stage's shared memory
+                                 // serves as three more output staging tiles (out_ring)
+  int out_ring;                  // 1: every 64-column chunk of a tile has its own staging tile (short-K products, whose
+                                 // epilogue would otherwise wait for each chunk's store to be read before the next)
   int hm_group;                  // > 0: head-major output, hm_group 16-column pieces per head (see launch_gemm)
   int epilogue;
 };
@@ -152,7 +156,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tma_load_2d(sa + A_STAGE_BYTES, &tmB, &full_bar[stage], 0, 0);
             tma_load_2d(sa + K2_A1_OFF, &tmA2, &full_bar[stage], 64, arow);
             tma_load_2d(sa + K2_B1_OFF, &tmB2, &full_bar[stage], 64, 0);
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            if (++stage == uint32_t(p.nstages)) { stage = 0; phase ^= 1u; }
           }
           continue;
         }
@@ -163,7 +167,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           mbar_expect_tx(&full_bar[stage], A_STAGE_BYTES + p.tg_bn * SLAB_BYTES);
           tma_load_2d(sa, &tmA, &full_bar[stage], a_col0 + ks * slab_elems, m0 + (bt * p.tg + g) * p.a_row_stride);
           tma_load_2d(sa + A_STAGE_BYTES, &tmB, &full_bar[stage], ks * slab_elems, p.tg > 1 ? 0 : n0);
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if (++stage == uint32_t(p.nstages)) { stage = 0; phase ^= 1u; }
         }
       }
     }
@@ -196,7 +200,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               tc_commit(&empty_bar[stage]);
             }
             __syncwarp();
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            if (++stage == uint32_t(p.nstages)) { stage = 0; phase ^= 1u; }
           }
         } else
         for (int gk = 0; gk < p.tg * p.k_slabs; ++gk) {
@@ -218,7 +222,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tc_commit(&empty_bar[stage]);             // stage reusable once these MMAs have read it
           }
           __syncwarp();
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if (++stage == uint32_t(p.nstages)) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
         if (elect_one()) tc_commit(&acc_full[acc]);   // accumulator complete
@@ -320,10 +324,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             packed[u] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
                                    pack_bf16x2(v[6], v[7]));
           }
-          if (et == 0) tma_store_wait_read<0>();        // the staging tile is free again
-          epi_sync();
+          // staging tile of this chunk: the one after the ring, or (out_ring) one of four, the last three carved
+          // out of the unused last pipeline stage; then only the tile's first chunk waits for earlier stores
+          uint8_t* so = stage_out;
+          if (p.out_ring && c > 0) so = smem + (STAGES - 1) * STAGE_BYTES + (c - 1) * OUT_STAGE_BYTES;
+          if (!p.out_ring || c == 0) {
+            if (et == 0) tma_store_wait_read<0>();      // the staging tile(s) are free again
+            epi_sync();
+          }
           if (p.hm_group == 0) {
-            uint8_t* srow = stage_out + erow * 128;
+            uint8_t* srow = so + erow * 128;
 #pragma unroll
             for (int u = 0; u < 4; ++u)
               *reinterpret_cast<uint4*>(srow + (((half * 4 + u) ^ (erow & 7)) << 4)) = packed[u];
@@ -340,7 +350,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           epi_sync();
           if (et == 0) {
             if (p.hm_group == 0) {
-              tma_store_2d(&tmOut, stage_out, bt * p.tg * p.o_col_stride + col0, m0);  // clipped at M and at the row end
+              tma_store_2d(&tmOut, so, bt * p.tg * p.o_col_stride + col0, m0);  // clipped at M and at the row end
             } else {
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
@@ -477,6 +487,8 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
     p.bn = p.tg * N;
   }
   p.k2 = (p.tg > 1 && !int8 && K == 80) ? 1 : 0;
+  p.out_ring = (p.tg > 1 && head_dim == 0) ? 1 : 0;            // grouped short-K products: the store chain is what binds
+  p.nstages = p.out_ring ? STAGES - 1 : STAGES;
   p.tiles_n = p.tg > 1 ? 1 : (N + p.bn - 1) / p.bn;
   if (p.tg > 1) p.N = p.tg * N;                                  // logical width of a grouped tile
   p.tiles_per_batch = ((M + BM - 1) / BM) * p.tiles_n;
