@@ -3,6 +3,8 @@ batch, normalisation + encoder on the device, one D2H copy of the embeddings.
 
 ``encode`` is the blocking form; ``submit`` / ``result`` is the pipelined form (two slots, copies on their own
 streams): the upload of batch i+1 and the download of batch i-1 overlap the encoder pass of batch i.
+With ``graph=True`` the normalise + encoder launch sequence (about 230 kernels for ViT-H) is recorded once per
+staging buffer as a CUDA graph and replayed, which takes the per-launch host cost out of small-batch latency.
 
 This is the call a data-parallel worker makes per batch (one process per GPU).  It replaces the
 upload + ``Sam.preprocess`` + ``image_encoder`` sequence of ``SamPredictor.set_torch_image``
@@ -20,8 +22,12 @@ PIXEL_STD = (58.395, 57.12, 57.375)      # build_sam.py:140
 
 class EncoderSession:
     def __init__(self, encoder, batch: int, device: Optional[torch.device] = None,
-                 pixel_mean: Sequence[float] = PIXEL_MEAN, pixel_std: Sequence[float] = PIXEL_STD) -> None:
+                 pixel_mean: Sequence[float] = PIXEL_MEAN, pixel_std: Sequence[float] = PIXEL_STD,
+                 graph: bool = False) -> None:
         self.encoder = encoder
+        self.graph = graph
+        self._graphs = {}          # device input buffer address -> (CUDAGraph, embeddings written by a replay)
+        self._pool = None
         self.device = device or next(encoder.parameters()).device
         if self.device.type != "cuda":
             raise RuntimeError("EncoderSession needs the encoder on a CUDA device")
@@ -46,8 +52,31 @@ class EncoderSession:
 
     def encode_device(self, images_u8: torch.Tensor) -> torch.Tensor:
         """uint8 ``[B,3,S,S]`` on the device -> embeddings ``[B,out_chans,S/16,S/16]`` (bf16, device)."""
+        if self.graph and images_u8.shape[0] == self.batch:
+            return self._replay(images_u8)
         x = ops.normalize_u8(images_u8, self.mean, self.std, out=self.dev_norm[: images_u8.shape[0]])
         return self.encoder(x)
+
+    def _replay(self, dev_in: torch.Tensor) -> torch.Tensor:
+        """Replay (recording it on first use) the graph that reads ``dev_in``; its output tensor is reused by
+        every replay, so a caller that keeps embeddings across calls must copy them."""
+        ent = self._graphs.get(dev_in.data_ptr())
+        if ent is None:
+            run = lambda: self.encoder(ops.normalize_u8(dev_in, self.mean, self.std, out=self.dev_norm))
+            main = torch.cuda.current_stream(self.device)
+            side = torch.cuda.Stream(self.device)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):          # weight packing and allocator warm-up stay outside the recording
+                run()
+                run()
+            main.wait_stream(side)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=self._pool):
+                emb = run()
+            self._pool = g.pool()                  # the graphs never run concurrently: one pool for their scratch
+            ent = self._graphs[dev_in.data_ptr()] = (g, emb)
+        ent[0].replay()
+        return ent[1]
 
     def encode(self, images_u8_host: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Host uint8 batch (or what is already in ``self.host_in``) -> host bf16 embeddings.
@@ -99,13 +128,16 @@ class EncoderSession:
             sl["dev_in"].copy_(sl["host_in"], non_blocking=True)
             sl["uploaded"].record(self._s_in)
         main.wait_event(sl["uploaded"])
+        if self.graph:
+            main.wait_event(sl["downloaded"])             # a replay overwrites the embeddings of this slot's last pass
         emb = self.encode_device(sl["dev_in"])
         sl["computed"].record(main)
         self._s_out.wait_event(sl["computed"])
         with torch.cuda.stream(self._s_out):
             sl["host_out"].copy_(emb, non_blocking=True)
             sl["downloaded"].record(self._s_out)
-        emb.record_stream(self._s_out)
+        if not self.graph:
+            emb.record_stream(self._s_out)
         sl["emb"], sl["busy"] = emb, True
         return slot
 

@@ -152,3 +152,29 @@ def test_encoder_session_blocking_and_pipelined_agree(cuda):
         assert torch.equal(a, b)
     with pytest.raises(RuntimeError):
         sess.result(0)                                   # nothing in flight any more
+
+
+def test_encoder_session_graph_replay_matches_eager(cuda):
+    """EncoderSession(graph=True) records the normalise + encoder launches once per staging buffer and replays
+    them: blocking and pipelined results are bit for bit those of the eager session."""
+    from segment_anything_fast_b200 import EncoderSession
+    sd = eo.seeded_state_dict(TINY, seed=1)
+    enc = build_encoder(TINY, sd)
+    eager = EncoderSession(enc, batch=2)
+    graph = EncoderSession(enc, batch=2, graph=True)
+    g = torch.Generator().manual_seed(32)
+    batches = [torch.randint(0, 256, (2, 3, 1024, 1024), generator=g, dtype=torch.uint8) for _ in range(5)]
+    want = [eager.encode(b).clone() for b in batches]
+    for b, w in zip(batches[:2], want[:2]):
+        assert torch.equal(graph.encode(b), w)
+    got, pending = [], None
+    for b in batches:
+        slot = graph.submit(b)
+        if pending is not None:
+            got.append(graph.result(pending).clone())
+        pending = slot
+    got.append(graph.result(pending).clone())
+    cuda.check_status()
+    assert len(graph._graphs) == 2                       # one recording per device staging buffer
+    for a, b in zip(want, got):
+        assert torch.equal(a, b)
