@@ -231,6 +231,17 @@ int samb_normalize_u8(const uint8_t* x, void* y, int B, int C, int H, int W, con
 int samb_mask_stats(const void* logits, int is_bf16, int64_t N, int H, int W, float thr, float offset,
                     int32_t* inter, int32_t* uni, int32_t* boxes, uint8_t* binary, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Uncompressed run-length encoding of boolean masks [N, H, W] (bytes 0 / 1; W <= 4096) in column-major
+ * pixel order, the layout pycocotools reads: row n of counts [N, cap] receives the run lengths (the
+ * leading run is of zeros and has length 0 when pixel (0,0) is set) and n_counts[n] how many there are.
+ * A mask with more than cap runs still reports its n_counts; its row of counts is then unspecified and
+ * the caller repeats the call with a larger cap.
+ * ref: mask_to_rle_pytorch (utils/amg.py:144-170) and mask_to_rle_pytorch_2 (utils/amg.py:106-141), called
+ * at automatic_mask_generator.py:257. */
+int samb_mask_rle(const uint8_t* masks, int64_t N, int H, int W, int32_t* counts, int32_t* n_counts, int cap,
+                  void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,12 +1,14 @@
 """CPU restatement of the mask filters the automatic mask generator applies to predicted mask logits.
 
-TEST INFRASTRUCTURE ONLY (checker for ``samb_mask_stats``).  numpy, integer-exact.  Pinned by
-``tests/golden/amg_fp32.npz``, outputs of the reference's own functions on seeded logits.
+TEST INFRASTRUCTURE ONLY (checker for ``samb_mask_stats`` and ``samb_mask_rle``).  numpy, integer-exact.  Pinned by
+``tests/golden/amg_fp32.npz``, outputs of the reference's own functions on seeded logits and masks.
 
 Reference code followed (segment_anything_fast/utils/amg.py):
   calculate_stability_score :193-213 — IoU of the masks thresholded at ``thr + offset`` and ``thr - offset``
   (one contains the other, so the IoU is a ratio of two pixel counts);
-  batched_mask_to_box :340-383 — XYXY bounds of a boolean mask, [0,0,0,0] when it is empty.
+  batched_mask_to_box :340-383 — XYXY bounds of a boolean mask, [0,0,0,0] when it is empty;
+  mask_to_rle_pytorch :144-170 (and its batched twin :106-141) — run lengths of the mask read column by column,
+  starting with a run of zeros; rle_to_mask :173-185 is the inverse.
 """
 import numpy as np
 
@@ -33,3 +35,27 @@ def batched_mask_to_box(masks: np.ndarray) -> np.ndarray:
         if ys.size:
             out[i] = (xs.min(), ys.min(), xs.max(), ys.max())
     return out
+
+
+def mask_to_rle(masks: np.ndarray):
+    """Boolean ``[N, H, W]`` -> list of ``{"size": [H, W], "counts": [...]}``."""
+    out = []
+    n, h, w = masks.shape
+    for m in masks:
+        flat = np.ascontiguousarray(m.T).reshape(-1).astype(bool)           # column-major pixel order
+        edges = np.flatnonzero(flat[1:] != flat[:-1]) + 1
+        bounds = np.concatenate(([0], edges, [h * w]))
+        counts = ([0] if flat[0] else []) + np.diff(bounds).tolist()
+        out.append({"size": [h, w], "counts": counts})
+    return out
+
+
+def rle_to_mask(rle) -> np.ndarray:
+    h, w = rle["size"]
+    flat = np.zeros(h * w, dtype=bool)
+    pos, val = 0, False
+    for c in rle["counts"]:
+        flat[pos:pos + c] = val
+        pos += c
+        val = not val
+    return flat.reshape(w, h).T

@@ -1,10 +1,10 @@
-"""The automatic mask generator's per-mask filters on the GPU, under the reference's function names
-(segment_anything_fast/utils/amg.py:193-213, 340-383), so that ``automatic_mask_generator.py`` can import
-them from here instead.  ``mask_stats`` is the fused form: one pass over the logits gives the stability
+"""The automatic mask generator's per-mask filters and run-length encoding on the GPU, under the reference's
+function names (segment_anything_fast/utils/amg.py:106-170, 193-213, 340-383), so that
+``automatic_mask_generator.py`` can import them from here instead.  ``mask_stats`` is the fused form: one pass over the logits gives the stability
 score, the boxes and the thresholded masks that ``_process_batch`` computes with four passes
 (automatic_mask_generator.py:335-345).
 """
-from typing import Optional, Tuple
+from typing import Any, Dict, List, Optional, Tuple
 
 import torch
 
@@ -44,3 +44,36 @@ def batched_mask_to_box(masks: torch.Tensor) -> torch.Tensor:
     if masks.numel() == 0:
         return torch.zeros(*masks.shape[:-2], 4, device=masks.device)
     return mask_stats(masks.to(torch.float32), 0.5, 0.0, want_binary=False)[1].to(torch.int64)
+
+
+def mask_rle_counts(masks: torch.Tensor, cap: int = 4096) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Boolean masks ``[N, H, W]`` (CUDA) -> run lengths ``[N, cap']`` (int32, column-major pixel order, leading run
+    of zeros) and the number of runs ``[N]`` of each mask; ``cap'`` grows to the longest encoding when ``cap`` is
+    too small (one more launch).  Reads ``n_counts`` back, so it synchronises the stream."""
+    _need(masks, torch.bool, "masks")
+    if masks.dim() != 3:
+        raise RuntimeError("mask_rle_counts: masks must be [N, H, W]")
+    x = masks.contiguous().view(torch.uint8)
+    N, H, W = x.shape
+    n_counts = torch.empty(N, dtype=torch.int32, device=x.device)
+    while True:
+        counts = torch.empty(N, cap, dtype=torch.int32, device=x.device)
+        _lib.check(_lib.load().samb_mask_rle(x.data_ptr(), N, H, W, counts.data_ptr(), n_counts.data_ptr(), cap, _stream()),
+                   "samb_mask_rle")
+        need = int(n_counts.max().item()) if N else 0
+        if need <= cap:
+            return counts[:, :max(need, 1)], n_counts
+        cap = need
+
+
+def mask_to_rle_pytorch(tensor: torch.Tensor) -> List[Dict[str, Any]]:
+    """Masks ``[N, H, W]`` -> ``[{"size": [H, W], "counts": [...]}, ...]``, the uncompressed RLE pycocotools reads."""
+    if tensor.shape[0] == 0:
+        return []
+    _, h, w = tensor.shape
+    counts, n = mask_rle_counts(tensor.to(torch.bool))
+    rows, n = counts.cpu().tolist(), n.cpu().tolist()
+    return [{"size": [h, w], "counts": r[:k]} for r, k in zip(rows, n)]
+
+
+mask_to_rle_pytorch_2 = mask_to_rle_pytorch

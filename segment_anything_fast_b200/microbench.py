@@ -6,6 +6,7 @@ the shape allows it).  One JSON line per run:
     python -m segment_anything_fast_b200.microbench attn-window --batch 200 --heads 16 --dim 80
     python -m segment_anything_fast_b200.microbench layernorm --rows 131072 --cols 1280 [--quant]
     python -m segment_anything_fast_b200.microbench mask-stats --n 192 --h 1024 --w 1024 [--bf16]
+    python -m segment_anything_fast_b200.microbench mask-rle --n 192 --h 1024 --w 1024
 
 The two attention commands at their defaults are the standalone relative-position attention
 benchmark (q, k, v ~ N(0,1), rel_h / rel_w ~ N(0,0.5), bf16).
@@ -53,7 +54,10 @@ def main():
     ms_ = sub.add_parser("mask-stats")
     ms_.add_argument("--n", type=int, default=192); ms_.add_argument("--h", type=int, default=1024)
     ms_.add_argument("--w", type=int, default=1024); ms_.add_argument("--bf16", action="store_true")
-    for p in (g, ag, aw, ln, ms_):
+    mr = sub.add_parser("mask-rle")
+    mr.add_argument("--n", type=int, default=192); mr.add_argument("--h", type=int, default=1024)
+    mr.add_argument("--w", type=int, default=1024)
+    for p in (g, ag, aw, ln, ms_, mr):
         p.add_argument("--iters", type=int, default=10); p.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
     torch.manual_seed(0)
@@ -104,6 +108,21 @@ def main():
         ms = _time(lambda: amg.mask_stats(x, 0.0, 1.0), a.iters, a.warmup)
         nbytes = x.numel() * (x.element_size() + 1)                            # logits in, binary masks out
         out.update(shape=[a.n, a.h, a.w], dtype="bf16" if a.bf16 else "f32", ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1))
+    elif a.cmd == "mask-rle":
+        from . import _lib
+        # blob-like masks: a coarse random field upsampled and thresholded (a few hundred runs per mask)
+        coarse = torch.randn(a.n, 1, 16, 16, device=dev)
+        m = (torch.nn.functional.interpolate(coarse, size=(a.h, a.w), mode="bilinear")[:, 0] > 0.3).contiguous()
+        cap = 8192
+        counts = torch.empty(a.n, cap, dtype=torch.int32, device=dev)
+        n_counts = torch.empty(a.n, dtype=torch.int32, device=dev)
+        mv = m.view(torch.uint8)
+        fn = lambda: _lib.check(_lib.load().samb_mask_rle(mv.data_ptr(), a.n, a.h, a.w, counts.data_ptr(), n_counts.data_ptr(),
+                                                          cap, ops._stream()), "samb_mask_rle")
+        ms = _time(fn, a.iters, a.warmup)
+        runs = int(n_counts.sum().item())
+        nbytes = m.numel() + runs * 4                                          # masks in once, run lengths out
+        out.update(shape=[a.n, a.h, a.w], runs_per_mask=round(runs / a.n, 1), ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1))
     else:
         R, C = a.rows, a.cols
         x = torch.randn(R, C, device=dev).bfloat16()

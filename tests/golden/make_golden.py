@@ -76,7 +76,15 @@ def golden_amg():
     logits[3, 5:9, 40:50] = 4.0           # one rectangle touching the right border
     score = calculate_stability_score(logits, 0.0, 1.0)
     boxes = batched_mask_to_box(logits > 0.0)
-    np.savez_compressed(os.path.join(HERE, "amg_fp32.npz"), logits=logits.numpy(), score=score.numpy(), boxes=boxes.numpy())
+    # run-length encodings of the thresholded masks (both reference encoders agree; checked here)
+    from segment_anything_fast.utils.amg import mask_to_rle_pytorch, mask_to_rle_pytorch_2
+    masks = logits > 0.0
+    rles = mask_to_rle_pytorch(masks)
+    assert rles == mask_to_rle_pytorch_2(masks)
+    rle_len = np.array([len(r["counts"]) for r in rles], dtype=np.int64)
+    rle_counts = np.concatenate([np.asarray(r["counts"], dtype=np.int64) for r in rles])
+    np.savez_compressed(os.path.join(HERE, "amg_fp32.npz"), logits=logits.numpy(), score=score.numpy(), boxes=boxes.numpy(),
+                        rle_len=rle_len, rle_counts=rle_counts)
 
 
 def main():

@@ -44,3 +44,4 @@ def test_argument_errors_are_caught_on_the_host(lib):
     assert lib.samb_gemm_bf16(None, 8, None, 8, None, None, 0, 0, None, 8, 1, 8, 8, 0, None, None) == -1
     assert lib.samb_layernorm_bf16(None, None, None, None, 1, 8, 1e-6, 0, 0, None) == -1
     assert lib.samb_selftest_bounded_wait(None, 10, None) == -1
+    assert lib.samb_mask_rle(None, 1, 8, 8, None, None, 16, None) == -1

@@ -122,3 +122,21 @@ def test_decoder_oracle_matches_reference_modules(golden_dir):
     assert torch.allclose(iou, torch.from_numpy(g["iou"]), atol=1e-4)
     area = masks.float().mean((2, 3))
     assert torch.allclose(area, torch.from_numpy(g["area"]), atol=1e-4)
+
+
+def test_amg_oracle_matches_reference_functions(golden_dir):
+    """Stability score, mask boxes and run-length encoding restatements against the outputs of the reference's
+    own functions on the same seeded logits (integer exact); the encoding decodes back to the mask."""
+    from oracle import amg_oracle as ao
+    g = _load(golden_dir, "amg_fp32.npz")
+    logits = g["logits"]
+    score = ao.calculate_stability_score(logits, 0.0, 1.0)
+    assert np.array_equal(np.nan_to_num(score, nan=-1), np.nan_to_num(g["score"], nan=-1))
+    masks = logits > 0
+    assert np.array_equal(ao.batched_mask_to_box(masks), g["boxes"])
+    rles = ao.mask_to_rle(masks)
+    assert [len(r["counts"]) for r in rles] == g["rle_len"].tolist()
+    assert np.array_equal(np.concatenate([np.asarray(r["counts"]) for r in rles]), g["rle_counts"])
+    for r, m in zip(rles, masks):
+        assert r["size"] == list(m.shape) and sum(r["counts"]) == m.size
+        assert np.array_equal(ao.rle_to_mask(r), m)
