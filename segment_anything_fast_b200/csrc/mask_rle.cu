@@ -9,13 +9,14 @@
 // (row, which of the four columns changed); a block-wide exclusive scan in (column, band) order gives each
 // (column, band) its rank; pass 2 stores the column-major index of every change at its rank, from the list, or by
 // walking the band again when a thread saw more changed rows than its list holds (noise-like masks); pass 3 turns
-// consecutive indices into run lengths in place.  The mask is read once for blob-like masks.  No atomics, no scratch
+// consecutive indices into run lengths (staged in shared memory when the mask has at most 8192 of them, else in place).  The mask is read once for blob-like masks.  No atomics, no scratch
 // memory: a mask with more runs than `cap` reports the count it needs and leaves its row of `counts` unspecified.
 #include "common.cuh"
 
 namespace samb {
 namespace {
 
+constexpr int kPosLen = 8192;                        // boundaries a block can stage in shared memory (4 bytes each)
 constexpr int kListLen = 48;                         // changed rows a thread can note (2 bytes each)
 constexpr uint32_t kNibbleMul = (1u << 24) | (1u << 17) | (1u << 10) | (1u << 3);   // bytes 0/1 -> bits 24..27
 
@@ -40,6 +41,7 @@ mask_rle_kernel(const uint8_t* __restrict__ masks, int H, int W, int32_t* __rest
   constexpr int kRowsPerBatch = kMaxThreads <= 512 ? 16 : 8;
   __shared__ int s_cnt[4 * kMaxThreads];             // [column][band] change counts, then their exclusive prefix
   extern __shared__ uint16_t s_list[];               // [list_len][blockDim.x]: (row in band) << 4 | changed columns
+  int* s_pos = reinterpret_cast<int*>(s_list + size_t(kListLen) * blockDim.x);   // [kPosLen] staged boundaries
   __shared__ int warp_tot[32];
   __shared__ int s_total;
   const long long n = blockIdx.x;
@@ -142,10 +144,14 @@ mask_rle_kernel(const uint8_t* __restrict__ masks, int H, int W, int32_t* __rest
   const int nchg = s_total;
   const int first = __ldg(m) != 0 ? 1 : 0;
 
-  // ---- pass 2: column-major index of every change, at slot first + 1 + rank (slot `first` is index 0)
+  // ---- pass 2: column-major index of every change, at slot first + 1 + rank (slot `first` is index 0).
+  // Masks with few enough boundaries stage them in shared memory (boundary k at s_pos[k]) and pass 3 writes the run
+  // lengths in one coalesced sweep; the others go through the `counts` row itself.
+  const bool staged = nchg + 1 <= kPosLen;
   if (threadIdx.x == 0) {
     if (first && cap > 0) out[0] = 0;
-    if (first < cap) out[first] = 0;
+    if (staged) s_pos[0] = 0;
+    else if (first < cap) out[first] = 0;
     n_counts[n] = first + nchg + 1;
   }
   if (live && noted != 0) {
@@ -159,7 +165,8 @@ mask_rle_kernel(const uint8_t* __restrict__ masks, int H, int W, int32_t* __rest
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           if ((ent >> j) & 1u) {
-            if (slot[j] < cap) out[slot[j]] = idx + j * H;
+            if (staged) s_pos[slot[j] - first] = idx + j * H;
+            else if (slot[j] < cap) out[slot[j]] = idx + j * H;
             ++slot[j];
           }
         }
@@ -179,7 +186,8 @@ mask_rle_kernel(const uint8_t* __restrict__ masks, int H, int W, int32_t* __rest
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 if ((chg >> (8 * j)) & 0xffu) {
-                  if (slot[j] < cap) out[slot[j]] = (c0 + j) * H + y0 + r;
+                  if (staged) s_pos[slot[j] - first] = (c0 + j) * H + y0 + r;
+                  else if (slot[j] < cap) out[slot[j]] = (c0 + j) * H + y0 + r;
                   ++slot[j];
                 }
               }
@@ -192,8 +200,14 @@ mask_rle_kernel(const uint8_t* __restrict__ masks, int H, int W, int32_t* __rest
   }
   __syncthreads();
 
-  // ---- pass 3: boundaries -> run lengths, in place, a block-wide chunk at a time
+  // ---- pass 3: boundaries -> run lengths
   const int hw = H * W;
+  if (staged) {
+    for (int k = int(threadIdx.x); k <= nchg; k += int(blockDim.x))
+      if (first + k < cap) out[first + k] = (k < nchg ? s_pos[k + 1] : hw) - s_pos[k];
+    return;
+  }
+  // in place, a block-wide chunk at a time
   for (int base = 0; base <= nchg; base += int(blockDim.x)) {
     const int k = base + int(threadIdx.x);
     const bool ok = k <= nchg && first + k < cap;
@@ -227,10 +241,10 @@ extern "C" int samb_mask_rle(const uint8_t* masks, int64_t N, int H, int W, int3
   auto st = static_cast<cudaStream_t>(stream);
   const bool vec = W % 4 == 0 && (reinterpret_cast<uintptr_t>(masks) & 3u) == 0;
   const int list_len = band_rows <= 4096 ? kListLen : 0;       // a list entry keeps 12 bits of row
-  const size_t list_bytes = size_t(kListLen) * threads * sizeof(uint16_t);
+  const size_t list_bytes = size_t(kListLen) * threads * sizeof(uint16_t) + size_t(kPosLen) * sizeof(int);
   auto kern = vec ? (max_threads == 512 ? mask_rle_kernel<true, 512> : mask_rle_kernel<true, 1024>)
                   : (max_threads == 512 ? mask_rle_kernel<false, 512> : mask_rle_kernel<false, 1024>);
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(size_t(kListLen) * 1024 * sizeof(uint16_t))) !=
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(size_t(kListLen) * 1024 * sizeof(uint16_t) + size_t(kPosLen) * sizeof(int))) !=
       cudaSuccess)
     return SAMB_E_LAUNCH;
   kern<<<unsigned(N), threads, list_bytes, st>>>(masks, H, W, counts, n_counts, cap, col_threads, bands, band_rows, list_len);
