@@ -35,7 +35,7 @@ __device__ __forceinline__ uint32_t load_cols(const uint8_t* __restrict__ row, i
 // col_threads + group.  Masks up to 2048 columns run 512-thread blocks (two per SM, 16 rows in flight per thread);
 // wider ones 1024-thread blocks with 8 rows in flight.
 template <bool kVec, int kMaxThreads>
-__global__ void __launch_bounds__(kMaxThreads)
+__global__ void __launch_bounds__(kMaxThreads, kMaxThreads <= 512 ? 2 : 1)
 mask_rle_kernel(const uint8_t* __restrict__ masks, int H, int W, int32_t* __restrict__ counts,
                 int32_t* __restrict__ n_counts, int cap, int col_threads, int bands, int band_rows, int list_len) {
   constexpr int kRowsPerBatch = kMaxThreads <= 512 ? 16 : 8;
