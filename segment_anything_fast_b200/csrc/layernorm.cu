@@ -57,14 +57,26 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return u;
 }
 
-// rint(x / sc), bit-identical to the IEEE quotient, without paying for a division per element:
-// x * (1/sc) is within 2^-23 relative (1.5e-5 absolute for |x/sc| <= 127.5) of the true quotient, so the
-// two roundings can only disagree next to a half-integer; only there is the real division evaluated.
-__device__ __forceinline__ float div_rint(float x, float sc, float inv_sc) {
-  const float t = x * inv_sc;
-  float r = rintf(t);
-  if (fabsf(fabsf(t - r) - 0.5f) < 4e-5f) r = rintf(__fdiv_rn(x, sc));
-  return r;
+// Eight values -> eight int8 (two words), each rint(x / sc) bit-identical to the IEEE quotient, without a division
+// or a conversion instruction per element.  x * (1/sc) is within 2^-23 relative (1.5e-5 absolute for |x/sc| <= 127.5)
+// of the true quotient, so the two roundings can only disagree next to a half-integer; only there is the real
+// division evaluated.  Adding 1.5 * 2^23 rounds to the nearest even integer and leaves it, in two's complement,
+// in the low mantissa bits, so its low byte is the int8.  |x / sc| <= 127 (1 + 2^-24) because sc is the row's
+// absmax / 127 (or larger), so nothing needs clamping.
+__device__ __forceinline__ uint2 quant8(const float (&f)[8], float sc, float inv_sc) {
+  constexpr float kMagic = 12582912.0f;
+  uint32_t b[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float t = __fmul_rn(f[j], inv_sc);
+    float y = __fadd_rn(t, kMagic);
+    const float r = __fadd_rn(y, -kMagic);
+    if (fabsf(fabsf(t - r) - 0.5f) < 4e-5f) y = __fadd_rn(rintf(__fdiv_rn(f[j], sc)), kMagic);
+    b[j] = __float_as_uint(y);
+  }
+  const uint32_t b01 = __byte_perm(b[0], b[1], 0x0040), b23 = __byte_perm(b[2], b[3], 0x0040);
+  const uint32_t b45 = __byte_perm(b[4], b[5], 0x0040), b67 = __byte_perm(b[6], b[7], 0x0040);
+  return make_uint2(__byte_perm(b01, b23, 0x5410), __byte_perm(b45, b67, 0x5410));
 }
 
 // kNorm: apply LayerNorm; kQuant: emit int8 + scale instead of bf16.
@@ -178,14 +190,7 @@ row_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
     if (vi < nvec) {
       float f[8];
       unpack8(raw[i], f);
-      uint32_t w[2] = {0u, 0u};
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float t = div_rint(f[j], sc, inv_sc);
-        t = fminf(fmaxf(t, -127.f), 127.f);
-        w[j >> 2] |= (uint32_t(int(t)) & 0xffu) << ((j & 3) * 8);
-      }
-      qr[vi] = make_uint2(w[0], w[1]);
+      qr[vi] = quant8(f, sc, inv_sc);
     }
   }
 }
@@ -233,14 +238,7 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ yq, 
     if (vi < nvec) {
       float f[8];
       unpack8(raw[i], f);
-      uint32_t w[2] = {0u, 0u};
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float t = div_rint(f[j], sc, inv_sc);
-        t = fminf(fmaxf(t, -127.f), 127.f);
-        w[j >> 2] |= (uint32_t(int(t)) & 0xffu) << ((j & 3) * 8);
-      }
-      qr[vi] = make_uint2(w[0], w[1]);
+      qr[vi] = quant8(f, sc, inv_sc);
     }
   }
 }
@@ -289,14 +287,7 @@ quant_rows_wide_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__
     if (vi < nvec) {
       float f[8];
       unpack8(raw[i], f);
-      uint32_t w[2] = {0u, 0u};
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float t = div_rint(f[j], sc, inv_sc);
-        t = fminf(fmaxf(t, -127.f), 127.f);
-        w[j >> 2] |= (uint32_t(int(t)) & 0xffu) << ((j & 3) * 8);
-      }
-      qr[vi] = make_uint2(w[0], w[1]);
+      qr[vi] = quant8(f, sc, inv_sc);
     }
   }
 }

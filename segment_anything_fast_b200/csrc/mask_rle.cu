@@ -9,8 +9,9 @@
 // (row, which of the four columns changed); a block-wide exclusive scan in (column, band) order gives each
 // (column, band) its rank; pass 2 stores the column-major index of every change at its rank, from the list, or by
 // walking the band again when a thread saw more changed rows than its list holds (noise-like masks); pass 3 turns
-// consecutive indices into run lengths (staged in shared memory when the mask has at most 8192 of them, else in place).  The mask is read once for blob-like masks.  No atomics, no scratch
-// memory: a mask with more runs than `cap` reports the count it needs and leaves its row of `counts` unspecified.
+// consecutive indices into run lengths (staged in shared memory when the mask has at most 8192 of them, else in
+// place).  The mask is read once for blob-like masks.  No atomics, no scratch memory: a mask with more runs than
+// `cap` reports the count it needs and leaves its row of `counts` unspecified.
 #include "common.cuh"
 
 namespace samb {
