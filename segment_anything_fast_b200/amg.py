@@ -71,6 +71,8 @@ def mask_to_rle_pytorch(tensor: torch.Tensor) -> List[Dict[str, Any]]:
     if tensor.shape[0] == 0:
         return []
     _, h, w = tensor.shape
+    if not tensor.is_cuda:                                # the small-region post-processing hands over host masks
+        tensor = tensor.cuda()
     counts, n = mask_rle_counts(tensor.to(torch.bool))
     rows, n = counts.cpu().tolist(), n.cpu().tolist()
     return [{"size": [h, w], "counts": r[:k]} for r, k in zip(rows, n)]

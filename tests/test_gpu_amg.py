@@ -114,6 +114,7 @@ def test_mask_rle_after_mask_stats_pipeline():
     logits = torch.nn.functional.interpolate(torch.randn(5, 1, 32, 40, generator=g), size=(512, 640), mode="bilinear")[:, 0]
     _, _, binary = amg.mask_stats(logits.cuda(), 0.0, 1.0)
     rles = amg.mask_to_rle_pytorch(binary)
+    assert amg.mask_to_rle_pytorch(binary.cpu()[:1]) == rles[:1]          # host masks are uploaded, not encoded on the CPU
     assert rles == ao.mask_to_rle((logits > 0).numpy())
     for r, m in zip(rles, logits > 0):
         assert sum(r["counts"][1::2]) == int(m.sum())                    # area_from_rle, utils/amg.py:188-189
