@@ -137,7 +137,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
-      bool ok = true;
+      bool ok = true, b_loaded = false;
       for (long long tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
         const int bt = int(tile / p.tiles_per_batch);
         const long long tb = tile - bt * p.tiles_per_batch;
@@ -151,11 +151,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 1))) break;
             uint8_t* sa = smem + stage * STAGE_BYTES;
             const int arow = m0 + (bt * p.tg + g) * p.a_row_stride;
-            mbar_expect_tx(&full_bar[stage], A_STAGE_BYTES + p.tg_bn * SLAB_BYTES + BM * 32 + p.tg_bn * 32);
+            // every product multiplies by the same tables: they are fetched once, with the CTA's first product,
+            // into stage 0, and stay there (later fills of stage 0 bring only the A parts)
+            const bool with_b = !b_loaded;
+            mbar_expect_tx(&full_bar[stage], A_STAGE_BYTES + BM * 32 + (with_b ? p.tg_bn * SLAB_BYTES + p.tg_bn * 32 : 0));
             tma_load_2d(sa, &tmA, &full_bar[stage], 0, arow);
-            tma_load_2d(sa + A_STAGE_BYTES, &tmB, &full_bar[stage], 0, 0);
             tma_load_2d(sa + K2_A1_OFF, &tmA2, &full_bar[stage], 64, arow);
-            tma_load_2d(sa + K2_B1_OFF, &tmB2, &full_bar[stage], 64, 0);
+            if (with_b) {
+              tma_load_2d(sa + A_STAGE_BYTES, &tmB, &full_bar[stage], 0, 0);
+              tma_load_2d(sa + K2_B1_OFF, &tmB2, &full_bar[stage], 64, 0);
+              b_loaded = true;
+            }
             if (++stage == uint32_t(p.nstages)) { stage = 0; phase ^= 1u; }
           }
           continue;
@@ -192,11 +198,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tc_fence_after();
             if (elect_one()) {
               const uint64_t adesc = desc0 + stage * (STAGE_BYTES / 16);
-              const uint64_t bdesc = adesc + A_STAGE_BYTES / 16;
+              const uint64_t bdesc = desc0 + A_STAGE_BYTES / 16;      // the tables live in stage 0
 #pragma unroll
               for (int k4 = 0; k4 < 4; ++k4) umma_f16_ss(d_tmem, adesc + k4 * 2, bdesc + k4 * 2, idesc, k4 != 0 ? 1u : 0u);
-              umma_f16_ss(d_tmem, desc1 + (stage * STAGE_BYTES + K2_A1_OFF) / 16,
-                          desc1 + (stage * STAGE_BYTES + K2_B1_OFF) / 16, idesc, 1u);
+              umma_f16_ss(d_tmem, desc1 + (stage * STAGE_BYTES + K2_A1_OFF) / 16, desc1 + K2_B1_OFF / 16, idesc, 1u);
               tc_commit(&empty_bar[stage]);
             }
             __syncwarp();
