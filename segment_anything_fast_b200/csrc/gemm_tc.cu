@@ -53,6 +53,8 @@ struct GemmParams {
   int a_row_stride;              // batch b reads A rows [b*a_row_stride + m, ...) (head-major operand planes)
   int tg, tg_bn;                 // tg > 1: a tile is tg independent products of tg_bn columns each (consecutive
                                  // batches sharing W), so narrow batched outputs still fill a 256-column tile
+  int b_resident;                // one column tile and few K slabs: W is fetched with the CTA's first tile only and
+                                 // slab ks stays in stage ks (later fills of those stages bring only A)
   int k2;                        // grouped tiles with K = 80 bf16: a stage holds a whole product (64 + 16 columns of K)
   int nstages;                   // pipeline stages in use: STAGES, or STAGES - 1 when the last stage's shared memory
                                  // serves as three more output staging tiles (out_ring)
@@ -170,11 +172,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const int g = gk / p.k_slabs, ks = gk - g * p.k_slabs;       // product inside the tile, K slab
           if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 1))) break;
           uint8_t* sa = smem + stage * STAGE_BYTES;
-          mbar_expect_tx(&full_bar[stage], A_STAGE_BYTES + p.tg_bn * SLAB_BYTES);
+          const bool with_b = !(p.b_resident && b_loaded);
+          mbar_expect_tx(&full_bar[stage], A_STAGE_BYTES + (with_b ? p.tg_bn * SLAB_BYTES : 0));
           tma_load_2d(sa, &tmA, &full_bar[stage], a_col0 + ks * slab_elems, m0 + (bt * p.tg + g) * p.a_row_stride);
-          tma_load_2d(sa + A_STAGE_BYTES, &tmB, &full_bar[stage], ks * slab_elems, p.tg > 1 ? 0 : n0);
+          if (with_b) tma_load_2d(sa + A_STAGE_BYTES, &tmB, &full_bar[stage], ks * slab_elems, p.tg > 1 ? 0 : n0);
           if (++stage == uint32_t(p.nstages)) { stage = 0; phase ^= 1u; }
         }
+        b_loaded = true;
       }
     }
   } else if (warp == 1) {
@@ -215,7 +219,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tc_fence_after();
           if (elect_one()) {
             const uint64_t adesc = desc0 + stage * (STAGE_BYTES / 16);
-            const uint64_t bdesc = adesc + A_STAGE_BYTES / 16;
+            const uint64_t bdesc = desc0 + (p.b_resident ? ks : int(stage)) * (STAGE_BYTES / 16) + A_STAGE_BYTES / 16;
             const int nsteps = ks == p.k_slabs - 1 ? p.last_ksteps : 4;
 #pragma unroll
             for (int k4 = 0; k4 < 4; ++k4) {         // 32 bytes of K per MMA
@@ -492,6 +496,7 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
     p.bn = p.tg * N;
   }
   p.k2 = (p.tg > 1 && !int8 && K == 80) ? 1 : 0;
+  p.b_resident = (p.tg == 1 && N <= p.bn && p.k_slabs <= STAGES - 1 && batch > 1 && a_row_stride != 0) ? 1 : 0;
   // one staging tile per chunk where the epilogue binds: grouped short-K products, and the int8 GELU epilogue
   p.out_ring = ((p.tg > 1 && head_dim == 0) || (epi_bound && head_dim == 0 && !raw && p.bn == BN)) ? 1 : 0;
   p.nstages = p.out_ring ? STAGES - 1 : STAGES;
