@@ -89,7 +89,7 @@ def golden_amg():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of segment-anything-fast to import")
     ap.add_argument("--only", choices=["decoder", "amg"], default=None, help="regenerate just this file")
     args = ap.parse_args()
     os.environ["SEGMENT_ANYTHING_FAST_USE_FLASH_4"] = "0"
