@@ -7,6 +7,7 @@ the shape allows it).  One JSON line per run:
     python -m segment_anything_fast_b200.microbench layernorm --rows 131072 --cols 1280 [--quant]
     python -m segment_anything_fast_b200.microbench mask-stats --n 192 --h 1024 --w 1024 [--bf16]
     python -m segment_anything_fast_b200.microbench mask-rle --n 192 --h 1024 --w 1024
+    python -m segment_anything_fast_b200.microbench tab-products --rows 131072 --heads 16 --dim 80 --t 64
 
 The two attention commands at their defaults are the standalone relative-position attention
 benchmark (q, k, v ~ N(0,1), rel_h / rel_w ~ N(0,0.5), bf16).
@@ -57,7 +58,10 @@ def main():
     mr = sub.add_parser("mask-rle")
     mr.add_argument("--n", type=int, default=192); mr.add_argument("--h", type=int, default=1024)
     mr.add_argument("--w", type=int, default=1024)
-    for p in (g, ag, aw, ln, ms_, mr):
+    tp = sub.add_parser("tab-products")
+    tp.add_argument("--rows", type=int, default=131072); tp.add_argument("--heads", type=int, default=16)
+    tp.add_argument("--dim", type=int, default=80); tp.add_argument("--t", type=int, default=64)
+    for p in (g, ag, aw, ln, ms_, mr, tp):
         p.add_argument("--iters", type=int, default=10); p.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
     torch.manual_seed(0)
@@ -108,6 +112,16 @@ def main():
         ms = _time(lambda: amg.mask_stats(x, 0.0, 1.0), a.iters, a.warmup)
         nbytes = x.numel() * (x.element_size() + 1)                            # logits in, binary masks out
         out.update(shape=[a.n, a.h, a.w], dtype="bf16" if a.bf16 else "f32", ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1))
+    elif a.cmd == "tab-products":
+        # rel-pos table products of one block: q planes [3H, rows, d] x tables [T, d] -> [rows, H*T]
+        # (T = 64 for the 14x14 windows, 256 for the 64x64 global grid)
+        qkv = torch.randn(3 * a.heads, a.rows, a.dim, device=dev).bfloat16()
+        tab = torch.randn(a.t, a.dim, device=dev).bfloat16()
+        cs = torch.ones(a.t, device=dev)
+        y = torch.empty(a.rows, a.heads * a.t, device=dev, dtype=torch.bfloat16)
+        ms = _time(lambda: ops.relpos_table_products(qkv, tab, cs, a.heads, out=y), a.iters, a.warmup)
+        nbytes = a.heads * a.rows * a.dim * 2 + y.numel() * 2                  # q planes in, products out
+        out.update(shape=[a.heads, a.rows, a.dim, a.t], ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1))
     elif a.cmd == "mask-rle":
         from . import _lib
         # blob-like masks: a coarse random field upsampled and thresholded (a few hundred runs per mask)
