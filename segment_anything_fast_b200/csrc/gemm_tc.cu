@@ -498,7 +498,8 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
   p.k2 = (p.tg > 1 && !int8 && K == 80) ? 1 : 0;
   p.b_resident = (p.tg == 1 && N <= p.bn && p.k_slabs <= STAGES - 1 && batch > 1 && a_row_stride != 0) ? 1 : 0;
   // one staging tile per chunk where the epilogue binds: grouped short-K products, and the int8 GELU epilogue
-  p.out_ring = ((p.tg > 1 && head_dim == 0) || (epi_bound && head_dim == 0 && !raw && p.bn == BN)) ? 1 : 0;
+  p.out_ring = (((p.tg > 1 || (p.b_resident && p.bn == BN && !raw)) && head_dim == 0) ||
+                (epi_bound && head_dim == 0 && !raw && p.bn == BN)) ? 1 : 0;
   p.nstages = p.out_ring ? STAGES - 1 : STAGES;
   p.tiles_n = p.tg > 1 ? 1 : (N + p.bn - 1) / p.bn;
   if (p.tg > 1) p.N = p.tg * N;                                  // logical width of a grouped tile
