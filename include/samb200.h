@@ -12,6 +12,12 @@
  *     (0x7E << 24) | (site << 16) | (cta & 0xffff) there and the kernel drains and returns.
  *   - bf16 tensors are row-major, 16-byte aligned, with row lengths that are multiples of 8
  *     elements (16 for int8).  Small vectors (bias, LayerNorm gain/offset, scales) are float32.
+ *   - Threading: no entry point keeps per-call state, so calls from different host threads do not disturb
+ *     one another's results.  The library does keep a few process-wide caches of device facts (architecture
+ *     check and SM count per device ordinal, how many CTA pairs fit on a GPU, the driver entry point used to
+ *     build TMA tensor maps).  They are filled on first use without locking: concurrent first calls write the
+ *     same values, the occupancy figure assumes that every GPU of the process is the same model, and none of
+ *     them holds a caller pointer.  One process per GPU, calls from one thread, is the tested arrangement.
  *   - Citations "ref:" name the file:line of pytorch-labs/segment-anything-fast that the entry
  *     point replaces on the image-encoder path.
  */
@@ -52,6 +58,14 @@ int samb_decode_status(int32_t status_word);
 /* Waits (bounded, ~`limit_polls` polls) on a barrier that nothing signals; the kernel must come
  * back with the timeout code in *status.  Exercises the give-up path without faulting anything. */
 int samb_selftest_bounded_wait(int32_t* status, uint32_t limit_polls, void* stream);
+/* Tensor-pipe rate probe (measurement aid, no counterpart in the reference): `ctas` CTAs each issue
+ * `rounds` x 16 back-to-back tcgen05.mma (M 128, N 256; kind::i8 when int8 != 0, else kind::f16 on bf16) on
+ * operands resident in shared memory.  *ops_out (host, optional) receives the operations launched (2 per
+ * multiply-add); the caller times the launch with events.  `sink` (device, optional) is never written in
+ * practice; it keeps the accumulators observable.  Gives the measured int8 / bf16 peak that roofline
+ * fractions of the GEMMs are quoted against. */
+int samb_selftest_mma_rate(int int8, int rounds, int ctas, int32_t* status, int32_t* sink, double* ops_out,
+                           void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * LayerNorm over the last dim of x[rows, C] (bf16 in, fp32 statistics, bf16 out).
@@ -112,7 +126,7 @@ int samb_layernorm2d_nchw(const void* x, const float* gamma, const float* beta, 
  * Attention with the decomposed relative-position bias, global blocks:
  *   o = softmax(scale * q k^T + rel_h[..., i, kh(j)] + rel_w[..., i, kw(j)]) v,  key j = kh*64 + kw.
  * q, k, v, o: contiguous bf16 [B, H, N, d]; rel_h: [B, H, N, N/64]; rel_w: [B, H, N, 64] (bf16).
- * N a multiple of 128, N <= 4096, d in {64, 80}.  tcgen05 flash attention: logits and P·V in tensor
+ * N a multiple of 256, N <= 4096, d in {64, 80}.  tcgen05 flash attention: logits and P·V in tensor
  * memory, K/V tiles by TMA, rel_w added on the tensor core through a one-hot operand, rel_h folded
  * into the exponent's FMA.
  * ref: _attention_rel_h_rel_w and the Triton kernel it dispatches to, flash_4.py:30-145,335-370

@@ -1,13 +1,15 @@
 """Single-kernel timings through the C ABI (CUDA events, L2 flushed by inputs larger than L2 where
 the shape allows it).  One JSON line per run:
 
-    python -m segment_anything_fast_b200.microbench gemm --m 131072 --n 3840 --k 1280 --epilogue bias [--int8 | --sp24]
-    python -m segment_anything_fast_b200.microbench attn-global --batch 8 --heads 16 --tokens 4096 --dim 80
-    python -m segment_anything_fast_b200.microbench attn-window --batch 200 --heads 16 --dim 80
-    python -m segment_anything_fast_b200.microbench layernorm --rows 131072 --cols 1280 [--quant]
-    python -m segment_anything_fast_b200.microbench mask-stats --n 192 --h 1024 --w 1024 [--bf16]
-    python -m segment_anything_fast_b200.microbench mask-rle --n 192 --h 1024 --w 1024
-    python -m segment_anything_fast_b200.microbench tab-products --rows 131072 --heads 16 --dim 80 --t 64
+    python microbench.py gemm --m 131072 --n 3840 --k 1280 --epilogue bias [--int8 | --sp24]
+    python microbench.py attn-global --batch 8 --heads 16 --tokens 4096 --dim 80
+    python microbench.py attn-window --batch 200 --heads 16 --dim 80
+    python microbench.py layernorm --rows 131072 --cols 1280 [--quant]
+    python microbench.py mask-stats --n 192 --h 1024 --w 1024 [--bf16]
+    python microbench.py mask-rle --n 192 --h 1024 --w 1024
+    python microbench.py tab-products --rows 131072 --heads 16 --dim 80 --t 64
+    python microbench.py quant-rows --rows 131072 --cols 5120
+    python microbench.py attn-global --arm sdpa | --arm ref-triton        (the reference's GPU paths, for comparison)
 
 The two attention commands at their defaults are the standalone relative-position attention
 benchmark (q, k, v ~ N(0,1), rel_h / rel_w ~ N(0,0.5), bf16).
@@ -17,7 +19,12 @@ import json
 
 import torch
 
-from . import ops
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from segment_anything_fast_b200 import ops  # noqa: E402
 
 
 def _time(fn, iters, warmup):
@@ -32,6 +39,26 @@ def _time(fn, iters, warmup):
     torch.cuda.synchronize()
     ops.check_status()
     return a.elapsed_time(b) / iters
+
+
+def _attention_arm(arm, q, k, v, rh, rw):
+    """The callable an attention subcommand times: this library's kernel, or one of the reference's two GPU paths
+    (measurement only; neither is part of the product)."""
+    if arm == "sdpa":
+        B, H, N, _ = q.shape
+        def run():
+            bias = (rh.unsqueeze(-1) + rw.unsqueeze(-2)).view(B, H, N, N)          # materialised as the reference does
+            return torch.nn.functional.scaled_dot_product_attention(q, k, v, attn_mask=bias)
+        return run
+    if arm == "ref-triton":
+        os.environ["SEGMENT_ANYTHING_FAST_USE_FLASH_4"] = "1"
+        from oracle.make_ref import REF_DIR
+        sys.path.insert(0, REF_DIR)
+        os.chdir(os.environ.get("TMPDIR", "/tmp"))                               # the autotuner writes its cache to the cwd
+        from segment_anything_fast.flash_4 import _attention_rel_h_rel_w
+        return lambda: _attention_rel_h_rel_w(q, k, v, rh.unsqueeze(-1), rw.unsqueeze(-2))
+    N = q.shape[2]
+    return (lambda: ops.attn_relpos_global(q, k, v, rh, rw)) if N != 196 else (lambda: ops.attn_relpos_window(q, k, v, rh, rw))
 
 
 def main():
@@ -61,7 +88,14 @@ def main():
     tp = sub.add_parser("tab-products")
     tp.add_argument("--rows", type=int, default=131072); tp.add_argument("--heads", type=int, default=16)
     tp.add_argument("--dim", type=int, default=80); tp.add_argument("--t", type=int, default=64)
-    for p in (g, ag, aw, ln, ms_, mr, tp):
+    for p in (ag, aw):
+        p.add_argument("--arm", choices=["b200", "sdpa", "ref-triton"], default="b200",
+                       help="b200: this library's kernel; sdpa: torch SDPA with the materialised [B,H,N,N] bias, the "
+                            "reference's fallback (flash_4.py:368-370); ref-triton: the reference's own Triton kernel "
+                            "from a copy of its package under oracle/_ref (flash_4.py:30-145; autotunes on first use)")
+    qr = sub.add_parser("quant-rows")
+    qr.add_argument("--rows", type=int, default=131072); qr.add_argument("--cols", type=int, default=1280)
+    for p in (g, ag, aw, ln, ms_, mr, tp, qr):
         p.add_argument("--iters", type=int, default=10); p.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
     torch.manual_seed(0)
@@ -95,19 +129,23 @@ def main():
         q, k, v = (torch.randn(B, H, N, d, device=dev).bfloat16() for _ in range(3))
         rh = (torch.randn(B, H, N, N // 64, device=dev) * 0.5).bfloat16()
         rw = (torch.randn(B, H, N, 64, device=dev) * 0.5).bfloat16()
-        ms = _time(lambda: ops.attn_relpos_global(q, k, v, rh, rw), a.iters, a.warmup)
-        out.update(shape=[B, H, N, d], ms=round(ms, 4), tflops=round(4.0 * B * H * N * N * d / ms / 1e9, 1))
+        ms = _time(_attention_arm(a.arm, q, k, v, rh, rw), a.iters, a.warmup)
+        out.update(arm=a.arm, shape=[B, H, N, d], ms=round(ms, 4), tflops=round(4.0 * B * H * N * N * d / ms / 1e9, 1))
     elif a.cmd == "attn-window":
         B, H, d = a.batch, a.heads, a.dim
         q, k, v = (torch.randn(B, H, 196, d, device=dev).bfloat16() for _ in range(3))
         rh = (torch.randn(B, H, 196, 14, device=dev) * 0.5).bfloat16()
         rw = (torch.randn(B, H, 196, 14, device=dev) * 0.5).bfloat16()
-        ms = _time(lambda: ops.attn_relpos_window(q, k, v, rh, rw), a.iters, a.warmup)
+        ms = _time(_attention_arm(a.arm, q, k, v, rh, rw), a.iters, a.warmup)
         nbytes = 4 * B * H * 196 * d * 2 + 2 * B * H * 196 * 14 * 2          # q, k, v, o + rel_h, rel_w
-        out.update(shape=[B, H, 196, d], ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1),
+        out.update(arm=a.arm, shape=[B, H, 196, d], ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1),
                    tflops=round(4.0 * B * H * 196 * 196 * d / ms / 1e9, 1))
+    elif a.cmd == "quant-rows":
+        x = torch.randn(a.rows, a.cols, device=dev).bfloat16()
+        ms = _time(lambda: ops.quant_rows_i8(x), a.iters, a.warmup)
+        out.update(shape=[a.rows, a.cols], ms=round(ms, 4), gbs=round((a.rows * a.cols * 3 + a.rows * 4) / ms / 1e6, 1))
     elif a.cmd == "mask-stats":
-        from . import amg
+        from segment_anything_fast_b200 import amg
         x = (torch.randn(a.n, a.h, a.w, device=dev) * 2.0).to(torch.bfloat16 if a.bf16 else torch.float32)
         ms = _time(lambda: amg.mask_stats(x, 0.0, 1.0), a.iters, a.warmup)
         nbytes = x.numel() * (x.element_size() + 1)                            # logits in, binary masks out
@@ -123,7 +161,7 @@ def main():
         nbytes = a.heads * a.rows * a.dim * 2 + y.numel() * 2                  # q planes in, products out
         out.update(shape=[a.heads, a.rows, a.dim, a.t], ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1))
     elif a.cmd == "mask-rle":
-        from . import _lib
+        from segment_anything_fast_b200 import _lib
         # blob-like masks: a coarse random field upsampled and thresholded (a few hundred runs per mask)
         coarse = torch.randn(a.n, 1, 16, 16, device=dev)
         m = (torch.nn.functional.interpolate(coarse, size=(a.h, a.w), mode="bilinear")[:, 0] > 0.3).contiguous()

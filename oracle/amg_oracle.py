@@ -59,3 +59,35 @@ def rle_to_mask(rle) -> np.ndarray:
         pos += c
         val = not val
     return flat.reshape(w, h).T
+
+
+def is_box_near_crop_edge(boxes: np.ndarray, crop_box, orig_box, atol: float = 20.0) -> np.ndarray:
+    """utils/amg.py:78-88: a box edge within ``atol`` of a crop edge that is not also within ``atol`` of the
+    image edge."""
+    x0, y0 = crop_box[0], crop_box[1]
+    b = boxes.astype(np.float32) + np.array([x0, y0, x0, y0], dtype=np.float32)
+    near_crop = np.abs(b - np.asarray(crop_box, dtype=np.float32)[None]) <= atol
+    near_image = np.abs(b - np.asarray(orig_box, dtype=np.float32)[None]) <= atol
+    return np.any(near_crop & ~near_image, axis=1)
+
+
+def process_batch_filters(mask_logits: np.ndarray, iou_preds: np.ndarray, crop_box, orig_size, pred_iou_thresh=0.88,
+                          mask_threshold=0.0, stability_score_offset=1.0, stability_score_thresh=0.95):
+    """``_process_batch_2`` (automatic_mask_generator.py:312-359) step by step, filtering after every step as the
+    reference does: predicted IoU, stability score, threshold + boxes, crop-edge boxes.  ``mask_logits
+    [P, C, H, W]``, ``iou_preds [P, C]`` -> (indices of the kept masks in the flattened ``P*C`` order, their
+    stability scores, boxes, boolean masks)."""
+    flat = mask_logits.reshape((-1,) + mask_logits.shape[2:]).astype(np.float32)
+    iou = iou_preds.reshape(-1)
+    idx = np.arange(flat.shape[0])
+    if pred_iou_thresh > 0.0:
+        idx = idx[iou[idx] > np.float32(pred_iou_thresh)]
+    score = calculate_stability_score(flat[idx], mask_threshold, stability_score_offset)
+    if stability_score_thresh > 0.0:
+        sel = score >= np.float32(stability_score_thresh)
+        idx, score = idx[sel], score[sel]
+    masks = flat[idx] > np.float32(mask_threshold)
+    boxes = batched_mask_to_box(masks)
+    orig_h, orig_w = orig_size
+    sel = ~is_box_near_crop_edge(boxes, crop_box, [0, 0, orig_w, orig_h]) if len(idx) else np.zeros(0, dtype=bool)
+    return idx[sel], score[sel], boxes[sel], masks[sel]

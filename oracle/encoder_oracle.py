@@ -135,12 +135,17 @@ def seeded_state_dict(cfg: EncoderConfig, seed: int = 0, std: float = 0.02,
     return sd
 
 
+def seeded_images_u8(batch: int, seed: int = 0, img_size: int = 1024) -> torch.Tensor:
+    """The raw pixels of ``seeded_images``: uint8 U{0..255}, ``[B,3,S,S]`` contiguous."""
+    g = torch.Generator().manual_seed(seed)
+    u8 = torch.randint(0, 256, (batch, img_size, img_size, 3), generator=g, dtype=torch.uint8)
+    return u8.permute(0, 3, 1, 2).contiguous()
+
+
 def seeded_images(batch: int, seed: int = 0, img_size: int = 1024) -> torch.Tensor:
     """uint8-valued images U{0..255}, normalised with SAM's pixel mean/std the way
     ``Sam.preprocess`` does (sam.py:164-174) → float32 ``[B,3,S,S]``."""
-    g = torch.Generator().manual_seed(seed)
-    u8 = torch.randint(0, 256, (batch, img_size, img_size, 3), generator=g, dtype=torch.uint8)
-    x = u8.permute(0, 3, 1, 2).to(torch.float32)
+    x = seeded_images_u8(batch, seed, img_size).to(torch.float32)
     mean = torch.tensor(PIXEL_MEAN).view(1, 3, 1, 1)
     std = torch.tensor(PIXEL_STD).view(1, 3, 1, 1)
     return (x - mean) / std

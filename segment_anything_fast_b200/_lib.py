@@ -20,6 +20,7 @@ SIGNATURES = {
     "samb_error_string": (c_char_p, [c_int]),
     "samb_decode_status": (c_int, [c_int32]),
     "samb_selftest_bounded_wait": (c_int, [_P, c_uint32, _P]),
+    "samb_selftest_mma_rate": (c_int, [c_int, c_int, c_int, _P, _P, ctypes.POINTER(ctypes.c_double), _P]),
     "samb_layernorm_bf16": (c_int, [_P, _P, _P, _P, c_int64, c_int, c_float, c_int, c_int, _P]),
     "samb_layernorm_quant_i8": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int, c_float, c_int, c_int, _P]),
     "samb_quant_rows_i8": (c_int, [_P, _P, _P, c_int64, c_int, _P]),

@@ -79,3 +79,45 @@ def mask_to_rle_pytorch(tensor: torch.Tensor) -> List[Dict[str, Any]]:
 
 
 mask_to_rle_pytorch_2 = mask_to_rle_pytorch
+
+
+def is_box_near_crop_edge(boxes: torch.Tensor, crop_box, orig_box, atol: float = 20.0) -> torch.Tensor:
+    """True for boxes that touch an edge of the crop which is not an edge of the image (utils/amg.py:78-88)."""
+    crop = torch.as_tensor(crop_box, dtype=torch.float, device=boxes.device)
+    orig = torch.as_tensor(orig_box, dtype=torch.float, device=boxes.device)
+    x0, y0 = float(crop_box[0]), float(crop_box[1])
+    b = boxes.float() + torch.tensor([x0, y0, x0, y0], device=boxes.device)         # uncrop_boxes_xyxy
+    near_crop = (b - crop[None]).abs() <= atol
+    near_image = (b - orig[None]).abs() <= atol
+    return (near_crop & ~near_image).any(dim=1)
+
+
+def process_batch_filters(mask_logits: torch.Tensor, iou_preds: torch.Tensor, points: torch.Tensor, crop_box,
+                          orig_size: Tuple[int, int], pred_iou_thresh: float = 0.88, mask_threshold: float = 0.0,
+                          stability_score_offset: float = 1.0, stability_score_thresh: float = 0.95) -> Dict[str, Any]:
+    """The filter stage the mask generator runs on one batch of point prompts
+    (``_process_batch_2``, automatic_mask_generator.py:312-359) with one fused pass over the logits.
+
+    ``mask_logits [P, C, H, W]`` (the decoder's masks upsampled to the crop, un-thresholded), ``iou_preds [P, C]``,
+    ``points [P, 2]``.  Keeps the masks whose predicted IoU exceeds ``pred_iou_thresh``, whose stability score
+    reaches ``stability_score_thresh`` and whose box does not touch a crop edge inside the image.  The reference
+    filters after each step, so later steps see fewer masks; the order of the survivors is the same because every
+    filter is a per-mask predicate.  Returns ``masks`` (boolean ``[K, H, W]``), ``iou_preds``, ``points``,
+    ``stability_score``, ``boxes`` (int64 XYXY in crop coordinates) and ``keep`` (indices into the flattened
+    ``P*C`` masks)."""
+    P, C = mask_logits.shape[:2]
+    orig_h, orig_w = orig_size
+    flat = mask_logits.flatten(0, 1)
+    iou = iou_preds.flatten(0, 1)
+    pts = points.to(mask_logits.device).repeat_interleave(C, dim=0)
+    keep = torch.ones(P * C, dtype=torch.bool, device=flat.device)
+    if pred_iou_thresh > 0.0:
+        keep &= iou > pred_iou_thresh
+    score, boxes, binary = mask_stats(flat, mask_threshold, stability_score_offset)
+    if stability_score_thresh > 0.0:
+        keep &= score >= stability_score_thresh
+    boxes = boxes.to(torch.int64)
+    keep &= ~is_box_near_crop_edge(boxes, crop_box, [0, 0, orig_w, orig_h])
+    idx = keep.nonzero().squeeze(1)
+    return {"masks": binary[idx], "iou_preds": iou[idx], "points": pts[idx], "stability_score": score[idx],
+            "boxes": boxes[idx], "keep": idx}

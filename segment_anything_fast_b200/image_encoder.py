@@ -80,8 +80,8 @@ class PatchEmbed(nn.Module):
         self.proj = nn.Conv2d(in_chans, embed_dim, kernel_size=kernel_size, stride=stride, padding=padding)
 
 
-def _f32(t: torch.Tensor) -> torch.Tensor:
-    return t.detach().to(torch.float32).contiguous()
+def _f32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    return None if t is None else t.detach().to(torch.float32).contiguous()
 
 
 def _bf16(t: torch.Tensor) -> torch.Tensor:
@@ -166,11 +166,19 @@ class ImageEncoderViT(nn.Module):
         return tab, cs, T, t_w_off
 
     def _pack(self) -> dict:
+        C = self.embed_dim
+        g = self.img_size // self.patch_size
+        # the attention kernels know two geometries: a 64 x 64 token raster attended globally (keys indexed
+        # kh*64 + kw) and 14 x 14 windows; anything else would index the bias tables wrongly without an error
+        for i, blk in enumerate(self.blocks):
+            if blk.window_size == 0 and g != 64:
+                raise RuntimeError(f"block {i}: global attention is built for a 64x64 token grid "
+                                   f"(img_size / patch_size = {g})")
+            if blk.window_size not in (0, 14):
+                raise RuntimeError(f"block {i}: window_size {blk.window_size} is not supported (0 or 14)")
         dev = self.patch_embed.proj.weight.device
         if dev.type != "cuda":
             raise RuntimeError("ImageEncoderViT (B200) needs its parameters on a CUDA device; there is no CPU path")
-        C = self.embed_dim
-        g = self.img_size // self.patch_size
         pk: dict = {"blocks": []}
         pe = self.patch_embed.proj
         pk["pe_w"] = _bf16(pe.weight.reshape(C, -1))

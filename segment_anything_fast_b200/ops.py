@@ -16,6 +16,16 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+def _same_device(index: Optional[int], name: str) -> None:
+    """Every launch goes to the *current* device and its current stream (the C side reads the current
+    device for its architecture check and SM count), so a tensor living on another GPU would hand that
+    GPU's pointers to a kernel running here.  Reject it before anything is enqueued."""
+    cur = torch.cuda.current_device()
+    if index is not None and index != cur:
+        raise RuntimeError(f"{name} is on cuda:{index} but the current device is cuda:{cur}; "
+                           f"call torch.cuda.set_device({index}) (or use `with torch.cuda.device({index})`) first")
+
+
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
@@ -46,6 +56,7 @@ def _need(t: torch.Tensor, dtype: torch.dtype, name: str) -> None:
         raise RuntimeError(f"{name}: expected a CUDA tensor (there is no CPU path)")
     if t.dtype != dtype:
         raise RuntimeError(f"{name}: expected {dtype}, got {t.dtype}")
+    _same_device(t.device.index, name)
 
 
 def _rows2d(t: torch.Tensor, name: str) -> torch.Tensor:

@@ -26,7 +26,7 @@ class EncoderSession:
                  graph: bool = False) -> None:
         self.encoder = encoder
         self.graph = graph
-        self._graphs = {}          # device input buffer address -> (CUDAGraph, embeddings written by a replay)
+        self._graphs = {}          # device input buffer address -> (CUDAGraph, embeddings written by a replay, weights key)
         self._pool = None
         self.device = device or next(encoder.parameters()).device
         if self.device.type != "cuda":
@@ -38,6 +38,9 @@ class EncoderSession:
         self.host_out = torch.empty(batch, oc, g, g, dtype=torch.bfloat16).pin_memory()
         self.dev_in = torch.empty(batch, 3, S, S, dtype=torch.uint8, device=self.device)
         self.dev_norm = torch.empty(batch, 3, S, S, dtype=torch.bfloat16, device=self.device)
+        # host copy of the device status word, refreshed with every download: a bounded wait that ran out
+        # inside a kernel must surface as an exception, not as silently wrong embeddings
+        self._host_status = torch.zeros(1, dtype=torch.int32).pin_memory()
         # second slot and the copy streams of the pipelined form are created on first use
         self._slots = None
         self._next = 0
@@ -61,6 +64,11 @@ class EncoderSession:
         """Replay (recording it on first use) the graph that reads ``dev_in``; its output tensor is reused by
         every replay, so a caller that keeps embeddings across calls must copy them."""
         ent = self._graphs.get(dev_in.data_ptr())
+        key = self.encoder._params_key()
+        if ent is not None and ent[2] != key:
+            # weights, dtype, quantisation or pruning changed since the recording: the graph still points at
+            # the old packed buffers, so it is recorded again
+            ent = None
         if ent is None:
             run = lambda: self.encoder(ops.normalize_u8(dev_in, self.mean, self.std, out=self.dev_norm))
             main = torch.cuda.current_stream(self.device)
@@ -74,7 +82,7 @@ class EncoderSession:
             with torch.cuda.graph(g, pool=self._pool):
                 emb = run()
             self._pool = g.pool()                  # the graphs never run concurrently: one pool for their scratch
-            ent = self._graphs[dev_in.data_ptr()] = (g, emb)
+            ent = self._graphs[dev_in.data_ptr()] = (g, emb, key)
         ent[0].replay()
         return ent[1]
 
@@ -86,8 +94,17 @@ class EncoderSession:
         self.dev_in.copy_(self.host_in, non_blocking=True)
         emb = self.encode_device(self.dev_in)
         self.host_out.copy_(emb, non_blocking=True)
+        self._host_status.copy_(ops.status_word(self.device), non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
+        self._raise_on_status(self._host_status)
         return self.host_out
+
+    def _raise_on_status(self, host_word: torch.Tensor) -> None:
+        v = int(host_word.item())
+        if v != 0:
+            ops.status_word(self.device).zero_()
+            raise RuntimeError(f"EncoderSession: a kernel reported device status 0x{v & 0xffffffff:08x} "
+                               "(a bounded hardware-barrier wait ran out); the embeddings of this batch are not valid")
 
     # ------------------------------------------------------------------ pipelined form
     def _init_slots(self) -> None:
@@ -99,6 +116,7 @@ class EncoderSession:
                 "host_in": self.host_in if i == 0 else torch.empty_like(self.host_in).pin_memory(),
                 "host_out": self.host_out if i == 0 else torch.empty_like(self.host_out).pin_memory(),
                 "dev_in": self.dev_in if i == 0 else torch.empty_like(self.dev_in),
+                "host_status": torch.zeros(1, dtype=torch.int32).pin_memory(),
                 "uploaded": mk(), "computed": mk(), "downloaded": mk(), "emb": None, "busy": False})
         self._s_in = torch.cuda.Stream(self.device)
         self._s_out = torch.cuda.Stream(self.device)
@@ -135,6 +153,7 @@ class EncoderSession:
         self._s_out.wait_event(sl["computed"])
         with torch.cuda.stream(self._s_out):
             sl["host_out"].copy_(emb, non_blocking=True)
+            sl["host_status"].copy_(ops.status_word(self.device), non_blocking=True)
             sl["downloaded"].record(self._s_out)
         if not self.graph:
             emb.record_stream(self._s_out)
@@ -148,4 +167,5 @@ class EncoderSession:
             raise RuntimeError("EncoderSession.result: nothing was submitted in this slot")
         sl["downloaded"].synchronize()
         sl["emb"], sl["busy"] = None, False
+        self._raise_on_status(sl["host_status"])
         return sl["host_out"]

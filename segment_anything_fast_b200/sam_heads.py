@@ -3,10 +3,9 @@ encoder (points / boxes), two-way transformer mask decoder, mask post-processing
 container holding them next to the B200 image encoder.
 
 Parameter names and shapes are the reference's (segment_anything_fast/modeling/prompt_encoder.py,
-mask_decoder.py, transformer.py, sam.py), so a reference checkpoint loads with ``load_state_dict``;
-the dense mask-prompt branch (``mask_downscaling``) is carried as parameters for that purpose but not
-evaluated (``masks=`` prompts raise).  The modules are thin: the arithmetic is a handful of small
-matmuls per prompt, run by torch's own GPU operators; none of it is on the encoder's hot path.
+mask_decoder.py, transformer.py, sam.py), so a reference checkpoint loads with ``load_state_dict``.
+The modules are thin: the arithmetic is a handful of small matmuls per prompt, run by torch's own GPU
+operators; none of it is on the encoder's hot path.
 """
 import math
 from typing import Optional, Tuple
@@ -63,7 +62,7 @@ class PromptEncoder(nn.Module):
         self.point_embeddings = nn.ModuleList([nn.Embedding(1, embed_dim) for _ in range(4)])
         self.not_a_point_embed = nn.Embedding(1, embed_dim)
         self.no_mask_embed = nn.Embedding(1, embed_dim)
-        # parameters of the mask-prompt branch, kept so that reference checkpoints load strictly
+        # the mask-prompt branch (prompt_encoder.py:50-58, 111-114)
         self.mask_downscaling = nn.Sequential(
             nn.Conv2d(1, mask_in_chans // 4, kernel_size=2, stride=2), _Norm2d(mask_in_chans // 4), nn.GELU(),
             nn.Conv2d(mask_in_chans // 4, mask_in_chans, kernel_size=2, stride=2), _Norm2d(mask_in_chans), nn.GELU(),
@@ -74,8 +73,6 @@ class PromptEncoder(nn.Module):
 
     def forward(self, points: Optional[Tuple[torch.Tensor, torch.Tensor]], boxes: Optional[torch.Tensor],
                 masks: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-        if masks is not None:
-            raise NotImplementedError("mask prompts are not evaluated by this package")
         S = float(self.input_image_size[1])
         w = [e.weight for e in self.point_embeddings]
         sparse = None
@@ -97,9 +94,14 @@ class PromptEncoder(nn.Module):
             e = self.pe_layer.encode(c / S)
             sparse = torch.stack([e[:, 0] + w[2], e[:, 1] + w[3]], dim=1)
         if sparse is None:
-            raise ValueError("at least one of points / boxes is required")
-        h, wd = self.image_embedding_size
-        dense = self.no_mask_embed.weight.reshape(1, -1, 1, 1).expand(sparse.shape[0], -1, h, wd)
+            if masks is None:
+                raise ValueError("at least one of points / boxes / masks is required")
+            sparse = w[0].new_zeros(masks.shape[0], 0, self.embed_dim)       # a mask prompt alone: no sparse tokens
+        if masks is not None:                                                # _embed_masks, prompt_encoder.py:111-114
+            dense = self.mask_downscaling(masks.to(w[0].dtype))
+        else:
+            h, wd = self.image_embedding_size
+            dense = self.no_mask_embed.weight.reshape(1, -1, 1, 1).expand(sparse.shape[0], -1, h, wd)
         return sparse.to(dense.dtype), dense
 
 
@@ -261,6 +263,26 @@ class Sam(nn.Module):
         masks = F.interpolate(masks, (S, S), mode="bilinear", align_corners=False)
         masks = masks[..., :input_size[0], :input_size[1]]
         return F.interpolate(masks, original_size, mode="bilinear", align_corners=False)
+
+    @torch.no_grad()
+    def forward(self, batched_input, multimask_output: bool):
+        """``Sam.forward`` (sam.py:54-131).  ``batched_input`` is a list of per-image dictionaries: ``image``
+        (``[3, H, W]`` float pixels, already resized so that the long side is ``img_size``), ``original_size``
+        ``(H, W)``, and optionally ``point_coords [B, N, 2]`` + ``point_labels [B, N]``, ``boxes [B, 4]``,
+        ``mask_inputs [B, 1, 256, 256]``.  All images go through the encoder in one batch; returns one dictionary
+        per image with ``masks`` (boolean, at the original size), ``iou_predictions`` and ``low_res_logits``."""
+        x = torch.stack([self.preprocess(r["image"]) for r in batched_input], dim=0)
+        model_dtype = self.mask_decoder.iou_prediction_head.layers[0].weight.dtype
+        emb = self.image_encoder(x.to(model_dtype))
+        pe = self.prompt_encoder.get_dense_pe()
+        outputs = []
+        for rec, e in zip(batched_input, emb):
+            points = (rec["point_coords"], rec["point_labels"]) if "point_coords" in rec else None
+            sparse, dense = self.prompt_encoder(points, rec.get("boxes"), rec.get("mask_inputs"))
+            low, iou = self.mask_decoder(e.unsqueeze(0), pe, sparse, dense, multimask_output)
+            masks = self.postprocess_masks(low, tuple(rec["image"].shape[-2:]), tuple(rec["original_size"]))
+            outputs.append({"masks": masks > self.mask_threshold, "iou_predictions": iou, "low_res_logits": low})
+        return outputs
 
     @torch.no_grad()
     def predict_boxes(self, images: torch.Tensor, boxes: torch.Tensor, multimask_output: bool = True):

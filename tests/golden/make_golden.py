@@ -65,6 +65,56 @@ def golden_decoder():
         dense_pe=sam.prompt_encoder.get_dense_pe()[:, :, ::8, ::8].numpy(), sparse_points=sp_pts.numpy())
 
 
+def golden_sam_forward():
+    """(h) the reference's ``Sam.forward`` (sam.py:54-131) with the mask-prompt branch of its prompt encoder
+    (prompt_encoder.py:111-114), on seeded decoder weights, with a stand-in image encoder (the encoder itself is
+    covered by (a)/(b)): one non-square image with two boxes, one square image with points + a mask input."""
+    from segment_anything_fast.build_sam import sam_model_registry
+
+    from oracle import decoder_oracle as do
+
+    torch.manual_seed(0)
+    sam = sam_model_registry["vit_b"]().eval()
+    cfg = do.DecoderConfig()
+    sd = dict(do.seeded_state_dict(cfg, seed=3))
+    sd.update(do.seeded_mask_downscaling(cfg, seed=3))
+    sam.prompt_encoder.load_state_dict({k[len("prompt_encoder."):]: v for k, v in sd.items() if k.startswith("prompt_encoder.")})
+    sam.mask_decoder.load_state_dict({k[len("mask_decoder."):]: v for k, v in sd.items() if k.startswith("mask_decoder.")})
+    sam.image_encoder = do.StubImageEncoder(seed=7)
+    recs = do.sam_forward_inputs(seed=9)
+    out = {}
+    for mm in (True, False):
+        res = sam(recs, multimask_output=mm)
+        for i, r in enumerate(res):
+            t = f"mm{int(mm)}_img{i}"
+            out[t + "_low"] = r["low_res_logits"][:, :, ::4, ::4].numpy()
+            out[t + "_iou"] = r["iou_predictions"].numpy()
+            out[t + "_area"] = r["masks"].float().mean((2, 3)).numpy()
+            out[t + "_masks"] = np.packbits(r["masks"][:, :, ::8, ::8].numpy())
+            out[t + "_shape"] = np.array(r["masks"].shape)
+    dense = sam.prompt_encoder(points=(recs[1]["point_coords"], recs[1]["point_labels"]), boxes=None,
+                               masks=recs[1]["mask_inputs"])[1]
+    out["dense_from_mask"] = dense[:, :, ::4, ::4].detach().numpy()
+    # the reference's SamPredictor on the same model: set_image on a 480 x 640 uint8 image, a box prompt, then
+    # points + the first answer's best low-resolution logits fed back as mask_input (predictor.py:34-168)
+    from segment_anything_fast.predictor import SamPredictor
+    pred = SamPredictor(sam)
+    img, box, pts, labels = do.predictor_inputs(seed=11)
+    pred.set_image(img)
+    out["pred_resized"] = pred.transform.apply_image(img)[::8, ::8]
+    out["pred_features"] = pred.get_image_embedding()[:, ::8, ::4, ::4].numpy()
+    m, q, low = pred.predict(box=box, multimask_output=True)
+    out["pred_box_masks"] = np.packbits(m[:, ::4, ::4])
+    out["pred_box_area"] = m.reshape(3, -1).mean(1)
+    out["pred_box_iou"], out["pred_box_low"] = q, low[:, ::4, ::4]
+    best = int(q.argmax())
+    m2, q2, low2 = pred.predict(point_coords=pts, point_labels=labels, mask_input=low[best:best + 1],
+                                multimask_output=False, return_logits=True)
+    out["pred_pts_logits"] = m2[:, ::8, ::8]
+    out["pred_pts_iou"], out["pred_pts_low"] = q2, low2[:, ::4, ::4]
+    np.savez_compressed(os.path.join(HERE, "sam_forward_fp32.npz"), **out)
+
+
 def golden_amg():
     """(g) the automatic mask generator's logit filters on seeded logits (an empty and a full mask included)."""
     from segment_anything_fast.utils.amg import batched_mask_to_box, calculate_stability_score
@@ -83,20 +133,31 @@ def golden_amg():
     assert rles == mask_to_rle_pytorch_2(masks)
     rle_len = np.array([len(r["counts"]) for r in rles], dtype=np.int64)
     rle_counts = np.concatenate([np.asarray(r["counts"], dtype=np.int64) for r in rles])
+    # crop-edge filter of _process_batch_2 on seeded boxes inside a crop of a larger image
+    from segment_anything_fast.utils.amg import is_box_near_crop_edge
+    ge = torch.Generator().manual_seed(9)
+    lo = torch.randint(0, 200, (64, 2), generator=ge)
+    eb = torch.cat([lo, lo + torch.randint(1, 120, (64, 2), generator=ge)], dim=1).clamp(max=299)
+    crop, orig = [100, 50, 400, 350], [0, 0, 420, 350]
+    edge = is_box_near_crop_edge(eb, crop, orig)
     np.savez_compressed(os.path.join(HERE, "amg_fp32.npz"), logits=logits.numpy(), score=score.numpy(), boxes=boxes.numpy(),
-                        rle_len=rle_len, rle_counts=rle_counts)
+                        rle_len=rle_len, rle_counts=rle_counts, edge_boxes=eb.numpy(), edge_crop=np.array(crop),
+                        edge_orig=np.array(orig), edge_out=edge.numpy())
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="checkout of segment-anything-fast to import")
-    ap.add_argument("--only", choices=["decoder", "amg"], default=None, help="regenerate just this file")
+    ap.add_argument("--only", choices=["decoder", "amg", "sam_forward"], default=None, help="regenerate just this file")
     args = ap.parse_args()
     os.environ["SEGMENT_ANYTHING_FAST_USE_FLASH_4"] = "0"
     sys.path.insert(0, args.reference)
     torch.set_grad_enabled(False)
     if args.only == "decoder":
         golden_decoder()
+        return
+    if args.only == "sam_forward":
+        golden_sam_forward()
         return
     if args.only == "amg":
         golden_amg()
@@ -180,6 +241,7 @@ def main():
         keep0=(lin[0].weight != 0).numpy(), keep1=(lin[1].weight != 0).numpy())
     golden_decoder()
     golden_amg()
+    golden_sam_forward()
     print("golden vectors written to", HERE)
 
 

@@ -1,0 +1,248 @@
+"""GPU checks of what sits either side of the encoder kernels on the timed path and at the Python boundary:
+the uint8 normalisation kernel and ``EncoderSession`` against the oracle, the attention drop-in with the
+reference's argument shapes, the dispatcher op, ``Sam.forward`` / ``SamPredictor`` with the CUDA encoder, the
+mask-generator filter stage, and the re-recording of a CUDA graph after the weights change."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import amg_oracle as ao
+from oracle import decoder_oracle as do
+from oracle import encoder_oracle as eo
+
+pytestmark = pytest.mark.gpu
+
+TINY = eo.EncoderConfig(embed_dim=160, depth=4, num_heads=2, global_attn_indexes=(1, 3), out_chans=32)
+TINY256 = eo.EncoderConfig(embed_dim=160, depth=4, num_heads=2, global_attn_indexes=(1, 3), out_chans=256)
+
+
+def _cos(a, b):
+    return torch.nn.functional.cosine_similarity(a.flatten().double(), b.flatten().double(), dim=0).item()
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from segment_anything_fast_b200 import ops as _ops
+    return _ops
+
+
+# ----------------------------------------------------------------------------- preprocess + session
+@pytest.mark.parametrize("B,S", [(2, 1024), (1, 64), (3, 256)])
+def test_normalize_u8_is_bit_exact(ops, B, S):
+    """``samb_normalize_u8`` against ``(u8 - mean) / std`` in fp32 (Sam.preprocess, sam.py:164-168) rounded to
+    bf16 (the cast at predictor.py:88-90): the same bits, every pixel."""
+    u8 = eo.seeded_images_u8(B, seed=51, img_size=S)
+    want = eo.seeded_images(B, seed=51, img_size=S).to(torch.bfloat16)
+    got = ops.normalize_u8(u8.cuda(), eo.PIXEL_MEAN, eo.PIXEL_STD).cpu()
+    assert got.dtype == torch.bfloat16 and got.shape == want.shape
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_encoder_session_uint8_against_oracle(ops, graph):
+    """The benchmark's timed path, host uint8 pixels -> ``EncoderSession.encode`` -> host embeddings, against the
+    oracle's normalise -> encoder on the same pixels and weights."""
+    from test_gpu_encoder import build_encoder
+    from segment_anything_fast_b200 import EncoderSession
+    sd = eo.seeded_state_dict(TINY, seed=1)
+    enc = build_encoder(TINY, sd)
+    sess = EncoderSession(enc, batch=2, graph=graph)
+    u8 = eo.seeded_images_u8(2, seed=52)
+    got = sess.encode(u8).float().clone()
+    ref = eo.image_encoder_forward(eo.seeded_images(2, seed=52), sd, TINY, "fp32")
+    err = (got - ref).abs().max().item()
+    print(f"EncoderSession(graph={graph}) vs fp32 oracle: cosine {_cos(got, ref):.6f}, max-abs {err:.4f}")
+    assert _cos(got, ref) > 0.999
+    assert err < 0.1
+    direct = enc(eo.seeded_images(2, seed=52).to(torch.bfloat16).cuda()).float().cpu()
+    assert torch.equal(direct, got)                     # the session adds nothing but the normalisation
+
+
+def test_graph_is_recorded_again_after_the_weights_change(ops):
+    """A recorded graph points at the packed weights of its recording; new weights must not be ignored."""
+    from test_gpu_encoder import build_encoder
+    from segment_anything_fast_b200 import EncoderSession
+    sd1 = eo.seeded_state_dict(TINY, seed=1)
+    sd2 = eo.seeded_state_dict(TINY, seed=2)
+    enc = build_encoder(TINY, sd1)
+    sess = EncoderSession(enc, batch=1, graph=True)
+    u8 = eo.seeded_images_u8(1, seed=53)
+    a = sess.encode(u8).clone()
+    enc.load_state_dict({k: v.to(torch.bfloat16) for k, v in sd2.items()})
+    b = sess.encode(u8).clone()
+    want = build_encoder(TINY, sd2)(eo.seeded_images(1, seed=53).to(torch.bfloat16).cuda()).cpu()
+    assert not torch.equal(a, b)
+    assert torch.equal(b, want)
+    enc.set_quant("int8")
+    c = sess.encode(u8).clone()
+    want8 = build_encoder(TINY, sd2, quant="int8")(eo.seeded_images(1, seed=53).to(torch.bfloat16).cuda()).cpu()
+    assert torch.equal(c, want8)
+
+
+# ----------------------------------------------------------------------------- attention drop-in
+def _flash4_inputs(B, H, N, d, dtype, seed=20):
+    """The tensors of the reference's own op test (test/test_flash_4.py:10-31): N(0, 0.5), seed 20."""
+    torch.manual_seed(seed)
+    q, k, v = (torch.empty(B, H, N, d, dtype=dtype, device="cuda").normal_(0.0, 0.5) for _ in range(3))
+    w = int(N ** 0.5)
+    rel_h = torch.empty(B, H, N, w, 1, dtype=dtype, device="cuda").normal_(0.0, 0.5)
+    rel_w = torch.empty(B, H, N, 1, w, dtype=dtype, device="cuda").normal_(0.0, 0.5)
+    return q, k, v, rel_h, rel_w
+
+
+@pytest.mark.parametrize("B,H,N,d", [(1, 16, 4096, 80), (2, 12, 4096, 64), (8, 2, 4096, 80), (3, 2, 196, 80)])
+def test_attention_wrapper_reference_procedure(ops, B, H, N, d):
+    """``_attention_rel_h_rel_w`` with the reference's 5-D bias tensors, compared the way test/test_flash_4.py:33-39
+    compares: SDPA with the materialised bias, rtol = atol = 1e-3 (here the comparison arm is fp32 SDPA on the
+    bf16-rounded inputs)."""
+    from segment_anything_fast_b200.flash_4 import _attention_rel_h_rel_w
+    q, k, v, rel_h, rel_w = _flash4_inputs(B, H, N, d, torch.bfloat16)
+    out = _attention_rel_h_rel_w(q, k, v, rel_h, rel_w)
+    ops.check_status()
+    assert out.shape == q.shape and out.dtype == torch.bfloat16
+    for b in {0, B - 1}:
+        f = lambda t: t[b:b + 1].float()
+        bias = (f(rel_h) + f(rel_w)).view(1, H, N, N)
+        ref = torch.nn.functional.scaled_dot_product_attention(f(q), f(k), f(v), attn_mask=bias)
+        torch.testing.assert_close(out[b:b + 1].float(), ref, rtol=1e-3, atol=1e-3)
+
+
+def test_attention_wrapper_refuses_float16(ops):
+    """The reference's op test also sweeps float16 (test/test_flash_4.py:41-43); the B200 kernels are bf16 and
+    say so instead of converting behind the caller's back."""
+    from segment_anything_fast_b200.flash_4 import _attention_rel_h_rel_w
+    q, k, v, rel_h, rel_w = _flash4_inputs(1, 2, 256, 80, torch.float16)
+    with pytest.raises(RuntimeError, match="bfloat16"):
+        _attention_rel_h_rel_w(q, k, v, rel_h, rel_w)
+
+
+def test_dispatcher_op_on_cuda(ops):
+    """``torch.ops.samb200.custom_flash_aligned(q, k, v, cat(rel_h, rel_w), sm_scale)``: the call flash_4.py:352-355
+    makes, answered by the global-attention kernel; a non-default ``sm_scale`` is honoured."""
+    from segment_anything_fast_b200.flash_4 import _attention_rel_h_rel_w
+    q, k, v, rel_h, rel_w = _flash4_inputs(2, 3, 1024, 64, torch.bfloat16)       # 1024 tokens: rel_h is 16 wide
+    rel_h = rel_h[:, :, :, :16].contiguous()
+    rel_w = torch.empty(2, 3, 1024, 1, 64, dtype=torch.bfloat16, device="cuda").normal_(0.0, 0.5)
+    rel_h_w = torch.cat([rel_h.squeeze(-1), rel_w.squeeze(-2)], dim=-1)
+    out = torch.ops.samb200.custom_flash_aligned(q, k, v, rel_h_w, 64 ** -0.5)
+    assert torch.equal(out, _attention_rel_h_rel_w(q, k, v, rel_h, rel_w))
+    out2 = torch.ops.samb200.custom_flash_aligned(q, k, v, rel_h_w, 0.05)
+    ops.check_status()
+    bias = (rel_h.float() + rel_w.float()).view(2, 3, 1024, 1024)
+    ref = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float(), attn_mask=bias, scale=0.05)
+    torch.testing.assert_close(out2.float(), ref, rtol=1e-3, atol=1e-3)
+    with pytest.raises(RuntimeError, match="head dim"):
+        p = torch.nn.functional.pad(q, (0, 64))
+        torch.ops.samb200.custom_flash_aligned(p, p, p, rel_h_w, 0.1)
+
+
+# ----------------------------------------------------------------------------- Sam.forward / SamPredictor
+def _sam_on_gpu(enc_cfg, enc_sd, quant=None, sparse_mlp=False):
+    from test_gpu_encoder import build_encoder
+    from segment_anything_fast_b200 import apply_sparse
+    from segment_anything_fast_b200.sam_heads import Sam, build_heads
+    dcfg = do.DecoderConfig()
+    dsd = dict(do.seeded_state_dict(dcfg, seed=3))
+    dsd.update(do.seeded_mask_downscaling(dcfg, seed=3))
+    pe, md = build_heads()
+    pe.load_state_dict({k[len("prompt_encoder."):]: v for k, v in dsd.items() if k.startswith("prompt_encoder.")})
+    md.load_state_dict({k[len("mask_decoder."):]: v for k, v in dsd.items() if k.startswith("mask_decoder.")})
+    enc = build_encoder(enc_cfg, enc_sd, quant=quant)
+    if sparse_mlp:
+        apply_sparse(enc, mlp_only=True)
+    return Sam(enc, pe, md).cuda().eval(), dcfg, dsd
+
+
+def _iou(a, b):
+    inter = (a & b).flatten(2).sum(-1).double()
+    union = (a | b).flatten(2).sum(-1).double()
+    return torch.where(union > 0, inter / union.clamp(min=1), torch.ones_like(union))
+
+
+def test_sam_forward_on_gpu_against_oracle(ops):
+    """``Sam.forward`` with the CUDA encoder: non-square image + boxes, square image + points + mask input, against
+    the oracle's ``sam_forward`` over the fp32 encoder oracle on the same (bf16-rounded) weights."""
+    from test_gpu_masks import scene_images  # noqa: F401  (same scene generator family)
+    sd = eo.seeded_state_dict(TINY256, seed=11)
+    sam, dcfg, dsd = _sam_on_gpu(TINY256, sd)
+    recs = do.sam_forward_inputs(seed=9)
+    # piecewise-flat pixels instead of noise, so that the masks have object-like regions
+    g = torch.Generator().manual_seed(4)
+    for r in recs:
+        r["image"] = torch.nn.functional.interpolate(
+            torch.randint(0, 256, (1, 3, 6, 8), generator=g).float(), r["image"].shape[-2:], mode="nearest")[0]
+        if "mask_inputs" in r:                                    # a smooth blob, like a previous prediction's logits
+            r["mask_inputs"] = torch.nn.functional.interpolate(
+                torch.randn(1, 1, 4, 4, generator=g) * 6.0, (256, 256), mode="bilinear", align_corners=False)
+    dev = [{k: (v.cuda() if torch.is_tensor(v) else v) for k, v in r.items()} for r in recs]
+    got = sam(dev, multimask_output=True)
+    ops.check_status()
+    ref_sd = {k: v.to(torch.bfloat16).float() for k, v in sd.items()}
+    enc_oracle = lambda x: eo.image_encoder_forward(x, ref_sd, TINY256, "fp32")
+    want = do.sam_forward(dsd, dcfg, enc_oracle, recs, True)
+    for i, (a, b) in enumerate(zip(got, want)):
+        assert a["masks"].shape == b["masks"].shape
+        iou = _iou(a["masks"].cpu(), b["masks"])
+        area = b["masks"].float().mean((2, 3))
+        print(f"Sam.forward image {i}: IoU {[round(v, 4) for v in iou.flatten().tolist()]}")
+        assert ((iou >= 0.99) | (area < 1e-3)).all()
+        assert (a["iou_predictions"].float().cpu() - b["iou_predictions"]).abs().max().item() < 5e-2
+
+
+def test_sam_predictor_call_sequence_on_gpu(ops):
+    """``SamPredictor.set_torch_image`` + ``predict_torch`` (predictor.py:61-91,170-252) with the CUDA encoder, one
+    box per image, against the oracle pipeline."""
+    from test_gpu_masks import _boxes, scene_images
+    from segment_anything_fast_b200 import SamPredictor
+    sd = eo.seeded_state_dict(TINY256, seed=11)
+    sam, dcfg, dsd = _sam_on_gpu(TINY256, sd)
+    pred = SamPredictor(sam)
+    x = scene_images(2, seed=12)                                  # normalised scenes; undo the normalisation to get pixels
+    mean, std = torch.tensor(eo.PIXEL_MEAN).view(1, 3, 1, 1), torch.tensor(eo.PIXEL_STD).view(1, 3, 1, 1)
+    pixels = (x * std + mean).round()
+    boxes = _boxes(2, seed=13)
+    ref_sd = {k: v.to(torch.bfloat16).float() for k, v in sd.items()}
+    for i in range(2):
+        pred.set_torch_image(pixels[i:i + 1].cuda(), (1024, 1024))
+        masks, iou_p, low = pred.predict_torch(None, None, boxes=boxes[i:i + 1].cuda(), multimask_output=True)
+        ops.check_status()
+        assert masks.shape == (1, 3, 1024, 1024) and masks.dtype == torch.bool and low.shape == (1, 3, 256, 256)
+        emb = eo.image_encoder_forward((pixels[i:i + 1] - mean) / std, ref_sd, TINY256, "fp32")
+        m_ref, iou_ref, _ = do.predict_masks_from_embedding(dsd, dcfg, emb, boxes[i:i + 1])
+        iou = _iou(masks.cpu(), m_ref)[0]
+        area = m_ref.float().mean((2, 3))[0]
+        print(f"SamPredictor image {i}: IoU {[round(v, 4) for v in iou.tolist()]}")
+        assert ((iou >= 0.99) | (area < 1e-3)).all()
+        assert (iou_p[0].float().cpu() - iou_ref[0]).abs().max().item() < 5e-2
+
+
+# ----------------------------------------------------------------------------- mask generator filter stage
+def test_process_batch_filters_against_oracle(ops):
+    """The filter stage of ``_process_batch_2`` (automatic_mask_generator.py:312-359) on a batch of 16 point prompts
+    x 3 masks of blob-like logits inside a crop: same survivors, scores, boxes and masks as the step-by-step
+    restatement."""
+    from segment_anything_fast_b200 import amg
+    g = torch.Generator().manual_seed(61)
+    P, C, H, W = 16, 3, 300, 300
+    coarse = torch.randn(P, C, 10, 10, generator=g) * 6.0
+    logits = torch.nn.functional.interpolate(coarse, (H, W), mode="bilinear", align_corners=False)
+    logits[0] = -8.0                                             # empty masks
+    logits[1, 0] = 8.0                                           # a full mask: touches every crop edge
+    iou_preds = torch.rand(P, C, generator=g) * 0.3 + 0.75
+    points = torch.rand(P, 2, generator=g) * 300
+    crop_box, orig_size = [100, 50, 400, 350], (350, 420)
+    kw = dict(pred_iou_thresh=0.88, mask_threshold=0.0, stability_score_offset=1.0, stability_score_thresh=0.9)
+    out = amg.process_batch_filters(logits.cuda(), iou_preds.cuda(), points, crop_box, orig_size, **kw)
+    ops.check_status()
+    idx, score, boxes, masks = ao.process_batch_filters(logits.numpy(), iou_preds.numpy(), crop_box, orig_size, **kw)
+    assert 0 < len(idx) < P * C
+    assert np.array_equal(out["keep"].cpu().numpy(), idx)
+    assert np.array_equal(out["stability_score"].cpu().numpy(), score)
+    assert np.array_equal(out["boxes"].cpu().numpy(), boxes)
+    assert np.array_equal(out["masks"].cpu().numpy(), masks)
+    assert np.array_equal(out["iou_preds"].cpu().numpy(), iou_preds.reshape(-1).numpy()[idx])
+    assert np.array_equal(out["points"].cpu().numpy(), points.repeat_interleave(C, dim=0).numpy()[idx])
+    rles = amg.mask_to_rle_pytorch(out["masks"])
+    assert rles == ao.mask_to_rle(masks)

@@ -132,3 +132,103 @@ def test_other_registry_sizes_against_oracle(ops, name, cfg):
     ref = eo.image_encoder_forward(x, sd, cfg, "fp32")
     print(f"{name}: cosine {_cos(got, ref):.6f}, max-abs {(got - ref).abs().max().item():.4f}")
     assert _cos(got, ref) > 0.999
+
+
+# ---------------------------------------------------------------------------------------------------
+# ViT-H in the quantised configurations, and the box-prompt predictor on top of it, at the real size
+# ---------------------------------------------------------------------------------------------------
+_CASES = {}
+
+
+def _vit_h_case(mode):
+    """CUDA ViT-H embeddings of two scene images in ``mode`` (bf16 | int8 | int8_sp24) next to the oracle's
+    embeddings in the same arithmetic and in fp32, all on the same (bf16-rounded, where the mode says so 2:4-pruned)
+    weights.  Computed once per mode and shared by the tests below."""
+    if mode in _CASES:
+        return _CASES[mode]
+    from oracle import quant_oracle as qo
+    from test_gpu_encoder import build_encoder
+    from test_gpu_masks import scene_images
+    from segment_anything_fast_b200 import apply_sparse
+    sd = eo.seeded_state_dict(VIT_H, seed=21)
+    x = scene_images(2, seed=23)
+    enc = build_encoder(VIT_H, sd, quant=None if mode == "bf16" else "int8")
+    ref_sd = {k: v.to(torch.bfloat16).float() if v.is_floating_point() else v for k, v in sd.items()}
+    if mode == "int8_sp24":
+        apply_sparse(enc, mlp_only=True)
+        for k in list(ref_sd):
+            if ".mlp.lin" in k and k.endswith(".weight"):
+                ref_sd[k] = ref_sd[k] * qo.prune_2_4_mask(ref_sd[k]).float()
+    got = enc(x.to(torch.bfloat16).cuda()).float().cpu()
+    same = eo.image_encoder_forward(x, ref_sd, VIT_H, "bf16" if mode == "bf16" else "int8")
+    f32 = eo.image_encoder_forward(x, ref_sd, VIT_H, "fp32")
+    _CASES[mode] = (enc, x, got, same, f32)
+    return _CASES[mode]
+
+
+@pytest.mark.parametrize("mode", ["bf16", "int8", "int8_sp24"])
+def test_vit_h_encoder_modes_against_oracle(ops, mode):
+    """ViT-H (32 blocks, 1280 wide) in every arithmetic the benchmark runs: against the oracle in the same
+    arithmetic on the same weights, and against fp32.  max-abs is on the LayerNorm2d-normalised output (unit
+    scale); ``floor`` is how far the oracle's arithmetic of that mode is from fp32, i.e. what the rounding points
+    shared with the reference cost by themselves."""
+    _, _, got, same, f32 = _vit_h_case(mode)
+    ops.check_status()
+    floor = (same - f32).abs().max().item()
+    e_same, e_f32 = (got - same).abs().max().item(), (got - f32).abs().max().item()
+    print(f"ViT-H {mode}: vs oracle[{mode}] cosine {_cos(got, same):.6f} max-abs {e_same:.4f} | vs fp32 cosine "
+          f"{_cos(got, f32):.6f} max-abs {e_f32:.4f} | oracle[{mode}] vs fp32 cosine {_cos(same, f32):.6f} max-abs {floor:.4f}")
+    assert torch.isfinite(got).all()
+    assert _cos(got, same) > 0.999 and _cos(got, f32) > 0.999
+    assert e_f32 <= 2.0 * floor + 0.01
+    assert e_same <= 2.0 * floor + 0.01
+
+
+@pytest.mark.parametrize("mode", ["int8_sp24", "bf16"])
+def test_vit_h_box_prompt_masks_through_the_predictor(ops, mode):
+    """The sparse + int8 predictor configuration at its real size: ViT-H with 2:4-pruned int8 MLPs and int8
+    attention linears, one box per image, three masks each, through ``SamPredictor.set_torch_image`` /
+    ``predict_torch`` (predictor.py:61-91,170-252) and through ``Sam.predict_boxes``.  IoU against the oracle
+    pipeline in the same arithmetic (same pruned / quantised weights): mean over the masks at least 0.99, and every
+    mask at least 0.99 or, where two independently rounded evaluations cannot be that close, at least what the
+    oracle's own arithmetic of that mode reaches against fp32 on that mask (less 0.005); the same bound holds
+    against fp32."""
+    from oracle import decoder_oracle as do
+    from test_gpu_masks import _boxes, _iou
+    from segment_anything_fast_b200 import SamPredictor
+    from segment_anything_fast_b200.sam_heads import Sam, build_heads
+    enc, x, got, same, f32 = _vit_h_case(mode)
+    dcfg = do.DecoderConfig()
+    dsd = do.seeded_state_dict(dcfg, seed=3)
+    pe, md = build_heads()
+    pe.load_state_dict({k[len("prompt_encoder."):]: v for k, v in dsd.items() if k.startswith("prompt_encoder.")}, strict=False)
+    md.load_state_dict({k[len("mask_decoder."):]: v for k, v in dsd.items() if k.startswith("mask_decoder.")})
+    sam = Sam(enc, pe, md).cuda().eval()
+    pred = SamPredictor(sam)
+    boxes = _boxes(2, seed=24)
+    mean, std = torch.tensor(eo.PIXEL_MEAN).view(1, 3, 1, 1), torch.tensor(eo.PIXEL_STD).view(1, 3, 1, 1)
+    pixels = (x * std + mean).round()
+    batch_masks, _, _ = sam.predict_boxes(x.to(torch.bfloat16).cuda(), boxes.cuda())
+    ious = []
+    for i in range(2):
+        pred.set_torch_image(pixels[i:i + 1].cuda(), (1024, 1024))
+        assert torch.equal(pred.get_image_embedding().float().cpu(), got[i:i + 1])
+        masks, _, _ = pred.predict_torch(None, None, boxes=boxes[i:i + 1].cuda(), multimask_output=True)
+        ops.check_status()
+        assert torch.equal(masks, batch_masks[i:i + 1])
+        m_same, _, _ = do.predict_masks_from_embedding(dsd, dcfg, same[i:i + 1], boxes[i:i + 1])
+        m_f32, _, _ = do.predict_masks_from_embedding(dsd, dcfg, f32[i:i + 1], boxes[i:i + 1])
+        iou = _iou(masks.cpu(), m_same)[0]
+        exact = _iou(masks.cpu(), m_f32)[0]
+        floor = _iou(m_same, m_f32)[0]
+        area = m_same.float().mean((2, 3))[0]
+        print(f"ViT-H {mode} image {i}: IoU vs oracle[{mode}] {[round(v, 5) for v in iou.tolist()]}, vs fp32 "
+              f"{[round(v, 5) for v in exact.tolist()]} (oracle[{mode}] vs fp32 {[round(v, 5) for v in floor.tolist()]}), "
+              f"area {[round(v, 4) for v in area.tolist()]}")
+        for j in range(iou.numel()):
+            if area[j] >= 1e-3:
+                bound = min(0.99, floor[j].item() - 0.005)
+                assert iou[j].item() >= bound, (i, j)
+                assert exact[j].item() >= bound, (i, j)
+                ious.append(iou[j].item())
+    assert sum(ious) / len(ious) >= 0.99

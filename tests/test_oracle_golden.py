@@ -140,3 +140,24 @@ def test_amg_oracle_matches_reference_functions(golden_dir):
     for r, m in zip(rles, masks):
         assert r["size"] == list(m.shape) and sum(r["counts"]) == m.size
         assert np.array_equal(ao.rle_to_mask(r), m)
+
+
+def test_amg_crop_edge_filter_and_batch_filters(golden_dir):
+    """``is_box_near_crop_edge`` against the reference's output on seeded boxes, and the step-by-step
+    ``process_batch_filters`` restatement against a direct evaluation of its three predicates."""
+    import numpy as np
+    from oracle import amg_oracle as ao
+    g = _load(golden_dir, "amg_fp32.npz")
+    got = ao.is_box_near_crop_edge(g["edge_boxes"], g["edge_crop"].tolist(), g["edge_orig"].tolist())
+    assert np.array_equal(got, g["edge_out"]) and 0 < got.sum() < len(got)
+    rng = np.random.default_rng(3)
+    logits = np.repeat(np.repeat(rng.normal(0, 4, (5, 3, 6, 6)), 10, axis=2), 10, axis=3).astype(np.float32)
+    iou = rng.uniform(0.7, 1.0, (5, 3)).astype(np.float32)
+    crop, orig = [20, 10, 80, 70], (70, 100)
+    idx, score, boxes, masks = ao.process_batch_filters(logits, iou, crop, orig, 0.8, 0.0, 1.0, 0.5)
+    flat = logits.reshape(15, 60, 60)
+    s_all = ao.calculate_stability_score(flat, 0.0, 1.0)
+    b_all = ao.batched_mask_to_box(flat > 0)
+    keep = (iou.reshape(-1) > 0.8) & (s_all >= 0.5) & ~ao.is_box_near_crop_edge(b_all, crop, [0, 0, 100, 70])
+    assert np.array_equal(idx, np.flatnonzero(keep))
+    assert np.array_equal(score, s_all[keep]) and np.array_equal(boxes, b_all[keep]) and np.array_equal(masks, (flat > 0)[keep])
