@@ -66,13 +66,17 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 __device__ __forceinline__ uint2 quant8(const float (&f)[8], float sc, float inv_sc) {
   constexpr float kMagic = 12582912.0f;
   uint32_t b[8];
+  float worst = 0.f;                 // largest distance of a product from its rounded value: 0.5 = a tie
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const float t = __fmul_rn(f[j], inv_sc);
-    float y = __fadd_rn(t, kMagic);
-    const float r = __fadd_rn(y, -kMagic);
-    if (fabsf(fabsf(t - r) - 0.5f) < 4e-5f) y = __fadd_rn(rintf(__fdiv_rn(f[j], sc)), kMagic);
+    const float y = __fadd_rn(t, kMagic);
+    worst = fmaxf(worst, fabsf(t - __fadd_rn(y, -kMagic)));
     b[j] = __float_as_uint(y);
+  }
+  if (worst > 0.49996f) {            // rare: some element sits next to a half-integer; redo the eight exactly
+#pragma unroll
+    for (int j = 0; j < 8; ++j) b[j] = __float_as_uint(__fadd_rn(rintf(__fdiv_rn(f[j], sc)), kMagic));
   }
   const uint32_t b01 = __byte_perm(b[0], b[1], 0x0040), b23 = __byte_perm(b[2], b[3], 0x0040);
   const uint32_t b45 = __byte_perm(b[4], b[5], 0x0040), b67 = __byte_perm(b[6], b[7], 0x0040);
@@ -195,101 +199,231 @@ row_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
   }
 }
 
-// Per-row int8 quantisation for rows of up to kVec*256 elements: the row stays in registers as raw
-// 16-byte vectors between the absmax pass and the rounding pass.
-// kGelu: the row first goes through the exact-erf GELU and is rounded back to bf16 (the activation tensor
-// the reference materialises between lin1 and lin2), then quantised.
-template <int kVec, bool kGelu>
+__device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Persistent, prefetching form of the row kernels for raster-order rows of up to NV * 256 elements: a warp owns
+// every G-th row (G = warps in the grid) and keeps the next STAGES - 1 of its rows in flight as 16-byte cp.async
+// copies into a private shared-memory ring (each lane later reads back exactly the pieces it copied, so no
+// barrier is involved and nothing can hang), which decouples the bytes in flight per SM from the register
+// budget.  The arithmetic, and its order, are those of row_kernel / quant_rows_kernel: same bits out.
+template <bool kNorm, bool kQuant, bool kGelu, int NV, int STAGES>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ yq, float* __restrict__ scale,
-                  long long rows, int C) {
-  const int lane = threadIdx.x & 31;
-  const long long row = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-  if (row >= rows) return;
+rows_stream_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                   __nv_bfloat16* __restrict__ y, int8_t* __restrict__ yq, float* __restrict__ scale, long long rows,
+                   int C, float eps) {
+  extern __shared__ uint4 ring[];                         // [warp][stage][vector i][lane]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long G = (long long)gridDim.x * kWarpsPerBlock;
   const int nvec = C >> 3;
-  const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
-  uint4 raw[kVec];
-  float amax = 0.f;
+  uint4* mine = ring + (size_t)warp * STAGES * NV * 32 + lane;
+  auto issue = [&](long long row, int st) {
+    if (row < rows) {
+      const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
 #pragma unroll
-  for (int i = 0; i < kVec; ++i) {
-    const int vi = i * 32 + lane;
-    if (vi < nvec) {
-      raw[i] = xr[vi];
-      float f[8];
-      unpack8(raw[i], f);
-      if (kGelu) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = gelu_erf(f[j]);
-        raw[i] = pack8(f);
-        unpack8(raw[i], f);
+      for (int i = 0; i < NV; ++i) {
+        const int vi = i * 32 + lane;
+        if (vi < nvec) cp_async_16(smem_u32(mine + (st * NV + i) * 32), xr + vi);
       }
+    }
+    cp_async_commit();                                    // an empty group past the last row keeps the count uniform
+  };
+  const long long row0 = (long long)blockIdx.x * kWarpsPerBlock + warp;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+  for (int st = 0; st < STAGES - 1; ++st) issue(row0 + st * G, st);
+  int it = 0;
+  for (long long row = row0; row < rows; row += G, ++it) {
+    issue(row + (STAGES - 1) * G, (it + STAGES - 1) % STAGES);
+    cp_async_wait<STAGES - 1>();                          // this row's copies have landed
+    const int st = it % STAGES;
+    uint4 raw[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if (i * 32 + lane < nvec) raw[i] = mine[(st * NV + i) * 32];
+
+    float mean = 0.f, rstd = 1.f;
+    if (kNorm) {
+      float sm = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+        if (i * 32 + lane < nvec) {
+          float f[8];
+          unpack8(raw[i], f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) sm += f[j];
+        }
+      mean = warp_sum(sm) / float(C);
+      float q = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+        if (i * 32 + lane < nvec) {
+          float f[8];
+          unpack8(raw[i], f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float d = f[j] - mean;
+            q += d * d;
+          }
+        }
+      rstd = rsqrtf(warp_sum(q) / float(C) + eps);
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = i * 32 + lane;
+      if (vi < nvec) {
+        float f[8];
+        unpack8(raw[i], f);
+        if (kNorm) {
+          const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * vi), g1 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * vi + 1);
+          const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta) + 2 * vi), b1 = __ldg(reinterpret_cast<const float4*>(beta) + 2 * vi + 1);
+          const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+          const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = (f[j] - mean) * rstd * g[j] + b[j];
+        }
+        if (kGelu) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = gelu_erf(f[j]);
+        }
+        if (!kQuant) {
+          reinterpret_cast<uint4*>(y + row * C)[vi] = pack8(f);
+        } else {
+          if (kNorm || kGelu) {                           // quantise the bf16-rounded value
+            raw[i] = pack8(f);
+            unpack8(raw[i], f);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+        }
+      }
+    }
+    if (kQuant) {
+      amax = warp_max(amax);
+      const float sc = __fdiv_rn(fmaxf(amax, kAbsmaxFloor), 127.0f);
+      const float inv_sc = __frcp_rn(sc);
+      if (lane == 0) scale[row] = sc;
+      uint2* qr = reinterpret_cast<uint2*>(yq + row * C);
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int vi = i * 32 + lane;
+        if (vi < nvec) {
+          float f[8];
+          unpack8(raw[i], f);
+          qr[vi] = quant8(f, sc, inv_sc);
+        }
+      }
     }
   }
-  amax = warp_max(amax);
-  const float sc = __fdiv_rn(fmaxf(amax, kAbsmaxFloor), 127.0f);
-  const float inv_sc = __frcp_rn(sc);
-  if (lane == 0) scale[row] = sc;
-  uint2* qr = reinterpret_cast<uint2*>(yq + row * C);
-#pragma unroll
-  for (int i = 0; i < kVec; ++i) {
-    const int vi = i * 32 + lane;
-    if (vi < nvec) {
-      float f[8];
-      unpack8(raw[i], f);
-      qr[vi] = quant8(f, sc, inv_sc);
-    }
-  }
+  cp_async_wait<0>();
 }
 
-// Wide rows (C up to 3 * 256 * 8 = 6144): one 256-thread block per row, up to three 16-byte vectors per
-// thread, absmax through shared memory.
-template <bool kGelu>
+// Host side of rows_stream_kernel: picks the vector count, sizes the ring and the persistent grid.
+template <bool kNorm, bool kQuant, bool kGelu, int NV, int STAGES>
+int launch_stream_nv(const __nv_bfloat16* x, const float* gamma, const float* beta, __nv_bfloat16* y, int8_t* yq,
+                     float* scale, long long rows, int C, float eps, cudaStream_t st) {
+  auto kern = rows_stream_kernel<kNorm, kQuant, kGelu, NV, STAGES>;
+  constexpr int kSmem = kWarpsPerBlock * STAGES * NV * 32 * 16;
+  static int per_sm = 0;                // resident blocks per SM of this instantiation (a device fact, asked once)
+  if (per_sm == 0) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) return SAMB_E_LAUNCH;
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kWarpsPerBlock * 32, kSmem) != cudaSuccess || n < 1)
+      return SAMB_E_LAUNCH;
+    per_sm = n;
+  }
+  long long blocks = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  const long long cap = (long long)sm_count() * per_sm;     // persistent: exactly one resident wave
+  if (blocks > cap) blocks = cap;
+  kern<<<unsigned(blocks), kWarpsPerBlock * 32, kSmem, st>>>(x, gamma, beta, y, yq, scale, rows, C, eps);
+  return launch_status();
+}
+template <bool kNorm, bool kQuant, bool kGelu>
+int launch_stream(const __nv_bfloat16* x, const float* gamma, const float* beta, __nv_bfloat16* y, int8_t* yq,
+                  float* scale, long long rows, int C, float eps, cudaStream_t st) {
+  const int nv = (C / 8 + 31) / 32;
+  if (nv <= 1) return launch_stream_nv<kNorm, kQuant, kGelu, 1, 4>(x, gamma, beta, y, yq, scale, rows, C, eps, st);
+  if (nv <= 3) return launch_stream_nv<kNorm, kQuant, kGelu, 3, 4>(x, gamma, beta, y, yq, scale, rows, C, eps, st);
+  if (nv <= 5) return launch_stream_nv<kNorm, kQuant, kGelu, 5, 4>(x, gamma, beta, y, yq, scale, rows, C, eps, st);
+  return launch_stream_nv<kNorm, kQuant, kGelu, 8, 3>(x, gamma, beta, y, yq, scale, rows, C, eps, st);
+}
+
+// Wide rows (C up to 3 * 256 * 8 = 6144): a 256-thread block per row, up to three 16-byte vectors per thread,
+// absmax through shared memory.  Persistent blocks walk every gridDim-th row and keep their next STAGES - 1 rows
+// in flight as cp.async copies into a per-thread ring (each thread reads back its own pieces).
+// kGelu: the row first goes through the exact-erf GELU and is rounded back to bf16 (the activation tensor
+// the reference materialises between lin1 and lin2), then quantised.
+template <bool kGelu, int STAGES>
 __global__ void __launch_bounds__(256)
-quant_rows_wide_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ yq, float* __restrict__ scale, int C) {
-  __shared__ float s_max[8];
-  const long long row = blockIdx.x;
+quant_rows_wide_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ yq, float* __restrict__ scale,
+                       long long rows, int C) {
+  extern __shared__ uint4 ring[];                         // [stage][vector i][thread]
+  __shared__ float s_max[2][8];
   const int nvec = C >> 3;
-  const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
-  uint4 raw[3];
-  float amax = 0.f;
+  uint4* mine = ring + threadIdx.x;
+  auto issue = [&](long long row, int st) {
+    if (row < rows) {
+      const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
 #pragma unroll
-  for (int i = 0; i < 3; ++i) {
-    const int vi = i * 256 + threadIdx.x;
-    if (vi < nvec) {
-      raw[i] = xr[vi];
-      float f[8];
-      unpack8(raw[i], f);
-      if (kGelu) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = gelu_erf(f[j]);
-        raw[i] = pack8(f);
-        unpack8(raw[i], f);
+      for (int i = 0; i < 3; ++i) {
+        const int vi = i * 256 + threadIdx.x;
+        if (vi < nvec) cp_async_16(smem_u32(mine + (st * 3 + i) * 256), xr + vi);
       }
+    }
+    cp_async_commit();
+  };
 #pragma unroll
-      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+  for (int st = 0; st < STAGES - 1; ++st) issue((long long)blockIdx.x + (long long)st * gridDim.x, st);
+  int it = 0;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x, ++it) {
+    issue(row + (long long)(STAGES - 1) * gridDim.x, (it + STAGES - 1) % STAGES);
+    cp_async_wait<STAGES - 1>();
+    const int st = it % STAGES;
+    uint4 raw[3];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      const int vi = i * 256 + threadIdx.x;
+      if (vi < nvec) {
+        raw[i] = mine[(st * 3 + i) * 256];
+        float f[8];
+        unpack8(raw[i], f);
+        if (kGelu) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = gelu_erf(f[j]);
+          raw[i] = pack8(f);
+          unpack8(raw[i], f);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+      }
+    }
+    amax = warp_max(amax);
+    float* sm = s_max[it & 1];                            // two buffers: one barrier per row is enough
+    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = sm[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) amax = fmaxf(amax, sm[w]);
+    const float sc = __fdiv_rn(fmaxf(amax, kAbsmaxFloor), 127.0f);
+    const float inv_sc = __frcp_rn(sc);
+    if (threadIdx.x == 0) scale[row] = sc;
+    uint2* qr = reinterpret_cast<uint2*>(yq + row * C);
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      const int vi = i * 256 + threadIdx.x;
+      if (vi < nvec) {
+        float f[8];
+        unpack8(raw[i], f);
+        qr[vi] = quant8(f, sc, inv_sc);
+      }
     }
   }
-  amax = warp_max(amax);
-  if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = amax;
-  __syncthreads();
-  amax = s_max[0];
-#pragma unroll
-  for (int w = 1; w < 8; ++w) amax = fmaxf(amax, s_max[w]);
-  const float sc = __fdiv_rn(fmaxf(amax, kAbsmaxFloor), 127.0f);
-  const float inv_sc = __frcp_rn(sc);
-  if (threadIdx.x == 0) scale[row] = sc;
-  uint2* qr = reinterpret_cast<uint2*>(yq + row * C);
-#pragma unroll
-  for (int i = 0; i < 3; ++i) {
-    const int vi = i * 256 + threadIdx.x;
-    if (vi < nvec) {
-      float f[8];
-      unpack8(raw[i], f);
-      qr[vi] = quant8(f, sc, inv_sc);
-    }
-  }
+  cp_async_wait<0>();
 }
 
 // Channel LayerNorm of x[tokens, C] (NHWC rows) written as out[img, C, hw] (NCHW).  One block
@@ -364,6 +498,10 @@ int launch_rows(const void* x, const float* gamma, const float* beta, void* y, i
   if (out_rows == 0) return SAMB_OK;
   const long long blocks = (out_rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
   if (blocks > 0x7fffffffLL) return SAMB_E_SHAPE;
+  if (window == 0)                     // raster order: the persistent prefetching kernel
+    return launch_stream<kNorm, kQuant, false>(static_cast<const __nv_bfloat16*>(x), gamma, beta,
+                                               static_cast<__nv_bfloat16*>(y), yq, scale, out_rows, C, eps,
+                                               static_cast<cudaStream_t>(stream));
   row_kernel<kNorm, kQuant><<<unsigned(blocks), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), gamma, beta, static_cast<__nv_bfloat16*>(y), yq, scale, out_rows, C, eps,
       map);
@@ -385,14 +523,22 @@ int launch_quant_rows(const void* x, int8_t* yq, float* scale, int64_t rows, int
   auto st = static_cast<cudaStream_t>(stream);
   auto xb = static_cast<const __nv_bfloat16*>(x);
   if (C <= 8 * 256) {
-    if (gelu) quant_rows_kernel<8, true><<<unsigned(blocks), kWarpsPerBlock * 32, 0, st>>>(xb, yq, scale, rows, C);
-    else quant_rows_kernel<8, false><<<unsigned(blocks), kWarpsPerBlock * 32, 0, st>>>(xb, yq, scale, rows, C);
-  } else if (rows > 0x7fffffffLL) {
-    return SAMB_E_SHAPE;
-  } else if (gelu) {
-    quant_rows_wide_kernel<true><<<unsigned(rows), 256, 0, st>>>(xb, yq, scale, C);
+    if (gelu) return launch_stream<false, true, true>(xb, nullptr, nullptr, nullptr, yq, scale, rows, C, 0.f, st);
+    return launch_stream<false, true, false>(xb, nullptr, nullptr, nullptr, yq, scale, rows, C, 0.f, st);
   } else {
-    quant_rows_wide_kernel<false><<<unsigned(rows), 256, 0, st>>>(xb, yq, scale, C);
+    constexpr int kStages = 3, kSmem = kStages * 3 * 256 * 16;
+    static int per_sm[2] = {0, 0};      // resident blocks per SM (a device fact, asked once per variant)
+    if (per_sm[gelu] == 0) {
+      int n = 0;
+      const cudaError_t e = gelu ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quant_rows_wide_kernel<true, kStages>, 256, kSmem)
+                                 : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quant_rows_wide_kernel<false, kStages>, 256, kSmem);
+      if (e != cudaSuccess || n < 1) return SAMB_E_LAUNCH;
+      per_sm[gelu] = n;
+    }
+    const long long cap = (long long)sm_count() * per_sm[gelu];
+    const long long nb = rows < cap ? rows : cap;
+    if (gelu) quant_rows_wide_kernel<true, kStages><<<unsigned(nb), 256, kSmem, st>>>(xb, yq, scale, rows, C);
+    else quant_rows_wide_kernel<false, kStages><<<unsigned(nb), 256, kSmem, st>>>(xb, yq, scale, rows, C);
   }
   return launch_status();
 }

@@ -180,14 +180,18 @@ def test_sam_forward_on_gpu_against_oracle(ops):
     got = sam(dev, multimask_output=True)
     ops.check_status()
     ref_sd = {k: v.to(torch.bfloat16).float() for k, v in sd.items()}
-    enc_oracle = lambda x: eo.image_encoder_forward(x, ref_sd, TINY256, "fp32")
-    want = do.sam_forward(dsd, dcfg, enc_oracle, recs, True)
-    for i, (a, b) in enumerate(zip(got, want)):
+    want = do.sam_forward(dsd, dcfg, lambda x: eo.image_encoder_forward(x, ref_sd, TINY256, "fp32"), recs, True)
+    same = do.sam_forward(dsd, dcfg, lambda x: eo.image_encoder_forward(x, ref_sd, TINY256, "bf16"), recs, True)
+    for i, (a, b, c) in enumerate(zip(got, want, same)):
         assert a["masks"].shape == b["masks"].shape
-        iou = _iou(a["masks"].cpu(), b["masks"])
-        area = b["masks"].float().mean((2, 3))
-        print(f"Sam.forward image {i}: IoU {[round(v, 4) for v in iou.flatten().tolist()]}")
-        assert ((iou >= 0.99) | (area < 1e-3)).all()
+        iou = _iou(a["masks"].cpu(), b["masks"]).flatten()
+        floor = _iou(c["masks"], b["masks"]).flatten()            # the oracle's own bf16 arithmetic against fp32
+        area = b["masks"].float().mean((2, 3)).flatten()
+        print(f"Sam.forward image {i}: IoU vs fp32 pipeline {[round(v, 4) for v in iou.tolist()]} "
+              f"(oracle bf16 vs fp32 {[round(v, 4) for v in floor.tolist()]})")
+        for j in range(iou.numel()):
+            if area[j] >= 1e-3:
+                assert iou[j].item() >= min(0.99, floor[j].item() - 0.01), (i, j)
         assert (a["iou_predictions"].float().cpu() - b["iou_predictions"]).abs().max().item() < 5e-2
 
 
@@ -221,13 +225,18 @@ def test_sam_predictor_call_sequence_on_gpu(ops):
 # ----------------------------------------------------------------------------- mask generator filter stage
 def test_process_batch_filters_against_oracle(ops):
     """The filter stage of ``_process_batch_2`` (automatic_mask_generator.py:312-359) on a batch of 16 point prompts
-    x 3 masks of blob-like logits inside a crop: same survivors, scores, boxes and masks as the step-by-step
+    x 3 masks of disc-shaped logits inside a crop: same survivors, scores, boxes and masks as the step-by-step
     restatement."""
     from segment_anything_fast_b200 import amg
     g = torch.Generator().manual_seed(61)
     P, C, H, W = 16, 3, 300, 300
-    coarse = torch.randn(P, C, 10, 10, generator=g) * 6.0
-    logits = torch.nn.functional.interpolate(coarse, (H, W), mode="bilinear", align_corners=False)
+    # cone-shaped logits over discs of random centre, radius and steepness: steep ones are stable, some touch the
+    # crop's inner edges, so that every filter keeps some masks and drops others
+    cy, cx = torch.rand(P, C, 1, 1, generator=g) * H, torch.rand(P, C, 1, 1, generator=g) * W
+    rad = torch.rand(P, C, 1, 1, generator=g) * 50 + 15
+    amp = torch.rand(P, C, 1, 1, generator=g) * 100 + 20
+    yy, xx = torch.arange(H).view(1, 1, H, 1).float(), torch.arange(W).view(1, 1, 1, W).float()
+    logits = amp * (1.0 - ((yy - cy) ** 2 + (xx - cx) ** 2).sqrt() / rad)
     logits[0] = -8.0                                             # empty masks
     logits[1, 0] = 8.0                                           # a full mask: touches every crop edge
     iou_preds = torch.rand(P, C, generator=g) * 0.3 + 0.75
@@ -237,7 +246,7 @@ def test_process_batch_filters_against_oracle(ops):
     out = amg.process_batch_filters(logits.cuda(), iou_preds.cuda(), points, crop_box, orig_size, **kw)
     ops.check_status()
     idx, score, boxes, masks = ao.process_batch_filters(logits.numpy(), iou_preds.numpy(), crop_box, orig_size, **kw)
-    assert 0 < len(idx) < P * C
+    assert 4 <= len(idx) < P * C // 2
     assert np.array_equal(out["keep"].cpu().numpy(), idx)
     assert np.array_equal(out["stability_score"].cpu().numpy(), score)
     assert np.array_equal(out["boxes"].cpu().numpy(), boxes)
