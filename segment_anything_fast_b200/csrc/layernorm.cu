@@ -40,14 +40,24 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
-  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {   // one shift or mask per element
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const float2 t = __bfloat1622float2(p[j]);
-    f[2 * j] = t.x;
-    f[2 * j + 1] = t.y;
+    f[2 * j] = __uint_as_float(w[j] << 16);
+    f[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
   }
+}
+// Running maximum of |x| over packed bf16 pairs, kept as a packed pair (max and abs are exact in bf16).
+__device__ __forceinline__ __nv_bfloat162 absmax8(__nv_bfloat162 m, const uint4& u) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) m = __hmax2(m, __habs2(p[j]));
+  return m;
+}
+__device__ __forceinline__ float absmax_fold(__nv_bfloat162 m) {
+  const float2 t = __bfloat1622float2(m);
+  return fmaxf(t.x, t.y);
 }
 __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   uint4 u;
@@ -59,19 +69,19 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 
 // Eight values -> eight int8 (two words), each rint(x / sc) bit-identical to the IEEE quotient, without a division
 // or a conversion instruction per element.  x * (1/sc) is within 2^-23 relative (1.5e-5 absolute for |x/sc| <= 127.5)
-// of the true quotient, so the two roundings can only disagree next to a half-integer; only there is the real
-// division evaluated.  Adding 1.5 * 2^23 rounds to the nearest even integer and leaves it, in two's complement,
-// in the low mantissa bits, so its low byte is the int8.  |x / sc| <= 127 (1 + 2^-24) because sc is the row's
+// of the true quotient, so rounding it can only disagree with rounding the quotient next to a half-integer; only
+// there is the real division evaluated.  fma(x, 1/sc, 1.5 * 2^23) rounds the exact product to the nearest (even)
+// integer and leaves it, in two's complement, in the low mantissa bits, so its low byte is the int8; a second fma
+// gives the distance of the product from that integer.  |x / sc| <= 127 (1 + 2^-24) because sc is the row's
 // absmax / 127 (or larger), so nothing needs clamping.
 __device__ __forceinline__ uint2 quant8(const float (&f)[8], float sc, float inv_sc) {
   constexpr float kMagic = 12582912.0f;
   uint32_t b[8];
-  float worst = 0.f;                 // largest distance of a product from its rounded value: 0.5 = a tie
+  float worst = 0.f;                 // largest distance of a product from the integer it rounded to: 0.5 = a tie
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const float t = __fmul_rn(f[j], inv_sc);
-    const float y = __fadd_rn(t, kMagic);
-    worst = fmaxf(worst, fabsf(t - __fadd_rn(y, -kMagic)));
+    const float y = fmaf(f[j], inv_sc, kMagic);                  // the exact product, rounded to an integer once
+    worst = fmaxf(worst, fabsf(fmaf(f[j], inv_sc, kMagic - y)));  // product minus that integer (kMagic - y is exact)
     b[j] = __float_as_uint(y);
   }
   if (worst > 0.49996f) {            // rare: some element sits next to a half-integer; redo the eight exactly
@@ -245,65 +255,61 @@ rows_stream_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
     for (int i = 0; i < NV; ++i)
       if (i * 32 + lane < nvec) raw[i] = mine[(st * NV + i) * 32];
 
-    float mean = 0.f, rstd = 1.f;
+    __nv_bfloat162 m2 = __floats2bfloat162_rn(0.f, 0.f);       // running |max| of the (bf16) values to quantise
     if (kNorm) {
+      // the row is unpacked once and stays in registers as fp32 through the three passes
+      float f[NV][8];
       float sm = 0.f;
 #pragma unroll
       for (int i = 0; i < NV; ++i)
         if (i * 32 + lane < nvec) {
-          float f[8];
-          unpack8(raw[i], f);
+          unpack8(raw[i], f[i]);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) sm += f[j];
+          for (int j = 0; j < 8; ++j) sm += f[i][j];
         }
-      mean = warp_sum(sm) / float(C);
+      const float mean = warp_sum(sm) / float(C);
       float q = 0.f;
 #pragma unroll
       for (int i = 0; i < NV; ++i)
         if (i * 32 + lane < nvec) {
-          float f[8];
-          unpack8(raw[i], f);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const float d = f[j] - mean;
-            q += d * d;
+            f[i][j] -= mean;
+            q += f[i][j] * f[i][j];
           }
         }
-      rstd = rsqrtf(warp_sum(q) / float(C) + eps);
-    }
-    float amax = 0.f;
+      const float rstd = rsqrtf(warp_sum(q) / float(C) + eps);
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int vi = i * 32 + lane;
-      if (vi < nvec) {
-        float f[8];
-        unpack8(raw[i], f);
-        if (kNorm) {
+      for (int i = 0; i < NV; ++i) {
+        const int vi = i * 32 + lane;
+        if (vi < nvec) {
           const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * vi), g1 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * vi + 1);
           const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta) + 2 * vi), b1 = __ldg(reinterpret_cast<const float4*>(beta) + 2 * vi + 1);
           const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
           const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-          for (int j = 0; j < 8; ++j) f[j] = (f[j] - mean) * rstd * g[j] + b[j];
-        }
-        if (kGelu) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) f[j] = gelu_erf(f[j]);
-        }
-        if (!kQuant) {
-          reinterpret_cast<uint4*>(y + row * C)[vi] = pack8(f);
-        } else {
-          if (kNorm || kGelu) {                           // quantise the bf16-rounded value
-            raw[i] = pack8(f);
-            unpack8(raw[i], f);
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+          for (int j = 0; j < 8; ++j) f[i][j] = f[i][j] * rstd * g[j] + b[j];
+          raw[i] = pack8(f[i]);
+          if (kQuant) m2 = absmax8(m2, raw[i]);
+          else reinterpret_cast<uint4*>(y + row * C)[vi] = raw[i];
         }
       }
+    } else {
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+        if (i * 32 + lane < nvec) {
+          if (kGelu) {                                    // bf16(gelu(x)) is what gets quantised
+            float f[8];
+            unpack8(raw[i], f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = gelu_erf(f[j]);
+            raw[i] = pack8(f);
+          }
+          m2 = absmax8(m2, raw[i]);
+        }
     }
     if (kQuant) {
-      amax = warp_max(amax);
+      const float amax = warp_max(absmax_fold(m2));
       const float sc = __fdiv_rn(fmaxf(amax, kAbsmaxFloor), 127.0f);
       const float inv_sc = __frcp_rn(sc);
       if (lane == 0) scale[row] = sc;
@@ -384,24 +390,23 @@ quant_rows_wide_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__
     cp_async_wait<STAGES - 1>();
     const int st = it % STAGES;
     uint4 raw[3];
-    float amax = 0.f;
+    __nv_bfloat162 m2 = __floats2bfloat162_rn(0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < 3; ++i) {
       const int vi = i * 256 + threadIdx.x;
       if (vi < nvec) {
         raw[i] = mine[(st * 3 + i) * 256];
-        float f[8];
-        unpack8(raw[i], f);
         if (kGelu) {
+          float f[8];
+          unpack8(raw[i], f);
 #pragma unroll
           for (int j = 0; j < 8; ++j) f[j] = gelu_erf(f[j]);
           raw[i] = pack8(f);
-          unpack8(raw[i], f);
         }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+        m2 = absmax8(m2, raw[i]);
       }
     }
+    float amax = absmax_fold(m2);
     amax = warp_max(amax);
     float* sm = s_max[it & 1];                            // two buffers: one barrier per row is enough
     if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = amax;

@@ -191,8 +191,8 @@ def test_vit_h_box_prompt_masks_through_the_predictor(ops, mode):
     ``predict_torch`` (predictor.py:61-91,170-252) and through ``Sam.predict_boxes``.  IoU against the oracle
     pipeline in the same arithmetic (same pruned / quantised weights): mean over the masks at least 0.99, and every
     mask at least 0.99 or, where two independently rounded evaluations cannot be that close, at least what the
-    oracle's own arithmetic of that mode reaches against fp32 on that mask (less 0.005); the same bound holds
-    against fp32.  Masks under 2 % of the frame (random weights produce such specks) are checked by the share of
+    oracle's own arithmetic of that mode reaches against fp32 on that mask (less 0.005); against fp32 the same
+    with a margin of 0.01.  Masks under 2 % of the frame (random weights produce such specks) are checked by the share of
     disagreeing pixels instead of the ratio."""
     from oracle import decoder_oracle as do
     from test_gpu_masks import _boxes, _iou
@@ -229,9 +229,9 @@ def test_vit_h_box_prompt_masks_through_the_predictor(ops, mode):
         diff = (masks.cpu() ^ m_same).float().mean((2, 3))[0]
         for j in range(iou.numel()):
             if area[j] >= 0.02:
-                bound = min(0.99, floor[j].item() - 0.005)
-                assert iou[j].item() >= bound, (i, j)
-                assert exact[j].item() >= bound, (i, j)
+                assert iou[j].item() >= min(0.99, floor[j].item() - 0.005), (i, j)
+                # against fp32 the CUDA masks can be as far as the oracle's own distance plus their distance from the oracle
+                assert exact[j].item() >= min(0.99, floor[j].item() - 0.01), (i, j)
                 ious.append(iou[j].item())
             else:           # a speck (< 2 % of the frame): its outline is rounding noise; bound the disagreeing pixels
                 assert diff[j].item() < 5e-3, (i, j)

@@ -153,6 +153,31 @@ def test_layernorm_quant_matches_oracle_bitwise_given_same_ln(ops):
     assert torch.equal(yq.cpu(), q_ref) and torch.equal(sc.cpu(), s_ref)
 
 
+@pytest.mark.parametrize("rows,C", [(1000, 1280), (8 * 148 * 4 * 3 + 5, 160), (777, 768), (515, 1024), (300, 2048), (7, 1280)])
+def test_layernorm_quant_raster_rows_bitwise(ops, rows, C):
+    """Raster-order rows (the persistent prefetching kernels): row counts that are not multiples of the warps in
+    flight, every vector-count variant.  The int8 rows and scales equal the oracle's quantisation of the bf16
+    LayerNorm kernel's own output bit for bit; values include exact ties (x / scale = k + 1/2)."""
+    g = torch.Generator().manual_seed(rows + C)
+    x = _bf16(torch.randn(rows, C, generator=g) * 2 + 0.25)
+    gamma = 1 + 0.1 * torch.randn(C, generator=g)
+    beta = 0.1 * torch.randn(C, generator=g)
+    y = ops.layernorm(x.cuda(), gamma.cuda(), beta.cuda(), 1e-6)
+    ref = torch.nn.functional.layer_norm(x.float(), (C,), gamma, beta, 1e-6)
+    torch.testing.assert_close(y.float().cpu(), ref, rtol=8e-3, atol=8e-3)
+    yq, sc = ops.layernorm_quant_i8(x.cuda(), gamma.cuda(), beta.cuda(), 1e-6)
+    q_ref, s_ref = qo.quantize_rows_absmax(y.float().cpu())
+    assert torch.equal(yq.cpu(), q_ref) and torch.equal(sc.cpu(), s_ref)
+    # rows holding ties: absmax 127 makes the scale exactly 1, and k + 0.5 is a bf16 value for small k
+    t = torch.zeros(64, C)
+    t[:, 0] = 127.0
+    t[:, 1:41] = torch.arange(-20, 20).float() + 0.5
+    t[:, 41] = -127.0
+    tq, ts = ops.quant_rows_i8(_bf16(t).cuda())
+    q_ref, s_ref = qo.quantize_rows_absmax(_bf16(t))
+    assert torch.equal(tq.cpu(), q_ref) and torch.equal(ts.cpu(), s_ref)
+
+
 def test_layernorm2d_nchw(ops):
     B, hw, C = 2, 64 * 64, 256
     g = torch.Generator().manual_seed(12)
