@@ -95,7 +95,9 @@ def main():
                             "from a copy of its package under oracle/_ref (flash_4.py:30-145; autotunes on first use)")
     qr = sub.add_parser("quant-rows")
     qr.add_argument("--rows", type=int, default=131072); qr.add_argument("--cols", type=int, default=1280)
-    for p in (g, ag, aw, ln, ms_, mr, tp, qr):
+    cp = sub.add_parser("copy", help="torch's own b.copy_(a) at a row-kernel size: what a plain copy reaches on this working set")
+    cp.add_argument("--rows", type=int, default=131072); cp.add_argument("--cols", type=int, default=1280)
+    for p in (g, ag, aw, ln, ms_, mr, tp, qr, cp):
         p.add_argument("--iters", type=int, default=10); p.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
     torch.manual_seed(0)
@@ -140,6 +142,11 @@ def main():
         nbytes = 4 * B * H * 196 * d * 2 + 2 * B * H * 196 * 14 * 2          # q, k, v, o + rel_h, rel_w
         out.update(arm=a.arm, shape=[B, H, 196, d], ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1),
                    tflops=round(4.0 * B * H * 196 * 196 * d / ms / 1e9, 1))
+    elif a.cmd == "copy":
+        x = torch.randn(a.rows, a.cols, device=dev).bfloat16()
+        y = torch.empty_like(x)
+        ms = _time(lambda: y.copy_(x), a.iters, a.warmup)
+        out.update(shape=[a.rows, a.cols], ms=round(ms, 4), gbs=round(a.rows * a.cols * 4 / ms / 1e6, 1))
     elif a.cmd == "quant-rows":
         x = torch.randn(a.rows, a.cols, device=dev).bfloat16()
         ms = _time(lambda: ops.quant_rows_i8(x), a.iters, a.warmup)

@@ -386,6 +386,92 @@ __device__ __forceinline__ float gelu_erf(float x) {
   return fmaf(-fabsf(x), e, fmaxf(x, 0.0f));
 }
 
+// Packed fp32 pairs (sm_100: one instruction performs two IEEE fp32 operations on a 64-bit register pair; each
+// half is rounded exactly as the scalar instruction would round it).  They halve the issue slots of fp32 math in
+// kernels that are bound by instruction issue rather than by the FMA pipe.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 ffma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 fadd2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 fsub2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 fmul2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// the two bf16 halves of a word as an fp32 pair
+__device__ __forceinline__ f32x2 bf16x2_to_f32x2(uint32_t w) {
+  return pack2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+
+// gelu_erf on a pair: the polynomial runs on packed fp32 instructions (seven for two elements); the clamp,
+// the two ex2 and the max(x, 0) stay scalar.  Each half gets exactly the bits gelu_erf gives it.
+__device__ __forceinline__ f32x2 gelu_erf2(f32x2 x2) {
+  float x0, x1;
+  unpack2(x2, x0, x1);
+  const f32x2 a2 = pack2(fminf(fabsf(x0), 6.0811f), fminf(fabsf(x1), 6.0811f));
+  f32x2 q = ffma2(pack2(-1.926999857e-06f, -1.926999857e-06f), a2, pack2(6.350679178e-05f, 6.350679178e-05f));
+  q = ffma2(q, a2, pack2(-9.461226873e-04f, -9.461226873e-04f));
+  q = ffma2(q, a2, pack2(8.571726270e-03f, 8.571726270e-03f));
+  q = ffma2(q, a2, pack2(-5.409686640e-02f, -5.409686640e-02f));
+  q = ffma2(q, a2, pack2(-4.583186507e-01f, -4.583186507e-01f));
+  q = ffma2(q, a2, pack2(-1.151316047e+00f, -1.151316047e+00f));
+  q = ffma2(q, a2, pack2(-9.999877214e-01f, -9.999877214e-01f));
+  float q0, q1, e0, e1;
+  unpack2(q, q0, q1);
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(q0));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(q1));
+  return ffma2(pack2(-fabsf(x0), -fabsf(x1)), pack2(e0, e1), pack2(fmaxf(x0, 0.0f), fmaxf(x1, 0.0f)));
+}
+
+// Eight accumulator columns of one output row through the GEMM epilogue arithmetic, two at a time:
+// int8: (float(acc) * a_scale) * w_scale[n]; then + bias[n]; then the exact GELU.  `ws` / `bs` point at eight
+// consecutive per-column values (16-byte aligned, shared memory).  Same roundings as the scalar sequence.
+template <bool kInt8, bool kScale, bool kBias, bool kGelu>
+__device__ __forceinline__ void epilogue8(const uint32_t* r, float a_scale, const float* ws, const float* bs,
+                                          float (&v)[8]) {
+  const f32x2 as2 = pack2(a_scale, a_scale);
+  ulonglong2 w01 = make_ulonglong2(0ull, 0ull), w23 = w01, b01 = w01, b23 = w01;
+  if (kScale) {
+    w01 = *reinterpret_cast<const ulonglong2*>(ws);
+    w23 = *reinterpret_cast<const ulonglong2*>(ws + 4);
+  }
+  if (kBias) {
+    b01 = *reinterpret_cast<const ulonglong2*>(bs);
+    b23 = *reinterpret_cast<const ulonglong2*>(bs + 4);
+  }
+  const f32x2 wv[4] = {w01.x, w01.y, w23.x, w23.y}, bv[4] = {b01.x, b01.y, b23.x, b23.y};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    f32x2 x;
+    if (kInt8) x = fmul2(pack2(float(int(r[2 * j])), float(int(r[2 * j + 1]))), as2);
+    else x = pack2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+    if (kScale) x = fmul2(x, wv[j]);
+    if (kBias) x = fadd2(x, bv[j]);
+    if (kGelu) x = gelu_erf2(x);
+    unpack2(x, v[2 * j], v[2 * j + 1]);
+  }
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

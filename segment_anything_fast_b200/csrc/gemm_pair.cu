@@ -222,25 +222,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
         for (int u = 0; u < NV; ++u) {
           const int ct0 = c * 64 + qc * CW + u * 8;      // first of these eight columns inside the tile
-          float v[8], ws[8], bs[8];
-          if (kInt8) {
-            const float4 w0 = *reinterpret_cast<const float4*>(s_wscale + ct0), w1 = *reinterpret_cast<const float4*>(s_wscale + ct0 + 4);
-            ws[0] = w0.x; ws[1] = w0.y; ws[2] = w0.z; ws[3] = w0.w; ws[4] = w1.x; ws[5] = w1.y; ws[6] = w1.z; ws[7] = w1.w;
-          }
-          if (kBias) {
-            const float4 b0 = *reinterpret_cast<const float4*>(s_bias + ct0), b1 = *reinterpret_cast<const float4*>(s_bias + ct0 + 4);
-            bs[0] = b0.x; bs[1] = b0.y; bs[2] = b0.z; bs[3] = b0.w; bs[4] = b1.x; bs[5] = b1.y; bs[6] = b1.z; bs[7] = b1.w;
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int cc = u * 8 + j;
-            float x;
-            if (kInt8) x = __fmul_rn(__fmul_rn(float(int(r[cc])), a_scale), ws[j]);
-            else x = __uint_as_float(r[cc]);
-            if (kBias) x = __fadd_rn(x, bs[j]);
-            if (kGelu) x = gelu_erf(x);
-            v[j] = x;
-          }
+          float v[8];
+          epilogue8<kInt8, kInt8, kBias, kGelu>(r + u * 8, a_scale, s_wscale + ct0, s_bias + ct0, v);
           if (kRes) {
             const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv[u]);
 #pragma unroll

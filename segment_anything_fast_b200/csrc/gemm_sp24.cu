@@ -281,12 +281,14 @@ gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
             for (int j = 0; j < 16; ++j)
               v[j] = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(cell0 + j * 128 + ((unit ^ (j & 7)) << 4)));
           }
+          const f32x2 ws2 = pack2(w_scale, w_scale), bias2 = pack2(bias, bias);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            float x = __fmul_rn(__fmul_rn(float(int(r[j])), sc[j]), w_scale);
-            if (kBias) x = __fadd_rn(x, bias);
-            if (kGelu) x = gelu_erf(x);
-            v[j] = kRes ? x + v[j] : x;
+          for (int j = 0; j < 16; j += 2) {              // two tokens per packed fp32 instruction
+            f32x2 x = fmul2(fmul2(pack2(float(int(r[j])), float(int(r[j + 1]))), pack2(sc[j], sc[j + 1])), ws2);
+            if (kBias) x = fadd2(x, bias2);
+            if (kGelu) x = gelu_erf2(x);
+            if (kRes) x = fadd2(x, pack2(v[j], v[j + 1]));
+            unpack2(x, v[j], v[j + 1]);
           }
 #pragma unroll
           for (int j = 0; j < 16; ++j)

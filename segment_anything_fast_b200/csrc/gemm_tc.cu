@@ -309,18 +309,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             float v[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int cc = u * 8 + j;                 // column inside this warp's 32
-              const int ct = c * 64 + half * 32 + cc;   // column inside the tile
-              float x;
-              if (kInt8) x = __fmul_rn(__fmul_rn(float(int(r[cc])), a_scale), s_wscale[ct]);
-              else x = __uint_as_float(r[cc]);
-              if (kColScale && !kInt8) x *= s_wscale[ct];
-              if (kBias) x = __fadd_rn(x, s_bias[ct]);
-              if (kGelu) x = gelu_erf(x);
-              v[j] = x;
-            }
+            const int ct0 = c * 64 + half * 32 + u * 8;   // first of these eight columns inside the tile
+            epilogue8<kInt8, kInt8 || kColScale, kBias, kGelu>(r + u * 8, a_scale, s_wscale + ct0, s_bias + ct0, v);
             if (kRes) {
               const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv[u]);
 #pragma unroll
@@ -447,7 +437,7 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
   // Large plain products run on CTA pairs; SAMB_GEMM_SINGLE_CTA=1 keeps them on this file's kernel (A/B timing).
   // An int8 product with a short K and the GELU epilogue is bound by that epilogue; the pair's shared
   // accumulator hand-off only couples it more tightly, so it stays on this file's kernel.
-  const bool epi_bound = int8 && K < 2048 && (epilogue & SAMB_EPI_GELU);
+  const bool epi_bound = int8 && K < 2048 && (epilogue & SAMB_EPI_GELU) && getenv("SAMB_GELU_SINGLE_CTA") != nullptr;
   if (!raw && batch == 1 && epilogue != EPI_COLSCALE && !epi_bound && getenv("SAMB_GEMM_SINGLE_CTA") == nullptr) {
     const int e = launch_gemm_pair(int8, A, lda, W, ldw, a_scale, w_scale, bias, residual, ldr, res_rows, out, ldo, M, N, K,
                                    epilogue, head_dim, status, stream);

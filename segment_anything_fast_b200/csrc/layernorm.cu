@@ -2,6 +2,8 @@
 // quantising each row to int8), plain per-row int8 quantisation, and the neck's channel LayerNorm
 // with an NHWC -> NCHW transposing store.  One warp owns one row; a lane holds up to 8 vectors of
 // 8 bf16 (C <= 2048), so every row is read once and written once with 16-byte accesses.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace samb {
@@ -74,17 +76,27 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 // integer and leaves it, in two's complement, in the low mantissa bits, so its low byte is the int8; a second fma
 // gives the distance of the product from that integer.  |x / sc| <= 127 (1 + 2^-24) because sc is the row's
 // absmax / 127 (or larger), so nothing needs clamping.
-__device__ __forceinline__ uint2 quant8(const float (&f)[8], float sc, float inv_sc) {
+__device__ __forceinline__ uint2 quant8(const uint4& raw, float sc, float inv_sc) {
   constexpr float kMagic = 12582912.0f;
+  const f32x2 magic2 = pack2(kMagic, kMagic), inv2 = pack2(inv_sc, inv_sc);
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
   uint32_t b[8];
   float worst = 0.f;                 // largest distance of a product from the integer it rounded to: 0.5 = a tie
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const float y = fmaf(f[j], inv_sc, kMagic);                  // the exact product, rounded to an integer once
-    worst = fmaxf(worst, fabsf(fmaf(f[j], inv_sc, kMagic - y)));  // product minus that integer (kMagic - y is exact)
-    b[j] = __float_as_uint(y);
+  for (int j = 0; j < 4; ++j) {      // two elements per packed fp32 instruction
+    const f32x2 x2 = bf16x2_to_f32x2(w[j]);
+    const f32x2 y2 = ffma2(x2, inv2, magic2);                    // the exact products, rounded to integers once
+    const f32x2 e2 = ffma2(x2, inv2, fsub2(magic2, y2));         // products minus those integers (magic - y is exact)
+    float y0, y1, e0, e1;
+    unpack2(y2, y0, y1);
+    unpack2(e2, e0, e1);
+    worst = fmaxf(fmaxf(worst, fabsf(e0)), fabsf(e1));
+    b[2 * j] = __float_as_uint(y0);
+    b[2 * j + 1] = __float_as_uint(y1);
   }
   if (worst > 0.49996f) {            // rare: some element sits next to a half-integer; redo the eight exactly
+    float f[8];
+    unpack8(raw, f);
 #pragma unroll
     for (int j = 0; j < 8; ++j) b[j] = __float_as_uint(__fadd_rn(rintf(__fdiv_rn(f[j], sc)), kMagic));
   }
@@ -202,9 +214,7 @@ row_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
   for (int i = 0; i < kMaxVec; ++i) {
     const int vi = i * 32 + lane;
     if (vi < nvec) {
-      float f[8];
-      unpack8(raw[i], f);
-      qr[vi] = quant8(f, sc, inv_sc);
+      qr[vi] = quant8(raw[i], sc, inv_sc);
     }
   }
 }
@@ -227,11 +237,14 @@ rows_stream_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
                    __nv_bfloat16* __restrict__ y, int8_t* __restrict__ yq, float* __restrict__ scale, long long rows,
                    int C, float eps) {
   extern __shared__ uint4 ring[];                         // [warp][stage][vector i][lane]
+  constexpr bool kDirect = STAGES == 0;                   // no ring: plain loads, many vectors per lane in flight
+  constexpr int kRing = kDirect ? 1 : STAGES;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long G = (long long)gridDim.x * kWarpsPerBlock;
   const int nvec = C >> 3;
-  uint4* mine = ring + (size_t)warp * STAGES * NV * 32 + lane;
+  uint4* mine = ring + (size_t)warp * kRing * NV * 32 + lane;
   auto issue = [&](long long row, int st) {
+    if (kDirect) return;
     if (row < rows) {
       const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
 #pragma unroll
@@ -244,52 +257,73 @@ rows_stream_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   };
   const long long row0 = (long long)blockIdx.x * kWarpsPerBlock + warp;
 #pragma unroll
-  for (int st = 0; st < STAGES - 1; ++st) issue(row0 + st * G, st);
+  for (int st = 0; st < kRing - 1; ++st) issue(row0 + st * G, st);
   int it = 0;
   for (long long row = row0; row < rows; row += G, ++it) {
-    issue(row + (STAGES - 1) * G, (it + STAGES - 1) % STAGES);
-    cp_async_wait<STAGES - 1>();                          // this row's copies have landed
-    const int st = it % STAGES;
     uint4 raw[NV];
+    if (kDirect) {
+      const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
 #pragma unroll
-    for (int i = 0; i < NV; ++i)
-      if (i * 32 + lane < nvec) raw[i] = mine[(st * NV + i) * 32];
+      for (int i = 0; i < NV; ++i)
+        if (i * 32 + lane < nvec) raw[i] = __ldcs(xr + i * 32 + lane);     // read once: streaming
+    } else {
+      issue(row + (kRing - 1) * G, (it + kRing - 1) % kRing);
+      cp_async_wait<kRing - 1>();                         // this row's copies have landed
+      const int st = it % kRing;
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+        if (i * 32 + lane < nvec) raw[i] = mine[(st * NV + i) * 32];
+    }
 
     __nv_bfloat162 m2 = __floats2bfloat162_rn(0.f, 0.f);       // running |max| of the (bf16) values to quantise
     if (kNorm) {
-      // the row is unpacked once and stays in registers as fp32 through the three passes
-      float f[NV][8];
-      float sm = 0.f;
+      // the row is unpacked once and stays in registers as fp32 pairs through the three passes
+      f32x2 v[NV][4];
+      f32x2 s2 = pack2(0.f, 0.f);
 #pragma unroll
       for (int i = 0; i < NV; ++i)
         if (i * 32 + lane < nvec) {
-          unpack8(raw[i], f[i]);
+          const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
 #pragma unroll
-          for (int j = 0; j < 8; ++j) sm += f[i][j];
-        }
-      const float mean = warp_sum(sm) / float(C);
-      float q = 0.f;
-#pragma unroll
-      for (int i = 0; i < NV; ++i)
-        if (i * 32 + lane < nvec) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            f[i][j] -= mean;
-            q += f[i][j] * f[i][j];
+          for (int j = 0; j < 4; ++j) {
+            v[i][j] = bf16x2_to_f32x2(w[j]);
+            s2 = fadd2(s2, v[i][j]);
           }
         }
-      const float rstd = rsqrtf(warp_sum(q) / float(C) + eps);
+      float s_lo, s_hi;
+      unpack2(s2, s_lo, s_hi);
+      const float mean = warp_sum(s_lo + s_hi) / float(C);
+      const f32x2 mean2 = pack2(mean, mean);
+      f32x2 q2 = pack2(0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+        if (i * 32 + lane < nvec) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            v[i][j] = fsub2(v[i][j], mean2);
+            q2 = ffma2(v[i][j], v[i][j], q2);
+          }
+        }
+      float q_lo, q_hi;
+      unpack2(q2, q_lo, q_hi);
+      const float rstd = rsqrtf(warp_sum(q_lo + q_hi) / float(C) + eps);
+      const f32x2 rstd2 = pack2(rstd, rstd);
 #pragma unroll
       for (int i = 0; i < NV; ++i) {
         const int vi = i * 32 + lane;
         if (vi < nvec) {
-          const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * vi), g1 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * vi + 1);
-          const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta) + 2 * vi), b1 = __ldg(reinterpret_cast<const float4*>(beta) + 2 * vi + 1);
-          const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-          const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+          // eight gains and eight offsets as four fp32 pairs each
+          const ulonglong2 g0 = __ldg(reinterpret_cast<const ulonglong2*>(gamma) + 2 * vi), g1 = __ldg(reinterpret_cast<const ulonglong2*>(gamma) + 2 * vi + 1);
+          const ulonglong2 b0 = __ldg(reinterpret_cast<const ulonglong2*>(beta) + 2 * vi), b1 = __ldg(reinterpret_cast<const ulonglong2*>(beta) + 2 * vi + 1);
+          const f32x2 g[4] = {g0.x, g0.y, g1.x, g1.y}, b[4] = {b0.x, b0.y, b1.x, b1.y};
+          uint32_t o[4];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) f[i][j] = f[i][j] * rstd * g[j] + b[j];
-          raw[i] = pack8(f[i]);
+          for (int j = 0; j < 4; ++j) {
+            float lo, hi;
+            unpack2(ffma2(fmul2(v[i][j], rstd2), g[j], b[j]), lo, hi);
+            o[j] = pack_bf16x2(lo, hi);
+          }
+          raw[i] = make_uint4(o[0], o[1], o[2], o[3]);
           if (kQuant) m2 = absmax8(m2, raw[i]);
           else reinterpret_cast<uint4*>(y + row * C)[vi] = raw[i];
         }
@@ -318,14 +352,12 @@ rows_stream_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
       for (int i = 0; i < NV; ++i) {
         const int vi = i * 32 + lane;
         if (vi < nvec) {
-          float f[8];
-          unpack8(raw[i], f);
-          qr[vi] = quant8(f, sc, inv_sc);
+          qr[vi] = quant8(raw[i], sc, inv_sc);
         }
       }
     }
   }
-  cp_async_wait<0>();
+  if (!kDirect) cp_async_wait<0>();
 }
 
 // Host side of rows_stream_kernel: picks the vector count, sizes the ring and the persistent grid.
@@ -334,28 +366,45 @@ int launch_stream_nv(const __nv_bfloat16* x, const float* gamma, const float* be
                      float* scale, long long rows, int C, float eps, cudaStream_t st) {
   auto kern = rows_stream_kernel<kNorm, kQuant, kGelu, NV, STAGES>;
   constexpr int kSmem = kWarpsPerBlock * STAGES * NV * 32 * 16;
-  static int per_sm = 0;                // resident blocks per SM of this instantiation (a device fact, asked once)
-  if (per_sm == 0) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) return SAMB_E_LAUNCH;
-    int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kWarpsPerBlock * 32, kSmem) != cudaSuccess || n < 1)
-      return SAMB_E_LAUNCH;
-    per_sm = n;
-  }
   long long blocks = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
-  const long long cap = (long long)sm_count() * per_sm;     // persistent: exactly one resident wave
-  if (blocks > cap) blocks = cap;
+  if (STAGES > 0) {                     // persistent: exactly one resident wave
+    static int per_sm = 0;              // resident blocks per SM of this instantiation (a device fact, asked once)
+    if (per_sm == 0) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) return SAMB_E_LAUNCH;
+      int n = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kWarpsPerBlock * 32, kSmem) != cudaSuccess || n < 1)
+        return SAMB_E_LAUNCH;
+      per_sm = n;
+    }
+    const long long cap = (long long)sm_count() * per_sm;
+    if (blocks > cap) blocks = cap;
+  } else if (blocks > 0x7fffffffLL) {
+    return SAMB_E_SHAPE;
+  }
   kern<<<unsigned(blocks), kWarpsPerBlock * 32, kSmem, st>>>(x, gamma, beta, y, yq, scale, rows, C, eps);
   return launch_status();
+}
+// SAMB_ROWS_DIRECT=1 in the environment (a tuning switch) makes the narrow-row kernels use plain loads, one
+// row per warp and a block per eight rows, instead of the persistent prefetching form.
+inline bool rows_direct() {
+  static int v = -1;
+  if (v < 0) v = getenv("SAMB_ROWS_DIRECT") != nullptr ? 1 : 0;
+  return v == 1;
 }
 template <bool kNorm, bool kQuant, bool kGelu>
 int launch_stream(const __nv_bfloat16* x, const float* gamma, const float* beta, __nv_bfloat16* y, int8_t* yq,
                   float* scale, long long rows, int C, float eps, cudaStream_t st) {
   const int nv = (C / 8 + 31) / 32;
-  if (nv <= 1) return launch_stream_nv<kNorm, kQuant, kGelu, 1, 4>(x, gamma, beta, y, yq, scale, rows, C, eps, st);
-  if (nv <= 3) return launch_stream_nv<kNorm, kQuant, kGelu, 3, 4>(x, gamma, beta, y, yq, scale, rows, C, eps, st);
-  if (nv <= 5) return launch_stream_nv<kNorm, kQuant, kGelu, 5, 4>(x, gamma, beta, y, yq, scale, rows, C, eps, st);
-  return launch_stream_nv<kNorm, kQuant, kGelu, 8, 3>(x, gamma, beta, y, yq, scale, rows, C, eps, st);
+  // measured on 131072 x 1280: quantise-only rows are fastest with plain loads (0.099 against 0.104 ms), LayerNorm
+  // + quantise with the prefetch ring (0.172 against 0.230 ms)
+#define SAMB_NV(NV, ST)                                                                                          \
+  return (rows_direct() || !kNorm) ? launch_stream_nv<kNorm, kQuant, kGelu, NV, 0>(x, gamma, beta, y, yq, scale, rows, C, eps, st) \
+                       : launch_stream_nv<kNorm, kQuant, kGelu, NV, ST>(x, gamma, beta, y, yq, scale, rows, C, eps, st)
+  if (nv <= 1) SAMB_NV(1, 4);
+  if (nv <= 3) SAMB_NV(3, 4);
+  if (nv <= 5) SAMB_NV(5, 4);
+  SAMB_NV(8, 3);
+#undef SAMB_NV
 }
 
 // Wide rows (C up to 3 * 256 * 8 = 6144): a 256-thread block per row, up to three 16-byte vectors per thread,
@@ -422,9 +471,7 @@ quant_rows_wide_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__
     for (int i = 0; i < 3; ++i) {
       const int vi = i * 256 + threadIdx.x;
       if (vi < nvec) {
-        float f[8];
-        unpack8(raw[i], f);
-        qr[vi] = quant8(f, sc, inv_sc);
+        qr[vi] = quant8(raw[i], sc, inv_sc);
       }
     }
   }
@@ -503,7 +550,9 @@ int launch_rows(const void* x, const float* gamma, const float* beta, void* y, i
   if (out_rows == 0) return SAMB_OK;
   const long long blocks = (out_rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
   if (blocks > 0x7fffffffLL) return SAMB_E_SHAPE;
-  if (window == 0)                     // raster order: the persistent prefetching kernel
+  // Raster order + int8 output: the persistent prefetching kernel (0.172 against 0.204 ms for 131072 x 1280).
+  // The bf16 form stays on row_kernel, which is the faster of the two there (0.141 against 0.149 ms).
+  if (window == 0 && (kQuant || getenv("SAMB_ROWS_STREAM") != nullptr))
     return launch_stream<kNorm, kQuant, false>(static_cast<const __nv_bfloat16*>(x), gamma, beta,
                                                static_cast<__nv_bfloat16*>(y), yq, scale, out_rows, C, eps,
                                                static_cast<cudaStream_t>(stream));
@@ -530,6 +579,15 @@ int launch_quant_rows(const void* x, int8_t* yq, float* scale, int64_t rows, int
   if (C <= 8 * 256) {
     if (gelu) return launch_stream<false, true, true>(xb, nullptr, nullptr, nullptr, yq, scale, rows, C, 0.f, st);
     return launch_stream<false, true, false>(xb, nullptr, nullptr, nullptr, yq, scale, rows, C, 0.f, st);
+  } else if (getenv("SAMB_WIDE_WARP") != nullptr) {
+    // tuning switch: a warp per row with 20 (24) 16-byte vectors per lane in flight (0.53 ms for 131072 x 5120
+    // against 0.43 ms for the block-per-row form below, which is the default)
+    if (C <= 20 * 256) {
+      if (gelu) return launch_stream_nv<false, true, true, 20, 0>(xb, nullptr, nullptr, nullptr, yq, scale, rows, C, 0.f, st);
+      return launch_stream_nv<false, true, false, 20, 0>(xb, nullptr, nullptr, nullptr, yq, scale, rows, C, 0.f, st);
+    }
+    if (gelu) return launch_stream_nv<false, true, true, 24, 0>(xb, nullptr, nullptr, nullptr, yq, scale, rows, C, 0.f, st);
+    return launch_stream_nv<false, true, false, 24, 0>(xb, nullptr, nullptr, nullptr, yq, scale, rows, C, 0.f, st);
   } else {
     constexpr int kStages = 3, kSmem = kStages * 3 * 256 * 16;
     static int per_sm[2] = {0, 0};      // resident blocks per SM (a device fact, asked once per variant)
