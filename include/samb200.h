@@ -147,6 +147,16 @@ int samb_attn_relpos_global_qkv(const void* qkv, const void* tab, int64_t ldt, i
                                 int64_t o_pitch, int B, int H, int N, int d, float scale, int32_t* status,
                                 void* stream);
 
+/* The same attention with the bias computed inside the kernel from the relative-position tables themselves:
+ * tables is bf16 [256, d] holding rel_pos_h (2*N/64 - 1 rows) from row 0 and rel_pos_w (127 rows) from row 128,
+ * zeros elsewhere.  Every CTA multiplies its 256 query rows by the table block on the tensor core before the key
+ * loop (q . rel_pos_h[m] and (q . rel_pos_w[m]) / scale, rounded to bf16 as a separately stored product would be)
+ * and reads rel_h[i, kh] = T_h[qh(i) - kh + N/64 - 1], rel_w[i, kw] = T_w[qw(i) - kw + 63] from shared memory, so
+ * no product tensor exists in global memory.  qkv / o as in samb_attn_relpos_global_qkv.
+ * ref: add_decomposed_rel_pos + get_rel_pos fused into the attention, modeling/image_encoder.py:305-372, 238-245. */
+int samb_attn_relpos_global_tables(const void* qkv, const void* tables, void* o, int64_t o_pitch, int B, int H, int N,
+                                   int d, float scale, int32_t* status, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Attention with the decomposed relative-position bias, windowed blocks: B independent windows of
  * window x window = N tokens (window must be 14), key j = kh*window + kw.

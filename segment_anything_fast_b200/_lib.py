@@ -33,6 +33,7 @@ SIGNATURES = {
     "samb_attn_relpos_global": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, _P, _P]),
     "samb_attn_relpos_global_qkv": (c_int, [_P, _P, c_int64, c_int, c_int, _P, c_int64, c_int, c_int, c_int, c_int,
                                             c_float, _P, _P]),
+    "samb_attn_relpos_global_tables": (c_int, [_P, _P, _P, c_int64, c_int, c_int, c_int, c_int, c_float, _P, _P]),
     "samb_attn_relpos_window": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, _P, _P]),
     "samb_attn_relpos_window_qkv": (c_int, [_P, _P, c_int64, c_int, c_int, _P, c_int64, c_int, c_int, c_int, c_int,
                                             c_int, c_float, _P, _P]),

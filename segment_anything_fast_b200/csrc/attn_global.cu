@@ -17,6 +17,13 @@
 //    per key tile (issuing a tcgen05.mma costs the issuing thread about as much whatever its size).
 //  * rel_h depends on the key row kh: two values per query row and key tile.  They are folded into
 //    the addend of the exp2 FMA, which costs nothing per element.
+// Where the bias comes from: as rel_h / rel_w tensors (mode 0), as table products computed by a separate GEMM
+// (mode 1), or (mode 2, what the encoder uses) from the relative-position tables themselves: the CTA multiplies
+// its 256 query rows by the [256 x d] table block [rel_pos_h | rel_pos_w] on the tensor core before the key loop
+// (two products of N = 256 into the logit / output columns, which are idle then), every thread rounds its row of
+// products to bf16 into shared memory (the P buffers, idle as well) and picks its 2 x 64 values
+// rel[k] = T[pos + S - 1 - k] from there, so neither the products nor get_rel_pos' gathered tables ever exist
+// in global memory.
 // Per tile: the 128x128 logits live in one TMEM buffer and are pulled into registers in one pass
 // (the buffer is handed back to the tensor core right away); P returns through shared memory in the
 // 128B-swizzled K-major layout; O accumulates in TMEM across key tiles.  The running maximum is only
@@ -45,7 +52,7 @@ struct AttnParams {
   long long ldt;                 // elements per token row of T
   int t_head_stride;             // columns per head in T
   int t_w_off;                   // column offset of the rel_pos_w products inside a head's slice
-  int rel_mode;
+  int rel_mode;                  // 0 tensors, 1 table products in global memory, 2 products computed by this kernel
   __nv_bfloat16* o;
   long long o_pitch;             // elements between consecutive output rows
   int o_head_stride;             // column offset per head in the output row
@@ -68,7 +75,7 @@ struct Smem {
   static constexpr int BYTES = OFF_BAR + 256 + 1024;
 };
 
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+__device__ __forceinline__ uint32_t bfpack2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
@@ -81,7 +88,8 @@ __device__ __forceinline__ float fast_exp2(float x) {
 template <int D>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                   const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmT,
+                   const AttnParams p) {
   using L = Smem<D>;
   constexpr int CH = L::CH;
   extern __shared__ uint8_t smem_raw[];
@@ -97,7 +105,8 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* s_free = s_full + 2;                // [2] tile t's threads hold the logits in registers
   uint64_t* p_full = s_free + 2;                // [2] P of tile t is in shared memory (and O rescaled)
   uint64_t* pv_done = p_full + 2;               // [2] P V of tile t finished: P buffer free, O stable
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+  uint64_t* t_full = pv_done + 2;               // mode 2: both tiles' table products are in TMEM
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(t_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -122,6 +131,7 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(q_full, 1);
+    mbar_init(t_full, 1);
     mbar_init(pro_done, 8);                     // one arrival per softmax warp
     for (int s = 0; s < KV_STAGES; ++s) {
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
@@ -133,6 +143,7 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+    if (p.rel_mode == 2) tma_prefetch_desc(&tmT);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
@@ -147,8 +158,10 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      mbar_expect_tx(q_full, CH * L::Q_CHUNK);
+      mbar_expect_tx(q_full, (p.rel_mode == 2 ? 2 : 1) * CH * L::Q_CHUNK);
       tma_load_3d(smem + L::OFF_Q, &tmQ, q_full, 0, rq + n0, 0);
+      // the [256 x d] table block, laid out like a 256-row Q block, parked in the (still idle) P buffers
+      if (p.rel_mode == 2) tma_load_3d(smem + L::OFF_P, &tmT, q_full, 0, 0, 0);
       uint32_t stage = 0, phase = 0;
       for (int j = 0; j < nblk; ++j) {
         uint8_t* sk = smem + L::OFF_KV + stage * 2 * L::KV_TILE;
@@ -176,7 +189,24 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       // V: MN-major 32B swizzle, column chunks 4096 B apart (LBO), 8-key groups 256 B apart (SBO)
       const uint64_t dv = make_smem_desc(smem_u32(smem + L::OFF_KV + L::KV_TILE), 4096, 256, kSwizzle32B);
       constexpr uint32_t kStageUnits = 2 * L::KV_TILE / 16;
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 2) && mbar_wait(pro_done, 0, abort_flag, p.status, 3);
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 2);
+      if (ok && p.rel_mode == 2) {
+        // T_t = Q_t * [rel_pos_h | rel_pos_w]^T, N = 256: tile A into columns 0..255, tile B into 256..511
+        tc_fence_after();
+        if (elect_one()) {
+          constexpr uint32_t idesc_t = make_idesc(kAccF32, kFmtBF16, kFmtBF16, BM, 256);
+          const uint64_t dt = make_smem_desc(smem_u32(smem + L::OFF_P), 16, 256, kSwizzle32B);
+#pragma unroll
+          for (int t = 0; t < 2; ++t)
+#pragma unroll
+            for (int c = 0; c < CH; ++c)
+              umma_f16_ss(tmem_base + t * 256, dq + t * (4096 / 16) + c * (L::Q_CHUNK / 16), dt + c * (L::Q_CHUNK / 16),
+                          idesc_t, c != 0);
+          tc_commit(t_full);
+        }
+        __syncwarp();
+      }
+      ok = ok && mbar_wait(pro_done, 0, abort_flag, p.status, 3);
 
       auto issue_s = [&](int t, int j) {         // S_t = [Q_t | relw_t] * [K_j | E]^T
         if (elect_one()) {
@@ -310,7 +340,9 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       };
       const __nv_bfloat16 *base_h, *base_w;
-      if (!rev) {
+      if (p.rel_mode == 2) {
+        base_h = base_w = nullptr;
+      } else if (!rev) {
         base_h = p.rel_h + ((long long)bh * p.N + n) * p.Sh;
         base_w = p.rel_w + ((long long)bh * p.N + n) * SW;
       } else {
@@ -318,8 +350,55 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         base_w = base_h + p.t_w_off;
       }
       uint32_t rw[32];
+      if (p.rel_mode == 2) {
+        // This row's 256 products sit in TMEM (tile A: columns 0..255, tile B: 256..511).  One half at a time
+        // (rel_pos_h, then rel_pos_w divided by scale): round to bf16, park the 128 values in this row's 256 bytes
+        // of its tile's P buffer (16-byte units XOR-swizzled by the row, so a warp's stores spread over the banks),
+        // and read rel[k] = T[pos + S - 1 - k] back two bytes at a time.
+        bool got = mbar_wait(t_full, 0, abort_flag, p.status, 12);
+        tc_fence_after();
+        uint8_t* srow = smem + L::OFF_P + (t * BM + i) * 256;
+        const float inv_s = 1.0f / p.scale;
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+          uint32_t tv[128];
+          const uint32_t ta = lane_addr + t * 256 + half * 128;
+          tmem_ld_32x32b_x32(ta, *reinterpret_cast<uint32_t(*)[32]>(&tv[0]));
+          tmem_ld_32x32b_x32(ta + 32, *reinterpret_cast<uint32_t(*)[32]>(&tv[32]));
+          tmem_ld_32x32b_x32(ta + 64, *reinterpret_cast<uint32_t(*)[32]>(&tv[64]));
+          tmem_ld_32x32b_x32(ta + 96, *reinterpret_cast<uint32_t(*)[32]>(&tv[96]));
+          tmem_ld_wait();
+          const float mul = half ? inv_s : 1.0f;
+#pragma unroll
+          for (int u = 0; u < 16; ++u) {
+            uint32_t w4[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              w4[q] = bfpack2(__uint_as_float(tv[u * 8 + 2 * q]) * mul, __uint_as_float(tv[u * 8 + 2 * q + 1]) * mul);
+            *reinterpret_cast<uint4*>(srow + ((u ^ (i & 15)) << 4)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+          }
+          const int pos = half ? qw : qh, count = half ? SW : p.Sh;
+          auto elem = [&](int k) -> uint32_t {            // rel[k], k < count, as bf16 bits
+            const int e = pos + count - 1 - k;
+            return *reinterpret_cast<const uint16_t*>(srow + (((e >> 3) ^ (i & 15)) << 4) + (e & 7) * 2);
+          };
+#pragma unroll
+          for (int q = 0; q < 32; ++q) {
+            uint32_t w = 0u;
+            if (2 * q < count && got) w = elem(2 * q) | (elem(2 * q + 1) << 16);
+            if (half) rw[q] = w;
+            else relh_loc[q] = w;
+          }
+        }
+        // tile A's rel_w operand columns (336..) lie inside tile B's product columns: nobody stores to tensor
+        // memory before every softmax thread has read its products
+        tc_fence_before();
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        tc_fence_after();
+      } else {
       load_row(base_w, qw, SW, rw);
       load_row(base_h, qh, p.Sh, relh_loc);
+      }
       uint8_t* e_row = smem + L::OFF_E + i * 128;
       uint32_t wpk[32];                                    // (rel_w[2k], rel_w[2k+1]) / scale as bf16 pairs: the A operand row
 #pragma unroll
@@ -329,7 +408,7 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int tt = 0; tt < 4; ++tt) {
           const int k0 = u * 8 + 2 * tt;
           const uint32_t pr = rw[u * 4 + tt];
-          wpk[u * 4 + tt] = pack2(__uint_as_float(pr << 16) * inv_scale, __uint_as_float(pr & 0xffff0000u) * inv_scale);
+          wpk[u * 4 + tt] = bfpack2(__uint_as_float(pr << 16) * inv_scale, __uint_as_float(pr & 0xffff0000u) * inv_scale);
           e[tt] = ((i & 63) == k0 ? 0x3F80u : 0u) | ((i & 63) == k0 + 1 ? 0x3F800000u : 0u);
         }
         const int phys = (u ^ (i & 7)) << 4;
@@ -403,7 +482,7 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           l_blk += e[q];
         }
         *reinterpret_cast<uint4*>(p_tile + (u >> 3) * 16384 + (((u & 7) ^ (i & 7)) << 4)) =
-            make_uint4(pack2(e[0], e[1]), pack2(e[2], e[3]), pack2(e[4], e[5]), pack2(e[6], e[7]));
+            make_uint4(bfpack2(e[0], e[1]), bfpack2(e[2], e[3]), bfpack2(e[4], e[5]), bfpack2(e[6], e[7]));
       }
       l_run += l_blk;
       tc_fence_before();
@@ -425,9 +504,9 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
         for (int q = 0; q < 16; ++q) f[q] = __uint_as_float(r[q]) * inv_l;
         *reinterpret_cast<uint4*>(orow + c * 16) =
-            make_uint4(pack2(f[0], f[1]), pack2(f[2], f[3]), pack2(f[4], f[5]), pack2(f[6], f[7]));
+            make_uint4(bfpack2(f[0], f[1]), bfpack2(f[2], f[3]), bfpack2(f[4], f[5]), bfpack2(f[6], f[7]));
         *reinterpret_cast<uint4*>(orow + c * 16 + 8) =
-            make_uint4(pack2(f[8], f[9]), pack2(f[10], f[11]), pack2(f[12], f[13]), pack2(f[14], f[15]));
+            make_uint4(bfpack2(f[8], f[9]), bfpack2(f[10], f[11]), bfpack2(f[12], f[13]), bfpack2(f[14], f[15]));
       }
     }
   }
@@ -442,8 +521,8 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
 template <int D>
 int launch_d(const void* q, const void* k, const void* v, long long rows, long long cols, long long pitch_elems,
-             const AttnParams& p, int BH, void* stream) {
-  CUtensorMap tm[3];
+             const AttnParams& p, int BH, void* stream, const void* tables = nullptr) {
+  CUtensorMap tm[4];
   const void* base[3] = {q, k, v};
   for (int t = 0; t < 3; ++t) {
     const uint64_t dims[3] = {16, uint64_t(rows), uint64_t(cols / 16)};
@@ -453,12 +532,21 @@ int launch_d(const void* q, const void* k, const void* v, long long rows, long l
                                 box, CU_TENSOR_MAP_SWIZZLE_32B))
       return e;
   }
+  tm[3] = tm[0];
+  if (tables != nullptr) {                       // [256 rows][D] table block, fetched like a 256-row Q block
+    const uint64_t dims[3] = {16, 256, uint64_t(D / 16)};
+    const uint64_t strides[3] = {2, uint64_t(D) * 2, 32};
+    const uint32_t box[3] = {16, 256u, uint32_t(D / 16)};
+    if (int e = make_tensor_map(&tm[3], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(tables), dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_32B))
+      return e;
+  }
   auto kern = attn_global_kernel<D>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<D>::BYTES) != cudaSuccess)
     return SAMB_E_LAUNCH;
   const long long grid = (long long)BH * (p.N / (2 * BM));
   if (grid > 0x7fffffffLL) return SAMB_E_SHAPE;
-  kern<<<unsigned(grid), NUM_THREADS, Smem<D>::BYTES, static_cast<cudaStream_t>(stream)>>>(tm[0], tm[1], tm[2], p);
+  kern<<<unsigned(grid), NUM_THREADS, Smem<D>::BYTES, static_cast<cudaStream_t>(stream)>>>(tm[0], tm[1], tm[2], tm[3], p);
   return launch_status();
 }
 
@@ -521,6 +609,30 @@ int samb_attn_relpos_global_qkv(const void* qkv, const void* tab, int64_t ldt, i
   const long long rows = 3LL * H * B * N;
   return d == 80 ? launch_d<80>(qkv, qkv, qkv, rows, d, d, p, B * H, stream)
                  : launch_d<64>(qkv, qkv, qkv, rows, d, d, p, B * H, stream);
+}
+
+int samb_attn_relpos_global_tables(const void* qkv, const void* tables, void* o, int64_t o_pitch, int B, int H, int N,
+                                   int d, float scale, int32_t* status, void* stream) {
+  using namespace samb;
+  if (!qkv || !tables || !o || !status) return SAMB_E_BADARG;
+  if (B <= 0 || H <= 0 || N <= 0) return SAMB_E_BADARG;
+  if ((d != 64 && d != 80) || N % 256 || N > 4096) return SAMB_E_SHAPE;
+  if (3LL * H * B * N > 0x7fffffffLL || o_pitch % 8 || o_pitch < (int64_t)H * d) return SAMB_E_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(tables) | reinterpret_cast<uintptr_t>(qkv)) & 15u)
+    return SAMB_E_ALIGN;
+  if (int e = check_device_arch()) return e;
+  AttnParams p{};
+  p.rel_mode = 2;
+  p.o = static_cast<__nv_bfloat16*>(o);
+  p.o_pitch = o_pitch;
+  p.o_head_stride = d;
+  p.qkv_fused = 1;
+  p.H = H; p.N = N; p.Sh = N / 64;
+  p.scale = scale;
+  p.status = status;
+  const long long rows = 3LL * H * B * N;
+  return d == 80 ? launch_d<80>(qkv, qkv, qkv, rows, d, d, p, B * H, stream, tables)
+                 : launch_d<64>(qkv, qkv, qkv, rows, d, d, p, B * H, stream, tables);
 }
 
 }  // extern "C"

@@ -291,6 +291,24 @@ def attn_relpos_global_qkv(qkv: torch.Tensor, tab: torch.Tensor, t_head_stride: 
     return out
 
 
+def attn_relpos_global_tables(qkv: torch.Tensor, tables: torch.Tensor, B: int, H: int, N: int, d: int,
+                              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Global-block attention over the head-major ``qkv [3H, B*N, d]`` buffer with the rel-pos bias computed inside
+    the kernel from ``tables [256, d]`` (rel_pos_h from row 0, rel_pos_w from row 128); returns ``[B*N, H*d]``."""
+    _need(qkv, torch.bfloat16, "qkv"); _need(tables, torch.bfloat16, "tables")
+    if not qkv.is_contiguous() or qkv.shape != (3 * H, B * N, d):
+        raise RuntimeError("qkv must be contiguous [3H, B*N, d]")
+    if not tables.is_contiguous() or tables.shape != (256, d):
+        raise RuntimeError("tables must be contiguous [256, d]")
+    if out is None:
+        out = torch.empty(B * N, H * d, dtype=torch.bfloat16, device=qkv.device)
+    st = status_word(qkv.device)
+    _lib.check(_lib.load().samb_attn_relpos_global_tables(
+        qkv.data_ptr(), tables.data_ptr(), out.data_ptr(), out.stride(0), B, H, N, d, float(d ** -0.5), st.data_ptr(),
+        _stream()), "samb_attn_relpos_global_tables")
+    return out
+
+
 def attn_relpos_window(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rel_h: torch.Tensor,
                        rel_w: torch.Tensor, scale: Optional[float] = None) -> torch.Tensor:
     """Windowed attention with rel-pos bias: q, k, v ``[B,H,196,d]``, rel_h / rel_w ``[B,H,196,14]``."""

@@ -85,6 +85,36 @@ def test_global_attention_fused_qkv_layout(ops, B, H, d):
     ops.check_status()
     assert (out - ref).abs().max().item() < 2e-2
     assert _cos(out, ref) > 0.999
+    # the same with the products computed inside the attention kernel from the tables (no product tensor at all)
+    fused = ops.attn_relpos_global_tables(qkv_hm, tables.cuda(), B, H, N, d).float().cpu()
+    ops.check_status()
+    print(f"in-kernel table products: max-abs vs oracle {(fused - ref).abs().max().item():.4f}, "
+          f"vs the stored-product path {(fused - out).abs().max().item():.5f}")
+    assert (fused - ref).abs().max().item() < 2e-2
+    assert _cos(fused, ref) > 0.999
+    assert (fused - out).abs().max().item() < 4e-3        # same roundings; only the accumulation order may differ
+
+
+@pytest.mark.parametrize("B,H,d,N", [(1, 2, 80, 1024), (2, 1, 64, 256)])
+def test_global_attention_in_kernel_tables_small_rasters(ops, B, H, d, N):
+    """Shorter rasters (16 and 4 rows of 64 tokens): the table block holds 2*N/64 - 1 rel_pos_h rows."""
+    S_h = N // 64
+    torch.manual_seed(N)
+    qkv = torch.empty(B * N, 3 * H * d).normal_(0.0, 1.0).bfloat16()
+    rph = torch.empty(2 * S_h - 1, d).normal_(0.0, 0.1).bfloat16()
+    rpw = torch.empty(127, d).normal_(0.0, 0.1).bfloat16()
+    t = qkv.float().reshape(B, N, 3, H, d).permute(2, 0, 3, 1, 4)
+    q, k, v = (t[i].reshape(B * H, N, d) for i in range(3))
+    rel_h, rel_w = eo.decomposed_rel_pos(q, rph.float(), rpw.float(), (S_h, 64))
+    ref = eo.attention_rel_h_rel_w(q, k, v, rel_h.bfloat16().float(), rel_w.bfloat16().float())
+    ref = ref.reshape(B, H, N, d).permute(0, 2, 1, 3).reshape(B * N, H * d)
+    tables = torch.zeros(256, d, dtype=torch.bfloat16)
+    tables[:2 * S_h - 1], tables[128:255] = rph, rpw
+    qkv_hm = qkv.reshape(B * N, 3 * H, d).permute(1, 0, 2).contiguous().cuda()
+    out = ops.attn_relpos_global_tables(qkv_hm, tables.cuda(), B, H, N, d).float().cpu()
+    ops.check_status()
+    assert (out - ref).abs().max().item() < 2e-2
+    assert _cos(out, ref) > 0.999
 
 
 @pytest.mark.parametrize("B,H,d,std", [(3, 2, 80, 0.5), (25, 4, 80, 1.0), (2, 3, 64, 1.0)])
