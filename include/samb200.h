@@ -185,6 +185,17 @@ int samb_attn_relpos_window_raster(const void* qkv, const void* qkv_bias, const 
                                    int t_head_stride, int t_w_off, void* o, int64_t o_pitch, int B, int H, int grid,
                                    int window, int d, float scale, int32_t* status, void* stream);
 
+/* The same with the bias computed inside the kernel from the relative-position tables: tables is bf16 [64, d]
+ * holding rel_pos_h (2*window - 1 rows) from row 0 and rel_pos_w from row 32, zeros elsewhere.  For every
+ * (window, head) the kernel multiplies the queries by the table block on the tensor core (q . rel_pos_h[m] and
+ * (q . rel_pos_w[m]) / scale, rounded to bf16 as a stored product would be) and every query row shifts its
+ * 2 x window values rel[k] = T[pos + window - 1 - k] out of the products in registers; no product tensor exists
+ * in global memory.  ref: add_decomposed_rel_pos + get_rel_pos, modeling/image_encoder.py:305-372, inside the
+ * windowed attention of :238-245. */
+int samb_attn_relpos_window_tables(const void* qkv, const void* qkv_bias, const void* tables, void* o, int64_t o_pitch,
+                                   int B, int H, int grid, int window, int d, float scale, int32_t* status,
+                                   void* stream);
+
 /* Head-major variants of the qkv projection: out is [N / head_dim][M][head_dim] (bf16), i.e. one
  * contiguous [M, head_dim] plane per (q|k|v, head) instead of M rows of N columns, so that the
  * attention kernels stream whole contiguous tiles.  Epilogue: + bias (may be NULL).  head_dim a

@@ -45,6 +45,7 @@ SIGNATURES = {
     "samb_gemm_i8_heads": (c_int, [_P, c_int64, _P, _P, c_int64, _P, _P, _P, c_int64, c_int, c_int, c_int, _P, _P]),
     "samb_attn_relpos_window_raster": (c_int, [_P, _P, _P, c_int64, c_int, c_int, _P, c_int64, c_int, c_int, c_int, c_int,
                                                c_int, c_float, _P, _P]),
+    "samb_attn_relpos_window_tables": (c_int, [_P, _P, _P, _P, c_int64, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P]),
     "samb_mask_stats": (c_int, [_P, c_int, c_int64, c_int, c_int, c_float, c_float, _P, _P, _P, _P, _P]),
     "samb_mask_rle": (c_int, [_P, c_int64, c_int, c_int, _P, _P, c_int, _P]),
     "samb_sp24_meta_bytes": (c_int64, [c_int, c_int]),

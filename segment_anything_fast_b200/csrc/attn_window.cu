@@ -14,7 +14,11 @@
 //    columns [112, 192) of the same tile.
 //  * rel_w rides on the tensor core: A = [Q | rel_w/scale (16 columns)], B = [K | E], E[j, j % WS] = 1.
 //  * rel_h is constant over runs of WS keys and is folded into the exp2 FMA addend.
-//  * The bias values of item k+1 are fetched into registers before the softmax of item k starts.
+//  * The bias values of item k+1 are fetched into registers before the softmax of item k starts (tensor / stored
+//    product sources).  With the tables themselves as the source (what the encoder uses), the tile's MMA warp first
+//    multiplies the tile's Q rows by the resident [64 x d] block [rel_pos_h | rel_pos_w] (N = 64, into the logit
+//    columns, which are idle then); every thread reads its 2 x 27 products from tensor memory and shifts out its
+//    2 x 14 values rel[k] = T[pos + 13 - k] in registers, so no product tensor exists in global memory.
 // Padded layouts (qkv_fused 0 / 1): zero-padded window tokens are ordinary rows of the padded qkv buffer;
 // rows N..207 of the K/V box belong to the next window and their probabilities are written as zero.
 // Raster layout (qkv_fused 2): q/k/v stay in raster token order and never hold pad tokens.  A window is
@@ -39,7 +43,7 @@ struct WinParams {
   const __nv_bfloat16* rel_w;
   const __nv_bfloat16* tab;      // mode 1: table products [W*N, ldt]
   long long ldt;
-  int t_head_stride, t_w_off, rel_mode;
+  int t_head_stride, t_w_off, rel_mode;   // rel_mode: 0 tensors, 1 stored table products, 2 products computed here
   __nv_bfloat16* o;
   long long o_pitch;
   int qkv_fused;                 // 0: q/k/v/o are [W*H*N, d]; 1: head-major qkv [3H][W*N][d], o rows are raster tokens
@@ -57,18 +61,23 @@ struct WinSmem {
   static constexpr int NK = (N + 15) / 16 * 16;      // keys rounded up to the MMA granule (208)
   static constexpr int CH = D / 16;
   static constexpr int KSTEPS = NK / 16;
-  static constexpr int Q_CHUNK = 256 * 32;           // 256 query rows per 16-column chunk
+  static constexpr int Q_CHUNK = NK * 32;            // query rows per 16-column chunk; tile 1's product reads up to
+                                                     // row 255, i.e. past the chunk: rows >= N are never stored
   static constexpr int KV_CHUNK = NK * 32;
   static constexpr int STAGE = CH * (Q_CHUNK + 2 * KV_CHUNK);   // Q | K | V of one item
   static constexpr int OFF_K = CH * Q_CHUNK;         // inside a stage
   static constexpr int OFF_V = OFF_K + CH * KV_CHUNK;
   static constexpr int OFF_RELW = STAGES * STAGE;    // [256][16] bf16, 32B swizzle (per item)
-  static constexpr int OFF_E = OFF_RELW + Q_CHUNK;   // [NK][16] bf16 one-hot (constant)
-  static constexpr int OFF_BAR = OFF_E + KV_CHUNK;
+  static constexpr int OFF_E = OFF_RELW + 256 * 32;  // [NK][16] bf16 one-hot (constant)
+  static constexpr int OFF_TAB = OFF_E + KV_CHUNK;   // [CH][64][16] bf16 table block [rel_pos_h | rel_pos_w], 32B swizzle
+  static constexpr int TAB_CHUNK = 64 * 32;
+  static constexpr int OFF_BAR = OFF_TAB + CH * TAB_CHUNK;
   static constexpr int OFF_PADTAB = OFF_BAR + 256;   // [3][N] key index of the i-th pad token per border-window kind
   static constexpr int BYTES = OFF_PADTAB + 3 * 256 + 1024;
   static_assert(N <= 256 && NK <= 256 && WS <= 16, "window too large for this kernel");
-  static_assert(STAGE % 1024 == 0 && NK / 2 <= kOCol && kOCol + D <= 256, "layout");
+  static_assert(STAGE % 256 == 0 && Q_CHUNK % 256 == 0 && NK / 2 <= kOCol && kOCol + D <= 256, "layout");
+  static_assert(CH * Q_CHUNK >= N * D * 2, "the output rows are staged in the Q region");
+  static_assert(BYTES <= 227 * 1024, "shared memory");
 };
 
 __device__ __forceinline__ uint32_t wpack2(float lo, float hi) {
@@ -82,10 +91,31 @@ __device__ __forceinline__ float wexp2(float x) {
 }
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
 
+// out[e] = v[s + WS - 1 - e], e < WS: the WS consecutive products T[pos .. pos + WS - 1] of a row, in key order
+// (rel[k] = T[pos + WS - 1 - k]).  A four-stage shifter on registers; s < 16.
+template <int WS>
+__device__ __forceinline__ void select_shifted(const uint32_t (&v)[32], int s, float (&out)[WS]) {
+  uint32_t a[24], b[20], c[18];
+  const bool s8 = s & 8, s4 = s & 4, s2 = s & 2, s1 = s & 1;
+#pragma unroll
+  for (int q = 0; q < 24; ++q) a[q] = s8 ? v[q + 8] : v[q];
+#pragma unroll
+  for (int q = 0; q < 20; ++q) b[q] = s4 ? a[q + 4] : a[q];
+#pragma unroll
+  for (int q = 0; q < 18; ++q) c[q] = s2 ? b[q + 2] : b[q];
+#pragma unroll
+  for (int e = 0; e < WS; ++e) {
+    const int q = WS - 1 - e;
+    out[e] = __uint_as_float(s1 ? c[q + 1] : c[q]);
+  }
+}
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
 template <int D, int WS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const WinParams p) {
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                   const __grid_constant__ CUtensorMap tmT, const WinParams p) {
   using L = WinSmem<D, WS>;
   constexpr int N = L::N, NK = L::NK, CH = L::CH;
   extern __shared__ uint8_t smem_raw[];
@@ -101,7 +131,9 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* s_done = bars + 14;     // [2][2]   logits product of tile t for items of parity k & 1 has read its Q rows:
                                     //          what the OTHER tile waits for before it stages output over them.  Two
                                     //          barriers per tile because a tile may be a whole item ahead of the other.
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  uint64_t* t_full = bars + 18;     // [2]      mode 2: the table products of tile t are in TMEM
+  uint64_t* tab_full = bars + 20;   //          mode 2: the table block is in shared memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   unsigned int* out_cnt = reinterpret_cast<unsigned int*>(tmem_slot + 2);   // [STAGES] softmax warps that staged their rows
 
@@ -116,9 +148,12 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_init(&pro_done[t], 4);
       mbar_init(&s_done[t * 2], 1); mbar_init(&s_done[t * 2 + 1], 1);
       mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 4); mbar_init(&o_full[t], 1); mbar_init(&t_free[t], 4);
+      mbar_init(&t_full[t], 1);
     }
+    mbar_init(tab_full, 1);
     fence_mbar_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmO);
+    if (p.rel_mode == 2) tma_prefetch_desc(&tmT);
   }
   if (p.qkv_fused == 2) {
     // rows N..NK-1 of every K / V chunk are never written by a copy in this mode: zero them once (their
@@ -153,6 +188,10 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
+      if (p.rel_mode == 2) {                         // the table block, once per CTA
+        mbar_expect_tx(tab_full, CH * L::TAB_CHUNK);
+        tma_load_3d(smem + L::OFF_TAB, &tmT, tab_full, 0, 0, 0);
+      }
       uint32_t stage = 0, phase = 0;
       for (int it = blockIdx.x; it < p.items; it += gridDim.x) {
         const int w = it / p.H, h = it - w * p.H;
@@ -201,11 +240,28 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // V: MN-major, column chunks KV_CHUNK apart (LBO), 8-key groups 256 B apart (SBO)
     const uint64_t dv0 = make_smem_desc(smem_u32(smem + L::OFF_V), L::KV_CHUNK, 256, kSwizzle32B);
     const uint32_t d_tmem = tmem_base + t * 256;
+    constexpr uint32_t idesc_t = make_idesc(kAccF32, kFmtBF16, kFmtBF16, 128, 64);
+    const uint64_t dtab = make_smem_desc(smem_u32(smem + L::OFF_TAB), 16, 256, kSwizzle32B);
     uint32_t stage = 0, phase = 0, k = 0;
     bool ok = true;
+    if (p.rel_mode == 2) ok = mbar_wait(tab_full, 0, abort_flag, p.status, 11);
     for (int it = blockIdx.x; ok && it < p.items; it += gridDim.x, ++k) {
       const uint32_t par = k & 1u;
       if (!(ok = mbar_wait(&full[stage], phase, abort_flag, p.status, 2))) break;
+      if (p.rel_mode == 2) {
+        // table products of this tile's queries into columns 0..63.  The tensor pipe runs this CTA's products in
+        // issue order, so the previous item's P V (which read P from these columns) is done by then; the
+        // previous output sits in columns kOCol.. and is not touched.
+        tc_fence_after();
+        if (elect_one()) {
+          const uint64_t dq = dq0 + stage * (L::STAGE / 16);
+#pragma unroll
+          for (int c = 0; c < CH; ++c)
+            umma_f16_ss(d_tmem, dq + (c * L::Q_CHUNK + t * 4096) / 16, dtab + c * (L::TAB_CHUNK / 16), idesc_t, c != 0);
+          tc_commit(&t_full[t]);
+        }
+        __syncwarp();
+      }
       if (!(ok = mbar_wait(&pro_done[t], par, abort_flag, p.status, 3))) break;
       if (!(ok = mbar_wait(&t_free[t], par ^ 1u, abort_flag, p.status, 4))) break;
       tc_fence_after();
@@ -315,7 +371,7 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int q = 0; q < 12; ++q) rawv[0][q] = rawv[1][q] = 0u;
 
     int it = blockIdx.x;
-    if (it < p.items) fetch_bias(it);
+    if (it < p.items && p.rel_mode != 2) fetch_bias(it);
     bool ok = true;
     for (uint32_t k = 0; ok && it < p.items; it += gridDim.x, ++k) {
       const uint32_t par = k & 1u;
@@ -336,13 +392,33 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           }
         }
         float rw[16];
-        uint32_t eh[WS], ew[WS];
-        bias_elems(0, sh_h, eh);
-        bias_elems(1, sh_w, ew);
+        if (p.rel_mode == 2) {
+          // this row's products with the tables are in columns 0..63 of the tile (rel_pos_h at 0, rel_pos_w at 32);
+          // rounded to bf16 as a stored product tensor would be, so that both sources give the same bits
+          ok = mbar_wait(&t_full[t], par, abort_flag, p.status, 12);
+          tc_fence_after();
+          uint32_t th[32], tw[32];
+          tmem_ld_32x32b_x32(lane_addr, th);
+          tmem_ld_32x32b_x32(lane_addr + 32, tw);
+          tmem_ld_wait();
+          tc_fence_before();                                     // the logits product overwrites these columns
+          float sel[WS];
+          select_shifted<WS>(th, qh & 15, sel);
 #pragma unroll
-        for (int q = 0; q < 16; ++q) rw[q] = q < WS ? bf16_bits_to_float(ew[q < WS ? q : 0]) * inv_scale : 0.f;
+          for (int q = 0; q < WS; ++q) bh[q] = round_bf16(sel[q]) * kLog2e;
+          select_shifted<WS>(tw, qw, sel);
+          const float inv_s = 1.0f / p.scale;
 #pragma unroll
-        for (int q = 0; q < WS; ++q) bh[q] = bf16_bits_to_float(eh[q]) * kLog2e;
+          for (int q = 0; q < 16; ++q) rw[q] = q < WS ? round_bf16(sel[q < WS ? q : 0] * inv_s) : 0.f;
+        } else {
+          uint32_t eh[WS], ew[WS];
+          bias_elems(0, sh_h, eh);
+          bias_elems(1, sh_w, ew);
+#pragma unroll
+          for (int q = 0; q < 16; ++q) rw[q] = q < WS ? bf16_bits_to_float(ew[q < WS ? q : 0]) * inv_scale : 0.f;
+#pragma unroll
+          for (int q = 0; q < WS; ++q) bh[q] = bf16_bits_to_float(eh[q]) * kLog2e;
+        }
         uint8_t* rrow = smem + L::OFF_RELW + n * 32;
         *reinterpret_cast<uint4*>(rrow + ((0 ^ sw) << 4)) =
             make_uint4(wpack2(rw[0], rw[1]), wpack2(rw[2], rw[3]), wpack2(rw[4], rw[5]), wpack2(rw[6], rw[7]));
@@ -351,7 +427,7 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (vy < WS || vx < WS) {
           // border window: pad tokens' K and V rows <- projection bias.  Both tile groups write both (the same
           // values), so neither tile's products depend on the other group's progress.
-          ok = mbar_wait(&full[k % STAGES], (k / STAGES) & 1u, abort_flag, p.status, 9);   // the zero fill has landed
+          ok = ok && mbar_wait(&full[k % STAGES], (k / STAGES) & 1u, abort_flag, p.status, 9);   // the zero fill has landed
           const int n_pad = vy * (WS - vx) + (WS - vy) * WS;
           const uint8_t* tabp = smem + L::OFF_PADTAB + (vy == WS ? 0 : (vx == WS ? 1 : 2)) * 256;
           uint8_t* stage_base = smem + (k % STAGES) * L::STAGE;
@@ -425,7 +501,7 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       // P V product and the output staging.  (Requested before the softmax they had to be spilled, and the spill
       // waited for the loads.)
       const int it_next = it + gridDim.x;
-      if (it_next < p.items) fetch_bias(it_next);
+      if (it_next < p.items && p.rel_mode != 2) fetch_bias(it_next);
 
       if (!(ok = mbar_wait(&o_full[t], par, abort_flag, p.status, 7))) break;
       tc_fence_after();
@@ -492,9 +568,9 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
 template <int D, int WS>
 int launch_window(const void* q, const void* k, const void* v, long long rows, long long cols, WinParams p,
-                  long long items, void* stream) {
+                  long long items, void* stream, const void* tables = nullptr) {
   using L = WinSmem<D, WS>;
-  CUtensorMap tmQ, tmK, tmV;
+  CUtensorMap tmQ, tmK, tmV, tmT;
   if (p.qkv_fused == 2) {
     // raster planes [3H * B][grid][grid][D]: one WS x WS box of 16 columns per copy
     const uint64_t g = uint64_t(p.grid);
@@ -508,7 +584,7 @@ int launch_window(const void* q, const void* k, const void* v, long long rows, l
   } else {
   const uint64_t dims[3] = {16, uint64_t(rows), uint64_t(cols / 16)};
   const uint64_t strides[3] = {2, uint64_t(cols) * 2, 32};
-  const uint32_t box_q[3] = {16, 256, uint32_t(D / 16)};
+  const uint32_t box_q[3] = {16, uint32_t(L::NK), uint32_t(D / 16)};
   const uint32_t box_kv[3] = {16, uint32_t(L::NK), uint32_t(D / 16)};
   if (int e = make_tensor_map(&tmQ, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box_q,
                               CU_TENSOR_MAP_SWIZZLE_32B))
@@ -537,13 +613,22 @@ int launch_window(const void* q, const void* k, const void* v, long long rows, l
                                 CU_TENSOR_MAP_SWIZZLE_NONE))
       return e;
   }
+  tmT = tmQ;
+  if (tables != nullptr) {                         // [64 rows][D]: rel_pos_h from row 0, rel_pos_w from row 32
+    const uint64_t dims[3] = {16, 64, uint64_t(D / 16)};
+    const uint64_t strides[3] = {2, uint64_t(D) * 2, 32};
+    const uint32_t box[3] = {16, 64u, uint32_t(D / 16)};
+    if (int e = make_tensor_map(&tmT, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(tables), dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_32B))
+      return e;
+  }
   auto kern = attn_window_kernel<D, WS>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES) != cudaSuccess)
     return SAMB_E_LAUNCH;
   if (items > 0x7fffffffLL) return SAMB_E_SHAPE;
   p.items = int(items);
   const long long grid = items < sm_count() ? items : sm_count();
-  kern<<<unsigned(grid), NUM_THREADS, L::BYTES, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmO, p);
+  kern<<<unsigned(grid), NUM_THREADS, L::BYTES, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmO, tmT, p);
   return launch_status();
 }
 
@@ -636,6 +721,34 @@ int samb_attn_relpos_window_raster(const void* qkv, const void* qkv_bias, const 
   p.status = status;
   return d == 80 ? launch_window<80, 14>(qkv, qkv, qkv, 0, d, p, W * H, stream)
                  : launch_window<64, 14>(qkv, qkv, qkv, 0, d, p, W * H, stream);
+}
+
+int samb_attn_relpos_window_tables(const void* qkv, const void* qkv_bias, const void* tables, void* o, int64_t o_pitch,
+                                   int B, int H, int grid, int window, int d, float scale, int32_t* status,
+                                   void* stream) {
+  using namespace samb;
+  if (!qkv || !qkv_bias || !tables || !o || !status) return SAMB_E_BADARG;
+  if (B <= 0 || H <= 0 || grid <= 0) return SAMB_E_BADARG;
+  if (window != 14 || (d != 64 && d != 80)) return SAMB_E_SHAPE;
+  const int nw = (grid + window - 1) / window;
+  const long long W = (long long)B * nw * nw;
+  if (3LL * H * B * grid * grid > 0x7fffffffLL || W * H > 0x7fffffffLL || o_pitch % 8 || o_pitch < (int64_t)H * d)
+    return SAMB_E_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(tables) | reinterpret_cast<uintptr_t>(qkv) |
+       reinterpret_cast<uintptr_t>(qkv_bias)) & 15u)
+    return SAMB_E_ALIGN;
+  if (int e = check_device_arch()) return e;
+  WinParams p{};
+  p.rel_mode = 2;
+  p.o = static_cast<__nv_bfloat16*>(o);
+  p.o_pitch = o_pitch;
+  p.qkv_fused = 2;
+  p.H = H; p.grid = grid; p.nw = nw; p.B = B; p.vlast = grid - (nw - 1) * window;
+  p.kv_bias = static_cast<const __nv_bfloat16*>(qkv_bias);
+  p.scale = scale;
+  p.status = status;
+  return d == 80 ? launch_window<80, 14>(qkv, qkv, qkv, 0, d, p, W * H, stream, tables)
+                 : launch_window<64, 14>(qkv, qkv, qkv, 0, d, p, W * H, stream, tables);
 }
 
 }  // extern "C"

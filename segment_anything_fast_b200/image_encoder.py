@@ -272,11 +272,10 @@ class ImageEncoderViT(nn.Module):
             wq = bw["qkv"]
             qkv = (ops.gemm_heads(xn, xs, wq["wq"], wq["ws"], wq["b"], d) if self.quant == "int8"
                    else ops.gemm_heads(xn, None, wq["w"], None, wq["b"], d))          # [3H, rows, d]
+            # the rel-pos bias comes out of the attention kernels' own products of q with the tables (bw["tab"])
             if ws:
-                tab = ops.relpos_table_products(qkv, bw["tab"], bw["tab_scale"], H)
-                o = ops.attn_relpos_window_raster(qkv, bw["qkv_b16"], tab, bw["T"], bw["t_w_off"], B, H, g, ws, d)
-                del tab
-            else:          # the bias comes out of the attention kernel's own products with the tables
+                o = ops.attn_relpos_window_tables(qkv, bw["qkv_b16"], bw["tab"], B, H, g, ws, d)
+            else:
                 o = ops.attn_relpos_global_tables(qkv, bw["tab"], B, H, g * g, d)
             del qkv, xn
             oa, os_ = self._act(o)

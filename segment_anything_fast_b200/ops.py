@@ -368,6 +368,26 @@ def attn_relpos_window_raster(qkv: torch.Tensor, qkv_bias: torch.Tensor, tab: to
     return out
 
 
+def attn_relpos_window_tables(qkv: torch.Tensor, qkv_bias: torch.Tensor, tables: torch.Tensor, B: int, H: int,
+                              grid: int, window: int, d: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``attn_relpos_window_raster`` with the rel-pos bias computed inside the kernel from ``tables [64, d]``
+    (rel_pos_h from row 0, rel_pos_w from row 32).  Returns raster-order ``[B*grid*grid, H*d]``."""
+    _need(qkv, torch.bfloat16, "qkv"); _need(tables, torch.bfloat16, "tables"); _need(qkv_bias, torch.bfloat16, "qkv_bias")
+    if not qkv.is_contiguous() or qkv.shape != (3 * H, B * grid * grid, d):
+        raise RuntimeError("qkv must be contiguous [3H, B*grid*grid, d]")
+    if not qkv_bias.is_contiguous() or qkv_bias.numel() != 3 * H * d:
+        raise RuntimeError("qkv_bias must be contiguous [3H*d]")
+    if not tables.is_contiguous() or tables.shape != (64, d):
+        raise RuntimeError("tables must be contiguous [64, d]")
+    if out is None:
+        out = torch.empty(B * grid * grid, H * d, dtype=torch.bfloat16, device=qkv.device)
+    st = status_word(qkv.device)
+    _lib.check(_lib.load().samb_attn_relpos_window_tables(
+        qkv.data_ptr(), qkv_bias.data_ptr(), tables.data_ptr(), out.data_ptr(), out.stride(0), B, H, grid, window, d,
+        float(d ** -0.5), st.data_ptr(), _stream()), "samb_attn_relpos_window_tables")
+    return out
+
+
 def gemm_heads(a: torch.Tensor, a_scale: Optional[torch.Tensor], w: torch.Tensor, w_scale: Optional[torch.Tensor],
                bias: Optional[torch.Tensor], head_dim: int) -> torch.Tensor:
     """qkv projection with a head-major result ``[N/head_dim, M, head_dim]`` (bf16).  ``a``/``w`` are bf16,

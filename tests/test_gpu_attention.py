@@ -198,3 +198,11 @@ def test_window_attention_raster_layout(ops, B, H, d, grid):
     print(f"raster window attention grid {grid}: max-abs {(out - ref).abs().max().item():.4f} cos {_cos(out, ref):.6f}")
     assert (out - ref).abs().max().item() < 2e-2
     assert _cos(out, ref) > 0.999
+    # the same with the products computed inside the attention kernel from the tables (no product tensor at all)
+    fused = ops.attn_relpos_window_tables(qkv_hm, bias.bfloat16().cuda(), tables.cuda(), B, H, grid, ws, d).float().cpu()
+    ops.check_status()
+    print(f"in-kernel table products: max-abs vs oracle {(fused - ref).abs().max().item():.4f}, "
+          f"vs the stored-product path {(fused - out).abs().max().item():.5f}")
+    assert (fused - ref).abs().max().item() < 2e-2
+    assert _cos(fused, ref) > 0.999
+    assert (fused - out).abs().max().item() < 4e-3        # same roundings; only the accumulation order may differ
