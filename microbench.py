@@ -89,6 +89,9 @@ def main():
     tp.add_argument("--rows", type=int, default=131072); tp.add_argument("--heads", type=int, default=16)
     tp.add_argument("--dim", type=int, default=80); tp.add_argument("--t", type=int, default=64)
     for p in (ag, aw):
+        p.add_argument("--tables", action="store_true",
+                       help="the encoder's form: head-major raster-order qkv of --batch images (64 x 64 tokens), rel-pos "
+                            "products computed in the kernel from the tables")
         p.add_argument("--arm", choices=["b200", "sdpa", "ref-triton"], default="b200",
                        help="b200: this library's kernel; sdpa: torch SDPA with the materialised [B,H,N,N] bias, the "
                             "reference's fallback (flash_4.py:368-370); ref-triton: the reference's own Triton kernel "
@@ -128,6 +131,14 @@ def main():
                    tflops=round(2.0 * M * N * K / ms / 1e9, 1))
     elif a.cmd == "attn-global":
         B, H, N, d = a.batch, a.heads, a.tokens, a.dim
+        if a.tables:
+            qkv = torch.randn(3 * H, B * N, d, device=dev).bfloat16()
+            tables = (torch.randn(256, d, device=dev) * 0.1).bfloat16()
+            y = torch.empty(B * N, H * d, device=dev, dtype=torch.bfloat16)
+            ms = _time(lambda: ops.attn_relpos_global_tables(qkv, tables, B, H, N, d, out=y), a.iters, a.warmup)
+            out.update(arm="b200-tables", shape=[B, H, N, d], ms=round(ms, 4), tflops=round(4.0 * B * H * N * N * d / ms / 1e9, 1))
+            print(json.dumps(out))
+            return
         q, k, v = (torch.randn(B, H, N, d, device=dev).bfloat16() for _ in range(3))
         rh = (torch.randn(B, H, N, N // 64, device=dev) * 0.5).bfloat16()
         rw = (torch.randn(B, H, N, 64, device=dev) * 0.5).bfloat16()
@@ -135,6 +146,16 @@ def main():
         out.update(arm=a.arm, shape=[B, H, N, d], ms=round(ms, 4), tflops=round(4.0 * B * H * N * N * d / ms / 1e9, 1))
     elif a.cmd == "attn-window":
         B, H, d = a.batch, a.heads, a.dim
+        if a.tables:                                       # B images: 25 windows each, gathered from raster order
+            qkv = torch.randn(3 * H, B * 4096, d, device=dev).bfloat16()
+            tables = (torch.randn(64, d, device=dev) * 0.1).bfloat16()
+            bias = torch.randn(3 * H * d, device=dev).bfloat16()
+            y = torch.empty(B * 4096, H * d, device=dev, dtype=torch.bfloat16)
+            ms = _time(lambda: ops.attn_relpos_window_tables(qkv, bias, tables, B, H, 64, 14, d, out=y), a.iters, a.warmup)
+            nbytes = 4 * B * 4096 * H * d * 2                                  # q, k, v in, o out (real tokens)
+            out.update(arm="b200-tables", shape=[B * 25, H, 196, d], ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1))
+            print(json.dumps(out))
+            return
         q, k, v = (torch.randn(B, H, 196, d, device=dev).bfloat16() for _ in range(3))
         rh = (torch.randn(B, H, 196, 14, device=dev) * 0.5).bfloat16()
         rw = (torch.randn(B, H, 196, 14, device=dev) * 0.5).bfloat16()

@@ -20,15 +20,21 @@ namespace {
 constexpr int BM = 128;                        // rows per CTA (256 per pair)
 constexpr int BN = 256;
 constexpr int SLAB_BYTES = 128;
-constexpr int STAGES = 6;
 constexpr int A_STAGE_BYTES = BM * SLAB_BYTES;          // 16 KiB: this CTA's rows of A
 constexpr int B_STAGE_BYTES = (BN / 2) * SLAB_BYTES;    // 16 KiB: this CTA's half of the W tile
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int NUM_ACC = 2;
 constexpr int TMEM_COLS = NUM_ACC * BN;
-constexpr int MAX_THREADS = 576;                // TMA warp, MMA warp, up to 16 epilogue warps
 constexpr int OUT_STAGE_BYTES = BM * 128;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_STAGE_BYTES + 2 * BN * 4 + 1024 + 256;
+// Operand ring and output staging share the shared memory.  bf16: 6 stages + 1 staging tile (a 256-wide tile
+// takes 2 x as many tensor-pipe cycles per output byte as in int8, the store is never the hold-up).  int8: a
+// stage holds twice the K depth, 5 are plenty, and the room goes to three staging tiles that rotate per
+// 64-column chunk, so that a chunk never waits for the previous chunk's store to drain.
+__host__ __device__ constexpr int pair_stages(bool int8) { return int8 ? 5 : 6; }
+__host__ __device__ constexpr int pair_out_bufs(bool int8) { return int8 ? 3 : 1; }
+__host__ __device__ constexpr int pair_smem_bytes(bool int8) {
+  return pair_stages(int8) * STAGE_BYTES + pair_out_bufs(int8) * OUT_STAGE_BYTES + 2 * BN * 4 + 1024 + 256;
+}
 
 struct PairParams {
   void* out;
@@ -73,10 +79,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   constexpr int EPI_THREADS = 32 * kEpiWarps;
   constexpr int CW = 64 / (kEpiWarps / 4);               // columns of a 64-column chunk per warp: 32 or 16
   constexpr int NV = CW / 8;                             // 16-byte output pieces per thread and chunk
+  constexpr int STAGES = pair_stages(kInt8);
+  constexpr int OUT_BUFS = pair_out_bufs(kInt8);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* stage_out = smem + STAGES * STAGE_BYTES;
-  float* s_bias = reinterpret_cast<float*>(stage_out + OUT_STAGE_BYTES);
+  uint8_t* stage_out0 = smem + STAGES * STAGE_BYTES;
+  float* s_bias = reinterpret_cast<float*>(stage_out0 + OUT_BUFS * OUT_STAGE_BYTES);
   float* s_wscale = s_bias + BN;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_wscale + BN);
   uint64_t* empty_bar = full_bar + STAGES;
@@ -185,7 +193,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int erow = int(lane_base) + lane;
     const int et = int(threadIdx.x) - 64;
     const uint32_t acc_empty0 = map_to_cta(&acc_empty[0], 0);        // the leader's barrier
-    uint32_t acc = 0, acc_phase = 0;
+    uint32_t acc = 0, acc_phase = 0, chunk_no = 0;
     for (long long tile = pair; tile < p.num_tiles; tile += num_pairs) {
       const int m0 = int(tile / p.tiles_n) * (2 * BM) + int(rank) * BM;
       const int n0 = int(tile % p.tiles_n) * BN;
@@ -203,7 +211,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (kInt8 && row_ok) a_scale = __ldg(p.a_scale + row);
       const __nv_bfloat16* res_row = nullptr;
       if (kRes && row_ok) res_row = p.residual + (row % p.res_rows) * p.ldr + n0 + qc * CW;
-#pragma unroll 1
+      // The chunk loop is software-pipelined: the tensor-memory load of chunk c + 1 is in flight while chunk c goes
+      // through the arithmetic, and the accumulator is handed back to the MMA warp as soon as its last chunk has
+      // been read (before that chunk's arithmetic and store).
+      uint32_t rbuf[2][CW];
+      if constexpr (CW == 32) tmem_ld_32x32b_x32(t_addr, rbuf[0]);
+      else tmem_ld_32x32b_x16(t_addr, rbuf[0]);
+#pragma unroll
       for (int c = 0; c < BN / 64; ++c) {
         const int col0 = n0 + c * 64;
         uint4 rv[NV];
@@ -214,10 +228,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (row_ok) rv[u] = __ldg(reinterpret_cast<const uint4*>(res_row + c * 64) + u);
           }
         }
-        uint32_t r[CW];
-        if constexpr (CW == 32) tmem_ld_32x32b_x32(t_addr + c * 64, r);
-        else tmem_ld_32x32b_x16(t_addr + c * 64, r);
-        tmem_ld_wait();
+        tmem_ld_wait();                                  // chunk c is in rbuf[c & 1]
+        if (c + 1 < BN / 64) {
+          if constexpr (CW == 32) tmem_ld_32x32b_x32(t_addr + (c + 1) * 64, rbuf[(c + 1) & 1]);
+          else tmem_ld_32x32b_x16(t_addr + (c + 1) * 64, rbuf[(c + 1) & 1]);
+        } else {
+          tc_fence_before();                             // every column of this accumulator has been read
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(acc_empty0 + acc * 8);
+        }
+        const uint32_t(&r)[CW] = rbuf[c & 1];
         uint4 packed[NV];
 #pragma unroll
         for (int u = 0; u < NV; ++u) {
@@ -236,8 +256,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           packed[u] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
                                  pack_bf16x2(v[6], v[7]));
         }
-        if (et == 0) tma_store_wait_read<0>();
-        epi_sync<EPI_THREADS>();
+        // Staging tile of this chunk.  With one tile, wait until the previous store has read it; with several,
+        // thread 0 already made sure (after issuing the previous store) that all but the latest store have
+        // drained, and the barrier below (of the previous chunk) published that.
+        uint8_t* stage_out = stage_out0 + (OUT_BUFS > 1 ? int(chunk_no % OUT_BUFS) : 0) * OUT_STAGE_BYTES;
+        if (OUT_BUFS == 1) {
+          if (et == 0) tma_store_wait_read<0>();
+          epi_sync<EPI_THREADS>();
+        }
         if (p.hm_group == 0) {
           uint8_t* srow = stage_out + erow * 128;
 #pragma unroll
@@ -265,11 +291,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           }
           tma_store_commit();
+          if (OUT_BUFS > 1) tma_store_wait_read<1>();    // every store but this one has read its staging tile
         }
+        ++chunk_no;
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(acc_empty0 + acc * 8);
       if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
     }
     if (et == 0) tma_store_wait_all<0>();
@@ -361,7 +386,8 @@ int launch_gemm_pair(bool int8, const void* A, int64_t lda, const void* W, int64
   p.num_tiles = ((M + 2 * BM - 1) / (2 * BM)) * p.tiles_n;
   p.hm_group = head_dim / 16;
 
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+  const int smem_bytes = pair_smem_bytes(int8);
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess)
     return SAMB_E_LAUNCH;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
@@ -372,7 +398,7 @@ int launch_gemm_pair(bool int8, const void* A, int64_t lda, const void* W, int64
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cfg.blockDim = dim3(int8 ? 64 + 32 * 16 : 64 + 32 * 8);
-  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = static_cast<cudaStream_t>(stream);
   cfg.gridDim = dim3(unsigned(sm_count() & ~1));
   static int cached_clusters[2][8] = {};                  // co-resident pairs per kernel variant (0 = not asked yet)

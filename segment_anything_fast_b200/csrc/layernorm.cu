@@ -136,31 +136,37 @@ row_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
     if (vi < nvec) raw[i] = xr[vi];
   }
 
+  // Statistics with one accumulator for the even and one for the odd elements of the lane: the same additions, in
+  // the same order, as the packed-pair arithmetic of rows_stream_kernel, so both kernels give the same bits.
   float mean = 0.f, rstd = 1.f;
   if (kNorm) {
-    float s = 0.f;
+    float s0 = 0.f, s1 = 0.f;
 #pragma unroll
     for (int i = 0; i < kMaxVec; ++i)
       if (i * 32 + lane < nvec) {
         float f[8];
         unpack8(raw[i], f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) s += f[j];
-      }
-    mean = warp_sum(s) / float(C);
-    float q = 0.f;
-#pragma unroll
-    for (int i = 0; i < kMaxVec; ++i)
-      if (i * 32 + lane < nvec) {
-        float f[8];
-        unpack8(raw[i], f);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float d = f[j] - mean;
-          q += d * d;
+        for (int j = 0; j < 4; ++j) {
+          s0 = __fadd_rn(s0, f[2 * j]);
+          s1 = __fadd_rn(s1, f[2 * j + 1]);
         }
       }
-    rstd = rsqrtf(warp_sum(q) / float(C) + eps);
+    mean = warp_sum(__fadd_rn(s0, s1)) / float(C);
+    float q0 = 0.f, q1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i)
+      if (i * 32 + lane < nvec) {
+        float f[8];
+        unpack8(raw[i], f);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float d0 = __fsub_rn(f[2 * j], mean), d1 = __fsub_rn(f[2 * j + 1], mean);
+          q0 = fmaf(d0, d0, q0);
+          q1 = fmaf(d1, d1, q1);
+        }
+      }
+    rstd = rsqrtf(warp_sum(__fadd_rn(q0, q1)) / float(C) + eps);
   }
 
   // normalised (bf16-rounded) values of vector i
@@ -172,7 +178,7 @@ row_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
       const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
       const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] = (f[j] - mean) * rstd * g[j] + b[j];
+      for (int j = 0; j < 8; ++j) f[j] = fmaf(__fmul_rn(__fsub_rn(f[j], mean), rstd), g[j], b[j]);
     }
   };
 
