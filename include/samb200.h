@@ -115,6 +115,19 @@ int samb_gemm_i8(const int8_t* Aq, int64_t lda, const float* a_scale, const int8
                  const float* w_scale, const float* bias, const void* residual, int64_t ldr, int64_t res_rows,
                  void* out, int64_t ldo, int64_t M, int N, int K, int epilogue, int32_t* status, void* stream);
 
+/* The int8 Linear of samb_gemm_i8 (epilogue: SAMB_EPI_BIAS and / or SAMB_EPI_GELU only) that also hands its
+ * output on as the next int8 Linear's input: out[M, N] (bf16, as samb_gemm_i8 writes it) plus its per-row symmetric
+ * int8 quantisation yq[M, N] (contiguous rows of N), y_scale[M] = max(absmax_m, 1e-5) / 127, the same values
+ * samb_quant_rows_i8 gives on `out`.  The GEMM epilogue leaves every row's |max| in row_absmax_scratch (M floats of
+ * caller-owned scratch memory, any contents on entry: it is cleared first) through atomic maxima, so the
+ * quantisation is a streaming pass with no reduction.  Two calls sharing one scratch array must not overlap.
+ * ref: lin1 -> act -> lin2 of MLPBlock with torchao's dynamically quantised Linears, modeling/common.py:21-26,
+ * experiments/eval_combo.py:357-360 (lin2's activation-side quantisation of lin1's output). */
+int samb_gemm_i8_requant(const int8_t* Aq, int64_t lda, const float* a_scale, const int8_t* Wq, int64_t ldw,
+                         const float* w_scale, const float* bias, void* out, int64_t ldo, int8_t* yq, float* y_scale,
+                         float* row_absmax_scratch, int64_t M, int N, int K, int epilogue, int32_t* status,
+                         void* stream);
+
 /* Channel LayerNorm of x[tokens, C] (token-major rows, bf16): each row is normalised over its C
  * channels in fp32.  With to_nchw != 0 the result is stored as out[tokens/hw, C, hw] (hw multiple
  * of 32), else in the input layout.

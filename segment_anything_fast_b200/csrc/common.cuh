@@ -500,7 +500,13 @@ int check_device_arch();   // 0 if the current device is sm_100, SAMB_E_ARCH oth
 int launch_gemm_pair(bool int8, const void* A, int64_t lda, const void* W, int64_t ldw, const float* a_scale,
                      const float* w_scale, const float* bias, const void* residual, int64_t ldr, int64_t res_rows,
                      void* out, int64_t ldo, int64_t M, int N, int K, int epilogue, int head_dim, int32_t* status,
-                     void* stream);
+                     void* stream, float* row_absmax = nullptr);
+// The int8 Linear GEMM (gemm_tc.cu) that also leaves, through atomic maxima, the largest |bf16(out[m, n])| of every
+// output row m in row_absmax[m] (float, non-negative, zeroed by the caller beforehand).
+int launch_gemm_i8_rowmax(const int8_t* Aq, int64_t lda, const float* a_scale, const int8_t* Wq, int64_t ldw,
+                          const float* w_scale, const float* bias, const void* residual, int64_t ldr, int64_t res_rows,
+                          void* out, int64_t ldo, int64_t M, int N, int K, int epilogue, int32_t* status, void* stream,
+                          float* row_absmax);
 int sm_count();
 
 inline int launch_status() {

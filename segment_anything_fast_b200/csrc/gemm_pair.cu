@@ -12,6 +12,7 @@
 // exist in both CTAs and receive one commit each from the leader, `acc_empty` lives in the leader and
 // counts the epilogue warps of both CTAs.  No copy is multicast.
 #include "common.cuh"
+#include "rowquant.cuh"
 
 namespace samb {
 
@@ -42,6 +43,7 @@ struct PairParams {
   const __nv_bfloat16* residual;
   const float* a_scale;
   const float* w_scale;
+  float* row_absmax;             // optional: atomic maximum of |bf16(out[m, :])| per row (see launch_gemm_i8_rowmax)
   int* status;
   long long M;
   long long ldr, res_rows;
@@ -214,6 +216,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       // The chunk loop is software-pipelined: the tensor-memory load of chunk c + 1 is in flight while chunk c goes
       // through the arithmetic, and the accumulator is handed back to the MMA warp as soon as its last chunk has
       // been read (before that chunk's arithmetic and store).
+      __nv_bfloat162 m2 = __floats2bfloat162_rn(0.f, 0.f);   // running |max| of this row's outputs in this tile
       uint32_t rbuf[2][CW];
       if constexpr (CW == 32) tmem_ld_32x32b_x32(t_addr, rbuf[0]);
       else tmem_ld_32x32b_x16(t_addr, rbuf[0]);
@@ -255,6 +258,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           packed[u] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
                                  pack_bf16x2(v[6], v[7]));
+          if (p.row_absmax != nullptr) m2 = absmax8(m2, packed[u]);
         }
         // Staging tile of this chunk.  With one tile, wait until the previous store has read it; with several,
         // thread 0 already made sure (after issuing the previous store) that all but the latest store have
@@ -295,6 +299,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         ++chunk_no;
       }
+      // non-negative floats order like their bit patterns: one integer atomic per row and tile
+      if (p.row_absmax != nullptr && row_ok)
+        atomicMax(reinterpret_cast<int*>(p.row_absmax + row), __float_as_int(absmax_fold(m2)));
       if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
     }
     if (et == 0) tma_store_wait_all<0>();
@@ -331,7 +338,7 @@ PairFn pick_pair(int epi) {
 int launch_gemm_pair(bool int8, const void* A, int64_t lda, const void* W, int64_t ldw, const float* a_scale,
                      const float* w_scale, const float* bias, const void* residual, int64_t ldr, int64_t res_rows,
                      void* out, int64_t ldo, int64_t M, int N, int K, int epilogue, int head_dim, int32_t* status,
-                     void* stream) {
+                     void* stream, float* row_absmax) {
   if (N % BN || M < 8 * 2 * BM) return SAMB_E_SHAPE;
   auto kern = int8 ? pick_pair<true>(epilogue) : pick_pair<false>(epilogue);
   if (kern == nullptr) return SAMB_E_SHAPE;
@@ -374,6 +381,7 @@ int launch_gemm_pair(bool int8, const void* A, int64_t lda, const void* W, int64
   p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.a_scale = a_scale;
   p.w_scale = w_scale;
+  p.row_absmax = row_absmax;
   p.status = status;
   p.M = M;
   p.ldr = ldr;

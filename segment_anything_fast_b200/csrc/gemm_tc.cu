@@ -10,6 +10,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "rowquant.cuh"
 
 namespace samb {
 
@@ -38,6 +39,7 @@ struct GemmParams {
   const __nv_bfloat16* residual;
   const float* a_scale;
   const float* w_scale;
+  float* row_absmax;             // optional: atomic maximum of |bf16(out[m, :])| per row (see launch_gemm_i8_rowmax)
   int* status;
   long long M;
   long long ldo, ldr, res_rows;
@@ -287,6 +289,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       } else {
         float a_scale = 1.0f;
         if (kInt8 && row_ok) a_scale = __ldg(p.a_scale + row);
+        __nv_bfloat162 m2 = __floats2bfloat162_rn(0.f, 0.f);   // running |max| of this row's outputs in this tile
         const __nv_bfloat16* res_row = nullptr;
         if (kRes && row_ok) res_row = p.residual + (row % p.res_rows) * p.ldr + n0 + half * 32;
 #pragma unroll 1
@@ -322,6 +325,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             packed[u] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
                                    pack_bf16x2(v[6], v[7]));
+            if (p.row_absmax != nullptr) m2 = absmax8(m2, packed[u]);
           }
           // staging tile of this chunk: the one after the ring, or (out_ring) one of four, the last three carved
           // out of the unused last pipeline stage; then only the tile's first chunk waits for earlier stores
@@ -363,6 +367,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tma_store_commit();
           }
         }
+        // non-negative floats order like their bit patterns: one integer atomic per row and tile
+        if (p.row_absmax != nullptr && row_ok)
+          atomicMax(reinterpret_cast<int*>(p.row_absmax + row), __float_as_int(absmax_fold(m2)));
       }
       tc_fence_before();
       mbar_arrive_warp(&acc_empty[acc]);
@@ -405,7 +412,8 @@ inline int kmul_of(bool int8) { return int8 ? 16 : 8; }
 int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ldw, const float* a_scale,
                 const float* w_scale, const float* bias, const void* residual, int64_t ldr, int64_t res_rows,
                 void* out, int64_t ldo, int64_t M, int N, int K, int epilogue, int32_t* status, void* stream,
-                int batch = 1, int a_col_stride = 0, int o_col_stride = 0, int64_t a_row_stride = 0, int head_dim = 0) {
+                int batch = 1, int a_col_stride = 0, int o_col_stride = 0, int64_t a_row_stride = 0, int head_dim = 0,
+                float* row_absmax = nullptr) {
   if (A == nullptr || W == nullptr || out == nullptr || status == nullptr) return SAMB_E_BADARG;
   if (M < 0 || N <= 0 || K <= 0 || batch <= 0) return SAMB_E_BADARG;
   if (epilogue == EPI_COLSCALE) {
@@ -440,7 +448,7 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
   const bool epi_bound = int8 && K < 2048 && (epilogue & SAMB_EPI_GELU) && getenv("SAMB_GELU_SINGLE_CTA") != nullptr;
   if (!raw && batch == 1 && epilogue != EPI_COLSCALE && !epi_bound && getenv("SAMB_GEMM_SINGLE_CTA") == nullptr) {
     const int e = launch_gemm_pair(int8, A, lda, W, ldw, a_scale, w_scale, bias, residual, ldr, res_rows, out, ldo, M, N, K,
-                                   epilogue, head_dim, status, stream);
+                                   epilogue, head_dim, status, stream, row_absmax);
     if (e != SAMB_E_SHAPE) return e;
   }
 
@@ -469,6 +477,7 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
   p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.a_scale = a_scale;
   p.w_scale = w_scale;
+  p.row_absmax = row_absmax;
   p.status = status;
   p.M = M;
   p.ldo = ldo;
@@ -540,6 +549,15 @@ int launch_gemm(bool int8, const void* A, int64_t lda, const void* W, int64_t ld
 }
 
 }  // namespace
+
+int launch_gemm_i8_rowmax(const int8_t* Aq, int64_t lda, const float* a_scale, const int8_t* Wq, int64_t ldw,
+                          const float* w_scale, const float* bias, const void* residual, int64_t ldr, int64_t res_rows,
+                          void* out, int64_t ldo, int64_t M, int N, int K, int epilogue, int32_t* status, void* stream,
+                          float* row_absmax) {
+  if (epilogue & SAMB_EPI_RAW) return SAMB_E_BADARG;
+  return launch_gemm(true, Aq, lda, Wq, ldw, a_scale, w_scale, bias, residual, ldr, res_rows, out, ldo, M, N, K, epilogue,
+                     status, stream, 1, 0, 0, 0, 0, row_absmax);
+}
 }  // namespace samb
 
 extern "C" {

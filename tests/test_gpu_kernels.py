@@ -301,6 +301,30 @@ def test_gelu_quant_rows_matches_oracle(ops, rows, C):
     assert (d != 0).float().mean().item() < 1e-3
 
 
+@pytest.mark.parametrize("M,N,K,gelu", [(4096 + 100, 512, 1280, True), (300, 160, 160, True), (2048, 5120, 1280, True),
+                                        (1000, 640, 320, False)])
+def test_gemm_i8_requant_equals_gemm_then_row_quantisation(ops, M, N, K, gelu):
+    """The re-quantising Linear (row maxima from the GEMM epilogue's atomics, streaming quantisation): its bf16
+    output is the plain int8 GEMM's, and its int8 rows / scales are what the row quantiser gives on that output,
+    bit for bit; on CTA pairs (first and third shape) and on the single-CTA kernel, and twice in a row (the scratch
+    is cleared inside the call)."""
+    g = torch.Generator().manual_seed(M + N)
+    x = _bf16(torch.randn(M, K, generator=g))
+    w = torch.randn(N, K, generator=g) * 0.05
+    b = torch.randn(N, generator=g) * 0.1
+    xq, sx = ops.quant_rows_i8(x.cuda())
+    wq, sw = qo.quantize_rows_absmax(w)
+    plain = ops.gemm_i8(xq, sx, wq.cuda(), sw.cuda(), b.cuda(), gelu=gelu)
+    q_ref, s_ref = ops.quant_rows_i8(plain)
+    for _ in range(2):
+        yq, ys, out = ops.gemm_i8_requant(xq, sx, wq.cuda(), sw.cuda(), b.cuda(), gelu=gelu)
+        ops.check_status()
+        assert torch.equal(out, plain)
+        assert torch.equal(ys, s_ref) and torch.equal(yq, q_ref)
+    oq, os_ = qo.quantize_rows_absmax(plain.float().cpu())              # and the oracle's quantiser on the same rows
+    assert torch.equal(yq.cpu(), oq) and torch.equal(ys.cpu(), os_)
+
+
 # ------------------------------------------------------------------ CTA-pair GEMM
 @pytest.mark.parametrize("M,N,K", [(4096 + 100, 512, 1280), (8192, 1280, 5120), (2048, 256, 64)])
 def test_gemm_pair_kernel_equals_single_cta_kernel(ops, M, N, K, monkeypatch):
