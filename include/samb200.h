@@ -128,6 +128,23 @@ int samb_gemm_i8_requant(const int8_t* Aq, int64_t lda, const float* a_scale, co
                          float* row_absmax_scratch, int64_t M, int N, int K, int epilogue, int32_t* status,
                          void* stream);
 
+/* samb_gemm_i8_requant for callers that cannot allocate device memory (no counterpart in the reference).
+ * Some hosts of this library have nowhere to get scratch from: a plug-in running inside an inference server whose
+ * memory pool is closed to it, a process whose device memory was handed out in full at start-up, a real-time loop
+ * that must keep away from the allocator (cudaMalloc synchronises the device).  They pass only inputs and
+ * outputs; the one-float-per-row scratch is an array inside the library's own device image instead
+ * (1 MiB, held by every GPU that loads the library until the process exits).
+ *  - At most samb_gemm_i8_requant_static_max_rows() rows (262144); more returns SAMB_E_SHAPE.
+ *  - The first call on a device looks up the array's device address (with that device current).  Make that first
+ *    call outside any stream capture.
+ *  - Every call on a device uses the same array (it is cleared at the start of each call), so two calls that may
+ *    overlap on the GPU (different streams) race; serialise them.
+ *  - Nothing is allocated or freed, by this entry point or by anything it calls. */
+int64_t samb_gemm_i8_requant_static_max_rows(void);
+int samb_gemm_i8_requant_static(const int8_t* Aq, int64_t lda, const float* a_scale, const int8_t* Wq, int64_t ldw,
+                                const float* w_scale, const float* bias, void* out, int64_t ldo, int8_t* yq,
+                                float* y_scale, int64_t M, int N, int K, int epilogue, int32_t* status, void* stream);
+
 /* Channel LayerNorm of x[tokens, C] (token-major rows, bf16): each row is normalised over its C
  * channels in fp32.  With to_nchw != 0 the result is stored as out[tokens/hw, C, hw] (hw multiple
  * of 32), else in the input layout.

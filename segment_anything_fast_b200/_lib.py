@@ -31,6 +31,9 @@ SIGNATURES = {
                              c_int, c_int, c_int, _P, _P]),
     "samb_gemm_i8_requant": (c_int, [_P, c_int64, _P, _P, c_int64, _P, _P, _P, c_int64, _P, _P, _P, c_int64, c_int,
                                      c_int, c_int, _P, _P]),
+    "samb_gemm_i8_requant_static_max_rows": (c_int64, []),
+    "samb_gemm_i8_requant_static": (c_int, [_P, c_int64, _P, _P, c_int64, _P, _P, _P, c_int64, _P, _P, c_int64, c_int,
+                                            c_int, c_int, _P, _P]),
     "samb_layernorm2d_nchw": (c_int, [_P, _P, _P, _P, c_int64, c_int, c_int, c_float, c_int, _P]),
     "samb_attn_relpos_global": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, _P, _P]),
     "samb_attn_relpos_global_qkv": (c_int, [_P, _P, c_int64, c_int, c_int, _P, c_int64, c_int, c_int, c_int, c_int,

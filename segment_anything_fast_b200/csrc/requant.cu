@@ -3,7 +3,9 @@
 // streaming kernel then turns the bf16 rows into int8 with the scale that maximum gives (the arithmetic of
 // quant_rows_kernel, bit for bit).  Used for mlp.lin1 -> GELU -> quantise -> mlp.lin2 in the int8 encoder.
 //
-// The scratch is one float per output row, supplied by the caller.
+// The scratch is one float per output row.  samb_gemm_i8_requant takes it from the caller;
+// samb_gemm_i8_requant_static keeps it in an array that is part of this library's device image, for callers that
+// have no way to allocate device memory.
 #include "common.cuh"
 #include "rowquant.cuh"
 
@@ -42,6 +44,32 @@ quant_given_absmax_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, co
   for (; i < nvec; i += 32) qr[i] = quant8(__ldcs(xr + i), sc, inv_sc);
 }
 
+// ---- scratch that needs no allocation --------------------------------------------------------------------------
+// One float per output row, for products of up to kStaticRows rows (1 MiB).  The array belongs to the library's
+// device image: every GPU on which the library's kernels get loaded holds it until the process exits.
+constexpr long long kStaticRows = 262144;
+static __device__ __align__(256) float g_row_absmax_static[kStaticRows];
+
+// Device address of the array on the current device.  In host code the array's name is only a handle for the
+// runtime, not an address a kernel could use, so the address is asked for once per device, with that device
+// current, and kept.  cudaGetSymbolAddress allocates nothing; it may have to load this library's device code on
+// the device first, which is why the first call per device belongs before any stream capture.
+int static_scratch(float** out) {
+  static float* addr[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return SAMB_E_LAUNCH;
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_row_absmax_static) != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return SAMB_E_LAUNCH;
+    }
+    addr[dev] = static_cast<float*>(p);
+  }
+  *out = addr[dev];
+  return SAMB_OK;
+}
+
 int requant(const int8_t* Aq, int64_t lda, const float* a_scale, const int8_t* Wq, int64_t ldw, const float* w_scale,
             const float* bias, void* out, int64_t ldo, int8_t* yq, float* y_scale, float* row_absmax, int64_t M, int N,
             int K, int epilogue, int32_t* status, void* stream) {
@@ -77,6 +105,18 @@ int samb_gemm_i8_requant(const int8_t* Aq, int64_t lda, const float* a_scale, co
                          void* stream) {
   return samb::requant(Aq, lda, a_scale, Wq, ldw, w_scale, bias, out, ldo, yq, y_scale, row_absmax_scratch, M, N, K,
                        epilogue, status, stream);
+}
+
+int64_t samb_gemm_i8_requant_static_max_rows(void) { return samb::kStaticRows; }
+
+int samb_gemm_i8_requant_static(const int8_t* Aq, int64_t lda, const float* a_scale, const int8_t* Wq, int64_t ldw,
+                                const float* w_scale, const float* bias, void* out, int64_t ldo, int8_t* yq,
+                                float* y_scale, int64_t M, int N, int K, int epilogue, int32_t* status, void* stream) {
+  if (M > samb::kStaticRows) return SAMB_E_SHAPE;       // more rows than the built-in scratch holds
+  float* scratch = nullptr;
+  if (int e = samb::static_scratch(&scratch)) return e;
+  return samb::requant(Aq, lda, a_scale, Wq, ldw, w_scale, bias, out, ldo, yq, y_scale, scratch, M, N, K, epilogue,
+                       status, stream);
 }
 
 }  // extern "C"
