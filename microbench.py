@@ -70,6 +70,8 @@ def main():
     g.add_argument("--epilogue", choices=["none", "bias", "gelu", "residual"], default="bias")
     g.add_argument("--int8", action="store_true")
     g.add_argument("--sp24", action="store_true", help="int8 with a 2:4-sparse weight on the sparse tensor-core path")
+    g.add_argument("--requant", action="store_true",
+                   help="int8 product + per-row re-quantisation of its output (row maxima from the GEMM epilogue)")
     ag = sub.add_parser("attn-global")
     ag.add_argument("--batch", type=int, default=8); ag.add_argument("--heads", type=int, default=16)
     ag.add_argument("--tokens", type=int, default=4096); ag.add_argument("--dim", type=int, default=80)
@@ -119,6 +121,8 @@ def main():
                 w.view(N, K // 4, 4)[:, :, 2:] = 0               # any 2:4 pattern times the same
                 wc, meta = ops.pack_sp24(w)
                 fn = lambda: ops.gemm_i8_sp24(x, sx, wc, meta, sw, bias, res, gelu=a.epilogue == "gelu", out=y)
+            elif a.requant:
+                fn = lambda: ops.gemm_i8_requant(x, sx, w, sw, bias, gelu=a.epilogue == "gelu", out=y)
             else:
                 fn = lambda: ops.gemm_i8(x, sx, w, sw, bias, res, gelu=a.epilogue == "gelu", out=y)
         else:
