@@ -275,6 +275,13 @@ int samb_relpos_table_products(const void* q_planes, const void* tables, const f
  * ref: PatchEmbed.forward, modeling/image_encoder.py:398-406. */
 int samb_patch_rows(const void* x, void* a, int B, int Cin, int grid, int patch, void* stream);
 
+/* samb_patch_rows on the raw pixels: x[B, 3, grid*patch, grid*patch] uint8 -> the same patch rows holding
+ * bf16((x - mean[c]) / std[c]) (mean / std: HOST arrays of 3 floats), i.e. Sam.preprocess' normalisation, the cast to
+ * the model dtype and the im2col of the patch embedding in one pass; no normalised copy of the image exists.
+ * patch multiple of 16.  ref: modeling/sam.py:164-168, predictor.py:88-90, modeling/image_encoder.py:398-406. */
+int samb_patch_rows_u8(const uint8_t* x, void* a, int B, int Cin, int grid, int patch, const float* mean_host,
+                       const float* std_host, void* stream);
+
 /* x[tokens, C] (token-major raster of grid x grid per image) -> a[tokens, 9*C]: the 3x3 neighbourhood
  * [ky][kx][c] of every token with zeros outside the raster (padding 1), the GEMM operand of the
  * neck's second convolution.  ref: nn.Conv2d(256, 256, 3, padding=1), modeling/image_encoder.py:97-103. */

@@ -44,6 +44,7 @@ SIGNATURES = {
                                             c_int, c_float, _P, _P]),
     "samb_normalize_u8": (c_int, [_P, _P, c_int, c_int, c_int, c_int, ctypes.POINTER(c_float), ctypes.POINTER(c_float), _P]),
     "samb_patch_rows": (c_int, [_P, _P, c_int, c_int, c_int, c_int, _P]),
+    "samb_patch_rows_u8": (c_int, [_P, _P, c_int, c_int, c_int, c_int, ctypes.POINTER(c_float), ctypes.POINTER(c_float), _P]),
     "samb_conv3x3_rows": (c_int, [_P, _P, c_int64, c_int, c_int, _P]),
     "samb_relpos_table_products": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int, c_int, c_int, _P, _P]),
     "samb_gemm_bf16_heads": (c_int, [_P, c_int64, _P, c_int64, _P, _P, c_int64, c_int, c_int, c_int, _P, _P]),

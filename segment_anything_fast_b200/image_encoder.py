@@ -249,19 +249,39 @@ class ImageEncoderViT(nn.Module):
 
     @torch.no_grad()
     def forward(self, x: torch.Tensor, taps: Optional[dict] = None) -> torch.Tensor:
+        """``x [B, C, S, S]`` normalised pixels in the model's dtype (the reference's call).  A device-side timeout
+        of a kernel's bounded wait is recorded in the per-device status word; callers that want to know call
+        ``ops.check_status()`` after their own synchronisation."""
+        self._check_input(x)
+        self.prepare()
+        rows = ops.patch_rows(x.to(torch.bfloat16).contiguous(), self.patch_size)
+        return self._encode_rows(rows, x.shape[0], taps).to(x.dtype)
+
+    @torch.no_grad()
+    def forward_u8(self, images_u8: torch.Tensor, pixel_mean, pixel_std, taps: Optional[dict] = None) -> torch.Tensor:
+        """Raw ``uint8 [B, 3, S, S]`` pixels in, bf16 embeddings out: ``Sam.preprocess``' normalisation
+        (sam.py:164-168) and the cast to the model dtype (predictor.py:88-90) happen inside the patch-embedding
+        gather, bit for bit what ``forward((x - mean) / std)`` computes, without a normalised copy of the image."""
+        self._check_input(images_u8)
+        if images_u8.dtype != torch.uint8:
+            raise RuntimeError("forward_u8 expects uint8 pixels")
+        self.prepare()
+        rows = ops.patch_rows_u8(images_u8.contiguous(), self.patch_size, pixel_mean, pixel_std)
+        return self._encode_rows(rows, images_u8.shape[0], taps)
+
+    def _check_input(self, x: torch.Tensor) -> None:
         if not x.is_cuda:
             raise RuntimeError("ImageEncoderViT (B200): input must be a CUDA tensor; there is no CPU path")
         if x.dim() != 4 or x.shape[2] != self.img_size or x.shape[3] != self.img_size:
             raise RuntimeError(f"expected [B, C, {self.img_size}, {self.img_size}] input")
-        self.prepare()
+
+    def _encode_rows(self, rows: torch.Tensor, B: int, taps: Optional[dict] = None) -> torch.Tensor:
+        """Patch rows ``[B*g*g, 3*P*P]`` (bf16) -> embeddings ``[B, out_chans, g, g]`` (bf16)."""
         pk = self._packed
-        in_dtype = x.dtype
-        B = x.shape[0]
         g = self.img_size // self.patch_size
         C, H = self.embed_dim, self.num_heads
         d = C // H
         M = B * g * g
-        rows = ops.patch_rows(x.to(torch.bfloat16).contiguous(), self.patch_size)
         cur = ops.gemm_bf16(rows, pk["pe_w"], pk["pe_b"], pk["pos"])
         del rows
         if taps is not None:
@@ -298,4 +318,4 @@ class ImageEncoderViT(nn.Module):
         y = ops.layernorm2d(y, pk["neck1"][0], pk["neck1"][1], g * g, pk["neck1"][2], to_nchw=False)
         y = ops.gemm_bf16(ops.conv3x3_rows(y, g), pk["neck2_w"])
         y = ops.layernorm2d(y, pk["neck3"][0], pk["neck3"][1], g * g, pk["neck3"][2], to_nchw=True)
-        return y.view(B, self.out_chans, g, g).to(in_dtype)
+        return y.view(B, self.out_chans, g, g)

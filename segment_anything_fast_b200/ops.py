@@ -476,6 +476,24 @@ def patch_rows(x: torch.Tensor, patch: int, out: Optional[torch.Tensor] = None) 
     return out
 
 
+def patch_rows_u8(x: torch.Tensor, patch: int, mean, std, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """uint8 NCHW image batch ``[B,3,S,S]`` -> normalised bf16 patch rows ``[B*(S/patch)^2, 3*patch*patch]``
+    (``(x - mean[c]) / std[c]``, then the gather of ``patch_rows``) in one pass."""
+    import ctypes
+    _need(x, torch.uint8, "x")
+    if x.dim() != 4 or not x.is_contiguous() or x.shape[1] != 3 or x.shape[2] != x.shape[3] or x.shape[2] % patch:
+        raise RuntimeError("x must be a contiguous square [B,3,S,S] uint8 batch whose side is a multiple of the patch size")
+    B, Cin, S, _ = x.shape
+    grid = S // patch
+    if out is None:
+        out = torch.empty(B * grid * grid, Cin * patch * patch, dtype=torch.bfloat16, device=x.device)
+    m = (ctypes.c_float * 3)(*[float(v) for v in mean])
+    s = (ctypes.c_float * 3)(*[float(v) for v in std])
+    _lib.check(_lib.load().samb_patch_rows_u8(x.data_ptr(), out.data_ptr(), B, Cin, grid, patch, m, s, _stream()),
+               "samb_patch_rows_u8")
+    return out
+
+
 def conv3x3_rows(x: torch.Tensor, grid: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Token rows ``[tokens, C]`` -> 3x3 neighbourhood rows ``[tokens, 9*C]`` (zero padding 1)."""
     _need(x, torch.bfloat16, "x")

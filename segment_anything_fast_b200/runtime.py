@@ -37,7 +37,7 @@ class EncoderSession:
         self.host_in = torch.empty(batch, 3, S, S, dtype=torch.uint8).pin_memory()
         self.host_out = torch.empty(batch, oc, g, g, dtype=torch.bfloat16).pin_memory()
         self.dev_in = torch.empty(batch, 3, S, S, dtype=torch.uint8, device=self.device)
-        self.dev_norm = torch.empty(batch, 3, S, S, dtype=torch.bfloat16, device=self.device)
+        self.dev_norm = None       # normalised bf16 copy of a batch: only for patch sizes the fused gather does not cover
         # host copy of the device status word, refreshed with every download: a bounded wait that ran out
         # inside a kernel must surface as an exception, not as silently wrong embeddings
         self._host_status = torch.zeros(1, dtype=torch.int32).pin_memory()
@@ -57,8 +57,21 @@ class EncoderSession:
         """uint8 ``[B,3,S,S]`` on the device -> embeddings ``[B,out_chans,S/16,S/16]`` (bf16, device)."""
         if self.graph and images_u8.shape[0] == self.batch:
             return self._replay(images_u8)
-        x = ops.normalize_u8(images_u8, self.mean, self.std, out=self.dev_norm[: images_u8.shape[0]])
+        return self._run(images_u8)
+
+    def _run(self, images_u8: torch.Tensor) -> torch.Tensor:
+        """Normalisation + encoder.  With 16-pixel-aligned patches the normalisation rides on the patch-embedding
+        gather (``forward_u8``); otherwise a normalised bf16 copy of the batch goes through ``forward``."""
+        if self.encoder.patch_size % 16 == 0:
+            return self.encoder.forward_u8(images_u8, self.mean, self.std)
+        x = ops.normalize_u8(images_u8, self.mean, self.std, out=self._norm_buffer()[: images_u8.shape[0]])
         return self.encoder(x)
+
+    def _norm_buffer(self) -> torch.Tensor:
+        if self.dev_norm is None:
+            S = self.host_in.shape[-1]
+            self.dev_norm = torch.empty(self.batch, 3, S, S, dtype=torch.bfloat16, device=self.device)
+        return self.dev_norm
 
     def _replay(self, dev_in: torch.Tensor) -> torch.Tensor:
         """Replay (recording it on first use) the graph that reads ``dev_in``; its output tensor is reused by
@@ -70,7 +83,7 @@ class EncoderSession:
             # the old packed buffers, so it is recorded again
             ent = None
         if ent is None:
-            run = lambda: self.encoder(ops.normalize_u8(dev_in, self.mean, self.std, out=self.dev_norm))
+            run = lambda: self._run(dev_in)
             main = torch.cuda.current_stream(self.device)
             side = torch.cuda.Stream(self.device)
             side.wait_stream(main)

@@ -40,6 +40,33 @@ def test_normalize_u8_is_bit_exact(ops, B, S):
     assert torch.equal(got.view(torch.int16), want.view(torch.int16))
 
 
+@pytest.mark.parametrize("B,S,P", [(2, 1024, 16), (1, 256, 32), (3, 64, 16)])
+def test_patch_rows_from_uint8_is_bit_exact(ops, B, S, P):
+    """``samb_patch_rows_u8`` (normalisation inside the patch-embedding gather) against the two-step path
+    normalise -> gather, and against the oracle's normalisation: the same bits."""
+    u8 = eo.seeded_images_u8(B, seed=54, img_size=S)
+    fused = ops.patch_rows_u8(u8.cuda(), P, eo.PIXEL_MEAN, eo.PIXEL_STD)
+    two_step = ops.patch_rows(ops.normalize_u8(u8.cuda(), eo.PIXEL_MEAN, eo.PIXEL_STD), P)
+    assert torch.equal(fused, two_step)
+    want = eo.seeded_images(B, seed=54, img_size=S).to(torch.bfloat16)            # [B, 3, S, S]
+    g = S // P
+    rows = want.reshape(B, 3, g, P, g, P).permute(0, 2, 4, 1, 3, 5).reshape(B * g * g, 3 * P * P)
+    assert torch.equal(fused.cpu().view(torch.int16), rows.contiguous().view(torch.int16))
+
+
+def test_forward_u8_equals_forward_on_normalised_pixels(ops):
+    from test_gpu_encoder import build_encoder
+    sd = eo.seeded_state_dict(TINY, seed=1)
+    enc = build_encoder(TINY, sd)
+    u8 = eo.seeded_images_u8(2, seed=55)
+    a = enc.forward_u8(u8.cuda(), eo.PIXEL_MEAN, eo.PIXEL_STD)
+    b = enc(eo.seeded_images(2, seed=55).to(torch.bfloat16).cuda())
+    ops.check_status()
+    assert a.dtype == torch.bfloat16 and torch.equal(a, b)
+    with pytest.raises(RuntimeError):
+        enc.forward_u8(u8.cuda().float(), eo.PIXEL_MEAN, eo.PIXEL_STD)
+
+
 @pytest.mark.parametrize("graph", [False, True])
 def test_encoder_session_uint8_against_oracle(ops, graph):
     """The benchmark's timed path, host uint8 pixels -> ``EncoderSession.encode`` -> host embeddings, against the
