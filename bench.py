@@ -119,7 +119,7 @@ class LaunchProfiler:
     def begin(self, name, args):
         if name in ("samb_abi_version", "samb_error_string", "samb_decode_status", "samb_sp24_meta_bytes"):
             return None                                        # host-only helpers: nothing is launched
-        self.launches += 3 if name == "samb_gemm_i8_requant" else 1     # clear + GEMM + streaming quantisation
+        self.launches += 3 if "requant" in name else 1                    # clear + GEMM + streaming quantisation
         pos = self.GEMMS.get(name)
         if pos is None:
             return None

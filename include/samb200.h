@@ -128,6 +128,14 @@ int samb_gemm_i8_requant(const int8_t* Aq, int64_t lda, const float* a_scale, co
                          float* row_absmax_scratch, int64_t M, int N, int K, int epilogue, int32_t* status,
                          void* stream);
 
+/* The same for a 2:4-compressed weight (samb_pack_sp24 output; arguments as samb_gemm_i8_sp24): the sparse kernel's
+ * epilogue stages its tile token-major, and one thread per token row leaves that row's |max| in the scratch.
+ * ref: as above, for the pruned mlp.lin1 of sparse.py:28-32. */
+int samb_gemm_i8_sp24_requant(const int8_t* Xq, int64_t ldx, const float* x_scale, const int8_t* Wc, int64_t ldc,
+                              const uint8_t* meta, const float* w_scale, const float* bias, void* out, int64_t ldo,
+                              int8_t* yq, float* y_scale, float* row_absmax_scratch, int64_t T, int N, int K,
+                              int epilogue, int32_t* status, void* stream);
+
 /* samb_gemm_i8_requant for callers that cannot allocate device memory (no counterpart in the reference).
  * Some hosts of this library have nowhere to get scratch from: a plug-in running inside an inference server whose
  * memory pool is closed to it, a process whose device memory was handed out in full at start-up, a real-time loop

@@ -31,6 +31,8 @@ SIGNATURES = {
                              c_int, c_int, c_int, _P, _P]),
     "samb_gemm_i8_requant": (c_int, [_P, c_int64, _P, _P, c_int64, _P, _P, _P, c_int64, _P, _P, _P, c_int64, c_int,
                                      c_int, c_int, _P, _P]),
+    "samb_gemm_i8_sp24_requant": (c_int, [_P, c_int64, _P, _P, c_int64, _P, _P, _P, _P, c_int64, _P, _P, _P, c_int64,
+                                          c_int, c_int, c_int, _P, _P]),
     "samb_gemm_i8_requant_static_max_rows": (c_int64, []),
     "samb_gemm_i8_requant_static": (c_int, [_P, c_int64, _P, _P, c_int64, _P, _P, _P, c_int64, _P, _P, c_int64, c_int,
                                             c_int, c_int, _P, _P]),

@@ -507,6 +507,11 @@ int launch_gemm_i8_rowmax(const int8_t* Aq, int64_t lda, const float* a_scale, c
                           const float* w_scale, const float* bias, const void* residual, int64_t ldr, int64_t res_rows,
                           void* out, int64_t ldo, int64_t M, int N, int K, int epilogue, int32_t* status, void* stream,
                           float* row_absmax);
+// The 2:4-sparse int8 Linear GEMM (gemm_sp24.cu); row_absmax as in launch_gemm_i8_rowmax (may be null).
+int launch_gemm_i8_sp24(const int8_t* Xq, int64_t ldx, const float* x_scale, const int8_t* Wc, int64_t ldc,
+                        const uint8_t* meta, const float* w_scale, const float* bias, const void* residual,
+                        int64_t ldr, int64_t res_rows, void* out, int64_t ldo, int64_t T, int N, int K, int epilogue,
+                        int32_t* status, void* stream, float* row_absmax);
 int sm_count();
 
 inline int launch_status() {

@@ -16,6 +16,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "rowquant.cuh"
 
 namespace samb {
 
@@ -50,6 +51,7 @@ struct SpParams {
   const __nv_bfloat16* residual;
   const float* a_scale;
   const float* w_scale;
+  float* row_absmax;            // optional: atomic maximum of |bf16(out[t, :])| per token row
   int* status;
   long long T;                  // tokens
   long long ldo, ldr, res_rows;
@@ -298,6 +300,19 @@ gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       if (!kRaw) {
         fence_proxy_async_smem();
         epi_sync();
+        if (p.row_absmax != nullptr && et < TT && t0 + et < p.T) {
+          // the staged tile is token-major: thread et takes token row et of both 64-channel halves (channels past
+          // N were computed from zero weights and a zero bias: they hold 0) and leaves its |max| with one atomic
+          __nv_bfloat162 m2 = __floats2bfloat162_rn(0.f, 0.f);
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            const uint8_t* rowp = s_tile + hf * OUT_HALF_BYTES + et * 128;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)      // physical unit order follows the row's swizzle: bank-conflict free
+              m2 = absmax8(m2, *reinterpret_cast<const uint4*>(rowp + ((u ^ (et & 7)) << 4)));
+          }
+          atomicMax(reinterpret_cast<int*>(p.row_absmax + t0 + et), __float_as_int(absmax_fold(m2)));
+        }
         if (et == 0) {
           tma_store_2d(&tmOut, s_tile, ct * TC, int(t0));                          // clipped at T and N
           if (ct * TC + 64 < p.N) tma_store_2d(&tmOut, s_tile + OUT_HALF_BYTES, ct * TC + 64, int(t0));
@@ -429,11 +444,13 @@ int samb_pack_sp24(const int8_t* Wq, int64_t ldw, int N, int K, int8_t* Wc, int6
   return samb::launch_status();
 }
 
-int samb_gemm_i8_sp24(const int8_t* Xq, int64_t ldx, const float* x_scale, const int8_t* Wc, int64_t ldc,
-                      const uint8_t* meta, const float* w_scale, const float* bias, const void* residual,
-                      int64_t ldr, int64_t res_rows, void* out, int64_t ldo, int64_t T, int N, int K, int epilogue,
-                      int32_t* status, void* stream) {
-  using namespace samb;
+}  // extern "C"
+
+namespace samb {
+int launch_gemm_i8_sp24(const int8_t* Xq, int64_t ldx, const float* x_scale, const int8_t* Wc, int64_t ldc,
+                        const uint8_t* meta, const float* w_scale, const float* bias, const void* residual,
+                        int64_t ldr, int64_t res_rows, void* out, int64_t ldo, int64_t T, int N, int K, int epilogue,
+                        int32_t* status, void* stream, float* row_absmax) {
   if (Xq == nullptr || Wc == nullptr || meta == nullptr || out == nullptr || status == nullptr) return SAMB_E_BADARG;
   if (T < 0 || N <= 0 || K <= 0) return SAMB_E_BADARG;
   if (epilogue & ~(SAMB_EPI_BIAS | SAMB_EPI_GELU | SAMB_EPI_RESIDUAL | SAMB_EPI_RAW)) return SAMB_E_BADARG;
@@ -458,6 +475,7 @@ int samb_gemm_i8_sp24(const int8_t* Xq, int64_t ldx, const float* x_scale, const
   p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.a_scale = x_scale;
   p.w_scale = w_scale;
+  p.row_absmax = row_absmax;
   p.status = status;
   p.T = T;
   p.ldo = ldo;
@@ -546,6 +564,17 @@ int samb_gemm_i8_sp24(const int8_t* Xq, int64_t ldx, const float* x_scale, const
   const long long grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
   kern<<<dim3(unsigned(grid)), dim3(NUM_THREADS), SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tmW, tmX, tmE, tmOut, tmRes, p);
   return launch_status();
+}
+}  // namespace samb
+
+extern "C" {
+
+int samb_gemm_i8_sp24(const int8_t* Xq, int64_t ldx, const float* x_scale, const int8_t* Wc, int64_t ldc,
+                      const uint8_t* meta, const float* w_scale, const float* bias, const void* residual,
+                      int64_t ldr, int64_t res_rows, void* out, int64_t ldo, int64_t T, int N, int K, int epilogue,
+                      int32_t* status, void* stream) {
+  return samb::launch_gemm_i8_sp24(Xq, ldx, x_scale, Wc, ldc, meta, w_scale, bias, residual, ldr, res_rows, out, ldo, T,
+                                   N, K, epilogue, status, stream, nullptr);
 }
 
 }  // extern "C"

@@ -70,9 +70,10 @@ int static_scratch(float** out) {
   return SAMB_OK;
 }
 
-int requant(const int8_t* Aq, int64_t lda, const float* a_scale, const int8_t* Wq, int64_t ldw, const float* w_scale,
-            const float* bias, void* out, int64_t ldo, int8_t* yq, float* y_scale, float* row_absmax, int64_t M, int N,
-            int K, int epilogue, int32_t* status, void* stream) {
+// Wc / meta null: dense weight Wq [N, K]; else the 2:4-compressed weight of samb_pack_sp24.
+int requant(const int8_t* Aq, int64_t lda, const float* a_scale, const int8_t* Wq, int64_t ldw, const uint8_t* meta,
+            const float* w_scale, const float* bias, void* out, int64_t ldo, int8_t* yq, float* y_scale,
+            float* row_absmax, int64_t M, int N, int K, int epilogue, int32_t* status, void* stream) {
   if (!Aq || !Wq || !out || !yq || !y_scale || !row_absmax || !status) return SAMB_E_BADARG;
   if (M < 0 || N <= 0 || K <= 0) return SAMB_E_BADARG;
   if (epilogue & ~(SAMB_EPI_BIAS | SAMB_EPI_GELU)) return SAMB_E_BADARG;     // no residual, no raw accumulators
@@ -84,9 +85,12 @@ int requant(const int8_t* Aq, int64_t lda, const float* a_scale, const int8_t* W
   const long long zb = (M + 255) / 256;
   zero_floats_kernel<<<unsigned(zb < 1184 ? zb : 1184), 256, 0, st>>>(row_absmax, M);
   if (int e = launch_status()) return e;
-  if (int e = launch_gemm_i8_rowmax(Aq, lda, a_scale, Wq, ldw, w_scale, bias, nullptr, 0, 0, out, ldo, M, N, K, epilogue,
-                                    status, stream, row_absmax))
-    return e;
+  const int e = meta == nullptr
+                    ? launch_gemm_i8_rowmax(Aq, lda, a_scale, Wq, ldw, w_scale, bias, nullptr, 0, 0, out, ldo, M, N, K,
+                                            epilogue, status, stream, row_absmax)
+                    : launch_gemm_i8_sp24(Aq, lda, a_scale, Wq, ldw, meta, w_scale, bias, nullptr, 0, 0, out, ldo, M, N, K,
+                                          epilogue, status, stream, row_absmax);
+  if (e) return e;
   const long long blocks = (M + kWarps - 1) / kWarps;
   if (blocks > 0x7fffffffLL) return SAMB_E_SHAPE;
   quant_given_absmax_kernel<<<unsigned(blocks), kWarps * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(out), ldo,
@@ -103,7 +107,16 @@ int samb_gemm_i8_requant(const int8_t* Aq, int64_t lda, const float* a_scale, co
                          const float* w_scale, const float* bias, void* out, int64_t ldo, int8_t* yq, float* y_scale,
                          float* row_absmax_scratch, int64_t M, int N, int K, int epilogue, int32_t* status,
                          void* stream) {
-  return samb::requant(Aq, lda, a_scale, Wq, ldw, w_scale, bias, out, ldo, yq, y_scale, row_absmax_scratch, M, N, K,
+  return samb::requant(Aq, lda, a_scale, Wq, ldw, nullptr, w_scale, bias, out, ldo, yq, y_scale, row_absmax_scratch, M,
+                       N, K, epilogue, status, stream);
+}
+
+int samb_gemm_i8_sp24_requant(const int8_t* Xq, int64_t ldx, const float* x_scale, const int8_t* Wc, int64_t ldc,
+                              const uint8_t* meta, const float* w_scale, const float* bias, void* out, int64_t ldo,
+                              int8_t* yq, float* y_scale, float* row_absmax_scratch, int64_t T, int N, int K,
+                              int epilogue, int32_t* status, void* stream) {
+  if (meta == nullptr) return SAMB_E_BADARG;
+  return samb::requant(Xq, ldx, x_scale, Wc, ldc, meta, w_scale, bias, out, ldo, yq, y_scale, row_absmax_scratch, T, N, K,
                        epilogue, status, stream);
 }
 
@@ -115,8 +128,8 @@ int samb_gemm_i8_requant_static(const int8_t* Aq, int64_t lda, const float* a_sc
   if (M > samb::kStaticRows) return SAMB_E_SHAPE;       // more rows than the built-in scratch holds
   float* scratch = nullptr;
   if (int e = samb::static_scratch(&scratch)) return e;
-  return samb::requant(Aq, lda, a_scale, Wq, ldw, w_scale, bias, out, ldo, yq, y_scale, scratch, M, N, K, epilogue,
-                       status, stream);
+  return samb::requant(Aq, lda, a_scale, Wq, ldw, nullptr, w_scale, bias, out, ldo, yq, y_scale, scratch, M, N, K,
+                       epilogue, status, stream);
 }
 
 }  // extern "C"

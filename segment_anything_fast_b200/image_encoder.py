@@ -302,11 +302,14 @@ class ImageEncoderViT(nn.Module):
             x1 = self._linear(oa, os_, bw["proj"], residual=cur)
             del o, oa
             xn2, xs2 = self._norm(x1, bw["n2"])
-            if self.quant == "int8" and "wq" in bw["lin1"]:
-                # dense int8 lin1: the row maxima of GELU(lin1) come out of the GEMM epilogue, the quantisation
-                # for lin2 is a streaming pass (no reduction over the 5120-wide hidden rows)
+            if self.quant == "int8":
+                # int8 lin1 (dense or 2:4): the row maxima of GELU(lin1) come out of the GEMM epilogue, the
+                # quantisation for lin2 is a streaming pass (no reduction over the 5120-wide hidden rows)
                 w1 = bw["lin1"]
-                ha, hs, hid = ops.gemm_i8_requant(xn2, xs2, w1["wq"], w1["ws"], w1["b"], gelu=True)
+                if "wc" in w1:
+                    ha, hs, hid = ops.gemm_i8_requant(xn2, xs2, w1["wc"], w1["ws"], w1["b"], gelu=True, meta=w1["meta"])
+                else:
+                    ha, hs, hid = ops.gemm_i8_requant(xn2, xs2, w1["wq"], w1["ws"], w1["b"], gelu=True)
             else:
                 hid = self._linear(xn2, xs2, bw["lin1"], gelu=True)
                 ha, hs = self._act(hid)

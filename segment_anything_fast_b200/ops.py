@@ -186,17 +186,18 @@ def gemm_i8(aq: torch.Tensor, a_scale: Optional[torch.Tensor], wq: torch.Tensor,
 
 
 def gemm_i8_requant(aq: torch.Tensor, a_scale: torch.Tensor, wq: torch.Tensor, w_scale: torch.Tensor,
-                    bias: Optional[torch.Tensor] = None, gelu: bool = False,
-                    out: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+                    bias: Optional[torch.Tensor] = None, gelu: bool = False, out: Optional[torch.Tensor] = None,
+                    meta: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """int8 Linear (+ bias, + GELU) whose output is also quantised per row for the next int8 Linear: returns
     ``(yq int8 [M, N], y_scale [M], out bf16 [M, N])``.  The row maxima come out of the GEMM epilogue (atomic
-    maxima into a scratch array of M floats), so no pass over ``out`` reduces anything."""
+    maxima into a scratch array of M floats), so no pass over ``out`` reduces anything.  With ``meta`` the weight
+    is the 2:4-compressed pair ``(wq = wc [N, K/2], meta)`` of ``pack_sp24``."""
     _need(aq, torch.int8, "aq"); _need(wq, torch.int8, "wq")
     _need(a_scale, torch.float32, "a_scale"); _need(w_scale, torch.float32, "w_scale")
     aq, wq = _rows2d(aq, "aq"), _rows2d(wq, "wq")
     M, K = aq.shape
     N = wq.shape[0]
-    if wq.shape[1] != K:
+    if wq.shape[1] * (2 if meta is not None else 1) != K:
         raise RuntimeError("gemm_i8_requant: inner dimensions differ")
     epi = 0
     if bias is not None:
@@ -209,6 +210,13 @@ def gemm_i8_requant(aq: torch.Tensor, a_scale: torch.Tensor, wq: torch.Tensor, w
     y_scale = torch.empty(M, dtype=torch.float32, device=aq.device)
     scratch = torch.empty(M, dtype=torch.float32, device=aq.device)
     st = status_word(aq.device)
+    if meta is not None:
+        _need(meta, torch.uint8, "meta")
+        _lib.check(_lib.load().samb_gemm_i8_sp24_requant(
+            aq.data_ptr(), aq.stride(0), a_scale.data_ptr(), wq.data_ptr(), wq.stride(0), meta.data_ptr(),
+            w_scale.data_ptr(), _ptr(bias), out.data_ptr(), out.stride(0), yq.data_ptr(), y_scale.data_ptr(),
+            scratch.data_ptr(), M, N, K, epi, st.data_ptr(), _stream()), "samb_gemm_i8_sp24_requant")
+        return yq, y_scale, out
     _lib.check(_lib.load().samb_gemm_i8_requant(
         aq.data_ptr(), aq.stride(0), a_scale.data_ptr(), wq.data_ptr(), wq.stride(0), w_scale.data_ptr(), _ptr(bias),
         out.data_ptr(), out.stride(0), yq.data_ptr(), y_scale.data_ptr(), scratch.data_ptr(), M, N, K, epi,

@@ -325,6 +325,26 @@ def test_gemm_i8_requant_equals_gemm_then_row_quantisation(ops, M, N, K, gelu):
     assert torch.equal(yq.cpu(), oq) and torch.equal(ys.cpu(), os_)
 
 
+@pytest.mark.parametrize("T,N,K,gelu", [(4096 + 100, 512, 1280, True), (300, 160, 160, True), (3000, 512, 640, False)])
+def test_gemm_i8_sp24_requant_equals_gemm_then_row_quantisation(ops, T, N, K, gelu):
+    """The same for a 2:4-compressed weight: the sparse kernel's epilogue supplies the row maxima (single-CTA with
+    the GELU, CTA pairs without)."""
+    g = torch.Generator().manual_seed(T + N)
+    x = _bf16(torch.randn(T, K, generator=g))
+    b = torch.randn(N, generator=g) * 0.1
+    xq, sx = ops.quant_rows_i8(x.cuda())
+    wq = _sparse_weight(N, K, seed=T)
+    sw = torch.rand(N, generator=g) * 0.002 + 0.0005
+    wc, meta = ops.pack_sp24(wq.cuda())
+    plain = ops.gemm_i8_sp24(xq, sx, wc, meta, sw.cuda(), b.cuda(), gelu=gelu)
+    q_ref, s_ref = ops.quant_rows_i8(plain)
+    for _ in range(2):
+        yq, ys, out = ops.gemm_i8_requant(xq, sx, wc, sw.cuda(), b.cuda(), gelu=gelu, meta=meta)
+        ops.check_status()
+        assert torch.equal(out, plain)
+        assert torch.equal(ys, s_ref) and torch.equal(yq, q_ref)
+
+
 # ------------------------------------------------------------------ CTA-pair GEMM
 @pytest.mark.parametrize("M,N,K", [(4096 + 100, 512, 1280), (8192, 1280, 5120), (2048, 256, 64)])
 def test_gemm_pair_kernel_equals_single_cta_kernel(ops, M, N, K, monkeypatch):
