@@ -30,23 +30,31 @@ constexpr int OUT_STAGE_BYTES = BM * 128;
 // Operand ring and output staging share the shared memory.  bf16: 6 stages + 1 staging tile (a 256-wide tile
 // takes 2 x as many tensor-pipe cycles per output byte as in int8, the store is never the hold-up).  int8: a
 // stage holds twice the K depth, 5 are plenty, and the room goes to three staging tiles that rotate per
-// 64-column chunk, so that a chunk never waits for the previous chunk's store to drain.
-__host__ __device__ constexpr int pair_stages(bool int8) { return int8 ? 5 : 6; }
-__host__ __device__ constexpr int pair_out_bufs(bool int8) { return int8 ? 3 : 1; }
-__host__ __device__ constexpr int pair_smem_bytes(bool int8) {
-  return pair_stages(int8) * STAGE_BYTES + pair_out_bufs(int8) * OUT_STAGE_BYTES + 2 * BN * 4 + 1024 + 256;
+// 64-column chunk, so that a chunk never waits for the previous chunk's store to drain.  With a residual the
+// staging tiles also receive the residual tile (TMA load, two chunks ahead of its use), which takes three of them.
+#ifndef SAMB_PAIR_RES_STAGES_BF16
+#define SAMB_PAIR_RES_STAGES_BF16 5
+#endif
+__host__ __device__ constexpr int pair_stages(bool int8, bool res) {
+  return int8 ? 5 : (res ? SAMB_PAIR_RES_STAGES_BF16 : 6);
+}
+__host__ __device__ constexpr int pair_out_bufs(bool int8, bool res) {
+  return int8 ? 3 : (res ? (SAMB_PAIR_RES_STAGES_BF16 == 5 ? 3 : 2) : 1);
+}
+__host__ __device__ constexpr int pair_smem_bytes(bool int8, bool res) {
+  return pair_stages(int8, res) * STAGE_BYTES + pair_out_bufs(int8, res) * OUT_STAGE_BYTES + (int8 ? 2 : 1) * BN * 4 +
+         1024 + 256;
 }
 
 struct PairParams {
   void* out;
   const float* bias;
-  const __nv_bfloat16* residual;
   const float* a_scale;
   const float* w_scale;
   float* row_absmax;             // optional: atomic maximum of |bf16(out[m, :])| per row (see launch_gemm_i8_rowmax)
   int* status;
   long long M;
-  long long ldr, res_rows;
+  long long res_rows;            // the residual row of output row m is m % res_rows (a multiple of 128, or >= M)
   int N, K;
   int k_slabs, last_ksteps;
   int tiles_n;
@@ -74,25 +82,28 @@ __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;" ::"n
 template <bool kInt8, int kEpi, int kEpiWarps>
 __global__ void __launch_bounds__(64 + 32 * kEpiWarps, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmOut, const PairParams p) {
+                 const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmRes,
+                 const PairParams p) {
   constexpr bool kBias = (kEpi & SAMB_EPI_BIAS) != 0;
   constexpr bool kGelu = (kEpi & SAMB_EPI_GELU) != 0;
   constexpr bool kRes = (kEpi & SAMB_EPI_RESIDUAL) != 0;
   constexpr int EPI_THREADS = 32 * kEpiWarps;
   constexpr int CW = 64 / (kEpiWarps / 4);               // columns of a 64-column chunk per warp: 32 or 16
   constexpr int NV = CW / 8;                             // 16-byte output pieces per thread and chunk
-  constexpr int STAGES = pair_stages(kInt8);
-  constexpr int OUT_BUFS = pair_out_bufs(kInt8);
+  constexpr int STAGES = pair_stages(kInt8, kRes);
+  constexpr int OUT_BUFS = pair_out_bufs(kInt8, kRes);
+  constexpr int RES_AHEAD = OUT_BUFS - 1;                // residual tiles in flight ahead of the chunk being worked on
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_out0 = smem + STAGES * STAGE_BYTES;
   float* s_bias = reinterpret_cast<float*>(stage_out0 + OUT_BUFS * OUT_STAGE_BYTES);
-  float* s_wscale = s_bias + BN;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_wscale + BN);
+  float* s_wscale = s_bias + BN;                         // int8 only (no room is set aside for it in bf16)
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_bias + (kInt8 ? 2 : 1) * BN);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* acc_full = empty_bar + STAGES;
   uint64_t* acc_empty = acc_full + NUM_ACC;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + NUM_ACC);
+  uint64_t* res_full = acc_empty + NUM_ACC;              // residual tile landed, per staging tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_full + 3);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -110,10 +121,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 2 * EPI_THREADS / 32);    // the epilogue warps of both CTAs
     }
+    for (int b = 0; b < 3; ++b) mbar_init(&res_full[b], 1);
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     tma_prefetch_desc(&tmOut);
+    if (kRes) tma_prefetch_desc(&tmRes);
   }
   cluster_sync_all();                                    // both CTAs' barriers exist before any remote use
   if (warp == 1) {
@@ -196,6 +209,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int et = int(threadIdx.x) - 64;
     const uint32_t acc_empty0 = map_to_cta(&acc_empty[0], 0);        // the leader's barrier
     uint32_t acc = 0, acc_phase = 0, chunk_no = 0;
+    // Residual: thread 0 has the TMA unit copy the residual's [128 x 64] tile of a chunk into the staging tile the
+    // chunk's output will be written to, RES_AHEAD chunks before the chunk is worked on; every thread then reads its
+    // 16-byte pieces from where it is about to write them.  (Reading the residual from global memory with a row
+    // per lane takes 32 cache lines per request, which made the epilogue the bottleneck of the K = 1280 products.)
+    const uint32_t my_chunks = uint32_t((p.num_tiles - pair + num_pairs - 1) / num_pairs) * (BN / 64);
+    auto fetch_residual = [&](uint32_t n) {              // chunk n of this CTA, thread 0 only
+      if (n >= my_chunks) return;
+      const long long t = pair + (long long)(n / (BN / 64)) * num_pairs;
+      const long long r0 = ((long long)(t / p.tiles_n) * (2 * BM) + int(rank) * BM) % p.res_rows;
+      const int b = int(n % OUT_BUFS);
+      mbar_expect_tx(&res_full[b], OUT_STAGE_BYTES);
+      tma_load_2d(stage_out0 + b * OUT_STAGE_BYTES, &tmRes, &res_full[b], int(t % p.tiles_n) * BN + int(n % (BN / 64)) * 64,
+                  int(r0));
+    };
+    if (kRes && et == 0)
+      for (int n = 0; n < RES_AHEAD; ++n) fetch_residual(uint32_t(n));
     for (long long tile = pair; tile < p.num_tiles; tile += num_pairs) {
       const int m0 = int(tile / p.tiles_n) * (2 * BM) + int(rank) * BM;
       const int n0 = int(tile % p.tiles_n) * BN;
@@ -211,8 +240,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t t_addr = tmem_base + (lane_base << 16) + acc * BN + qc * CW;
       float a_scale = 1.0f;
       if (kInt8 && row_ok) a_scale = __ldg(p.a_scale + row);
-      const __nv_bfloat16* res_row = nullptr;
-      if (kRes && row_ok) res_row = p.residual + (row % p.res_rows) * p.ldr + n0 + qc * CW;
       // The chunk loop is software-pipelined: the tensor-memory load of chunk c + 1 is in flight while chunk c goes
       // through the arithmetic, and the accumulator is handed back to the MMA warp as soon as its last chunk has
       // been read (before that chunk's arithmetic and store).
@@ -223,14 +250,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
       for (int c = 0; c < BN / 64; ++c) {
         const int col0 = n0 + c * 64;
-        uint4 rv[NV];
-        if (kRes) {
-#pragma unroll
-          for (int u = 0; u < NV; ++u) {
-            rv[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (row_ok) rv[u] = __ldg(reinterpret_cast<const uint4*>(res_row + c * 64) + u);
-          }
-        }
         tmem_ld_wait();                                  // chunk c is in rbuf[c & 1]
         if (c + 1 < BN / 64) {
           if constexpr (CW == 32) tmem_ld_32x32b_x32(t_addr + (c + 1) * 64, rbuf[(c + 1) & 1]);
@@ -241,6 +260,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (lane == 0) mbar_arrive_cluster(acc_empty0 + acc * 8);
         }
         const uint32_t(&r)[CW] = rbuf[c & 1];
+        uint8_t* stage_out = stage_out0 + (OUT_BUFS > 1 ? int(chunk_no % OUT_BUFS) : 0) * OUT_STAGE_BYTES;
+        uint4 rv[NV];
+        if (kRes) {
+          // a wait that gives up has raised the abort flag and the status word; the next accumulator wait ends the loop
+          mbar_wait(&res_full[chunk_no % OUT_BUFS], (chunk_no / OUT_BUFS) & 1u, abort_flag, p.status, 5);
+          const uint8_t* srow = stage_out + erow * 128;
+#pragma unroll
+          for (int u = 0; u < NV; ++u)
+            rv[u] = *reinterpret_cast<const uint4*>(srow + (((qc * NV + u) ^ (erow & 7)) << 4));
+        }
         uint4 packed[NV];
 #pragma unroll
         for (int u = 0; u < NV; ++u) {
@@ -263,7 +292,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // Staging tile of this chunk.  With one tile, wait until the previous store has read it; with several,
         // thread 0 already made sure (after issuing the previous store) that all but the latest store have
         // drained, and the barrier below (of the previous chunk) published that.
-        uint8_t* stage_out = stage_out0 + (OUT_BUFS > 1 ? int(chunk_no % OUT_BUFS) : 0) * OUT_STAGE_BYTES;
         if (OUT_BUFS == 1) {
           if (et == 0) tma_store_wait_read<0>();
           epi_sync<EPI_THREADS>();
@@ -296,6 +324,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           tma_store_commit();
           if (OUT_BUFS > 1) tma_store_wait_read<1>();    // every store but this one has read its staging tile
+          if (kRes) fetch_residual(chunk_no + RES_AHEAD);  // into the tile of the store before this one
         }
         ++chunk_no;
       }
@@ -317,7 +346,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
-using PairFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const PairParams);
+using PairFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const PairParams);
 
 template <bool kInt8>
 PairFn pick_pair(int epi) {
@@ -340,6 +369,12 @@ int launch_gemm_pair(bool int8, const void* A, int64_t lda, const void* W, int64
                      void* out, int64_t ldo, int64_t M, int N, int K, int epilogue, int head_dim, int32_t* status,
                      void* stream, float* row_absmax) {
   if (N % BN || M < 8 * 2 * BM) return SAMB_E_SHAPE;
+  const bool res = (epilogue & SAMB_EPI_RESIDUAL) != 0;
+  if (res_rows <= 0) res_rows = M;
+  // the residual comes in [128 x 64] boxes: a CTA's 128 rows may not wrap around the residual's rows, and the
+  // box wants 16-byte aligned rows
+  if (res && ((res_rows < M && res_rows % BM) || (ldr * 2) % 16 || (reinterpret_cast<uintptr_t>(residual) & 15u)))
+    return SAMB_E_SHAPE;
   auto kern = int8 ? pick_pair<true>(epilogue) : pick_pair<false>(epilogue);
   if (kern == nullptr) return SAMB_E_SHAPE;
   const int esz = int8 ? 1 : 2;
@@ -375,17 +410,24 @@ int launch_gemm_pair(bool int8, const void* A, int64_t lda, const void* W, int64
                                 CU_TENSOR_MAP_SWIZZLE_128B))
       return e;
   }
+  CUtensorMap tmRes = tmOut;
+  if (res) {
+    const uint64_t dims[2] = {uint64_t(N), uint64_t(res_rows < M ? res_rows : M)};
+    const uint64_t strides[2] = {2, uint64_t(ldr) * 2};
+    const uint32_t box[2] = {64, uint32_t(BM)};
+    if (int e = make_tensor_map(&tmRes, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(residual), dims, strides,
+                                box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return e;
+  }
   PairParams p;
   p.out = out;
   p.bias = bias;
-  p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.a_scale = a_scale;
   p.w_scale = w_scale;
   p.row_absmax = row_absmax;
   p.status = status;
   p.M = M;
-  p.ldr = ldr;
-  p.res_rows = res_rows > 0 ? res_rows : 1;
+  p.res_rows = res_rows;
   p.N = N;
   p.K = K;
   p.k_slabs = (K * esz + SLAB_BYTES - 1) / SLAB_BYTES;
@@ -394,7 +436,7 @@ int launch_gemm_pair(bool int8, const void* A, int64_t lda, const void* W, int64
   p.num_tiles = ((M + 2 * BM - 1) / (2 * BM)) * p.tiles_n;
   p.hm_group = head_dim / 16;
 
-  const int smem_bytes = pair_smem_bytes(int8);
+  const int smem_bytes = pair_smem_bytes(int8, res);
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess)
     return SAMB_E_LAUNCH;
   cudaLaunchConfig_t cfg = {};
@@ -420,7 +462,7 @@ int launch_gemm_pair(bool int8, const void* A, int64_t lda, const void* W, int64
   long long pairs = max_clusters < sm_count() / 2 ? max_clusters : sm_count() / 2;
   if (p.num_tiles < pairs) pairs = p.num_tiles;
   cfg.gridDim = dim3(unsigned(2 * pairs));
-  if (cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmOut, p) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmOut, tmRes, p) != cudaSuccess) {
     cudaGetLastError();
     return SAMB_E_LAUNCH;
   }
