@@ -114,7 +114,7 @@ class LaunchProfiler:
 
     def __init__(self):
         self.launches = 0
-        self.records = []          # (flops, start_event, end_event)
+        self.records = []          # (flops, start_event, end_event, (name, N, K))
 
     def begin(self, name, args):
         if name in ("samb_abi_version", "samb_error_string", "samb_decode_status", "samb_sp24_meta_bytes"):
@@ -129,7 +129,7 @@ class LaunchProfiler:
             return None
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
-        return (pos[3] * M * N * K, s, e)
+        return (pos[3] * M * N * K, s, e, (name, N, K))
 
     def end(self, tok):
         if tok is not None:
@@ -254,6 +254,13 @@ def measure_config(args, quant_name, device, dist, world, rank, local, tensor_pe
     ms = ev0.elapsed_time(ev1)
     gemm_flops = sum(r[0] for r in prof.records)
     gemm_ms = sum(r[1].elapsed_time(r[2]) for r in prof.records)
+    if args.gemm_breakdown and rank == 0:                      # average time per Linear shape, to stderr
+        by_shape = {}
+        for r in prof.records:
+            by_shape.setdefault(r[3], []).append(r[1].elapsed_time(r[2]))
+        for key, ts in sorted(by_shape.items()):
+            print(f"[{quant_name}] {key[0]} N={key[1]} K={key[2]}: {len(ts)} launches, mean {sum(ts) / len(ts):.4f} ms",
+                  file=sys.stderr)
     launches = prof.launches
 
     # ---- end to end: pinned host uint8 in, host embeddings out, every step (two batches in flight: the upload
@@ -446,6 +453,7 @@ def main():
                     help="run only this configuration (default: bf16 headline + int8 + int8-sp24 under `configs`)")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gemm-breakdown", action="store_true", help="print the mean time per Linear shape to stderr")
     ap.add_argument("--no-peak-probe", action="store_true", help="skip the tensor-pipe rate probe (int8 peak)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -5,9 +5,12 @@
 // CTA's shared memory and accumulates into both CTAs' tensor memory (128 rows each).  Against the
 // single-CTA kernel this halves the W bytes every CTA loads and reads per MMA (8 instead of 12 KB of
 // operands per 128 tensor-pipe cycles), which is what the single-CTA kernel is bound by, and leaves room
-// for a 6-deep ring.  Roles per CTA as in the single-CTA kernel: warp 0 TMA producer, warp 1 MMA issue
-// (leader CTA only), warps 2..17 epilogue of the CTA's own 128 rows (four warps per tensor-memory lane
-// quarter, 16 of every 64 columns each: the int8 epilogues are issue-bound with fewer).
+// for a 6-deep ring.  Roles per CTA: warp 0 TMA producer, warp 1 MMA issue (leader CTA only), warps 2..17
+// epilogue of the CTA's own 128 rows (four warps per tensor-memory lane quarter, 16 of every 64 columns each:
+// the int8 epilogues are issue-bound with fewer), and one more warp whose only job is the output: it waits
+// for a staged 64-column chunk, issues its TMA store, waits until the store has read the staging tile and
+// hands the tile back (with a residual: has the TMA unit fill it with the residual of a later chunk), so
+// that no epilogue thread ever waits for a store.
 // Barriers: `full` lives in the leader (both CTAs' copies are counted there), `empty` and `acc_full`
 // exist in both CTAs and receive one commit each from the leader, `acc_empty` lives in the leader and
 // counts the epilogue warps of both CTAs.  No copy is multicast.
@@ -42,7 +45,7 @@ __host__ __device__ constexpr int pair_out_bufs(bool int8, bool res) {
   return int8 ? 3 : (res ? (SAMB_PAIR_RES_STAGES_BF16 == 5 ? 3 : 2) : 1);
 }
 __host__ __device__ constexpr int pair_smem_bytes(bool int8, bool res) {
-  return pair_stages(int8, res) * STAGE_BYTES + pair_out_bufs(int8, res) * OUT_STAGE_BYTES + (int8 ? 2 : 1) * BN * 4 +
+  return pair_stages(int8, res) * STAGE_BYTES + pair_out_bufs(int8, res) * OUT_STAGE_BYTES + (int8 ? 4 : 2) * BN * 4 +
          1024 + 256;
 }
 
@@ -73,14 +76,12 @@ __device__ __forceinline__ bool epi_all(bool pred) {
       : "memory");
   return r != 0;
 }
-template <int kThreads>
-__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory"); }
 
 // kEpiWarps: 8 (two warps per tensor-memory lane quarter, 32 of every 64 columns each) or 16 (four per
 // quarter, 16 columns each).  The cheap int8 epilogues are issue-latency bound and gain from 16; the
 // bf16 ones are hidden behind the longer bf16 products either way and save barrier traffic with 8.
 template <bool kInt8, int kEpi, int kEpiWarps>
-__global__ void __launch_bounds__(64 + 32 * kEpiWarps, 1)
+__global__ void __launch_bounds__(96 + 32 * kEpiWarps, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmRes,
                  const PairParams p) {
@@ -92,18 +93,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   constexpr int NV = CW / 8;                             // 16-byte output pieces per thread and chunk
   constexpr int STAGES = pair_stages(kInt8, kRes);
   constexpr int OUT_BUFS = pair_out_bufs(kInt8, kRes);
-  constexpr int RES_AHEAD = OUT_BUFS - 1;                // residual tiles in flight ahead of the chunk being worked on
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_out0 = smem + STAGES * STAGE_BYTES;
-  float* s_bias = reinterpret_cast<float*>(stage_out0 + OUT_BUFS * OUT_STAGE_BYTES);
-  float* s_wscale = s_bias + BN;                         // int8 only (no room is set aside for it in bf16)
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_bias + (kInt8 ? 2 : 1) * BN);
+  float* s_bias0 = reinterpret_cast<float*>(stage_out0 + OUT_BUFS * OUT_STAGE_BYTES);   // [2][BN]: this tile, next tile
+  float* s_wscale0 = s_bias0 + 2 * BN;                   // [2][BN], int8 only (no room is set aside for it in bf16)
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_bias0 + (kInt8 ? 4 : 2) * BN);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* acc_full = empty_bar + STAGES;
   uint64_t* acc_empty = acc_full + NUM_ACC;
   uint64_t* res_full = acc_empty + NUM_ACC;              // residual tile landed, per staging tile
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_full + 3);
+  uint64_t* stage_full = res_full + 3;                   // chunk staged by every epilogue warp, per staging tile
+  uint64_t* stage_free = stage_full + 3;                 // the chunk's store has read the staging tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stage_free + 3);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -121,7 +123,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 2 * EPI_THREADS / 32);    // the epilogue warps of both CTAs
     }
-    for (int b = 0; b < 3; ++b) mbar_init(&res_full[b], 1);
+    for (int b = 0; b < 3; ++b) {
+      mbar_init(&res_full[b], 1);
+      mbar_init(&stage_full[b], kEpiWarps);
+      mbar_init(&stage_free[b], 1);
+    }
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
@@ -201,6 +207,56 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
       }
     }
+  } else if (warp == 2 + kEpiWarps) {
+    // ------------------------------------------------------------------ output warp: stores, residual loads
+    // One thread.  Chunk n of this CTA (64 columns of one of its tiles, in the order the epilogue works through them)
+    // lives in staging tile n % OUT_BUFS.  With a residual the TMA unit copies the residual's [128 x 64] tile of a
+    // chunk into that staging tile as soon as the store of the chunk that used the tile before has read it; the
+    // epilogue threads read their 16-byte pieces from where they are about to write.  (Reading the residual from
+    // global memory with a row per lane takes 32 cache lines per request, which made the epilogue the bottleneck
+    // of the K = 1280 products.)
+    if (lane == 0) {
+      const uint32_t my_chunks = uint32_t((p.num_tiles - pair + num_pairs - 1) / num_pairs) * (BN / 64);
+      auto chunk_coords = [&](uint32_t n, int& m0, int& col0) {
+        const long long t = pair + (long long)(n / (BN / 64)) * num_pairs;
+        m0 = int(t / p.tiles_n) * (2 * BM) + int(rank) * BM;
+        col0 = int(t % p.tiles_n) * BN + int(n % (BN / 64)) * 64;
+      };
+      auto fetch_residual = [&](uint32_t n) {
+        if (n >= my_chunks) return;
+        int m0, col0;
+        chunk_coords(n, m0, col0);
+        const int b = int(n % OUT_BUFS);
+        mbar_expect_tx(&res_full[b], OUT_STAGE_BYTES);
+        tma_load_2d(stage_out0 + b * OUT_STAGE_BYTES, &tmRes, &res_full[b], col0, int(m0 % p.res_rows));
+      };
+      if (kRes)
+        for (int n = 0; n < OUT_BUFS; ++n) fetch_residual(uint32_t(n));      // every staging tile starts out free
+      for (uint32_t n = 0; n < my_chunks; ++n) {
+        const int b = int(n % OUT_BUFS);
+        if (!mbar_wait(&stage_full[b], (n / OUT_BUFS) & 1u, abort_flag, p.status, 6)) break;
+        uint8_t* stage_out = stage_out0 + b * OUT_STAGE_BYTES;
+        int m0, col0;
+        chunk_coords(n, m0, col0);
+        if (p.hm_group == 0) {
+          tma_store_2d(&tmOut, stage_out, col0, m0);
+        } else {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int g = (col0 + q * 16) >> 4;
+            tma_store_4d(&tmOut, stage_out + q * 4096, 0, g % p.hm_group, m0, g / p.hm_group);
+          }
+        }
+        tma_store_commit();
+        // with several staging tiles, let this store run and hand back the tile of the one before it
+        tma_store_wait_read<(OUT_BUFS > 1 ? 1 : 0)>();
+        if (OUT_BUFS > 1 && n == 0) continue;
+        const uint32_t freed = OUT_BUFS > 1 ? n - 1 : n;
+        if (kRes) fetch_residual(freed + OUT_BUFS);
+        else mbar_arrive(&stage_free[freed % OUT_BUFS]);
+      }
+      tma_store_wait_all<0>();
+    }
   } else {
     // ------------------------------------------------------------------ epilogue warps, own 128 rows
     const uint32_t lane_base = uint32_t(warp & 3) * 32u;
@@ -208,63 +264,67 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int erow = int(lane_base) + lane;
     const int et = int(threadIdx.x) - 64;
     const uint32_t acc_empty0 = map_to_cta(&acc_empty[0], 0);        // the leader's barrier
-    uint32_t acc = 0, acc_phase = 0, chunk_no = 0;
-    // Residual: thread 0 has the TMA unit copy the residual's [128 x 64] tile of a chunk into the staging tile the
-    // chunk's output will be written to, RES_AHEAD chunks before the chunk is worked on; every thread then reads its
-    // 16-byte pieces from where it is about to write them.  (Reading the residual from global memory with a row
-    // per lane takes 32 cache lines per request, which made the epilogue the bottleneck of the K = 1280 products.)
-    const uint32_t my_chunks = uint32_t((p.num_tiles - pair + num_pairs - 1) / num_pairs) * (BN / 64);
-    auto fetch_residual = [&](uint32_t n) {              // chunk n of this CTA, thread 0 only
-      if (n >= my_chunks) return;
-      const long long t = pair + (long long)(n / (BN / 64)) * num_pairs;
-      const long long r0 = ((long long)(t / p.tiles_n) * (2 * BM) + int(rank) * BM) % p.res_rows;
-      const int b = int(n % OUT_BUFS);
-      mbar_expect_tx(&res_full[b], OUT_STAGE_BYTES);
-      tma_load_2d(stage_out0 + b * OUT_STAGE_BYTES, &tmRes, &res_full[b], int(t % p.tiles_n) * BN + int(n % (BN / 64)) * 64,
-                  int(r0));
+    uint32_t acc = 0, acc_phase = 0, chunk_no = 0, it = 0;
+    // Per-column bias / weight scale of a tile sit in shared memory, per-row activation scale in a register.  Those
+    // of the next tile are fetched into registers at the top of a tile and put in place at its end, so that their
+    // latency is never waited for.
+    float next_bias = 0.f, next_wscale = 0.f, next_ascale = 1.0f;
+    auto fetch_tile_params = [&](long long t) {
+      if (t >= p.num_tiles) return;
+      const int n0 = int(t % p.tiles_n) * BN;
+      if (et < BN) {
+        if (kBias) next_bias = __ldg(p.bias + n0 + et);
+        if (kInt8) next_wscale = __ldg(p.w_scale + n0 + et);
+      }
+      const long long row = (long long)int(t / p.tiles_n) * (2 * BM) + int(rank) * BM + erow;
+      next_ascale = 1.0f;
+      if (kInt8 && row < p.M) next_ascale = __ldg(p.a_scale + row);
     };
-    if (kRes && et == 0)
-      for (int n = 0; n < RES_AHEAD; ++n) fetch_residual(uint32_t(n));
-    for (long long tile = pair; tile < p.num_tiles; tile += num_pairs) {
+    fetch_tile_params(pair);
+    if (et < BN) {
+      if (kBias) s_bias0[et] = next_bias;
+      if (kInt8) s_wscale0[et] = next_wscale;
+    }
+    for (long long tile = pair; tile < p.num_tiles; tile += num_pairs, ++it) {
       const int m0 = int(tile / p.tiles_n) * (2 * BM) + int(rank) * BM;
-      const int n0 = int(tile % p.tiles_n) * BN;
       const long long row = (long long)m0 + erow;
       const bool row_ok = row < p.M;
-      if (et < BN) {
-        if (kBias) s_bias[et] = __ldg(p.bias + n0 + et);
-        if (kInt8) s_wscale[et] = __ldg(p.w_scale + n0 + et);
-      }
+      const float* s_bias = s_bias0 + (it & 1u) * BN;
+      const float* s_wscale = s_wscale0 + (it & 1u) * BN;
+      const float a_scale = next_ascale;
+      fetch_tile_params(tile + num_pairs);
       const bool got = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, 4);
-      if (!epi_all<EPI_THREADS>(got)) break;
+      if (!epi_all<EPI_THREADS>(got)) break;            // also publishes this tile's bias / scale columns
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (lane_base << 16) + acc * BN + qc * CW;
-      float a_scale = 1.0f;
-      if (kInt8 && row_ok) a_scale = __ldg(p.a_scale + row);
       // The chunk loop is software-pipelined: the tensor-memory load of chunk c + 1 is in flight while chunk c goes
       // through the arithmetic, and the accumulator is handed back to the MMA warp as soon as its last chunk has
-      // been read (before that chunk's arithmetic and store).
+      // been read (before that chunk's arithmetic and staging).
       __nv_bfloat162 m2 = __floats2bfloat162_rn(0.f, 0.f);   // running |max| of this row's outputs in this tile
       uint32_t rbuf[2][CW];
       if constexpr (CW == 32) tmem_ld_32x32b_x32(t_addr, rbuf[0]);
       else tmem_ld_32x32b_x16(t_addr, rbuf[0]);
 #pragma unroll
       for (int c = 0; c < BN / 64; ++c) {
-        const int col0 = n0 + c * 64;
         tmem_ld_wait();                                  // chunk c is in rbuf[c & 1]
         if (c + 1 < BN / 64) {
           if constexpr (CW == 32) tmem_ld_32x32b_x32(t_addr + (c + 1) * 64, rbuf[(c + 1) & 1]);
           else tmem_ld_32x32b_x16(t_addr + (c + 1) * 64, rbuf[(c + 1) & 1]);
         } else {
-          tc_fence_before();                             // every column of this accumulator has been read
+          // Every column of this accumulator is in registers (the wait above).  The arrival is relaxed: a release
+          // at cluster scope here stalled the warp for some 1.5 k cycles per tile, and there is nothing to publish;
+          // the loads it must not overtake have completed.
+          tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(acc_empty0 + acc * 8);
+          if (lane == 0) mbar_arrive_cluster_relaxed(acc_empty0 + acc * 8);
         }
         const uint32_t(&r)[CW] = rbuf[c & 1];
-        uint8_t* stage_out = stage_out0 + (OUT_BUFS > 1 ? int(chunk_no % OUT_BUFS) : 0) * OUT_STAGE_BYTES;
+        const uint32_t sbuf = chunk_no % OUT_BUFS, suse = chunk_no / OUT_BUFS;
+        uint8_t* stage_out = stage_out0 + sbuf * OUT_STAGE_BYTES;
         uint4 rv[NV];
         if (kRes) {
           // a wait that gives up has raised the abort flag and the status word; the next accumulator wait ends the loop
-          mbar_wait(&res_full[chunk_no % OUT_BUFS], (chunk_no / OUT_BUFS) & 1u, abort_flag, p.status, 5);
+          mbar_wait(&res_full[sbuf], suse & 1u, abort_flag, p.status, 5);
           const uint8_t* srow = stage_out + erow * 128;
 #pragma unroll
           for (int u = 0; u < NV; ++u)
@@ -289,13 +349,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                  pack_bf16x2(v[6], v[7]));
           if (p.row_absmax != nullptr) m2 = absmax8(m2, packed[u]);
         }
-        // Staging tile of this chunk.  With one tile, wait until the previous store has read it; with several,
-        // thread 0 already made sure (after issuing the previous store) that all but the latest store have
-        // drained, and the barrier below (of the previous chunk) published that.
-        if (OUT_BUFS == 1) {
-          if (et == 0) tma_store_wait_read<0>();
-          epi_sync<EPI_THREADS>();
-        }
+        // The staging tile is free once the store of the chunk that used it before has read it (with a residual
+        // the residual's arrival, waited for above, says as much).
+        if (!kRes && suse > 0) mbar_wait(&stage_free[sbuf], (suse - 1u) & 1u, abort_flag, p.status, 7);
         if (p.hm_group == 0) {
           uint8_t* srow = stage_out + erow * 128;
 #pragma unroll
@@ -311,29 +367,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
         fence_proxy_async_smem();
-        epi_sync<EPI_THREADS>();
-        if (et == 0) {
-          if (p.hm_group == 0) {
-            tma_store_2d(&tmOut, stage_out, col0, m0);
-          } else {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const int g = (col0 + q * 16) >> 4;
-              tma_store_4d(&tmOut, stage_out + q * 4096, 0, g % p.hm_group, m0, g / p.hm_group);
-            }
-          }
-          tma_store_commit();
-          if (OUT_BUFS > 1) tma_store_wait_read<1>();    // every store but this one has read its staging tile
-          if (kRes) fetch_residual(chunk_no + RES_AHEAD);  // into the tile of the store before this one
-        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&stage_full[sbuf]);   // the output warp stores the chunk once every warp has arrived
         ++chunk_no;
       }
       // non-negative floats order like their bit patterns: one integer atomic per row and tile
       if (p.row_absmax != nullptr && row_ok)
         atomicMax(reinterpret_cast<int*>(p.row_absmax + row), __float_as_int(absmax_fold(m2)));
+      if (et < BN) {                                      // the other half of the buffers: nobody reads it in this tile
+        if (kBias) s_bias0[((it & 1u) ^ 1u) * BN + et] = next_bias;
+        if (kInt8) s_wscale0[((it & 1u) ^ 1u) * BN + et] = next_wscale;
+      }
       if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
     }
-    if (et == 0) tma_store_wait_all<0>();
   }
 
   // ------------------------------------------------------------------ teardown
@@ -447,7 +493,7 @@ int launch_gemm_pair(bool int8, const void* A, int64_t lda, const void* W, int64
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cfg.blockDim = dim3(int8 ? 64 + 32 * 16 : 64 + 32 * 8);
+  cfg.blockDim = dim3(int8 ? 96 + 32 * 16 : 96 + 32 * 8);   // producer, MMA, epilogue warps, output warp
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = static_cast<cudaStream_t>(stream);
   cfg.gridDim = dim3(unsigned(sm_count() & ~1));

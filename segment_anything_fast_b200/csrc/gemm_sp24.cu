@@ -332,7 +332,7 @@ gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       tc_fence_before();
       if (kPair) {
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(acc_empty0 + acc * 8);
+        if (lane == 0) mbar_arrive_cluster_relaxed(acc_empty0 + acc * 8);   // nothing to publish: the loads have completed
       } else {
         mbar_arrive_warp(&acc_empty[acc]);
       }
