@@ -45,8 +45,7 @@ __host__ __device__ constexpr int pair_out_bufs(bool int8, bool res) {
   return int8 ? 3 : (res ? (SAMB_PAIR_RES_STAGES_BF16 == 5 ? 3 : 2) : 1);
 }
 __host__ __device__ constexpr int pair_smem_bytes(bool int8, bool res) {
-  return pair_stages(int8, res) * STAGE_BYTES + pair_out_bufs(int8, res) * OUT_STAGE_BYTES + (int8 ? 4 : 2) * BN * 4 +
-         1024 + 256;
+  return pair_stages(int8, res) * STAGE_BYTES + pair_out_bufs(int8, res) * OUT_STAGE_BYTES + 1024 + 256;
 }
 
 struct PairParams {
@@ -57,25 +56,13 @@ struct PairParams {
   float* row_absmax;             // optional: atomic maximum of |bf16(out[m, :])| per row (see launch_gemm_i8_rowmax)
   int* status;
   long long M;
-  long long res_rows;            // the residual row of output row m is m % res_rows (a multiple of 128, or >= M)
+  int res_rows;                  // the residual row of output row m is m % res_rows (a multiple of 128, or >= M)
   int N, K;
   int k_slabs, last_ksteps;
   int tiles_n;
-  long long num_tiles;
+  int num_tiles;                 // < 2^31 (checked by the launcher): tile arithmetic stays in 32 bits
   int hm_group;
 };
-
-template <int kThreads>
-__device__ __forceinline__ bool epi_all(bool pred) {
-  uint32_t r;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\t"
-      "bar.red.and.pred p, 1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(r)
-      : "r"(uint32_t(pred)), "n"(kThreads)
-      : "memory");
-  return r != 0;
-}
 
 // kEpiWarps: 8 (two warps per tensor-memory lane quarter, 32 of every 64 columns each) or 16 (four per
 // quarter, 16 columns each).  The cheap int8 epilogues are issue-latency bound and gain from 16; the
@@ -96,9 +83,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_out0 = smem + STAGES * STAGE_BYTES;
-  float* s_bias0 = reinterpret_cast<float*>(stage_out0 + OUT_BUFS * OUT_STAGE_BYTES);   // [2][BN]: this tile, next tile
-  float* s_wscale0 = s_bias0 + 2 * BN;                   // [2][BN], int8 only (no room is set aside for it in bf16)
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_bias0 + (kInt8 ? 4 : 2) * BN);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(stage_out0 + OUT_BUFS * OUT_STAGE_BYTES);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* acc_full = empty_bar + STAGES;
   uint64_t* acc_empty = acc_full + NUM_ACC;
@@ -111,7 +96,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();               // 0 = leader of the pair
-  const long long pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int pair = int(blockIdx.x >> 1), num_pairs = int(gridDim.x >> 1);
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -151,9 +136,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t full0 = map_to_cta(&full_bar[0], 0);            // the leader's barriers
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (long long tile = pair; ok && tile < p.num_tiles; tile += num_pairs) {
-        const int m0 = int(tile / p.tiles_n) * (2 * BM) + int(rank) * BM;
-        const int n0 = int(tile % p.tiles_n) * BN + int(rank) * (BN / 2);
+      for (int tile = pair; ok && tile < p.num_tiles; tile += num_pairs) {
+        const int m0 = (tile / p.tiles_n) * (2 * BM) + int(rank) * BM;
+        const int n0 = (tile % p.tiles_n) * BN + int(rank) * (BN / 2);
         for (int ks = 0; ks < p.k_slabs; ++ks) {
           if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 1))) break;
           uint8_t* sa = smem + stage * STAGE_BYTES;
@@ -174,7 +159,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t accf_own = map_to_cta(&acc_full[0], 0), accf_peer = map_to_cta(&acc_full[0], 1);
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
-      for (long long tile = pair; ok && tile < p.num_tiles; tile += num_pairs) {
+      for (int tile = pair; ok && tile < p.num_tiles; tile += num_pairs) {
         if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, 2))) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -218,9 +203,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (lane == 0) {
       const uint32_t my_chunks = uint32_t((p.num_tiles - pair + num_pairs - 1) / num_pairs) * (BN / 64);
       auto chunk_coords = [&](uint32_t n, int& m0, int& col0) {
-        const long long t = pair + (long long)(n / (BN / 64)) * num_pairs;
-        m0 = int(t / p.tiles_n) * (2 * BM) + int(rank) * BM;
-        col0 = int(t % p.tiles_n) * BN + int(n % (BN / 64)) * 64;
+        const int t = pair + int(n / (BN / 64)) * num_pairs;
+        m0 = (t / p.tiles_n) * (2 * BM) + int(rank) * BM;
+        col0 = (t % p.tiles_n) * BN + int(n % (BN / 64)) * 64;
       };
       auto fetch_residual = [&](uint32_t n) {
         if (n >= my_chunks) return;
@@ -228,7 +213,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         chunk_coords(n, m0, col0);
         const int b = int(n % OUT_BUFS);
         mbar_expect_tx(&res_full[b], OUT_STAGE_BYTES);
-        tma_load_2d(stage_out0 + b * OUT_STAGE_BYTES, &tmRes, &res_full[b], col0, int(m0 % p.res_rows));
+        tma_load_2d(stage_out0 + b * OUT_STAGE_BYTES, &tmRes, &res_full[b], col0, m0 % p.res_rows);
       };
       if (kRes)
         for (int n = 0; n < OUT_BUFS; ++n) fetch_residual(uint32_t(n));      // every staging tile starts out free
@@ -262,39 +247,29 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t lane_base = uint32_t(warp & 3) * 32u;
     const int qc = (warp - 2) >> 2;                      // which CW columns of every 64-column chunk
     const int erow = int(lane_base) + lane;
-    const int et = int(threadIdx.x) - 64;
     const uint32_t acc_empty0 = map_to_cta(&acc_empty[0], 0);        // the leader's barrier
-    uint32_t acc = 0, acc_phase = 0, chunk_no = 0, it = 0;
-    // Per-column bias / weight scale of a tile sit in shared memory, per-row activation scale in a register.  Those
-    // of the next tile are fetched into registers at the top of a tile and put in place at its end, so that their
-    // latency is never waited for.
-    float next_bias = 0.f, next_wscale = 0.f, next_ascale = 1.0f;
-    auto fetch_tile_params = [&](long long t) {
-      if (t >= p.num_tiles) return;
-      const int n0 = int(t % p.tiles_n) * BN;
-      if (et < BN) {
-        if (kBias) next_bias = __ldg(p.bias + n0 + et);
-        if (kInt8) next_wscale = __ldg(p.w_scale + n0 + et);
-      }
-      const long long row = (long long)int(t / p.tiles_n) * (2 * BM) + int(rank) * BM + erow;
+    uint32_t acc = 0, acc_phase = 0, chunk_no = 0;
+    // Per-column bias and weight scale are read from global memory where they are used (every lane of a warp reads
+    // the same 32 bytes, which stay in L1); the per-row activation scale of the next tile is fetched a tile ahead.
+    float next_ascale = 1.0f;
+    auto fetch_ascale = [&](int t) {
       next_ascale = 1.0f;
-      if (kInt8 && row < p.M) next_ascale = __ldg(p.a_scale + row);
+      if (!kInt8 || t >= p.num_tiles) return;
+      const long long row = (long long)(t / p.tiles_n) * (2 * BM) + int(rank) * BM + erow;
+      if (row < p.M) next_ascale = __ldg(p.a_scale + row);
     };
-    fetch_tile_params(pair);
-    if (et < BN) {
-      if (kBias) s_bias0[et] = next_bias;
-      if (kInt8) s_wscale0[et] = next_wscale;
-    }
-    for (long long tile = pair; tile < p.num_tiles; tile += num_pairs, ++it) {
-      const int m0 = int(tile / p.tiles_n) * (2 * BM) + int(rank) * BM;
+    fetch_ascale(pair);
+    for (int tile = pair; tile < p.num_tiles; tile += num_pairs) {
+      const int m0 = (tile / p.tiles_n) * (2 * BM) + int(rank) * BM;
+      const int n0 = (tile % p.tiles_n) * BN;
       const long long row = (long long)m0 + erow;
       const bool row_ok = row < p.M;
-      const float* s_bias = s_bias0 + (it & 1u) * BN;
-      const float* s_wscale = s_wscale0 + (it & 1u) * BN;
+      const float* g_bias = p.bias + n0;
+      const float* g_wscale = p.w_scale + n0;
       const float a_scale = next_ascale;
-      fetch_tile_params(tile + num_pairs);
-      const bool got = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, 4);
-      if (!epi_all<EPI_THREADS>(got)) break;            // also publishes this tile's bias / scale columns
+      fetch_ascale(tile + num_pairs);
+      // a wait that gives up ends the loop for the whole warp (its lanes meet again in __syncwarp below)
+      if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, 4))) break;
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (lane_base << 16) + acc * BN + qc * CW;
       // The chunk loop is software-pipelined: the tensor-memory load of chunk c + 1 is in flight while chunk c goes
@@ -321,37 +296,39 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const uint32_t(&r)[CW] = rbuf[c & 1];
         const uint32_t sbuf = chunk_no % OUT_BUFS, suse = chunk_no / OUT_BUFS;
         uint8_t* stage_out = stage_out0 + sbuf * OUT_STAGE_BYTES;
-        uint4 rv[NV];
-        if (kRes) {
-          // a wait that gives up has raised the abort flag and the status word; the next accumulator wait ends the loop
-          mbar_wait(&res_full[sbuf], suse & 1u, abort_flag, p.status, 5);
-          const uint8_t* srow = stage_out + erow * 128;
+        // Is the staging tile ready (the residual has landed / the store of the chunk that used it before has read
+        // it)?  Asked before the arithmetic, without blocking, so that the answer costs nothing when it is yes.
+        bool ready = true;
+        if (kRes) ready = mbar_test_wait(&res_full[sbuf], suse & 1u);
+        else if (suse > 0) ready = mbar_test_wait(&stage_free[sbuf], (suse - 1u) & 1u);
+        float v[NV][8];
 #pragma unroll
-          for (int u = 0; u < NV; ++u)
-            rv[u] = *reinterpret_cast<const uint4*>(srow + (((qc * NV + u) ^ (erow & 7)) << 4));
+        for (int u = 0; u < NV; ++u) {
+          const int ct0 = c * 64 + qc * CW + u * 8;      // first of these eight columns inside the tile
+          epilogue8<kInt8, kInt8, kBias, kGelu>(r + u * 8, a_scale, g_wscale + ct0, g_bias + ct0, v[u]);
+        }
+        // a wait that gives up has raised the abort flag and the status word; the next accumulator wait ends the loop
+        if (!ready) {
+          if (kRes) mbar_wait(&res_full[sbuf], suse & 1u, abort_flag, p.status, 5);
+          else mbar_wait(&stage_free[sbuf], (suse - 1u) & 1u, abort_flag, p.status, 7);
         }
         uint4 packed[NV];
 #pragma unroll
         for (int u = 0; u < NV; ++u) {
-          const int ct0 = c * 64 + qc * CW + u * 8;      // first of these eight columns inside the tile
-          float v[8];
-          epilogue8<kInt8, kInt8, kBias, kGelu>(r + u * 8, a_scale, s_wscale + ct0, s_bias + ct0, v);
           if (kRes) {
-            const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv[u]);
+            const uint4 rv = *reinterpret_cast<const uint4*>(stage_out + erow * 128 + (((qc * NV + u) ^ (erow & 7)) << 4));
+            const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const float2 f = __bfloat1622float2(rp[j]);
-              v[2 * j] += f.x;
-              v[2 * j + 1] += f.y;
+              v[u][2 * j] += f.x;
+              v[u][2 * j + 1] += f.y;
             }
           }
-          packed[u] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
-                                 pack_bf16x2(v[6], v[7]));
+          packed[u] = make_uint4(pack_bf16x2(v[u][0], v[u][1]), pack_bf16x2(v[u][2], v[u][3]),
+                                 pack_bf16x2(v[u][4], v[u][5]), pack_bf16x2(v[u][6], v[u][7]));
           if (p.row_absmax != nullptr) m2 = absmax8(m2, packed[u]);
         }
-        // The staging tile is free once the store of the chunk that used it before has read it (with a residual
-        // the residual's arrival, waited for above, says as much).
-        if (!kRes && suse > 0) mbar_wait(&stage_free[sbuf], (suse - 1u) & 1u, abort_flag, p.status, 7);
         if (p.hm_group == 0) {
           uint8_t* srow = stage_out + erow * 128;
 #pragma unroll
@@ -374,10 +351,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       // non-negative floats order like their bit patterns: one integer atomic per row and tile
       if (p.row_absmax != nullptr && row_ok)
         atomicMax(reinterpret_cast<int*>(p.row_absmax + row), __float_as_int(absmax_fold(m2)));
-      if (et < BN) {                                      // the other half of the buffers: nobody reads it in this tile
-        if (kBias) s_bias0[((it & 1u) ^ 1u) * BN + et] = next_bias;
-        if (kInt8) s_wscale0[((it & 1u) ^ 1u) * BN + et] = next_wscale;
-      }
       if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1u; }
     }
   }
@@ -421,6 +394,9 @@ int launch_gemm_pair(bool int8, const void* A, int64_t lda, const void* W, int64
   // box wants 16-byte aligned rows
   if (res && ((res_rows < M && res_rows % BM) || (ldr * 2) % 16 || (reinterpret_cast<uintptr_t>(residual) & 15u)))
     return SAMB_E_SHAPE;
+  // the epilogue reads bias and weight scale in 16-byte pieces; tile arithmetic is 32-bit
+  if ((reinterpret_cast<uintptr_t>(bias) | reinterpret_cast<uintptr_t>(w_scale)) & 15u) return SAMB_E_SHAPE;
+  if (((M + 2 * BM - 1) / (2 * BM)) * (N / BN) >= (1ll << 31) || M >= (1ll << 31)) return SAMB_E_SHAPE;
   auto kern = int8 ? pick_pair<true>(epilogue) : pick_pair<false>(epilogue);
   if (kern == nullptr) return SAMB_E_SHAPE;
   const int esz = int8 ? 1 : 2;
@@ -473,13 +449,13 @@ int launch_gemm_pair(bool int8, const void* A, int64_t lda, const void* W, int64
   p.row_absmax = row_absmax;
   p.status = status;
   p.M = M;
-  p.res_rows = res_rows;
+  p.res_rows = int(res_rows < M ? res_rows : M);
   p.N = N;
   p.K = K;
   p.k_slabs = (K * esz + SLAB_BYTES - 1) / SLAB_BYTES;
   p.last_ksteps = (K * esz - (p.k_slabs - 1) * SLAB_BYTES + 31) / 32;
   p.tiles_n = N / BN;
-  p.num_tiles = ((M + 2 * BM - 1) / (2 * BM)) * p.tiles_n;
+  p.num_tiles = int(((M + 2 * BM - 1) / (2 * BM)) * p.tiles_n);
   p.hm_group = head_dim / 16;
 
   const int smem_bytes = pair_smem_bytes(int8, res);
