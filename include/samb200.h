@@ -173,6 +173,13 @@ int samb_layernorm2d_nchw(const void* x, const float* gamma, const float* beta, 
 int samb_attn_relpos_global(const void* q, const void* k, const void* v, const void* rel_h, const void* rel_w,
                             void* o, int B, int H, int N, int d, float scale, int32_t* status, void* stream);
 
+/* The same operator on float16 tensors (q, k, v, rel_h, rel_w, o all float16): the tensor core multiplies
+ * float16 operands, the probabilities are rounded to float16, everything else (logits, softmax statistics, output
+ * accumulator) is fp32 as above.  ref: the float16 half of the reference's own test of the operator,
+ * test/test_flash_4.py:10-43 (dtype sweep). */
+int samb_attn_relpos_global_f16(const void* q, const void* k, const void* v, const void* rel_h, const void* rel_w,
+                                void* o, int B, int H, int N, int d, float scale, int32_t* status, void* stream);
+
 /* Same attention reading q/k/v from the head-major qkv buffer qkv[3*H][B*N][d] written by
  * samb_gemm_*_heads (planes: q heads, k heads, v heads) and writing o[B*N, o_pitch]
  * with head h at columns [h*d, (h+1)*d) (the layout proj consumes, image_encoder.py:249).  The bias

@@ -38,6 +38,7 @@ SIGNATURES = {
                                             c_int, c_int, _P, _P]),
     "samb_layernorm2d_nchw": (c_int, [_P, _P, _P, _P, c_int64, c_int, c_int, c_float, c_int, _P]),
     "samb_attn_relpos_global": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, _P, _P]),
+    "samb_attn_relpos_global_f16": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, _P, _P]),
     "samb_attn_relpos_global_qkv": (c_int, [_P, _P, c_int64, c_int, c_int, _P, c_int64, c_int, c_int, c_int, c_int,
                                             c_float, _P, _P]),
     "samb_attn_relpos_global_tables": (c_int, [_P, _P, _P, c_int64, c_int, c_int, c_int, c_int, c_float, _P, _P]),

@@ -29,6 +29,8 @@
 // 128B-swizzled K-major layout; O accumulates in TMEM across key tiles.  The running maximum is only
 // raised when it would grow by more than 2^8 (probabilities stay below 256, exact enough in fp32 /
 // bf16); only then is O rescaled in place, which after the first few key tiles almost never happens.
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace samb {
@@ -79,13 +81,30 @@ __device__ __forceinline__ uint32_t bfpack2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// Two 16-bit elements of the tensors' type (bfloat16, or float16 when kHalf) in one word.
+template <bool kHalf>
+__device__ __forceinline__ uint32_t pack_pair(float lo, float hi) {
+  if constexpr (kHalf) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    return bfpack2(lo, hi);
+  }
+}
+template <bool kHalf>
+__device__ __forceinline__ float2 unpack_pair(uint32_t w) {
+  if constexpr (kHalf) return __half22float2(*reinterpret_cast<const __half2*>(&w));
+  else return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 
-template <int D>
+// kHalf: q, k, v, the bias tensors and the output are float16 instead of bfloat16 (bias tensors only: the table
+// modes belong to the bf16 encoder).  Logits, softmax statistics and the output accumulator are fp32 either way.
+template <int D, bool kHalf>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmT,
@@ -179,8 +198,9 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // The whole warp runs the loop (warp-uniform control flow and descriptors); one elected lane
     // issues the tensor-core instructions and their commits.
     {
-      constexpr uint32_t idesc_s = make_idesc(kAccF32, kFmtBF16, kFmtBF16, BM, BK);
-      constexpr uint32_t idesc_o = make_idesc(kAccF32, kFmtBF16, kFmtBF16, BM, D, false, /*B MN-major*/ true);
+      constexpr uint32_t kFmt = kHalf ? kFmtF16 : kFmtBF16;
+      constexpr uint32_t idesc_s = make_idesc(kAccF32, kFmt, kFmt, BM, BK);
+      constexpr uint32_t idesc_o = make_idesc(kAccF32, kFmt, kFmt, BM, D, false, /*B MN-major*/ true);
       // Base descriptors; the start-address field counts 16-byte units, so "+ bytes / 16" moves a tile.
       const uint64_t dq = make_smem_desc(smem_u32(smem + L::OFF_Q), 16, 256, kSwizzle32B);        // K-major, 32B swizzle
       const uint64_t dk = make_smem_desc(smem_u32(smem + L::OFF_KV), 16, 256, kSwizzle32B);
@@ -408,8 +428,10 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int tt = 0; tt < 4; ++tt) {
           const int k0 = u * 8 + 2 * tt;
           const uint32_t pr = rw[u * 4 + tt];
-          wpk[u * 4 + tt] = bfpack2(__uint_as_float(pr << 16) * inv_scale, __uint_as_float(pr & 0xffff0000u) * inv_scale);
-          e[tt] = ((i & 63) == k0 ? 0x3F80u : 0u) | ((i & 63) == k0 + 1 ? 0x3F800000u : 0u);
+          const float2 prf = unpack_pair<kHalf>(pr);
+          wpk[u * 4 + tt] = pack_pair<kHalf>(prf.x * inv_scale, prf.y * inv_scale);
+          constexpr uint32_t kOne = kHalf ? 0x3C00u : 0x3F80u;            // 1.0 in the operands' type
+          e[tt] = ((i & 63) == k0 ? kOne : 0u) | ((i & 63) == k0 + 1 ? (kOne << 16) : 0u);
         }
         const int phys = (u ^ (i & 7)) << 4;
         if (t == 0) *reinterpret_cast<uint4*>(e_row + phys) = make_uint4(e[0], e[1], e[2], e[3]);
@@ -432,7 +454,8 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const uint32_t par = uint32_t(j) & 1u;
       // rel_h of this key tile's two raster rows
       const uint32_t hpair = relh_loc[j];
-      const float bh0 = __uint_as_float(hpair << 16) * kLog2e, bh1 = __uint_as_float(hpair & 0xffff0000u) * kLog2e;
+      const float2 hpf = unpack_pair<kHalf>(hpair);
+      const float bh0 = hpf.x * kLog2e, bh1 = hpf.y * kLog2e;
       if (!(ok = mbar_wait(&s_full[t], par, abort_flag, p.status, 8))) break;
       tc_fence_after();
       uint32_t s[128];
@@ -482,7 +505,8 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           l_blk += e[q];
         }
         *reinterpret_cast<uint4*>(p_tile + (u >> 3) * 16384 + (((u & 7) ^ (i & 7)) << 4)) =
-            make_uint4(bfpack2(e[0], e[1]), bfpack2(e[2], e[3]), bfpack2(e[4], e[5]), bfpack2(e[6], e[7]));
+            make_uint4(pack_pair<kHalf>(e[0], e[1]), pack_pair<kHalf>(e[2], e[3]), pack_pair<kHalf>(e[4], e[5]),
+                       pack_pair<kHalf>(e[6], e[7]));
       }
       l_run += l_blk;
       tc_fence_before();
@@ -504,9 +528,11 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
         for (int q = 0; q < 16; ++q) f[q] = __uint_as_float(r[q]) * inv_l;
         *reinterpret_cast<uint4*>(orow + c * 16) =
-            make_uint4(bfpack2(f[0], f[1]), bfpack2(f[2], f[3]), bfpack2(f[4], f[5]), bfpack2(f[6], f[7]));
+            make_uint4(pack_pair<kHalf>(f[0], f[1]), pack_pair<kHalf>(f[2], f[3]), pack_pair<kHalf>(f[4], f[5]),
+                       pack_pair<kHalf>(f[6], f[7]));
         *reinterpret_cast<uint4*>(orow + c * 16 + 8) =
-            make_uint4(bfpack2(f[8], f[9]), bfpack2(f[10], f[11]), bfpack2(f[12], f[13]), bfpack2(f[14], f[15]));
+            make_uint4(pack_pair<kHalf>(f[8], f[9]), pack_pair<kHalf>(f[10], f[11]), pack_pair<kHalf>(f[12], f[13]),
+                       pack_pair<kHalf>(f[14], f[15]));
       }
     }
   }
@@ -519,7 +545,7 @@ attn_global_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   }
 }
 
-template <int D>
+template <int D, bool kHalf = false>
 int launch_d(const void* q, const void* k, const void* v, long long rows, long long cols, long long pitch_elems,
              const AttnParams& p, int BH, void* stream, const void* tables = nullptr) {
   CUtensorMap tm[4];
@@ -541,7 +567,7 @@ int launch_d(const void* q, const void* k, const void* v, long long rows, long l
                                 CU_TENSOR_MAP_SWIZZLE_32B))
       return e;
   }
-  auto kern = attn_global_kernel<D>;
+  auto kern = attn_global_kernel<D, kHalf>;   // the copies move 2-byte elements: one tensor-map type serves both
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<D>::BYTES) != cudaSuccess)
     return SAMB_E_LAUNCH;
   const long long grid = (long long)BH * (p.N / (2 * BM));
@@ -555,8 +581,9 @@ int launch_d(const void* q, const void* k, const void* v, long long rows, long l
 
 extern "C" {
 
-int samb_attn_relpos_global(const void* q, const void* k, const void* v, const void* rel_h, const void* rel_w,
-                            void* o, int B, int H, int N, int d, float scale, int32_t* status, void* stream) {
+static int attn_relpos_global_any(bool half, const void* q, const void* k, const void* v, const void* rel_h,
+                                  const void* rel_w, void* o, int B, int H, int N, int d, float scale, int32_t* status,
+                                  void* stream) {
   using namespace samb;
   if (!q || !k || !v || !rel_h || !rel_w || !o || !status) return SAMB_E_BADARG;
   if (B <= 0 || H <= 0 || N <= 0) return SAMB_E_BADARG;
@@ -577,7 +604,20 @@ int samb_attn_relpos_global(const void* q, const void* k, const void* v, const v
   p.scale = scale;
   p.status = status;
   const long long rows = (long long)B * H * N;
+  if (half)
+    return d == 80 ? launch_d<80, true>(q, k, v, rows, d, d, p, B * H, stream)
+                   : launch_d<64, true>(q, k, v, rows, d, d, p, B * H, stream);
   return d == 80 ? launch_d<80>(q, k, v, rows, d, d, p, B * H, stream) : launch_d<64>(q, k, v, rows, d, d, p, B * H, stream);
+}
+
+int samb_attn_relpos_global(const void* q, const void* k, const void* v, const void* rel_h, const void* rel_w,
+                            void* o, int B, int H, int N, int d, float scale, int32_t* status, void* stream) {
+  return attn_relpos_global_any(false, q, k, v, rel_h, rel_w, o, B, H, N, d, scale, status, stream);
+}
+
+int samb_attn_relpos_global_f16(const void* q, const void* k, const void* v, const void* rel_h, const void* rel_w,
+                                void* o, int B, int H, int N, int d, float scale, int32_t* status, void* stream) {
+  return attn_relpos_global_any(true, q, k, v, rel_h, rel_w, o, B, H, N, d, scale, status, stream);
 }
 
 int samb_attn_relpos_global_qkv(const void* qkv, const void* tab, int64_t ldt, int t_head_stride, int t_w_off, void* o,
