@@ -35,6 +35,7 @@ namespace {
 constexpr int NUM_THREADS = 352;   // TMA warp, tile-0 MMA warp, 8 softmax warps, tile-1 MMA warp
 constexpr int TMEM_COLS = 512;   // tile 0 at column 0, tile 1 at column 256
 constexpr int kOCol = 112;       // P V result inside a tile's columns (P uses [0, 104))
+constexpr int kTCol = 192;       // mode 2: products with the table block, 64 columns (free once an item's P is complete)
 constexpr int STAGES = 2;
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -121,7 +122,7 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
-  uint64_t* full = bars + 0;        // [STAGES] q/k/v of an item have landed
+  uint64_t* full = bars + 0;        // [STAGES] k/v of an item have landed
   uint64_t* empty = bars + 2;       // [STAGES] every MMA reading the stage has finished and its output store was read
   uint64_t* pro_done = bars + 4;    // [2]      this item's rel_w rows of tile t are in shared memory
   uint64_t* s_full = bars + 6;      // [2]      logits of tile t are in TMEM
@@ -133,7 +134,8 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                                     //          barriers per tile because a tile may be a whole item ahead of the other.
   uint64_t* t_full = bars + 18;     // [2]      mode 2: the table products of tile t are in TMEM
   uint64_t* tab_full = bars + 20;   //          mode 2: the table block is in shared memory
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+  uint64_t* q_full = bars + 21;     // [STAGES] q of an item has landed (ahead of k/v: the table products only need q)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 23);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   unsigned int* out_cnt = reinterpret_cast<unsigned int*>(tmem_slot + 2);   // [STAGES] softmax warps that staged their rows
 
@@ -142,7 +144,7 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     // a stage is free when both tiles' MMAs that read it have finished AND the output store staged in it has been read
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 3); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&q_full[s], 1); mbar_init(&empty[s], 3); }
     out_cnt[0] = out_cnt[1] = 0u;
     for (int t = 0; t < 2; ++t) {
       mbar_init(&pro_done[t], 4);
@@ -208,18 +210,23 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           const int ww = p.nw * p.nw;
           const int b = w / ww, wi = w - b * ww;
           const int wy = wi / p.nw, wx = wi - wy * p.nw;
-          mbar_expect_tx(&full[stage], 3 * CH * N * 32);
+          mbar_expect_tx(&q_full[stage], CH * N * 32);
+          mbar_expect_tx(&full[stage], 2 * CH * N * 32);
 #pragma unroll
-          for (int c = 0; c < CH; ++c) {           // one WS x WS box per 16-column chunk
-            tma_load_4d(st + c * L::Q_CHUNK, &tmQ, &full[stage], c * 16, wx * WS, wy * WS, h * p.B + b);
+          for (int c = 0; c < CH; ++c)             // one WS x WS box per 16-column chunk; q first
+            tma_load_4d(st + c * L::Q_CHUNK, &tmQ, &q_full[stage], c * 16, wx * WS, wy * WS, h * p.B + b);
+#pragma unroll
+          for (int c = 0; c < CH; ++c)
             tma_load_4d(st + L::OFF_K + c * L::KV_CHUNK, &tmQ, &full[stage], c * 16, wx * WS, wy * WS, (p.H + h) * p.B + b);
+#pragma unroll
+          for (int c = 0; c < CH; ++c)
             tma_load_4d(st + L::OFF_V + c * L::KV_CHUNK, &tmQ, &full[stage], c * 16, wx * WS, wy * WS, (2 * p.H + h) * p.B + b);
-          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
           continue;
         }
-        mbar_expect_tx(&full[stage], L::STAGE);
-        tma_load_3d(st, &tmQ, &full[stage], 0, rq, 0);
+        mbar_expect_tx(&q_full[stage], CH * L::Q_CHUNK);
+        mbar_expect_tx(&full[stage], 2 * CH * L::KV_CHUNK);
+        tma_load_3d(st, &tmQ, &q_full[stage], 0, rq, 0);
         tma_load_3d(st + L::OFF_K, &tmK, &full[stage], 0, rk, 0);
         tma_load_3d(st + L::OFF_V, &tmV, &full[stage], 0, rv, 0);
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -244,24 +251,30 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const uint64_t dtab = make_smem_desc(smem_u32(smem + L::OFF_TAB), 16, 256, kSwizzle32B);
     uint32_t stage = 0, phase = 0, k = 0;
     bool ok = true;
-    if (p.rel_mode == 2) ok = mbar_wait(tab_full, 0, abort_flag, p.status, 11);
+    // Mode 2: the products of an item's queries with the table block go to columns kTCol.. of the tile, which
+    // are free from the moment the previous item's probabilities are complete (its logits are consumed, its P and O
+    // sit below kTCol).  They are issued one item ahead, in front of the previous item's P V, so that the softmax
+    // threads can pick an item's bias values while that P V runs instead of at the head of the item's own chain.
+    const bool ahead = p.rel_mode == 2;
+    auto issue_tables = [&](uint32_t st) {
+      tc_fence_after();
+      if (elect_one()) {
+        const uint64_t dq = dq0 + st * (L::STAGE / 16);
+#pragma unroll
+        for (int c = 0; c < CH; ++c)
+          umma_f16_ss(d_tmem + kTCol, dq + (c * L::Q_CHUNK + t * 4096) / 16, dtab + c * (L::TAB_CHUNK / 16), idesc_t, c != 0);
+        tc_commit(&t_full[t]);
+      }
+      __syncwarp();
+    };
+    if (ahead && int(blockIdx.x) < p.items) {
+      ok = mbar_wait(tab_full, 0, abort_flag, p.status, 11) && mbar_wait(&q_full[0], 0, abort_flag, p.status, 13);
+      if (ok) issue_tables(0);
+    }
     for (int it = blockIdx.x; ok && it < p.items; it += gridDim.x, ++k) {
       const uint32_t par = k & 1u;
+      if (!(ok = mbar_wait(&q_full[stage], phase, abort_flag, p.status, 2))) break;
       if (!(ok = mbar_wait(&full[stage], phase, abort_flag, p.status, 2))) break;
-      if (p.rel_mode == 2) {
-        // table products of this tile's queries into columns 0..63.  The tensor pipe runs this CTA's products in
-        // issue order, so the previous item's P V (which read P from these columns) is done by then; the
-        // previous output sits in columns kOCol.. and is not touched.
-        tc_fence_after();
-        if (elect_one()) {
-          const uint64_t dq = dq0 + stage * (L::STAGE / 16);
-#pragma unroll
-          for (int c = 0; c < CH; ++c)
-            umma_f16_ss(d_tmem, dq + (c * L::Q_CHUNK + t * 4096) / 16, dtab + c * (L::TAB_CHUNK / 16), idesc_t, c != 0);
-          tc_commit(&t_full[t]);
-        }
-        __syncwarp();
-      }
       if (!(ok = mbar_wait(&pro_done[t], par, abort_flag, p.status, 3))) break;
       if (!(ok = mbar_wait(&t_free[t], par ^ 1u, abort_flag, p.status, 4))) break;
       tc_fence_after();
@@ -277,6 +290,13 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       __syncwarp();
       if (!(ok = mbar_wait(&p_full[t], par, abort_flag, p.status, 5))) break;
+      // the next item's table products go first when its queries have landed (they normally have), else after P V
+      const uint32_t nstage = stage + 1 == STAGES ? 0u : stage + 1, nphase = nstage == 0 ? phase ^ 1u : phase;
+      bool tables_due = ahead && it + int(gridDim.x) < p.items;
+      if (tables_due && mbar_test_wait(&q_full[nstage], nphase)) {
+        issue_tables(nstage);
+        tables_due = false;
+      }
       tc_fence_after();
       if (elect_one()) {                           // P V of this tile: A = P from TMEM, B = V
         const uint64_t dv = dv0 + stage * (L::STAGE / 16);
@@ -287,7 +307,12 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tc_commit(&empty[stage]);                  // this tile has issued everything that reads the stage
       }
       __syncwarp();
-      if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      if (tables_due) {
+        if (!(ok = mbar_wait(&q_full[nstage], nphase, abort_flag, p.status, 13))) break;
+        issue_tables(nstage);
+      }
+      stage = nstage;
+      phase = nphase;
     }
   } else {
     // ---------------------------------------------------------------- softmax (one thread = one query row)
@@ -370,81 +395,101 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
     for (int q = 0; q < 12; ++q) rawv[0][q] = rawv[1][q] = 0u;
 
+    // ---- an item's bias: rel_h (bf16 pairs, kept in registers until the item's softmax), rel_w/scale into the
+    // A-operand tile, and for border windows the pad rows of the item's K / V tiles.  `kp` is the item's position in
+    // this CTA's sequence (stage and barrier parities follow from it).
+    auto prologue = [&](int it_p, uint32_t kp, uint32_t (&bhp)[WS / 2]) -> bool {
+      bool good = true;
+      // border window (raster layout): this thread's 16-byte piece of the projection bias, requested first
+      int vy = WS, vx = WS;
+      uint4 bk = make_uint4(0u, 0u, 0u, 0u), bv = bk;
+      const int ptid = (warp & 3) * 32 + lane, piece = ptid % (2 * CH);
+      if (p.qkv_fused == 2) {
+        const int wi = (it_p / p.H) % (p.nw * p.nw);
+        if (wi / p.nw == p.nw - 1) vy = p.vlast;
+        if (wi % p.nw == p.nw - 1) vx = p.vlast;
+        if ((vy < WS || vx < WS) && ptid < 12 * 2 * CH) {
+          bk = __ldg(reinterpret_cast<const uint4*>(p.kv_bias + (size_t)(p.H + it_p % p.H) * D) + piece);
+          bv = __ldg(reinterpret_cast<const uint4*>(p.kv_bias + (size_t)(2 * p.H + it_p % p.H) * D) + piece);
+        }
+      }
+      float rw[16];
+      if (p.rel_mode == 2) {
+        // this row's products with the tables are in columns kTCol.. of the tile (rel_pos_h first, rel_pos_w 32
+        // columns on); rounded to bf16 as a stored product tensor would be, so that both sources give the same bits
+        good = mbar_wait(&t_full[t], kp & 1u, abort_flag, p.status, 12);
+        tc_fence_after();
+        uint32_t th[32], tw[32];
+        tmem_ld_32x32b_x32(lane_addr + kTCol, th);
+        tmem_ld_32x32b_x32(lane_addr + kTCol + 32, tw);
+        tmem_ld_wait();
+        tc_fence_before();                                       // the next logits product overwrites part of these columns
+        float sel[WS];
+        select_shifted<WS>(th, qh & 15, sel);
+#pragma unroll
+        for (int q = 0; q < WS / 2; ++q) bhp[q] = wpack2(sel[2 * q], sel[2 * q + 1]);
+        select_shifted<WS>(tw, qw, sel);
+        const float inv_s = 1.0f / p.scale;
+#pragma unroll
+        for (int q = 0; q < 16; ++q) rw[q] = q < WS ? round_bf16(sel[q < WS ? q : 0] * inv_s) : 0.f;
+      } else {
+        uint32_t eh[WS], ew[WS];
+        bias_elems(0, sh_h, eh);
+        bias_elems(1, sh_w, ew);
+#pragma unroll
+        for (int q = 0; q < 16; ++q) rw[q] = q < WS ? bf16_bits_to_float(ew[q < WS ? q : 0]) * inv_scale : 0.f;
+#pragma unroll
+        for (int q = 0; q < WS / 2; ++q) bhp[q] = eh[2 * q] | (eh[2 * q + 1] << 16);
+      }
+      uint8_t* rrow = smem + L::OFF_RELW + n * 32;
+      *reinterpret_cast<uint4*>(rrow + ((0 ^ sw) << 4)) =
+          make_uint4(wpack2(rw[0], rw[1]), wpack2(rw[2], rw[3]), wpack2(rw[4], rw[5]), wpack2(rw[6], rw[7]));
+      *reinterpret_cast<uint4*>(rrow + ((1 ^ sw) << 4)) =
+          make_uint4(wpack2(rw[8], rw[9]), wpack2(rw[10], rw[11]), wpack2(rw[12], rw[13]), wpack2(rw[14], rw[15]));
+      if (vy < WS || vx < WS) {
+        // border window: pad tokens' K and V rows <- projection bias.  Both tile groups write both (the same
+        // values), so neither tile's products depend on the other group's progress.
+        good = good && mbar_wait(&full[kp % STAGES], (kp / STAGES) & 1u, abort_flag, p.status, 9);   // the zero fill has landed
+        const int n_pad = vy * (WS - vx) + (WS - vy) * WS;
+        const uint8_t* tabp = smem + L::OFF_PADTAB + (vy == WS ? 0 : (vx == WS ? 1 : 2)) * 256;
+        uint8_t* stage_base = smem + (kp % STAGES) * L::STAGE;
+        // thread = one 16-byte piece (of the 2 * CH per row) for every 12th pad row
+        const int c = piece >> 1, hf = piece & 1;
+        if (good && ptid < 12 * 2 * CH) {
+          for (int pi = ptid / (2 * CH); pi < n_pad; pi += 12) {
+            const int r = tabp[pi];
+            const int off = c * L::KV_CHUNK + r * 32 + ((hf ^ ((r >> 2) & 1)) << 4);
+            *reinterpret_cast<uint4*>(stage_base + L::OFF_K + off) = bk;
+            *reinterpret_cast<uint4*>(stage_base + L::OFF_V + off) = bv;
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive_warp(&pro_done[t]);
+      return good;
+    };
+
+    // Order of work per thread.  Mode 2: softmax of item k, then the bias of item k + 1 (its table products were issued
+    // ahead of item k's P V and land while that runs), then item k's output; the logits product of item k + 1 can
+    // start as soon as the output accumulator has been read.  Modes 0 / 1 (bias from global memory): the bias of an
+    // item at the head of the item, from values requested during the previous item's P V.
+    const bool ahead = p.rel_mode == 2;
     int it = blockIdx.x;
-    if (it < p.items && p.rel_mode != 2) fetch_bias(it);
     bool ok = true;
+    uint32_t bhp[WS / 2];
+#pragma unroll
+    for (int q = 0; q < WS / 2; ++q) bhp[q] = 0u;
+    if (it < p.items) {
+      if (!ahead) fetch_bias(it);
+      ok = prologue(it, 0u, bhp);
+    }
     for (uint32_t k = 0; ok && it < p.items; it += gridDim.x, ++k) {
       const uint32_t par = k & 1u;
-      // ---- this item's bias: rel_h into registers (log2 domain), rel_w/scale into the A-operand tile
       float bh[WS];
-      {
-        // border window (raster layout): this thread's 16-byte piece of the projection bias, requested first
-        int vy = WS, vx = WS;
-        uint4 bk = make_uint4(0u, 0u, 0u, 0u), bv = bk;
-        const int ptid = (warp & 3) * 32 + lane, piece = ptid % (2 * CH);
-        if (p.qkv_fused == 2) {
-          const int wi = (it / p.H) % (p.nw * p.nw);
-          if (wi / p.nw == p.nw - 1) vy = p.vlast;
-          if (wi % p.nw == p.nw - 1) vx = p.vlast;
-          if ((vy < WS || vx < WS) && ptid < 12 * 2 * CH) {
-            bk = __ldg(reinterpret_cast<const uint4*>(p.kv_bias + (size_t)(p.H + it % p.H) * D) + piece);
-            bv = __ldg(reinterpret_cast<const uint4*>(p.kv_bias + (size_t)(2 * p.H + it % p.H) * D) + piece);
-          }
-        }
-        float rw[16];
-        if (p.rel_mode == 2) {
-          // this row's products with the tables are in columns 0..63 of the tile (rel_pos_h at 0, rel_pos_w at 32);
-          // rounded to bf16 as a stored product tensor would be, so that both sources give the same bits
-          ok = mbar_wait(&t_full[t], par, abort_flag, p.status, 12);
-          tc_fence_after();
-          uint32_t th[32], tw[32];
-          tmem_ld_32x32b_x32(lane_addr, th);
-          tmem_ld_32x32b_x32(lane_addr + 32, tw);
-          tmem_ld_wait();
-          tc_fence_before();                                     // the logits product overwrites these columns
-          float sel[WS];
-          select_shifted<WS>(th, qh & 15, sel);
 #pragma unroll
-          for (int q = 0; q < WS; ++q) bh[q] = round_bf16(sel[q]) * kLog2e;
-          select_shifted<WS>(tw, qw, sel);
-          const float inv_s = 1.0f / p.scale;
-#pragma unroll
-          for (int q = 0; q < 16; ++q) rw[q] = q < WS ? round_bf16(sel[q < WS ? q : 0] * inv_s) : 0.f;
-        } else {
-          uint32_t eh[WS], ew[WS];
-          bias_elems(0, sh_h, eh);
-          bias_elems(1, sh_w, ew);
-#pragma unroll
-          for (int q = 0; q < 16; ++q) rw[q] = q < WS ? bf16_bits_to_float(ew[q < WS ? q : 0]) * inv_scale : 0.f;
-#pragma unroll
-          for (int q = 0; q < WS; ++q) bh[q] = bf16_bits_to_float(eh[q]) * kLog2e;
-        }
-        uint8_t* rrow = smem + L::OFF_RELW + n * 32;
-        *reinterpret_cast<uint4*>(rrow + ((0 ^ sw) << 4)) =
-            make_uint4(wpack2(rw[0], rw[1]), wpack2(rw[2], rw[3]), wpack2(rw[4], rw[5]), wpack2(rw[6], rw[7]));
-        *reinterpret_cast<uint4*>(rrow + ((1 ^ sw) << 4)) =
-            make_uint4(wpack2(rw[8], rw[9]), wpack2(rw[10], rw[11]), wpack2(rw[12], rw[13]), wpack2(rw[14], rw[15]));
-        if (vy < WS || vx < WS) {
-          // border window: pad tokens' K and V rows <- projection bias.  Both tile groups write both (the same
-          // values), so neither tile's products depend on the other group's progress.
-          ok = ok && mbar_wait(&full[k % STAGES], (k / STAGES) & 1u, abort_flag, p.status, 9);   // the zero fill has landed
-          const int n_pad = vy * (WS - vx) + (WS - vy) * WS;
-          const uint8_t* tabp = smem + L::OFF_PADTAB + (vy == WS ? 0 : (vx == WS ? 1 : 2)) * 256;
-          uint8_t* stage_base = smem + (k % STAGES) * L::STAGE;
-          // thread = one 16-byte piece (of the 2 * CH per row) for every 12th pad row
-          const int c = piece >> 1, hf = piece & 1;
-          if (ok && ptid < 12 * 2 * CH) {
-            for (int pi = ptid / (2 * CH); pi < n_pad; pi += 12) {
-              const int r = tabp[pi];
-              const int off = c * L::KV_CHUNK + r * 32 + ((hf ^ ((r >> 2) & 1)) << 4);
-              *reinterpret_cast<uint4*>(stage_base + L::OFF_K + off) = bk;
-              *reinterpret_cast<uint4*>(stage_base + L::OFF_V + off) = bv;
-            }
-          }
-        }
-        fence_proxy_async_smem();
-        mbar_arrive_warp(&pro_done[t]);
-        if (!ok) break;
+      for (int q = 0; q < WS / 2; ++q) {
+        bh[2 * q] = bf16_bits_to_float(bhp[q] & 0xffffu) * kLog2e;
+        bh[2 * q + 1] = __uint_as_float(bhp[q] & 0xffff0000u) * kLog2e;
       }
       if (!(ok = mbar_wait(&s_full[t], par, abort_flag, p.status, 6))) break;
       tc_fence_after();
@@ -499,9 +544,12 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_arrive_warp(&p_full[t]);
       // The next item's bias values are requested here, where few registers are live: they land during the
       // P V product and the output staging.  (Requested before the softmax they had to be spilled, and the spill
-      // waited for the loads.)
+      // waited for the loads.)  Mode 2 picks them from the table products right away.
       const int it_next = it + gridDim.x;
-      if (it_next < p.items && p.rel_mode != 2) fetch_bias(it_next);
+      if (it_next < p.items) {
+        if (ahead) ok = prologue(it_next, k + 1u, bhp);
+        else fetch_bias(it_next);
+      }
 
       if (!(ok = mbar_wait(&o_full[t], par, abort_flag, p.status, 7))) break;
       tc_fence_after();
@@ -554,6 +602,7 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
       __syncwarp();
+      if (!ahead && it_next < p.items) ok = prologue(it_next, k + 1u, bhp);
     }
     if (lane == 0) tma_store_wait_all<0>();
   }
