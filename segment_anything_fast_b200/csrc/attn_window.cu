@@ -52,6 +52,7 @@ struct WinParams {
   int B, vlast;                  // raster mode: images, valid extent of the last window of a row / column
   const __nv_bfloat16* kv_bias;  // raster mode: qkv projection bias [3H * D] (keys / values of pad tokens)
   int items;                     // number of (window, head) pairs
+  unsigned long long mH, mWW, mNW;   // ceil(2^40 / d) for d = H, nw * nw, nw (0: divide the slow way; see fdiv)
   float scale;
   int* status;
 };
@@ -81,6 +82,15 @@ struct WinSmem {
   static_assert(BYTES <= 227 * 1024, "shared memory");
 };
 
+// x / d for 0 <= x < 2^20 with m = ceil(2^40 / d): a multiplication instead of the ~100-instruction division, which
+// sits on every item's critical path (the border-window test of the bias prologue).  m == 0: plain division.
+__device__ __forceinline__ int fdiv(int x, int d, unsigned long long m) {
+  return m ? int((static_cast<unsigned long long>(static_cast<unsigned int>(x)) * m) >> 40) : x / d;
+}
+__host__ inline unsigned long long fdiv_magic(long long items, int d) {
+  if (items >= (1ll << 20) || d <= 0) return 0ull;
+  return ((1ull << 40) + static_cast<unsigned long long>(d) - 1) / static_cast<unsigned long long>(d);
+}
 __device__ __forceinline__ uint32_t wpack2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -135,17 +145,19 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* t_full = bars + 18;     // [2]      mode 2: the table products of tile t are in TMEM
   uint64_t* tab_full = bars + 20;   //          mode 2: the table block is in shared memory
   uint64_t* q_full = bars + 21;     // [STAGES] q of an item has landed (ahead of k/v: the table products only need q)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 23);
+  uint64_t* out_ready = bars + 23;  // [STAGES] every softmax warp has staged its output rows of the item in the stage
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 25);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  unsigned int* out_cnt = reinterpret_cast<unsigned int*>(tmem_slot + 2);   // [STAGES] softmax warps that staged their rows
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     // a stage is free when both tiles' MMAs that read it have finished AND the output store staged in it has been read
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&q_full[s], 1); mbar_init(&empty[s], 3); }
-    out_cnt[0] = out_cnt[1] = 0u;
+    // (the producer sends that store itself before it waits for `empty`)
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1); mbar_init(&q_full[s], 1); mbar_init(&empty[s], 2); mbar_init(&out_ready[s], 8);
+    }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&pro_done[t], 4);
       mbar_init(&s_done[t * 2], 1); mbar_init(&s_done[t * 2 + 1], 1);
@@ -194,9 +206,29 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mbar_expect_tx(tab_full, CH * L::TAB_CHUNK);
         tma_load_3d(smem + L::OFF_TAB, &tmT, tab_full, 0, 0, 0);
       }
+      // The item's output is staged in the Q region of its stage by the softmax warps; this thread sends it (one
+      // TMA store: a WS x WS x D box of the output tensor, which drops the pad tokens of border windows by clipping)
+      // when it comes back to the stage for the load of the item after next, so no softmax warp waits for a store.
+      auto send_output = [&](int it_o, uint32_t st_o, uint32_t use_parity) -> bool {
+        if (!mbar_wait(&out_ready[st_o], use_parity, abort_flag, p.status, 14)) return false;
+        int cx = 0, cy = 0, cz = 0, cw = it_o;
+        if (p.qkv_fused) {
+          const int w = fdiv(it_o, p.H, p.mH), h = it_o - w * p.H;
+          const int ww = p.nw * p.nw;
+          const int b = fdiv(w, ww, p.mWW), wi = w - b * ww;
+          const int wy = fdiv(wi, p.nw, p.mNW), wx = wi - wy * p.nw;
+          cx = h * D; cy = wx * WS; cz = wy * WS; cw = b;
+        }
+        tma_store_4d(&tmO, smem + st_o * L::STAGE, cx, cy, cz, cw);
+        tma_store_commit();
+        tma_store_wait_read<0>();                                // the staging rows have been read
+        return true;
+      };
       uint32_t stage = 0, phase = 0;
-      for (int it = blockIdx.x; it < p.items; it += gridDim.x) {
-        const int w = it / p.H, h = it - w * p.H;
+      int j = 0;
+      bool ok = true;
+      for (int it = blockIdx.x; it < p.items; it += gridDim.x, ++j) {
+        const int w = fdiv(it, p.H, p.mH), h = it - w * p.H;
         int rq, rk, rv;                              // first row of this item in the q, k, v operands
         if (p.qkv_fused) {                           // head-major buffer: planes [q heads | k heads | v heads]
           const int R = (p.items / p.H) * N;         // rows per plane
@@ -204,12 +236,13 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         } else {
           rq = rk = rv = it * N;
         }
-        if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 1)) break;
+        if (j >= STAGES && !(ok = send_output(it - STAGES * int(gridDim.x), stage, phase ^ 1u))) break;
+        if (!(ok = mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 1))) break;
         uint8_t* st = smem + stage * L::STAGE;
         if (p.qkv_fused == 2) {
           const int ww = p.nw * p.nw;
-          const int b = w / ww, wi = w - b * ww;
-          const int wy = wi / p.nw, wx = wi - wy * p.nw;
+          const int b = fdiv(w, ww, p.mWW), wi = w - b * ww;
+          const int wy = fdiv(wi, p.nw, p.mNW), wx = wi - wy * p.nw;
           mbar_expect_tx(&q_full[stage], CH * N * 32);
           mbar_expect_tx(&full[stage], 2 * CH * N * 32);
 #pragma unroll
@@ -231,6 +264,10 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tma_load_3d(st + L::OFF_V, &tmV, &full[stage], 0, rv, 0);
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
+      // the outputs of the last items (those no later load came back for)
+      for (int r = j > STAGES ? j - STAGES : 0; ok && r < j; ++r)
+        ok = send_output(int(blockIdx.x) + r * int(gridDim.x), uint32_t(r % STAGES), uint32_t(r / STAGES) & 1u);
+      tma_store_wait_all<0>();
     }
   } else if (warp == 1 || warp == 10) {
     // ---------------------------------------------------------------- MMA issue, one warp per query tile
@@ -405,12 +442,14 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       uint4 bk = make_uint4(0u, 0u, 0u, 0u), bv = bk;
       const int ptid = (warp & 3) * 32 + lane, piece = ptid % (2 * CH);
       if (p.qkv_fused == 2) {
-        const int wi = (it_p / p.H) % (p.nw * p.nw);
-        if (wi / p.nw == p.nw - 1) vy = p.vlast;
-        if (wi % p.nw == p.nw - 1) vx = p.vlast;
+        const int w = fdiv(it_p, p.H, p.mH), h = it_p - w * p.H, ww = p.nw * p.nw;
+        const int wi = w - fdiv(w, ww, p.mWW) * ww;
+        const int wy = fdiv(wi, p.nw, p.mNW), wx = wi - wy * p.nw;
+        if (wy == p.nw - 1) vy = p.vlast;
+        if (wx == p.nw - 1) vx = p.vlast;
         if ((vy < WS || vx < WS) && ptid < 12 * 2 * CH) {
-          bk = __ldg(reinterpret_cast<const uint4*>(p.kv_bias + (size_t)(p.H + it_p % p.H) * D) + piece);
-          bv = __ldg(reinterpret_cast<const uint4*>(p.kv_bias + (size_t)(2 * p.H + it_p % p.H) * D) + piece);
+          bk = __ldg(reinterpret_cast<const uint4*>(p.kv_bias + (size_t)(p.H + h) * D) + piece);
+          bv = __ldg(reinterpret_cast<const uint4*>(p.kv_bias + (size_t)(2 * p.H + h) * D) + piece);
         }
       }
       float rw[16];
@@ -578,33 +617,9 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
       fence_proxy_async_smem();
-      // the last of the eight softmax warps to stage its rows sends the item's store
-      __syncwarp();
-      if (lane == 0) {
-        __threadfence_block();
-        const unsigned int prior = atomicAdd(&out_cnt[k % STAGES], 1u);
-        if (prior == 7u) {
-          __threadfence_block();
-          out_cnt[k % STAGES] = 0u;
-          fence_proxy_async_smem();
-          int cx = 0, cy = 0, cz = 0, cw = it;
-          if (p.qkv_fused) {
-            const int w = it / p.H, h = it - w * p.H;
-            const int ww = p.nw * p.nw;
-            const int b = w / ww, wi = w - b * ww;
-            const int wy = wi / p.nw, wx = wi - wy * p.nw;
-            cx = h * D; cy = wx * WS; cz = wy * WS; cw = b;
-          }
-          tma_store_4d(&tmO, stg, cx, cy, cz, cw);
-          tma_store_commit();
-          tma_store_wait_read<0>();                              // the staging rows have been read
-          mbar_arrive(&empty[k % STAGES]);
-        }
-      }
-      __syncwarp();
+      mbar_arrive_warp(&out_ready[k % STAGES]);                   // the producer thread sends the item's store
       if (!ahead && it_next < p.items) ok = prologue(it_next, k + 1u, bhp);
     }
-    if (lane == 0) tma_store_wait_all<0>();
   }
 
   tc_fence_before();
@@ -676,6 +691,9 @@ int launch_window(const void* q, const void* k, const void* v, long long rows, l
     return SAMB_E_LAUNCH;
   if (items > 0x7fffffffLL) return SAMB_E_SHAPE;
   p.items = int(items);
+  p.mH = fdiv_magic(items, p.H);
+  p.mWW = fdiv_magic(items, p.nw * p.nw);
+  p.mNW = fdiv_magic(items, p.nw);
   const long long grid = items < sm_count() ? items : sm_count();
   kern<<<unsigned(grid), NUM_THREADS, L::BYTES, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmO, tmT, p);
   return launch_status();
