@@ -41,9 +41,10 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * OUT_BYTES + TT * 4 + 1024 
 constexpr int TT_P = 224;                      // tokens per pair tile (112 streamed by each CTA)
 constexpr int B_BYTES_P = (TT_P / 2) * KB;     // 14 KiB
 constexpr int STAGE_BYTES_P = A_BYTES + B_BYTES_P + E_BYTES;   // 24 KiB
-constexpr int STAGES_P = 4;
+constexpr int STAGES_P = 6;                    // 144 KiB of operands in flight: a stage is only ~220 tensor cycles of work
+constexpr int OUT_BUFS_P = 1;                  // one staging tile (the pair products have no GELU: the epilogue has slack)
 constexpr int OUT_HALF_BYTES_P = TT_P * 128;
-constexpr int SMEM_BYTES_P = STAGES_P * STAGE_BYTES_P + 4 * OUT_HALF_BYTES_P + TT_P * 4 + 1024 + 256;
+constexpr int SMEM_BYTES_P = STAGES_P * STAGE_BYTES_P + OUT_BUFS_P * 2 * OUT_HALF_BYTES_P + TT_P * 4 + 1024 + 256;
 
 struct SpParams {
   void* out;
@@ -90,12 +91,13 @@ gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   constexpr int STAGES = kPair ? STAGES_P : samb::STAGES;
   constexpr int OUT_HALF_BYTES = TT * 128;
   constexpr int OUT_BYTES = 2 * OUT_HALF_BYTES;
+  constexpr int OUT_BUFS = kPair ? OUT_BUFS_P : 2;                         // staging tiles
   constexpr int E_COL = NUM_ACC * TT;
   constexpr int kChunks = TT / 16;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_out = smem + STAGES * STAGE_BYTES;
-  float* s_tok = reinterpret_cast<float*>(stage_out + 2 * OUT_BYTES);      // [TT] per-token scales
+  float* s_tok = reinterpret_cast<float*>(stage_out + OUT_BUFS * OUT_BYTES);      // [TT] per-token scales
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_tok + TT);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* acc_full = empty_bar + STAGES;
@@ -238,7 +240,7 @@ gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       const long long t0 = (tile / p.tiles_c) * TT;
       const int n = ct * TC + ch;
       const bool ch_ok = n < p.N;
-      const uint32_t buf = it & 1u;
+      const uint32_t buf = OUT_BUFS == 2 ? (it & 1u) : 0u;
       // staging: [channel half][token][64 channels] bf16, 128-byte rows, 16-byte units XOR (token & 7)
       uint8_t* s_tile = stage_out + buf * OUT_BYTES;
       uint8_t* s_half = s_tile + (ch >> 6) * OUT_HALF_BYTES;
@@ -251,7 +253,7 @@ gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       // the stores of the tile before last (same staging tile) have been read: et == 0 waited for
       // them right after it issued the previous tile's stores, before the barrier below
       bool got = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, 4);
-      if (kRes && got) got = mbar_wait(&res_bar[buf], (it >> 1) & 1u, abort_flag, p.status, 5);
+      if (kRes && got) got = mbar_wait(&res_bar[buf], (it / OUT_BUFS) & 1u, abort_flag, p.status, 5);
       if (!epi_all(got)) break;                            // also publishes s_tok
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (lane_base << 16) + acc * TT;
@@ -317,15 +319,16 @@ gemm_sp24_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           tma_store_2d(&tmOut, s_tile, ct * TC, int(t0));                          // clipped at T and N
           if (ct * TC + 64 < p.N) tma_store_2d(&tmOut, s_tile + OUT_HALF_BYTES, ct * TC + 64, int(t0));
           tma_store_commit();
-          tma_store_wait_read<1>();                        // the other staging tile is free again
+          tma_store_wait_read<OUT_BUFS - 1>();             // the staging tile of the next tile is free again
           const long long next = tile + tile_step;
           if (kRes && next < p.num_tiles) {
             const int nct = int(next % p.tiles_c) * (kPair ? 2 : 1) + int(rank);
             const int nt0 = int(next / p.tiles_c) * TT;
-            uint8_t* dst = stage_out + (buf ^ 1u) * OUT_BYTES;
-            mbar_expect_tx(&res_bar[buf ^ 1u], OUT_BYTES);
-            tma_load_2d(dst, &tmRes, &res_bar[buf ^ 1u], nct * TC, nt0);
-            tma_load_2d(dst + OUT_HALF_BYTES, &tmRes, &res_bar[buf ^ 1u], nct * TC + 64, nt0);
+            const uint32_t nbuf = OUT_BUFS == 2 ? (buf ^ 1u) : 0u;
+            uint8_t* dst = stage_out + nbuf * OUT_BYTES;
+            mbar_expect_tx(&res_bar[nbuf], OUT_BYTES);
+            tma_load_2d(dst, &tmRes, &res_bar[nbuf], nct * TC, nt0);
+            tma_load_2d(dst + OUT_HALF_BYTES, &tmRes, &res_bar[nbuf], nct * TC + 64, nt0);
           }
         }
       }
