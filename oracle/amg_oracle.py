@@ -91,3 +91,109 @@ def process_batch_filters(mask_logits: np.ndarray, iou_preds: np.ndarray, crop_b
     orig_h, orig_w = orig_size
     sel = ~is_box_near_crop_edge(boxes, crop_box, [0, 0, orig_w, orig_h]) if len(idx) else np.zeros(0, dtype=bool)
     return idx[sel], score[sel], boxes[sel], masks[sel]
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# The generator around the filters (segment_anything_fast/automatic_mask_generator.py:204-274 and
+# utils/amg.py:216-274).  The point grids and crop boxes are pinned by ``tests/golden/amg_fp32.npz``; the reference's
+# generator itself cannot run without a GPU (it pins a jagged tensor, automatic_mask_generator.py:292), so
+# ``generate`` is a restatement composed of pinned parts.
+# ---------------------------------------------------------------------------------------------------------------
+def build_point_grid(n_per_side: int) -> np.ndarray:
+    """utils/amg.py:216-224: cell centres of an n x n grid over the unit square, x fastest."""
+    offset = 1 / (2 * n_per_side)
+    side = np.linspace(offset, 1 - offset, n_per_side)
+    pts = np.empty((n_per_side, n_per_side, 2), dtype=np.float64)
+    pts[..., 0] = side[None, :]
+    pts[..., 1] = side[:, None]
+    return pts.reshape(-1, 2)
+
+
+def generate_crop_boxes(im_size, n_layers: int, overlap_ratio: float):
+    """utils/amg.py:238-274: XYXY boxes, layer 0 = the image, layer i = (2**i)**2 overlapping crops."""
+    import math
+    im_h, im_w = im_size
+    boxes, layers = [[0, 0, im_w, im_h]], [0]
+    for i in range(n_layers):
+        n = 2 ** (i + 1)
+        overlap = int(overlap_ratio * min(im_h, im_w) * (2 / n))
+        cw = int(math.ceil((overlap * (n - 1) + im_w) / n))
+        ch = int(math.ceil((overlap * (n - 1) + im_h) / n))
+        for ix in range(n):
+            for iy in range(n):
+                x0, y0 = int((cw - overlap) * ix), int((ch - overlap) * iy)
+                boxes.append([x0, y0, min(x0 + cw, im_w), min(y0 + ch, im_h)])
+                layers.append(i + 1)
+    return boxes, layers
+
+
+def nms(boxes: np.ndarray, scores: np.ndarray, thr: float) -> np.ndarray:
+    """Greedy box NMS as ``torchvision.ops.nms`` defines it: visit boxes by decreasing score, drop a box whose IoU
+    with a kept box exceeds ``thr``; returns the kept indices in that order."""
+    b = boxes.astype(np.float64)
+    area = (b[:, 2] - b[:, 0]) * (b[:, 3] - b[:, 1])
+    order = np.argsort(-scores, kind="stable")
+    kept = []
+    for i in order:
+        ok = True
+        for j in kept:
+            iw = max(0.0, min(b[i, 2], b[j, 2]) - max(b[i, 0], b[j, 0]))
+            ih = max(0.0, min(b[i, 3], b[j, 3]) - max(b[i, 1], b[j, 1]))
+            inter = iw * ih
+            union = area[i] + area[j] - inter
+            if union > 0 and inter / union > thr:
+                ok = False
+                break
+        if ok:
+            kept.append(int(i))
+    return np.asarray(kept, dtype=np.int64)
+
+
+def generate(image: np.ndarray, predict_fn, points_per_side=32, points_per_batch=64, pred_iou_thresh=0.88,
+             stability_score_thresh=0.95, stability_score_offset=1.0, box_nms_thresh=0.7, crop_n_layers=0,
+             crop_nms_thresh=0.7, crop_overlap_ratio=512 / 1500, crop_n_points_downscale_factor=1, mask_threshold=0.0):
+    """``SamAutomaticMaskGenerator.generate`` with ``output_mode="uncompressed_rle"`` and no small-region pass.
+    ``predict_fn(crop_image, points)`` stands for ``set_image`` + ``predict_torch(multimask_output=True,
+    return_logits=True)``: crop ``h x w x 3`` uint8 and ``[P, 2]`` points in crop pixels -> (logits ``[P, 3, h, w]``,
+    predicted IoUs ``[P, 3]``) as numpy arrays."""
+    orig_h, orig_w = image.shape[:2]
+    grids = [build_point_grid(int(points_per_side / (crop_n_points_downscale_factor ** i))) for i in range(crop_n_layers + 1)]
+    crop_boxes, layers = generate_crop_boxes((orig_h, orig_w), crop_n_layers, crop_overlap_ratio)
+    recs = []
+    for crop_box, layer in zip(crop_boxes, layers):
+        x0, y0, x1, y1 = crop_box
+        crop = image[y0:y1, x0:x1]
+        ch, cw = crop.shape[:2]
+        points = grids[layer] * np.array([cw, ch], dtype=np.float64)[None]
+        rows = []
+        for s in range(0, len(points), points_per_batch):
+            pts = points[s:s + points_per_batch]
+            logits, iou = predict_fn(crop, pts)
+            idx, score, boxes, masks = process_batch_filters(logits, iou, crop_box, (orig_h, orig_w), pred_iou_thresh,
+                                                             mask_threshold, stability_score_offset, stability_score_thresh)
+            flat_iou = iou.reshape(-1)
+            for k, i in enumerate(idx):
+                rows.append({"mask": masks[k], "iou": float(flat_iou[i]), "point": pts[i // logits.shape[1]],
+                             "score": float(score[k]), "box": boxes[k]})
+        if rows:
+            keep = nms(np.stack([r["box"] for r in rows]), np.array([r["iou"] for r in rows], dtype=np.float32), box_nms_thresh)
+            rows = [rows[i] for i in keep]
+        for r in rows:
+            full = np.zeros((orig_h, orig_w), dtype=bool)
+            full[y0:y1, x0:x1] = r["mask"]
+            recs.append({"rle": mask_to_rle(full[None])[0], "predicted_iou": r["iou"], "stability_score": r["score"],
+                         "box": r["box"] + np.array([x0, y0, x0, y0]), "point": r["point"] + np.array([x0, y0]),
+                         "crop_box": list(crop_box)})
+    if len(crop_boxes) > 1 and recs:
+        cb = np.array([r["crop_box"] for r in recs], dtype=np.float64)
+        keep = nms(np.stack([r["box"] for r in recs]), (1.0 / ((cb[:, 2] - cb[:, 0]) * (cb[:, 3] - cb[:, 1]))).astype(np.float32),
+                   crop_nms_thresh)
+        recs = [recs[i] for i in keep]
+    out = []
+    for r in recs:
+        b, c = r["box"], r["crop_box"]
+        out.append({"segmentation": r["rle"], "area": int(sum(r["rle"]["counts"][1::2])),
+                    "bbox": [int(b[0]), int(b[1]), int(b[2] - b[0]), int(b[3] - b[1])],
+                    "predicted_iou": r["predicted_iou"], "point_coords": [[float(r["point"][0]), float(r["point"][1])]],
+                    "stability_score": r["stability_score"], "crop_box": [c[0], c[1], c[2] - c[0], c[3] - c[1]]})
+    return out

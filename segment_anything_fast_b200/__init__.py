@@ -9,6 +9,7 @@ from .build_sam import (build_image_encoder_vit_b, build_image_encoder_vit_h, bu
 from . import flash_4  # noqa: F401  (registers the samb200::custom_flash_aligned dispatcher op)
 from .image_encoder import ImageEncoderViT  # noqa: F401
 from .predictor import ResizeLongestSide, SamPredictor  # noqa: F401
+from .automatic_mask_generator import SamAutomaticMaskGenerator  # noqa: F401
 from .runtime import EncoderSession  # noqa: F401
 from .sparse import apply_fake_sparsity, apply_sparse  # noqa: F401
 from .sam_heads import MaskDecoder, PromptEncoder, Sam, TwoWayTransformer  # noqa: F401

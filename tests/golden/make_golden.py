@@ -140,9 +140,19 @@ def golden_amg():
     eb = torch.cat([lo, lo + torch.randint(1, 120, (64, 2), generator=ge)], dim=1).clamp(max=299)
     crop, orig = [100, 50, 400, 350], [0, 0, 420, 350]
     edge = is_box_near_crop_edge(eb, crop, orig)
+    # the generator's point grids and crop boxes (utils/amg.py:216-274)
+    from segment_anything_fast.utils.amg import build_all_layer_point_grids, generate_crop_boxes
+    grids = build_all_layer_point_grids(12, 2, 2)
+    geo = {f"grid{i}": g for i, g in enumerate(grids)}
+    for tag, size, layers, ratio in (("a", (480, 640), 2, 512 / 1500), ("b", (1024, 1024), 1, 512 / 1500),
+                                     ("c", (333, 517), 3, 0.2)):
+        cb, li = generate_crop_boxes(size, layers, ratio)
+        geo[f"crop_{tag}_args"] = np.array([size[0], size[1], layers, ratio], dtype=np.float64)
+        geo[f"crop_{tag}_boxes"] = np.array(cb, dtype=np.int64)
+        geo[f"crop_{tag}_layers"] = np.array(li, dtype=np.int64)
     np.savez_compressed(os.path.join(HERE, "amg_fp32.npz"), logits=logits.numpy(), score=score.numpy(), boxes=boxes.numpy(),
                         rle_len=rle_len, rle_counts=rle_counts, edge_boxes=eb.numpy(), edge_crop=np.array(crop),
-                        edge_orig=np.array(orig), edge_out=edge.numpy())
+                        edge_orig=np.array(orig), edge_out=edge.numpy(), **geo)
 
 
 def main():

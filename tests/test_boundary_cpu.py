@@ -269,3 +269,55 @@ def test_attention_wrapper_rejects_what_the_kernels_do_not_cover():
     with pytest.raises(RuntimeError, match="not covered"):
         _attention_rel_h_rel_w(q, q, q, torch.zeros(1, 1, 100, 10, 1, dtype=torch.bfloat16),
                                torch.zeros(1, 1, 100, 1, 10, dtype=torch.bfloat16))
+
+
+# ----------------------------------------------------------------------------- automatic mask generator (host side)
+def test_mask_generator_geometry_matches_reference(golden_dir):
+    """Point grids and crop boxes (utils/amg.py:216-274) of the package and of the oracle restatement against the
+    reference's own outputs; run-length decoding, areas and box formats against the oracle."""
+    from oracle import amg_oracle as ao
+    from segment_anything_fast_b200 import automatic_mask_generator as mg
+    gold = np.load(os.path.join(golden_dir, "amg_fp32.npz"))
+    grids = mg.build_all_layer_point_grids(12, 2, 2)
+    for i, g in enumerate(grids):
+        assert np.array_equal(g, gold[f"grid{i}"])
+        assert np.array_equal(ao.build_point_grid(int(12 / 2 ** i)), gold[f"grid{i}"])
+    for tag in "abc":
+        h, w, layers, ratio = gold[f"crop_{tag}_args"]
+        for fn in (mg.generate_crop_boxes, ao.generate_crop_boxes):
+            boxes, idx = fn((int(h), int(w)), int(layers), float(ratio))
+            assert np.array_equal(np.array(boxes), gold[f"crop_{tag}_boxes"])
+            assert np.array_equal(np.array(idx), gold[f"crop_{tag}_layers"])
+    rng = np.random.default_rng(3)
+    m = rng.random((4, 37, 53)) > 0.6
+    m[1], m[2] = False, True
+    for rle, mask in zip(ao.mask_to_rle(m), m):
+        assert np.array_equal(mg.rle_to_mask(rle), mask)
+        assert mg.area_from_rle(rle) == int(mask.sum())
+    assert mg.box_xyxy_to_xywh(torch.tensor([3, 4, 10, 20])).tolist() == [3, 4, 7, 16]
+
+
+def test_oracle_nms_is_torchvision_nms():
+    """The greedy NMS of the oracle's generator against ``torchvision.ops.nms``, which the reference calls through
+    ``batched_nms`` with a single category (automatic_mask_generator.py:216-221,259-264)."""
+    from oracle import amg_oracle as ao
+    from torchvision.ops import nms
+    g = torch.Generator().manual_seed(17)
+    lo = torch.randint(0, 300, (200, 2), generator=g).float()
+    boxes = torch.cat([lo, lo + torch.randint(5, 150, (200, 2), generator=g).float()], dim=1)
+    scores = torch.rand(200, generator=g)
+    for thr in (0.3, 0.7):
+        assert ao.nms(boxes.numpy(), scores.numpy(), thr).tolist() == nms(boxes, scores, thr).tolist()
+
+
+def test_mask_generator_arguments():
+    from segment_anything_fast_b200 import SamAutomaticMaskGenerator
+    model = types.SimpleNamespace(image_encoder=types.SimpleNamespace(img_size=1024), device=torch.device("cpu"))
+    with pytest.raises(ValueError, match="Exactly one"):
+        SamAutomaticMaskGenerator(model, points_per_side=None, point_grids=None)
+    with pytest.raises(ValueError, match="Exactly one"):
+        SamAutomaticMaskGenerator(model, points_per_side=8, point_grids=[np.zeros((1, 2))])
+    with pytest.raises(ValueError, match="output_mode"):
+        SamAutomaticMaskGenerator(model, output_mode="png")
+    gen = SamAutomaticMaskGenerator(model, points_per_side=4, crop_n_layers=1, crop_n_points_downscale_factor=2)
+    assert [g.shape for g in gen.point_grids] == [(16, 2), (4, 2)]

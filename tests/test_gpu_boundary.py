@@ -311,3 +311,107 @@ def test_process_batch_filters_against_oracle(ops):
     assert np.array_equal(out["points"].cpu().numpy(), points.repeat_interleave(C, dim=0).numpy()[idx])
     rles = amg.mask_to_rle_pytorch(out["masks"])
     assert rles == ao.mask_to_rle(masks)
+
+
+# ----------------------------------------------------------------------------- automatic mask generator
+def _cone_logits(size, points, image_tone):
+    """Deterministic stand-in for the decoder: three cone-shaped logit maps per point prompt (radius and steepness
+    depend on the channel, the point and the crop's mean colour) and predicted IoUs, as float32 numpy arrays."""
+    h, w = size
+    yy, xx = np.mgrid[0:h, 0:w].astype(np.float64)
+    P = points.shape[0]
+    logits = np.empty((P, 3, h, w), dtype=np.float32)
+    iou = np.empty((P, 3), dtype=np.float32)
+    for p, (px, py) in enumerate(np.round(np.asarray(points, dtype=np.float64) * 64.0) / 64.0):   # the generator hands
+        for c in range(3):                                    # the points over in float32: snap both sides to 1/64 pixel
+            key = (int(px) * 7 + int(py) * 13 + c * 29 + int(image_tone)) % 97
+            rad = 12.0 + 9.0 * c + 0.6 * key
+            amp = 4.0 + (key % 11) * 3.0
+            logits[p, c] = amp * (1.0 - np.sqrt((xx - px) ** 2 + (yy - py) ** 2) / rad)
+            iou[p, c] = 0.55 + 0.004 * key + 0.001 * c
+    return logits, iou
+
+
+class _ConePredictor:
+    """What the generator needs from ``SamPredictor``, answered by ``_cone_logits`` (computed on the host, so that
+    the generator under test and the oracle see the same bits)."""
+
+    def __init__(self):
+        import types
+        self.model = types.SimpleNamespace(mask_threshold=0.0)
+        self.transform = types.SimpleNamespace(apply_coords=lambda pts, size: pts)
+        self.device = torch.device("cuda")
+        self.calls = []
+
+    def set_image(self, crop):
+        self.size, self.tone = crop.shape[:2], float(crop.mean())
+
+    def reset_image(self):
+        self.size = None
+
+    def predict_torch(self, point_coords, point_labels, multimask_output=True, return_logits=False):
+        assert multimask_output and return_logits and point_coords.shape[1:] == (1, 2) and point_labels.shape[1] == 1
+        self.calls.append(point_coords.shape[0])
+        logits, iou = _cone_logits(self.size, point_coords[:, 0].cpu().numpy().astype(np.float64), self.tone)
+        return torch.as_tensor(logits).cuda(), torch.as_tensor(iou).cuda(), None
+
+
+@pytest.mark.parametrize("layers,mode", [(0, "uncompressed_rle"), (1, "uncompressed_rle"), (1, "binary_mask")])
+def test_mask_generator_against_oracle(ops, layers, mode):
+    """``SamAutomaticMaskGenerator.generate`` (automatic_mask_generator.py:144-274): crops, point batches, the fused
+    filter stage, NMS inside and between crops, the uncropping, the run-length encoding on the GPU and the records,
+    against the oracle's restatement fed with the same decoder stand-in.  Everything downstream of the logits is
+    integer-exact, so the records are equal."""
+    from segment_anything_fast_b200 import SamAutomaticMaskGenerator
+    from segment_anything_fast_b200.automatic_mask_generator import rle_to_mask
+    g = torch.Generator().manual_seed(23)
+    image = torch.randint(0, 256, (250, 330, 3), generator=g, dtype=torch.uint8).numpy()
+    kw = dict(points_per_side=7, points_per_batch=16, pred_iou_thresh=0.6, stability_score_thresh=0.8,
+              stability_score_offset=1.0, box_nms_thresh=0.5, crop_n_layers=layers, crop_nms_thresh=0.5,
+              crop_n_points_downscale_factor=1)
+    model = type("M", (), {"image_encoder": type("E", (), {"img_size": 1024})(), "device": torch.device("cuda")})()
+    gen = SamAutomaticMaskGenerator(model, output_mode=mode, **kw)
+    gen.predictor = _ConePredictor()
+    got = gen.generate(image)
+    ops.check_status()
+
+    def predict_fn(crop, pts):
+        return _cone_logits(crop.shape[:2], pts, float(crop.mean()))
+
+    want = ao.generate(image, predict_fn, **kw)
+    assert len(want) >= 8                                             # the filters and the NMS keep a real population
+    assert len(got) == len(want)
+    assert gen.predictor.calls[:4] == [16, 16, 16, 1]                 # 49 points in batches of 16
+    for a, b in zip(got, want):
+        assert a["bbox"] == b["bbox"] and a["area"] == b["area"] and a["crop_box"] == b["crop_box"]
+        assert a["point_coords"] == b["point_coords"]
+        assert abs(a["predicted_iou"] - b["predicted_iou"]) < 1e-6 and abs(a["stability_score"] - b["stability_score"]) < 1e-6
+        if mode == "binary_mask":
+            assert a["segmentation"].dtype == bool and np.array_equal(a["segmentation"], ao.rle_to_mask(b["segmentation"]))
+        else:
+            assert a["segmentation"] == b["segmentation"]
+            assert int(rle_to_mask(a["segmentation"]).sum()) == a["area"]
+    if layers:
+        assert len({tuple(r["crop_box"]) for r in got}) > 1               # masks from crops survive the cross-crop NMS
+
+
+def test_mask_generator_runs_on_the_cuda_encoder(ops):
+    """The generator on a ``Sam`` with the CUDA encoder (random weights): the records are consistent with their own
+    masks (area, box, point inside the crop) whatever the masks are."""
+    from segment_anything_fast_b200 import SamAutomaticMaskGenerator
+    sam, _, _ = _sam_on_gpu(TINY256, eo.seeded_state_dict(TINY256, seed=11))
+    gen = SamAutomaticMaskGenerator(sam, points_per_side=4, points_per_batch=8, pred_iou_thresh=0.0,
+                                    stability_score_thresh=0.0, crop_n_layers=0, output_mode="binary_mask")
+    g = torch.Generator().manual_seed(29)
+    image = torch.randint(0, 256, (3,), generator=g, dtype=torch.uint8).repeat(300, 400, 1)
+    image[60:200, 80:300] = torch.randint(0, 256, (3,), generator=g, dtype=torch.uint8)
+    recs = gen.generate(image.numpy())
+    ops.check_status()
+    assert len(recs) >= 1
+    for r in recs:
+        m = r["segmentation"]
+        assert m.shape == (300, 400) and int(m.sum()) == r["area"]
+        if r["area"]:
+            ys, xs = np.nonzero(m)
+            assert r["bbox"] == [int(xs.min()), int(ys.min()), int(xs.max() - xs.min()), int(ys.max() - ys.min())]
+        assert r["crop_box"] == [0, 0, 400, 300] and 0.0 <= r["stability_score"] <= 1.0
