@@ -162,6 +162,100 @@ row_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
   }
 }
 
+// LayerNorm of raster-order rows of exactly NV * 256 elements, bf16 out, with the affine parameters in registers.
+// In row_kernel every row re-reads its gamma / beta (8 bytes per 2-byte element, through L1), which is what holds
+// that kernel at 0.80 of the copy bandwidth.  Here a warp loads its 2 * NV * 8 parameter values once, then walks
+// rows (row = warp + k * all warps) with the loads of the next DEPTH rows already in flight.  Arithmetic and its order
+// are row_kernel's: same bits out.
+constexpr int kPersistWarps = 4;
+template <int NV, int DEPTH>
+__global__ void __launch_bounds__(kPersistWarps * 32, 3)
+ln_rows_persist_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
+                       const float* __restrict__ beta, __nv_bfloat16* __restrict__ y, long long rows, float eps) {
+  constexpr int C = NV * 256;
+  const int lane = threadIdx.x & 31;
+  const long long step = (long long)gridDim.x * kPersistWarps;
+  long long row = (long long)blockIdx.x * kPersistWarps + (threadIdx.x >> 5);
+  float g[NV][8], b[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = i * 32 + lane;
+    const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * vi), g1 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * vi + 1);
+    const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta) + 2 * vi), b1 = __ldg(reinterpret_cast<const float4*>(beta) + 2 * vi + 1);
+    g[i][0] = g0.x; g[i][1] = g0.y; g[i][2] = g0.z; g[i][3] = g0.w; g[i][4] = g1.x; g[i][5] = g1.y; g[i][6] = g1.z; g[i][7] = g1.w;
+    b[i][0] = b0.x; b[i][1] = b0.y; b[i][2] = b0.z; b[i][3] = b0.w; b[i][4] = b1.x; b[i][5] = b1.y; b[i][6] = b1.z; b[i][7] = b1.w;
+  }
+  uint4 ahead[DEPTH][NV];                                 // rows row, row + step, ... (slot 0 = the next to be worked on)
+#pragma unroll
+  for (int d = 0; d < DEPTH; ++d) {
+    const long long r = row + d * step;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      ahead[d][i] = r < rows ? __ldcs(reinterpret_cast<const uint4*>(x + r * C) + i * 32 + lane) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  for (; row < rows; row += step) {
+    uint4 raw[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) raw[i] = ahead[0][i];
+#pragma unroll
+    for (int d = 0; d + 1 < DEPTH; ++d)
+#pragma unroll
+      for (int i = 0; i < NV; ++i) ahead[d][i] = ahead[d + 1][i];
+    {
+      const long long r = row + DEPTH * step;
+      if (r < rows) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) ahead[DEPTH - 1][i] = __ldcs(reinterpret_cast<const uint4*>(x + r * C) + i * 32 + lane);
+      }
+    }
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      float f[8];
+      unpack8(raw[i], f);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        s0 = __fadd_rn(s0, f[2 * j]);
+        s1 = __fadd_rn(s1, f[2 * j + 1]);
+      }
+    }
+    const float mean = warp_sum(__fadd_rn(s0, s1)) / float(C);
+    float q0 = 0.f, q1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      float f[8];
+      unpack8(raw[i], f);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float d0 = __fsub_rn(f[2 * j], mean), d1 = __fsub_rn(f[2 * j + 1], mean);
+        q0 = fmaf(d0, d0, q0);
+        q1 = fmaf(d1, d1, q1);
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(__fadd_rn(q0, q1)) / float(C) + eps);
+    uint4* yr = reinterpret_cast<uint4*>(y + row * C);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      float f[8];
+      unpack8(raw[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = fmaf(__fmul_rn(__fsub_rn(f[j], mean), rstd), g[i][j], b[i][j]);
+      yr[i * 32 + lane] = pack8(f);
+    }
+  }
+}
+
+template <int NV>
+int launch_ln_persist(const __nv_bfloat16* x, const float* gamma, const float* beta, __nv_bfloat16* y, long long rows,
+                      float eps, cudaStream_t st) {
+  long long blocks = (long long)sm_count() * 3;
+  const long long need = (rows + kPersistWarps - 1) / kPersistWarps;
+  if (blocks > need) blocks = need;
+  // one row ahead: two ahead costs registers (spills at NV = 5) and measured slower (0.120 against 0.117 ms)
+  ln_rows_persist_kernel<NV, 1><<<unsigned(blocks), kPersistWarps * 32, 0, st>>>(x, gamma, beta, y, rows, eps);
+  return launch_status();
+}
+
 __device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void* gsrc) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
 }
@@ -494,11 +588,25 @@ int launch_rows(const void* x, const float* gamma, const float* beta, void* y, i
   const long long blocks = (out_rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
   if (blocks > 0x7fffffffLL) return SAMB_E_SHAPE;
   // Raster order + int8 output: the persistent prefetching kernel (0.172 against 0.204 ms for 131072 x 1280).
-  // The bf16 form stays on row_kernel, which is the faster of the two there (0.141 against 0.149 ms).
+  // The bf16 form does not gain from that kernel (0.149 against 0.141 ms for row_kernel); it has its own below.
   if (window == 0 && (kQuant || getenv("SAMB_ROWS_STREAM") != nullptr))
     return launch_stream<kNorm, kQuant, false>(static_cast<const __nv_bfloat16*>(x), gamma, beta,
                                                static_cast<__nv_bfloat16*>(y), yq, scale, out_rows, C, eps,
                                                static_cast<cudaStream_t>(stream));
+  // Raster order + bf16 output + a row of 3, 4 or 5 x 256 elements (ViT-B / L / H): parameters in registers.
+  if constexpr (kNorm && !kQuant) {
+    if (window == 0 && C % 256 == 0 && C / 256 >= 3 && C / 256 <= 5 && getenv("SAMB_LN_ROWKERNEL") == nullptr &&
+        !((reinterpret_cast<uintptr_t>(gamma) | reinterpret_cast<uintptr_t>(beta)) & 15u)) {
+      const auto* xb = static_cast<const __nv_bfloat16*>(x);
+      auto* yb = static_cast<__nv_bfloat16*>(y);
+      auto st = static_cast<cudaStream_t>(stream);
+      switch (C / 256) {
+        case 3: return launch_ln_persist<3>(xb, gamma, beta, yb, out_rows, eps, st);
+        case 4: return launch_ln_persist<4>(xb, gamma, beta, yb, out_rows, eps, st);
+        default: return launch_ln_persist<5>(xb, gamma, beta, yb, out_rows, eps, st);
+      }
+    }
+  }
   row_kernel<kNorm, kQuant><<<unsigned(blocks), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), gamma, beta, static_cast<__nv_bfloat16*>(y), yq, scale, out_rows, C, eps,
       map);
