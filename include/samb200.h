@@ -211,6 +211,12 @@ int samb_attn_relpos_global_tables(const void* qkv, const void* tables, void* o,
 int samb_attn_relpos_window(const void* q, const void* k, const void* v, const void* rel_h, const void* rel_w, void* o,
                             int B, int H, int window, int d, float scale, int32_t* status, void* stream);
 
+/* The same operator on float16 tensors (q, k, v, rel_h, rel_w, o all float16); logits, softmax statistics and the
+ * output accumulator stay fp32.  The reference sends this shape to SDPA, which takes either type
+ * (flash_4.py:368-370). */
+int samb_attn_relpos_window_f16(const void* q, const void* k, const void* v, const void* rel_h, const void* rel_w, void* o,
+                            int B, int H, int window, int d, float scale, int32_t* status, void* stream);
+
 /* Windowed attention over the head-major qkv projection of the window-partitioned, zero-padded token
  * order (the row order samb_layernorm_bf16 writes with window > 0): qkv[3*H][B*nw*nw*N][d].  The output goes
  * straight back to raster order, o[(b*grid + y)*grid + x, h*d ...] with pad tokens dropped, i.e.

@@ -43,6 +43,7 @@ SIGNATURES = {
                                             c_float, _P, _P]),
     "samb_attn_relpos_global_tables": (c_int, [_P, _P, _P, c_int64, c_int, c_int, c_int, c_int, c_float, _P, _P]),
     "samb_attn_relpos_window": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, _P, _P]),
+    "samb_attn_relpos_window_f16": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, _P, _P]),
     "samb_attn_relpos_window_qkv": (c_int, [_P, _P, c_int64, c_int, c_int, _P, c_int64, c_int, c_int, c_int, c_int,
                                             c_int, c_float, _P, _P]),
     "samb_normalize_u8": (c_int, [_P, _P, c_int, c_int, c_int, c_int, ctypes.POINTER(c_float), ctypes.POINTER(c_float), _P]),

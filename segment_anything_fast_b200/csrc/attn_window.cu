@@ -27,6 +27,8 @@
 // softmax warps overwrite the pad rows of the K and V tiles with k_bias / v_bias of the head before they
 // release their tile's first product; from there on a pad key is
 // an ordinary key, exactly as in the padded layouts.
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace samb {
@@ -91,7 +93,13 @@ __host__ inline unsigned long long fdiv_magic(long long items, int d) {
   if (items >= (1ll << 20) || d <= 0) return 0ull;
   return ((1ull << 40) + static_cast<unsigned long long>(d) - 1) / static_cast<unsigned long long>(d);
 }
+// two 16-bit elements of the tensors' type (bfloat16, or float16 when kHalf) in one word
+template <bool kHalf>
 __device__ __forceinline__ uint32_t wpack2(float lo, float hi) {
+  if constexpr (kHalf) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
@@ -100,7 +108,11 @@ __device__ __forceinline__ float wexp2(float x) {
   asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
+template <bool kHalf>
+__device__ __forceinline__ float bits_to_float(uint32_t bits16) {      // low 16 bits hold one element
+  if constexpr (kHalf) return __half2float(__ushort_as_half(static_cast<unsigned short>(bits16)));
+  return __uint_as_float(bits16 << 16);
+}
 
 // out[e] = v[s + WS - 1 - e], e < WS: the WS consecutive products T[pos .. pos + WS - 1] of a row, in key order
 // (rel[k] = T[pos + WS - 1 - k]).  A four-stage shifter on registers; s < 16.
@@ -122,7 +134,8 @@ __device__ __forceinline__ void select_shifted(const uint32_t (&v)[32], int s, f
 }
 __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
-template <int D, int WS>
+// kHalf: q, k, v, the bias tensors and the output are float16 (bias-tensor mode only; the table modes are bf16).
+template <int D, int WS, bool kHalf>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
@@ -275,8 +288,9 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // instructions, and each tile's chain S -> softmax -> P V -> output is serial: with a warp per tile the
     // two chains only meet in the tensor pipe, one tile's softmax overlapping the other tile's products.
     const int t = warp == 1 ? 0 : 1;
-    constexpr uint32_t idesc_s = make_idesc(kAccF32, kFmtBF16, kFmtBF16, 128, NK);
-    constexpr uint32_t idesc_o = make_idesc(kAccF32, kFmtBF16, kFmtBF16, 128, D, false, /*B MN-major*/ true);
+    constexpr uint32_t kFmt = kHalf ? kFmtF16 : kFmtBF16;
+    constexpr uint32_t idesc_s = make_idesc(kAccF32, kFmt, kFmt, 128, NK);
+    constexpr uint32_t idesc_o = make_idesc(kAccF32, kFmt, kFmt, 128, D, false, /*B MN-major*/ true);
     // K-major, 32B swizzle (8-row groups 256 B apart); start addresses move in 16-byte units
     const uint64_t dq0 = make_smem_desc(smem_u32(smem), 16, 256, kSwizzle32B);
     const uint64_t drw = make_smem_desc(smem_u32(smem + L::OFF_RELW), 16, 256, kSwizzle32B);
@@ -364,10 +378,11 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const float c2 = p.scale * kLog2e;
 
     if (n < NK) {                                                // constant one-hot row of key n
+      constexpr uint32_t kOne = kHalf ? 0x3C00u : 0x3F80u;       // 1.0 in the operands' type
       uint32_t e[8];
 #pragma unroll
       for (int q = 0; q < 8; ++q)
-        e[q] = (valid && qw == 2 * q ? 0x3F80u : 0u) | (valid && qw == 2 * q + 1 ? 0x3F800000u : 0u);
+        e[q] = (valid && qw == 2 * q ? kOne : 0u) | (valid && qw == 2 * q + 1 ? (kOne << 16) : 0u);
       uint8_t* erow = smem + L::OFF_E + n * 32;
       *reinterpret_cast<uint4*>(erow + ((0 ^ sw) << 4)) = make_uint4(e[0], e[1], e[2], e[3]);
       *reinterpret_cast<uint4*>(erow + ((1 ^ sw) << 4)) = make_uint4(e[4], e[5], e[6], e[7]);
@@ -466,7 +481,7 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         float sel[WS];
         select_shifted<WS>(th, qh & 15, sel);
 #pragma unroll
-        for (int q = 0; q < WS / 2; ++q) bhp[q] = wpack2(sel[2 * q], sel[2 * q + 1]);
+        for (int q = 0; q < WS / 2; ++q) bhp[q] = wpack2<kHalf>(sel[2 * q], sel[2 * q + 1]);
         select_shifted<WS>(tw, qw, sel);
         const float inv_s = 1.0f / p.scale;
 #pragma unroll
@@ -476,15 +491,15 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         bias_elems(0, sh_h, eh);
         bias_elems(1, sh_w, ew);
 #pragma unroll
-        for (int q = 0; q < 16; ++q) rw[q] = q < WS ? bf16_bits_to_float(ew[q < WS ? q : 0]) * inv_scale : 0.f;
+        for (int q = 0; q < 16; ++q) rw[q] = q < WS ? bits_to_float<kHalf>(ew[q < WS ? q : 0]) * inv_scale : 0.f;
 #pragma unroll
         for (int q = 0; q < WS / 2; ++q) bhp[q] = eh[2 * q] | (eh[2 * q + 1] << 16);
       }
       uint8_t* rrow = smem + L::OFF_RELW + n * 32;
       *reinterpret_cast<uint4*>(rrow + ((0 ^ sw) << 4)) =
-          make_uint4(wpack2(rw[0], rw[1]), wpack2(rw[2], rw[3]), wpack2(rw[4], rw[5]), wpack2(rw[6], rw[7]));
+          make_uint4(wpack2<kHalf>(rw[0], rw[1]), wpack2<kHalf>(rw[2], rw[3]), wpack2<kHalf>(rw[4], rw[5]), wpack2<kHalf>(rw[6], rw[7]));
       *reinterpret_cast<uint4*>(rrow + ((1 ^ sw) << 4)) =
-          make_uint4(wpack2(rw[8], rw[9]), wpack2(rw[10], rw[11]), wpack2(rw[12], rw[13]), wpack2(rw[14], rw[15]));
+          make_uint4(wpack2<kHalf>(rw[8], rw[9]), wpack2<kHalf>(rw[10], rw[11]), wpack2<kHalf>(rw[12], rw[13]), wpack2<kHalf>(rw[14], rw[15]));
       if (vy < WS || vx < WS) {
         // border window: pad tokens' K and V rows <- projection bias.  Both tile groups write both (the same
         // values), so neither tile's products depend on the other group's progress.
@@ -527,8 +542,8 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       float bh[WS];
 #pragma unroll
       for (int q = 0; q < WS / 2; ++q) {
-        bh[2 * q] = bf16_bits_to_float(bhp[q] & 0xffffu) * kLog2e;
-        bh[2 * q + 1] = __uint_as_float(bhp[q] & 0xffff0000u) * kLog2e;
+        bh[2 * q] = bits_to_float<kHalf>(bhp[q] & 0xffffu) * kLog2e;
+        bh[2 * q + 1] = bits_to_float<kHalf>(bhp[q] >> 16) * kLog2e;
       }
       if (!(ok = mbar_wait(&s_full[t], par, abort_flag, p.status, 6))) break;
       tc_fence_after();
@@ -572,8 +587,8 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             l += e[u];
           }
         }
-        const uint32_t pk[8] = {wpack2(e[0], e[1]), wpack2(e[2], e[3]), wpack2(e[4], e[5]), wpack2(e[6], e[7]),
-                                wpack2(e[8], e[9]), wpack2(e[10], e[11]), wpack2(e[12], e[13]), wpack2(e[14], e[15])};
+        const uint32_t pk[8] = {wpack2<kHalf>(e[0], e[1]), wpack2<kHalf>(e[2], e[3]), wpack2<kHalf>(e[4], e[5]), wpack2<kHalf>(e[6], e[7]),
+                                wpack2<kHalf>(e[8], e[9]), wpack2<kHalf>(e[10], e[11]), wpack2<kHalf>(e[12], e[13]), wpack2<kHalf>(e[14], e[15])};
         // columns [8c, 8c+8) hold logits 16..31 of chunk c/2, consumed in an earlier iteration (for c = 0:
         // chunk 0 itself, already in registers; chunk 1, in flight, starts at column 16)
         tmem_st_32x32b_x8(lane_addr + c * 8, pk);
@@ -612,8 +627,8 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
           for (int u = 0; u < 16; ++u) f[u] = __uint_as_float(ro[c][u]) * inv_l;
           uint4* dst = reinterpret_cast<uint4*>(stg + n * (D * 2) + c * 32);
-          dst[0] = make_uint4(wpack2(f[0], f[1]), wpack2(f[2], f[3]), wpack2(f[4], f[5]), wpack2(f[6], f[7]));
-          dst[1] = make_uint4(wpack2(f[8], f[9]), wpack2(f[10], f[11]), wpack2(f[12], f[13]), wpack2(f[14], f[15]));
+          dst[0] = make_uint4(wpack2<kHalf>(f[0], f[1]), wpack2<kHalf>(f[2], f[3]), wpack2<kHalf>(f[4], f[5]), wpack2<kHalf>(f[6], f[7]));
+          dst[1] = make_uint4(wpack2<kHalf>(f[8], f[9]), wpack2<kHalf>(f[10], f[11]), wpack2<kHalf>(f[12], f[13]), wpack2<kHalf>(f[14], f[15]));
         }
       }
       fence_proxy_async_smem();
@@ -630,7 +645,7 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   }
 }
 
-template <int D, int WS>
+template <int D, int WS, bool kHalf = false>
 int launch_window(const void* q, const void* k, const void* v, long long rows, long long cols, WinParams p,
                   long long items, void* stream, const void* tables = nullptr) {
   using L = WinSmem<D, WS>;
@@ -686,7 +701,7 @@ int launch_window(const void* q, const void* k, const void* v, long long rows, l
                                 CU_TENSOR_MAP_SWIZZLE_32B))
       return e;
   }
-  auto kern = attn_window_kernel<D, WS>;
+  auto kern = attn_window_kernel<D, WS, kHalf>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES) != cudaSuccess)
     return SAMB_E_LAUNCH;
   if (items > 0x7fffffffLL) return SAMB_E_SHAPE;
@@ -704,8 +719,9 @@ int launch_window(const void* q, const void* k, const void* v, long long rows, l
 
 extern "C" {
 
-int samb_attn_relpos_window(const void* q, const void* k, const void* v, const void* rel_h, const void* rel_w, void* o,
-                            int B, int H, int window, int d, float scale, int32_t* status, void* stream) {
+static int attn_relpos_window_any(bool half, const void* q, const void* k, const void* v, const void* rel_h,
+                                  const void* rel_w, void* o, int B, int H, int window, int d, float scale,
+                                  int32_t* status, void* stream) {
   using namespace samb;
   if (!q || !k || !v || !rel_h || !rel_w || !o || !status) return SAMB_E_BADARG;
   if (B <= 0 || H <= 0) return SAMB_E_BADARG;
@@ -724,8 +740,21 @@ int samb_attn_relpos_window(const void* q, const void* k, const void* v, const v
   p.H = H;
   p.scale = scale;
   p.status = status;
+  if (half)
+    return d == 80 ? launch_window<80, 14, true>(q, k, v, rows, d, p, (long long)B * H, stream)
+                   : launch_window<64, 14, true>(q, k, v, rows, d, p, (long long)B * H, stream);
   return d == 80 ? launch_window<80, 14>(q, k, v, rows, d, p, (long long)B * H, stream)
                  : launch_window<64, 14>(q, k, v, rows, d, p, (long long)B * H, stream);
+}
+
+int samb_attn_relpos_window(const void* q, const void* k, const void* v, const void* rel_h, const void* rel_w, void* o,
+                            int B, int H, int window, int d, float scale, int32_t* status, void* stream) {
+  return attn_relpos_window_any(false, q, k, v, rel_h, rel_w, o, B, H, window, d, scale, status, stream);
+}
+
+int samb_attn_relpos_window_f16(const void* q, const void* k, const void* v, const void* rel_h, const void* rel_w,
+                                void* o, int B, int H, int window, int d, float scale, int32_t* status, void* stream) {
+  return attn_relpos_window_any(true, q, k, v, rel_h, rel_w, o, B, H, window, d, scale, status, stream);
 }
 
 int samb_attn_relpos_window_qkv(const void* qkv, const void* tab, int64_t ldt, int t_head_stride, int t_w_off, void* o,

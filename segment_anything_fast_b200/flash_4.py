@@ -8,10 +8,9 @@
   implementations.  The namespace differs on purpose: the reference defines ``customflash`` when it is
   imported, and both packages may live in one process.
 
-The global-attention kernel (N a multiple of 256) exists for bfloat16 and for float16 tensors, the two types the
-reference's own test of the operator sweeps (test/test_flash_4.py:41-43); the 14 x 14 window kernel is bfloat16 only.
-A type a kernel does not take is rejected rather than converted: a silent float16 -> bfloat16 conversion would drop
-three mantissa bits of every input that a caller asking for fp16 expects to keep.
+Both kernels exist for bfloat16 and for float16 tensors, the two types the reference's own test of the operator
+sweeps (test/test_flash_4.py:41-43).  Any other type is rejected rather than converted, and so are mixed types: a
+silent conversion would change the precision the caller asked for.
 """
 import torch
 
@@ -21,11 +20,10 @@ _lib = torch.library.Library("samb200", "FRAGMENT")
 _lib.define("custom_flash_aligned(Tensor q, Tensor k, Tensor v, Tensor rel_h_w, float sm_scale) -> Tensor")
 
 
-def _check_dtype(*tensors: torch.Tensor, allow_half: bool) -> None:
+def _check_dtype(*tensors: torch.Tensor) -> None:
     want = tensors[0].dtype
-    if want != torch.bfloat16 and not (allow_half and want == torch.float16):
-        raise RuntimeError(f"this B200 attention kernel takes bfloat16 tensors"
-                           f"{' (or float16)' if allow_half else ''}, got {want}; "
+    if want not in (torch.bfloat16, torch.float16):
+        raise RuntimeError(f"the B200 attention kernels take bfloat16 or float16 tensors, got {want}; "
                            "convert explicitly with .to(torch.bfloat16) if that precision is acceptable")
     for t in tensors:
         if t.dtype != want:
@@ -42,7 +40,7 @@ def _custom_flash_aligned_cuda(q, k, v, rel_h_w, sm_scale):
     """q, k, v ``[B, H, N, d]``; ``rel_h_w [B, H, N, N/64 + 64]`` = ``cat(rel_h, rel_w)`` along the last axis, the
     layout flash_4.py:352,363 builds.  Head dim 64 or 80 (un-padded: the reference pads 80 to 128 for its Triton
     kernel, flash_4.py:359-361; this kernel runs 80 natively, so a 128-wide zero-padded tensor is refused)."""
-    _check_dtype(q, k, v, rel_h_w, allow_half=True)
+    _check_dtype(q, k, v, rel_h_w)
     B, H, N, d = q.shape
     Sh = N // 64
     if d not in (64, 80):
@@ -56,10 +54,10 @@ def _custom_flash_aligned_cuda(q, k, v, rel_h_w, sm_scale):
 
 def _attention_rel_h_rel_w(q_: torch.Tensor, k_: torch.Tensor, v_: torch.Tensor, rel_h_: torch.Tensor,
                            rel_w_: torch.Tensor) -> torch.Tensor:
-    """q_, k_, v_: ``[B, H, N, d]``; rel_h_: ``[B, H, N, Sh, 1]``; rel_w_: ``[B, H, N, 1, Sw]``; all bfloat16, or
-    all float16 for the 64-wide rasters."""
+    """q_, k_, v_: ``[B, H, N, d]``; rel_h_: ``[B, H, N, Sh, 1]``; rel_w_: ``[B, H, N, 1, Sw]``; all bfloat16 or all
+    float16."""
     B, H, N, d = q_.shape
-    _check_dtype(q_, k_, v_, rel_h_, rel_w_, allow_half=N != 196)
+    _check_dtype(q_, k_, v_, rel_h_, rel_w_)
     rel_h = rel_h_.squeeze(-1).contiguous()
     rel_w = rel_w_.squeeze(-2).contiguous()
     q, k, v = (t.contiguous() for t in (q_, k_, v_))

@@ -353,9 +353,12 @@ def attn_relpos_global_tables(qkv: torch.Tensor, tables: torch.Tensor, B: int, H
 
 def attn_relpos_window(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rel_h: torch.Tensor,
                        rel_w: torch.Tensor, scale: Optional[float] = None) -> torch.Tensor:
-    """Windowed attention with rel-pos bias: q, k, v ``[B,H,196,d]``, rel_h / rel_w ``[B,H,196,14]``."""
+    """Windowed attention with rel-pos bias: q, k, v ``[B,H,196,d]``, rel_h / rel_w ``[B,H,196,14]`` (all bfloat16 or
+    all float16) -> ``[B,H,196,d]`` of the same type."""
+    if q.dtype not in (torch.bfloat16, torch.float16):
+        raise RuntimeError(f"q must be bfloat16 or float16, got {q.dtype}")
     for name, t in (("q", q), ("k", k), ("v", v), ("rel_h", rel_h), ("rel_w", rel_w)):
-        _need(t, torch.bfloat16, name)
+        _need(t, q.dtype, name)
         if not t.is_contiguous():
             raise RuntimeError(f"{name} must be contiguous")
     B, H, N, d = q.shape
@@ -364,9 +367,10 @@ def attn_relpos_window(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rel_h:
         raise RuntimeError("rel_h / rel_w shapes do not match q")
     o = torch.empty_like(q)
     st = status_word(q.device)
-    _lib.check(_lib.load().samb_attn_relpos_window(
-        q.data_ptr(), k.data_ptr(), v.data_ptr(), rel_h.data_ptr(), rel_w.data_ptr(), o.data_ptr(), B, H, ws, d,
-        float(scale if scale is not None else d ** -0.5), st.data_ptr(), _stream()), "samb_attn_relpos_window")
+    lib = _lib.load()
+    fn = lib.samb_attn_relpos_window_f16 if q.dtype == torch.float16 else lib.samb_attn_relpos_window
+    _lib.check(fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), rel_h.data_ptr(), rel_w.data_ptr(), o.data_ptr(), B, H, ws, d,
+                  float(scale if scale is not None else d ** -0.5), st.data_ptr(), _stream()), "samb_attn_relpos_window")
     return o
 
 

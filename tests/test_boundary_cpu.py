@@ -261,10 +261,10 @@ def test_dispatcher_op_is_registered_with_the_reference_schema():
 
 def test_attention_wrapper_rejects_what_the_kernels_do_not_cover():
     from segment_anything_fast_b200.flash_4 import _attention_rel_h_rel_w
-    q = torch.zeros(1, 1, 196, 80, dtype=torch.float16)
+    q = torch.zeros(1, 1, 196, 80, dtype=torch.float32)
     with pytest.raises(RuntimeError, match="bfloat16"):
-        _attention_rel_h_rel_w(q, q, q, torch.zeros(1, 1, 196, 14, 1, dtype=torch.float16),
-                               torch.zeros(1, 1, 196, 1, 14, dtype=torch.float16))
+        _attention_rel_h_rel_w(q, q, q, torch.zeros(1, 1, 196, 14, 1, dtype=torch.float32),
+                               torch.zeros(1, 1, 196, 1, 14, dtype=torch.float32))
     q = torch.zeros(1, 1, 100, 80, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="not covered"):
         _attention_rel_h_rel_w(q, q, q, torch.zeros(1, 1, 100, 10, 1, dtype=torch.bfloat16),
