@@ -6,8 +6,10 @@
 // stream.  One persistent CTA per SM walks its items with a two-deep TMA ring (the loads of item
 // k+1 fly while item k is being computed):
 //   warp 0      TMA producer: Q (two 128-row tiles), K and V (N rounded up to 208 rows) per item
-//   warps 1, 10 tcgen05.mma issue, one warp per query tile: Q K^T into tensor memory, later P V
-//   warps 2..9  softmax, one thread per query row (warps 2..5 rows 0..127, warps 6..9 the rest)
+//   warps 1, 7  tcgen05.mma issue, one warp per query tile: Q K^T into tensor memory, later P V
+//   warps 2..6, 8, 9  softmax, one thread per query row (warps 2..5 rows 0..127; warps 8, 9, 6 rows 128..223 of
+//               tile 1: its fourth lane quarter, rows 224..255, lies beyond the window and the key padding, so the
+//               warp that would own it issues tile 1's products instead)
 //  * The logits of a tile occupy 208 TMEM columns.  The threads read them twice (row maximum, then
 //    exponentials) and write P back as packed bf16 pairs over the columns already consumed, so P V
 //    takes its A operand from tensor memory and P never touches shared memory.  The product lands in
@@ -34,7 +36,8 @@
 namespace samb {
 namespace {
 
-constexpr int NUM_THREADS = 352;   // TMA warp, tile-0 MMA warp, 8 softmax warps, tile-1 MMA warp
+constexpr int NUM_THREADS = 320;   // TMA warp, tile-0 MMA warp, 4 + 3 softmax warps, tile-1 MMA warp (warp 7: the
+                                   // lane quarter of tile 1 whose rows 224..255 lie beyond the window and the key padding)
 constexpr int TMEM_COLS = 512;   // tile 0 at column 0, tile 1 at column 256
 constexpr int kOCol = 112;       // P V result inside a tile's columns (P uses [0, 104))
 constexpr int kTCol = 192;       // mode 2: products with the table block, 64 columns (free once an item's P is complete)
@@ -169,12 +172,13 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // a stage is free when both tiles' MMAs that read it have finished AND the output store staged in it has been read
     // (the producer sends that store itself before it waits for `empty`)
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full[s], 1); mbar_init(&q_full[s], 1); mbar_init(&empty[s], 2); mbar_init(&out_ready[s], 8);
+      mbar_init(&full[s], 1); mbar_init(&q_full[s], 1); mbar_init(&empty[s], 2); mbar_init(&out_ready[s], 7);
     }
     for (int t = 0; t < 2; ++t) {
-      mbar_init(&pro_done[t], 4);
+      const int nw_t = t == 0 ? 4 : 3;          // softmax warps of the tile (tile 1 has real rows in three lane quarters)
+      mbar_init(&pro_done[t], nw_t);
       mbar_init(&s_done[t * 2], 1); mbar_init(&s_done[t * 2 + 1], 1);
-      mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 4); mbar_init(&o_full[t], 1); mbar_init(&t_free[t], 4);
+      mbar_init(&s_full[t], 1); mbar_init(&p_full[t], nw_t); mbar_init(&o_full[t], 1); mbar_init(&t_free[t], nw_t);
       mbar_init(&t_full[t], 1);
     }
     mbar_init(tab_full, 1);
@@ -282,7 +286,7 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         ok = send_output(int(blockIdx.x) + r * int(gridDim.x), uint32_t(r % STAGES), uint32_t(r / STAGES) & 1u);
       tma_store_wait_all<0>();
     }
-  } else if (warp == 1 || warp == 10) {
+  } else if (warp == 1 || warp == 7) {
     // ---------------------------------------------------------------- MMA issue, one warp per query tile
     // (whole warp, one elected lane issues).  Issuing holds the thread until the tensor pipe has taken the
     // instructions, and each tile's chain S -> softmax -> P V -> output is serial: with a warp per tile the
@@ -456,13 +460,14 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       int vy = WS, vx = WS;
       uint4 bk = make_uint4(0u, 0u, 0u, 0u), bv = bk;
       const int ptid = (warp & 3) * 32 + lane, piece = ptid % (2 * CH);
+      const int sweep = (t == 0 ? 128 : 96) / (2 * CH);      // pad rows patched per sweep by the tile's threads
       if (p.qkv_fused == 2) {
         const int w = fdiv(it_p, p.H, p.mH), h = it_p - w * p.H, ww = p.nw * p.nw;
         const int wi = w - fdiv(w, ww, p.mWW) * ww;
         const int wy = fdiv(wi, p.nw, p.mNW), wx = wi - wy * p.nw;
         if (wy == p.nw - 1) vy = p.vlast;
         if (wx == p.nw - 1) vx = p.vlast;
-        if ((vy < WS || vx < WS) && ptid < 12 * 2 * CH) {
+        if ((vy < WS || vx < WS) && ptid < sweep * 2 * CH) {
           bk = __ldg(reinterpret_cast<const uint4*>(p.kv_bias + (size_t)(p.H + h) * D) + piece);
           bv = __ldg(reinterpret_cast<const uint4*>(p.kv_bias + (size_t)(2 * p.H + h) * D) + piece);
         }
@@ -507,10 +512,10 @@ attn_window_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const int n_pad = vy * (WS - vx) + (WS - vy) * WS;
         const uint8_t* tabp = smem + L::OFF_PADTAB + (vy == WS ? 0 : (vx == WS ? 1 : 2)) * 256;
         uint8_t* stage_base = smem + (kp % STAGES) * L::STAGE;
-        // thread = one 16-byte piece (of the 2 * CH per row) for every 12th pad row
+        // thread = one 16-byte piece (of the 2 * CH per row) for every `sweep`-th pad row
         const int c = piece >> 1, hf = piece & 1;
-        if (good && ptid < 12 * 2 * CH) {
-          for (int pi = ptid / (2 * CH); pi < n_pad; pi += 12) {
+        if (good && ptid < sweep * 2 * CH) {
+          for (int pi = ptid / (2 * CH); pi < n_pad; pi += sweep) {
             const int r = tabp[pi];
             const int off = c * L::KV_CHUNK + r * 32 + ((hf ^ ((r >> 2) & 1)) << 4);
             *reinterpret_cast<uint4*>(stage_base + L::OFF_K + off) = bk;
