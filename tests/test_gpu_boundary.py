@@ -413,3 +413,15 @@ def test_mask_generator_runs_on_the_cuda_encoder(ops):
             ys, xs = np.nonzero(m)
             assert r["bbox"] == [int(xs.min()), int(ys.min()), int(xs.max() - xs.min()), int(ys.max() - ys.min())]
         assert r["crop_box"] == [0, 0, 400, 300] and 0.0 <= r["stability_score"] <= 1.0
+
+
+def test_mask_generator_with_no_survivors(ops):
+    """Thresholds nothing passes: every crop contributes empty tensors and the generator returns an empty list."""
+    from segment_anything_fast_b200 import SamAutomaticMaskGenerator
+    model = type("M", (), {"image_encoder": type("E", (), {"img_size": 1024})(), "device": torch.device("cuda")})()
+    gen = SamAutomaticMaskGenerator(model, points_per_side=3, points_per_batch=4, pred_iou_thresh=2.0, crop_n_layers=1,
+                                    output_mode="uncompressed_rle")
+    gen.predictor = _ConePredictor()
+    image = np.zeros((120, 160, 3), dtype=np.uint8)
+    assert gen.generate(image) == []
+    ops.check_status()
